@@ -1,0 +1,288 @@
+#!/usr/bin/env python
+"""Benchmark of the causal self-attention forward+backward path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl ours|reference]
+
+One "step" = one forward + one backward pass over one batch of the workload.  Default workload: the 7B-class GQA
+configuration (B=2, Hq=28, Hkv=4, S=8192, D=128, bf16), the one the headline metric is quoted on.  With N > 1
+(launched by torch.distributed.run, one rank per GPU) every rank runs the same per-GPU batch on its own shard of
+batch x KV-head groups -- the path needs no communication -- so scaling is weak and `value` is the sum of all
+ranks' FLOPs over the slowest rank's time.
+
+Prints ONE JSON line (rank 0).  `value` is device-resident throughput; `e2e` goes through the public host-buffer
+call (pinned host memory -> device -> results back to the host inside the timed region).
+`--impl reference` times the reference project's own OpenMP CPU attention (oracle/_ref, built from the reference
+sources) on a bounded sample of the same workload on this box's host cores.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "causal attention fwd+bwd TFLOP/s (causal-adjusted 7*B*Hq*S^2*D), aggregate over GPUs"
+UNIT = "TFLOP/s"
+FALLBACK_PEAKS = {"bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "hbm_gbs": 6650.0}
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        d["_source"] = "measured"
+        return d
+    d = dict(FALLBACK_PEAKS)
+    d["_source"] = "fallback"
+    return d
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU through NVML while the timed region runs (read-only)."""
+
+    def __init__(self, index: int, period_s: float = 0.1):
+        self.index, self.period, self.samples, self.reasons, self.max_mhz = index, period_s, [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.handle = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def _run(self):
+        nv = self.nv
+        names = {"hw_slowdown": getattr(nv, "nvmlClocksThrottleReasonHwSlowdown", 0x8),
+                 "hw_thermal_slowdown": getattr(nv, "nvmlClocksThrottleReasonHwThermalSlowdown", 0x40),
+                 "sw_thermal_slowdown": getattr(nv, "nvmlClocksThrottleReasonSwThermalSlowdown", 0x20),
+                 "sw_power_cap": getattr(nv, "nvmlClocksThrottleReasonSwPowerCap", 0x4)}
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.handle, nv.NVML_CLOCK_SM))
+                mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.handle)
+                for k, bit in names.items():
+                    if mask & bit:
+                        self.reasons.add(k)
+            except Exception:
+                pass
+            self._stop.wait(self.period)
+
+    def __enter__(self):
+        if self.nv is not None:
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *a):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join(timeout=2)
+
+    def summary(self):
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": 0}
+        s = sorted(self.samples)
+        return {"sm_mhz": s[len(s) // 2], "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": len(s)}
+
+
+def cpu_reference_sample(workload, steps: int, warmup: int):
+    """Times the reference's own CPU attention (attention core only) on ONE query head of ONE sequence at a reduced
+    length; the causal FLOP formula is applied to the sample so the unit matches the GPU metric."""
+    import numpy as np
+    from oracle import cpu
+    if not cpu.ref_available():
+        cpu.build()
+    kind = "reference" if cpu.ref_available() else "port"
+    S = min(workload.seq, 2048)
+    D = workload.head_dim
+    rng = np.random.default_rng(20261125)
+    q = (rng.standard_normal((1, 1, S, D)) * workload.qk_std).astype(np.float32)
+    k = (rng.standard_normal((1, 1, S, D)) * workload.qk_std).astype(np.float32)
+    v = (rng.standard_normal((1, 1, S, D)) * workload.v_std).astype(np.float32)
+    do = (rng.standard_normal((1, 1, S, D)) * workload.do_std).astype(np.float32)
+    flops = 7.0 * S * S * D
+    times = []
+    for i in range(warmup + steps):
+        t0 = time.perf_counter()
+        if kind == "reference":
+            _, _, _, _, secs = cpu.ref_core_fwd_bwd(q, k, v, do, want_outputs=False)
+            dt = secs[0] + secs[1]
+        else:
+            cpu.attn_fwd(q, k, v)
+            cpu.attn_bwd(q, k, v, do)
+            dt = time.perf_counter() - t0
+        if i >= warmup:
+            times.append(dt)
+    mean = sum(times) / len(times)
+    cores = cpu.ref_threads() if kind == "reference" else cpu.oracle_threads()
+    return {"value": flops / mean / 1e12, "unit": UNIT, "cores": cores, "kind": kind,
+            "sample": f"1 sequence x 1 query head, S={S}, D={D}, fp32, attention core only (dense S^2 work), "
+                      f"{len(times)} timed passes of {mean:.3f} s", "ms_per_step": mean * 1e3}
+
+
+def run_reference_arm(args, workload):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    res = cpu_reference_sample(workload, max(1, args.steps), max(1, min(args.warmup, 2)))
+    line = {"impl": "reference", "metric": METRIC, "value": res["value"], "unit": UNIT, "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": res["ms_per_step"], "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": workload.name, "B": workload.batch, "Hq": workload.q_heads, "Hkv": workload.kv_heads,
+                       "S": workload.seq, "D": workload.head_dim, "causal": True},
+            "cpu_baseline": {k: res[k] for k in ("value", "unit", "cores", "kind", "sample")},
+            "e2e": {"value": res["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--workload", default="gqa7b_d128")
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+
+    from sentinel_b200.workloads import WORKLOADS, make_inputs
+    w = WORKLOADS[args.workload]
+    if args.impl == "reference":
+        run_reference_arm(args, w)
+        return
+
+    import torch
+    import torch.distributed as dist
+    import sentinel_b200 as sb
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a B200 GPU: there is no CPU fallback for the product path")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    sb._lib.load()
+
+    # per-rank batch: the workload's own batch; each rank draws its own shard (different seed offset)
+    q, k, v, do = (t.pin_memory() for t in make_inputs(w, seed_offset=rank))
+    qd, kd, vd, dod = (t.to(dev, non_blocking=True) for t in (q, k, v, do))
+    o = torch.empty_like(qd)
+    lse = torch.empty(qd.shape[:3], dtype=torch.float32, device=dev)
+    dq, dk, dv = torch.empty_like(qd), torch.empty_like(kd), torch.empty_like(vd)
+    torch.cuda.synchronize()
+
+    def fwd():
+        sb.attention_forward(qd, kd, vd, out=o, lse=lse)
+
+    def bwd():
+        sb.attention_backward(qd, kd, vd, o, lse, dod, dq=dq, dk=dk, dv=dv)
+
+    def step():
+        fwd()
+        bwd()
+
+    def barrier():
+        if world > 1:
+            dist.barrier(device_ids=[local])
+        torch.cuda.synchronize()
+
+    def timed(fn, n):
+        """n calls of fn between CUDA events on the current stream; returns max-over-ranks milliseconds."""
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        e1.synchronize()
+        barrier()
+        ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item())
+
+    for _ in range(args.warmup):
+        step()
+    status = sb.poll_device_status()
+    if status != 0:
+        raise SystemExit(f"device-side wait timed out during warm-up (status word {status:#x})")
+
+    launches0 = sb.launch_count()
+    with ClockSampler(local) as clocks:
+        total_ms = timed(step, args.steps)
+        launches = sb.launch_count() - launches0
+        fwd_ms = timed(fwd, args.steps) / args.steps
+        bwd_ms = timed(bwd, args.steps) / args.steps
+    ms_per_step = total_ms / args.steps
+    flops_rank = w.flops
+    value = flops_rank * world / (ms_per_step * 1e-3) / 1e12
+
+    # end to end through the host-buffer call: H2D of Q,K,V,dO, forward+backward, D2H of O,LSE,dQ,dK,dV
+    def e2e_step():
+        sb.attention_forward_backward_host(q, k, v, do, device=dev)
+
+    for _ in range(2):
+        e2e_step()
+    e2e_steps = max(3, min(args.steps, 10))
+    e2e_ms = timed(e2e_step, e2e_steps) / e2e_steps
+    esz = q.element_size()
+    h2d = esz * (2 * q.numel() + 2 * k.numel())
+    d2h = esz * (2 * q.numel() + 2 * k.numel()) + 4 * lse.numel()
+    e2e_value = flops_rank * world / (e2e_ms * 1e-3) / 1e12
+    status = sb.poll_device_status()
+
+    peaks = load_peaks()
+    peak = float(peaks.get("bf16_tflops_sustained", FALLBACK_PEAKS["bf16_tflops_sustained"]))
+    bwd_flops = flops_rank * 5.0 / 7.0
+    achieved = bwd_flops / (bwd_ms * 1e-3) / 1e12
+    roofline = {"bound": "tensor", "kernel": "attention backward (delta pass + dK/dV/dQ kernel + dQ convert, timed as one call)",
+                "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+                "peak_source": f"{peaks['_source']} bf16_tflops_sustained (kernel timed inside a seconds-long loop)",
+                "traffic": None,
+                "fwd": {"achieved": flops_rank * 2.0 / 7.0 / (fwd_ms * 1e-3) / 1e12, "ms": fwd_ms},
+                "bwd_ms": bwd_ms,
+                "fwd_bwd_frac_of_burst_peak": flops_rank / (ms_per_step * 1e-3) / 1e12 / float(peaks.get("bf16_tflops", 1590.0))}
+
+    if rank == 0:
+        cpu_base = None
+        if world == 1 and not args.no_cpu_baseline:
+            try:
+                r = cpu_reference_sample(w, 3, 1)
+                cpu_base = {kk: r[kk] for kk in ("value", "unit", "cores", "kind", "sample")}
+            except Exception as exc:  # the checker is optional for the bench line, never for the product path
+                cpu_base = {"value": None, "unit": UNIT, "cores": 0, "kind": "port", "sample": f"unavailable: {exc}"}
+        line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+                "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+                "dtype": "bf16" if w.dtype == "bf16" else "f32", "data": "synthetic",
+                "config": {"workload": w.name, "B_per_gpu": w.batch, "global_batch": w.batch * world, "Hq": w.q_heads,
+                           "Hkv": w.kv_heads, "S": w.seq, "D": w.head_dim, "causal": True,
+                           "parallelism": f"batch x KV-group sharding over {world} GPU(s), no communication",
+                           "l2": "per-step working set (Q,K,V,O,dO,dQ,dK,dV,dQ-accumulator) > 0.8 GB, larger than the 126 MB L2",
+                           "kernel_path": sb.last_path()},
+                "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                        "ms_per_step": e2e_ms},
+                "gpu_launches": int(launches), "clocks": clocks.summary(), "roofline": roofline,
+                "device_status": status}
+        if cpu_base is not None:
+            line["cpu_baseline"] = cpu_base
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

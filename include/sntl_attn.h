@@ -1,0 +1,139 @@
+/*
+ * sntl_attn.h -- C ABI of the B200 (sm_100a) causal self-attention library.
+ *
+ * This is the boundary a Sentinel build binds instead of its flash-attention launch sites.  Every entry
+ * point takes plain pointers and sizes; the caller owns all tensors and all scratch memory, and names the
+ * CUDA stream.  No entry point allocates, frees or synchronises, so calls may sit inside a stream capture
+ * once the first (eager) call of each kind on a device has been made (that first call sets kernel
+ * attributes and encodes nothing that depends on data).
+ *
+ * Reference interfaces replaced (paths relative to the reference project root):
+ *   sntl_attn_fwd   <- CudaFlashAttention::forwardMultiHead
+ *                      sentinel/NeuralNet/Cuda/CudaFlashAttention.hpp:30, .cu:1543-1609
+ *                      (call site sentinel/NeuralNet/Cuda/CudaCausalSelfAttention.cu:237-249)
+ *   sntl_attn_bwd   <- CudaFlashAttention::backwardMultiHead
+ *                      sentinel/NeuralNet/Cuda/CudaFlashAttention.hpp:40, .cu:1615-1700
+ *                      (call site sentinel/NeuralNet/Cuda/CudaCausalSelfAttention.cu:421-438)
+ *   sntl_attn_bwd_workspace_bytes / sntl_attn_fwd_workspace_bytes
+ *                   <- the callee-side ensureSize of deltaWorkspace, CudaFlashAttention.cu:1638
+ *   shape checks    <- validateMultiHeadShape / resolveColumnWindow, CudaFlashAttention.cu:1458-1471, :1533-1539
+ *
+ * Differences from the reference that a binding must know:
+ *   - grouped-query attention is native: K/V carry kv_heads heads (the reference needs them repeated to
+ *     q_heads rows, CudaFlashAttention.cu:1467); kv_heads == q_heads reproduces the reference call.
+ *   - dK/dV are overwritten deterministically (the reference accumulates with atomics into buffers the
+ *     caller zeroes first, CudaCausalSelfAttention.cu:391-394 -- zeroing first stays harmless).
+ *   - head_dim 128 is supported (reference: maxHeadDimension = 64, CudaFlashAttention.hpp:16).
+ */
+#ifndef SNTL_ATTN_H
+#define SNTL_ATTN_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Status codes.  0 is success; the C++ compat layer maps BAD_ARGUMENT/UNSUPPORTED to std::invalid_argument
+ * and the rest to std::runtime_error, the reference's convention (CudaFlashAttention.cu:1459-1470, :1608). */
+enum {
+    SNTL_OK = 0,
+    SNTL_ERR_BAD_ARGUMENT = 1,   /* null pointer, non-positive extent, q_heads % kv_heads != 0, bad window */
+    SNTL_ERR_UNSUPPORTED = 2,    /* shape/dtype/layout combination no kernel covers */
+    SNTL_ERR_WORKSPACE = 3,      /* workspace missing or smaller than *_workspace_bytes() */
+    SNTL_ERR_CUDA = 4,           /* a CUDA runtime/driver call or a launch failed */
+    SNTL_ERR_NO_DEVICE = 5,      /* current device is not compute capability 10.x */
+    SNTL_ERR_DEVICE_TIMEOUT = 6  /* a bounded device-side wait ran out (reported by sntl_attn_poll_device_status) */
+};
+
+enum { SNTL_DTYPE_BF16 = 0, SNTL_DTYPE_F32 = 1 };
+
+/* Tensor layouts.
+ *   BHSD      token-major: element (b,h,s,d) at ((b*H + h)*S + s)*D + d; LSE/delta are [B][Hq][S] fp32.
+ *   SENTINEL  the reference's feature-major matrix, (H*D) rows x stride_columns columns, fp32 only:
+ *             element (b,h,s,d) at (h*D + d)*stride_columns + column_start + b*S + s, i.e. "packs" are
+ *             consecutive column windows of S tokens (CudaFlashAttention.cu:129-131, :358-361);
+ *             LSE is q_heads x stride_columns with the same column rule. */
+enum { SNTL_LAYOUT_BHSD = 0, SNTL_LAYOUT_SENTINEL = 1 };
+
+/* Flags. */
+enum {
+    /* fp32 tensors may be computed with bf16 tensor-core operands (fp32 accumulate).  Without it fp32
+     * tensors take the exact-fp32 kernel.  The reference rounds operands to fp16 on its flash path
+     * (CudaFlashAttention.cu:209-214), so this is the analogous trade. */
+    SNTL_FLAG_ALLOW_BF16_COMPUTE = 1,
+    /* never use the tensor-core kernels (diagnostics / cross-checks) */
+    SNTL_FLAG_FORCE_SIMT = 2
+};
+
+typedef struct sntl_attn_desc {
+    int32_t dtype;           /* SNTL_DTYPE_*  (element type of Q,K,V,O,dO,dQ,dK,dV) */
+    int32_t layout;          /* SNTL_LAYOUT_* */
+    int32_t batch;           /* independent sequences (the reference's packCount) */
+    int32_t q_heads;
+    int32_t kv_heads;        /* divides q_heads */
+    int32_t seq_q;           /* query tokens per sequence (the reference's columnCount) */
+    int32_t seq_kv;          /* key tokens per sequence; must equal seq_q when causal */
+    int32_t head_dim;        /* tensor-core kernels: 64 or 128; exact kernel: any even value <= 256 */
+    float scale;             /* softmax scale, normally 1/sqrt(head_dim) */
+    int32_t causal;          /* 1: key j visible to query i iff j <= i.  0: all keys visible */
+    int32_t stride_columns;  /* SENTINEL layout: columns of the matrices (q.cols); ignored for BHSD */
+    int32_t column_start;    /* SENTINEL layout: first column of the window; ignored for BHSD */
+    int32_t flags;           /* SNTL_FLAG_* */
+} sntl_attn_desc;
+
+/* Library version (major*10000 + minor*100 + patch). */
+int sntl_attn_version(void);
+
+/* Static text for a status code. */
+const char* sntl_status_string(int status);
+
+/* Scratch bytes sntl_attn_fwd needs for this descriptor (0 unless a layout/dtype staging copy is needed). */
+size_t sntl_attn_fwd_workspace_bytes(const sntl_attn_desc* desc);
+
+/* Scratch bytes sntl_attn_bwd needs: delta [B][Hq][Sq] fp32, the fp32 dQ accumulator of the tensor-core
+ * kernel, and staging copies when the layout/dtype is converted. */
+size_t sntl_attn_bwd_workspace_bytes(const sntl_attn_desc* desc);
+
+/* O = softmax(scale * Q K^T + mask) V and LSE = m + ln(sum exp(s - m)) (natural log) per (b, head, query).
+ * q,o: q_heads heads; k,v: kv_heads heads.  A query row with no visible key gets O = 0, LSE = -inf.
+ * workspace may be null when sntl_attn_fwd_workspace_bytes() is 0.  Asynchronous on `stream`
+ * (a cudaStream_t passed as void*; null = the legacy default stream). */
+int sntl_attn_fwd(const sntl_attn_desc* desc, const void* q, const void* k, const void* v, void* o, float* lse,
+                  void* workspace, size_t workspace_bytes, void* stream);
+
+/* dQ, dK, dV from dO with P recomputed as exp(scale*q.k - LSE) and delta = rowsum(dO o O).
+ * dq: q_heads heads, overwritten.  dk, dv: kv_heads heads, overwritten with the sum over the query heads
+ * of each group.  Asynchronous on `stream`. */
+int sntl_attn_bwd(const sntl_attn_desc* desc, const void* q, const void* k, const void* v, const void* o,
+                  const float* lse, const void* dout, void* dq, void* dk, void* dv, void* workspace,
+                  size_t workspace_bytes, void* stream);
+
+/* Log-sum-exp merge of two partial attention results over disjoint key sets (the ring schedule's
+ * combine step): o_acc,lse_acc <- merge((o_acc,lse_acc),(o_part,lse_part)).  BHSD layout, `rows` =
+ * B*Hq*Sq rows of head_dim elements; the accumulator and the partial may have different element types
+ * (an fp32 accumulator keeps repeated merges from compounding bf16 rounding).  A side whose LSE is -inf
+ * contributes nothing.  Asynchronous on `stream`.  No counterpart in the reference (it has no
+ * sequence-parallel path). */
+int sntl_attn_merge(int32_t acc_dtype, int32_t part_dtype, int64_t rows, int32_t head_dim, void* o_acc, float* lse_acc,
+                    const void* o_part, const float* lse_part, void* stream);
+
+/* Name of the kernel family the most recent sntl_attn_fwd / sntl_attn_bwd call on this thread dispatched to
+ * ("simt_f32", "tcgen05", ...), so a test can assert the path taken, like the reference's
+ * usedFlashAttention flag (CudaCausalSelfAttention.hpp:36). */
+const char* sntl_attn_last_path(void);
+
+/* Number of kernels this library has launched from this process so far (all entry points). */
+uint64_t sntl_attn_launch_count(void);
+
+/* Reads (and clears) the device-side status word the tensor-core kernels write when one of their bounded
+ * waits runs out.  Synchronises `stream`.  Returns SNTL_OK or SNTL_ERR_DEVICE_TIMEOUT; *detail (optional)
+ * receives the raw word (which wait, which CTA). */
+int sntl_attn_poll_device_status(void* stream, uint32_t* detail);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* SNTL_ATTN_H */

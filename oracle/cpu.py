@@ -1,0 +1,189 @@
+"""ctypes bindings for the two CPU checkers (TEST INFRASTRUCTURE, never on the product path).
+
+* ``liboracle_attn.so``  -- fp64 restatement of the reference algorithm (``attn_oracle.c``).
+* ``_ref/libsentinel_ref_attn.so`` -- the reference project's own CPU attention compiled from its
+  sources (``ref_harness.cpp`` + ``Makefile``); present only where it was built.
+
+Only tests, ``__graft_entry__.smoke()`` and the CPU-baseline / reference legs of ``bench.py`` may
+import this module.  All tensors are numpy fp32, token-major ``[B, H, S, D]``.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_ORACLE_SO = os.path.join(_HERE, "liboracle_attn.so")
+_REF_SO = os.path.join(_HERE, "_ref", "libsentinel_ref_attn.so")
+
+
+class _Shape(C.Structure):
+    _fields_ = [("batch", C.c_int), ("q_heads", C.c_int), ("kv_heads", C.c_int), ("seq_q", C.c_int),
+                ("seq_kv", C.c_int), ("head_dim", C.c_int), ("causal", C.c_int), ("scale", C.c_float)]
+
+
+def build(force: bool = False) -> None:
+    """Compile the checkers (make); the reference build is skipped when its sources are absent."""
+    if force or not os.path.exists(_ORACLE_SO) or \
+            os.path.getmtime(_ORACLE_SO) < os.path.getmtime(os.path.join(_HERE, "attn_oracle.c")):
+        subprocess.run(["make", "-C", _HERE, "-B"] if force else ["make", "-C", _HERE], check=True,
+                       stdout=subprocess.DEVNULL)
+
+
+_oracle = None
+_ref = None
+
+
+def _fp(a):
+    return a.ctypes.data_as(C.POINTER(C.c_float)) if a is not None else None
+
+
+def _ip(a):
+    return a.ctypes.data_as(C.POINTER(C.c_int)) if a is not None else None
+
+
+def oracle_lib():
+    global _oracle
+    if _oracle is None:
+        if not os.path.exists(_ORACLE_SO):
+            build()
+        _oracle = C.CDLL(_ORACLE_SO)
+    return _oracle
+
+
+def ref_available() -> bool:
+    return os.path.exists(_REF_SO)
+
+
+def ref_lib():
+    global _ref
+    if _ref is None:
+        if not ref_available():
+            raise FileNotFoundError(f"{_REF_SO} not built (reference sources absent at build time)")
+        _ref = C.CDLL(_REF_SO)
+        _ref.ref_threads.restype = C.c_int
+    return _ref
+
+
+def _f32(a):
+    return np.ascontiguousarray(a, dtype=np.float32)
+
+
+def _shape(q, k, causal, scale):
+    B, Hq, Sq, D = q.shape
+    _, Hkv, Skv, _ = k.shape
+    if scale is None:
+        scale = 1.0 / np.sqrt(D)
+    return _Shape(B, Hq, Hkv, Sq, Skv, D, int(bool(causal)), float(scale))
+
+
+def attn_fwd(q, k, v, causal=True, scale=None):
+    """fp64 oracle forward -> (O [B,Hq,Sq,D], LSE [B,Hq,Sq]) as fp32 arrays."""
+    q, k, v = _f32(q), _f32(k), _f32(v)
+    s = _shape(q, k, causal, scale)
+    o = np.empty_like(q)
+    lse = np.empty(q.shape[:3], np.float32)
+    rc = oracle_lib().oracle_attn_fwd(C.byref(s), _fp(q), _fp(k), _fp(v), _fp(o), _fp(lse))
+    assert rc == 0, rc
+    return o, lse
+
+
+def attn_bwd(q, k, v, dout, causal=True, scale=None):
+    """fp64 oracle backward -> (dQ, dK, dV, delta)."""
+    q, k, v, dout = _f32(q), _f32(k), _f32(v), _f32(dout)
+    s = _shape(q, k, causal, scale)
+    dq, dk, dv = np.empty_like(q), np.empty_like(k), np.empty_like(v)
+    delta = np.empty(q.shape[:3], np.float32)
+    rc = oracle_lib().oracle_attn_bwd(C.byref(s), _fp(q), _fp(k), _fp(v), _fp(dout), _fp(dq), _fp(dk), _fp(dv),
+                                      _fp(delta))
+    assert rc == 0, rc
+    return dq, dk, dv, delta
+
+
+def attn_rows(q, k, v, dout, b, h, rows, causal=True, scale=None):
+    """Sampled oracle: (O rows, LSE rows, dQ rows) for query indices ``rows`` of (b, h)."""
+    q, k, v = _f32(q), _f32(k), _f32(v)
+    dout = _f32(dout) if dout is not None else None
+    s = _shape(q, k, causal, scale)
+    rows = np.ascontiguousarray(rows, dtype=np.int32)
+    D = q.shape[-1]
+    o = np.empty((len(rows), D), np.float32)
+    lse = np.empty((len(rows),), np.float32)
+    dq = np.empty((len(rows), D), np.float32) if dout is not None else None
+    rc = oracle_lib().oracle_attn_rows(C.byref(s), int(b), int(h), _fp(q), _fp(k), _fp(v), _fp(dout), _ip(rows),
+                                       len(rows), _fp(o), _fp(lse), _fp(dq))
+    assert rc == 0, rc
+    return o, lse, dq
+
+
+def attn_cols(q, k, v, dout, b, hk, cols, causal=True, scale=None):
+    """Sampled oracle: (dK rows, dV rows) for key indices ``cols`` of (b, kv head hk)."""
+    q, k, v, dout = _f32(q), _f32(k), _f32(v), _f32(dout)
+    s = _shape(q, k, causal, scale)
+    cols = np.ascontiguousarray(cols, dtype=np.int32)
+    D = q.shape[-1]
+    dk = np.empty((len(cols), D), np.float32)
+    dv = np.empty((len(cols), D), np.float32)
+    rc = oracle_lib().oracle_attn_cols(C.byref(s), int(b), int(hk), _fp(q), _fp(k), _fp(v), _fp(dout), _ip(cols),
+                                       len(cols), _fp(dk), _fp(dv))
+    assert rc == 0, rc
+    return dk, dv
+
+
+def round_bf16(x):
+    """fp32 -> bf16 (round to nearest even) -> fp32, done in C so it does not depend on torch."""
+    y = _f32(x).copy()
+    oracle_lib().oracle_round_bf16(_fp(y), C.c_size_t(y.size))
+    return y
+
+
+def oracle_threads() -> int:
+    lib = oracle_lib()
+    lib.oracle_threads.restype = C.c_int
+    return lib.oracle_threads()
+
+
+def ref_layer_fwd_bwd(q, k, v, dout=None):
+    """The reference's public CausalSelfAttention layer on [Q;K;V] -> (O, LSE, dQ, dK, dV) (grads None without dout).
+
+    Causal, Sq == Skv, scale 1/sqrt(D): the only mode the reference layer has."""
+    q, k, v = _f32(q), _f32(k), _f32(v)
+    B, Hq, S, D = q.shape
+    Hkv = k.shape[1]
+    o = np.empty_like(q)
+    lse = np.empty((B, Hq, S), np.float32)
+    dq = dk = dv = None
+    if dout is not None:
+        dout = _f32(dout)
+        dq, dk, dv = np.empty_like(q), np.empty_like(k), np.empty_like(v)
+    rc = ref_lib().ref_layer_fwd_bwd(B, Hq, Hkv, S, D, _fp(q), _fp(k), _fp(v), _fp(dout), _fp(o), _fp(lse), _fp(dq),
+                                     _fp(dk), _fp(dv))
+    assert rc == 0, "reference layer threw"
+    return o, lse, dq, dk, dv
+
+
+def ref_core_fwd_bwd(q, k, v, dout=None, head_limit=0, want_outputs=True):
+    """The reference's primitives (Matrix::gemm, Softmax::applyInto) in the layer's dense order, attention core only.
+
+    Returns (O, dQ, dK, dV, (fwd_seconds, bwd_seconds))."""
+    q, k, v = _f32(q), _f32(k), _f32(v)
+    B, Hq, S, D = q.shape
+    Hkv = k.shape[1]
+    o = np.zeros_like(q) if want_outputs else None
+    dq = dk = dv = None
+    if dout is not None:
+        dout = _f32(dout)
+        if want_outputs:
+            dq, dk, dv = np.zeros_like(q), np.zeros_like(k), np.zeros_like(v)
+    secs = (C.c_double * 2)()
+    rc = ref_lib().ref_core_fwd_bwd(B, Hq, Hkv, S, D, int(head_limit), _fp(q), _fp(k), _fp(v), _fp(dout), _fp(o),
+                                    _fp(dq), _fp(dk), _fp(dv), secs)
+    assert rc == 0, "reference primitives threw"
+    return o, dq, dk, dv, (secs[0], secs[1])
+
+
+def ref_threads() -> int:
+    return ref_lib().ref_threads()

@@ -1,0 +1,307 @@
+// C ABI of the attention library: argument validation, path selection, workspace carving.
+// Mirrors the host-side duties of CudaFlashAttention::forwardMultiHead / backwardMultiHead
+// (sentinel/NeuralNet/Cuda/CudaFlashAttention.cu:1543-1609, :1615-1700): validate shapes and the column
+// window, pick a kernel, launch on the caller's stream, report launch errors.  Unlike the reference it never
+// allocates: scratch comes from the caller.
+#include "common.cuh"
+
+#include <atomic>
+#include <string.h>
+
+namespace sntl {
+
+static std::atomic<uint64_t> g_launches{0};
+static thread_local const char* g_last_path = "none";
+
+void count_launch(int n) { g_launches.fetch_add((uint64_t)n, std::memory_order_relaxed); }
+
+namespace {
+
+inline size_t align_up(size_t x, size_t a = 256) { return (x + a - 1) / a * a; }
+
+int validate(const sntl_attn_desc* d)
+{
+    if (!d) return SNTL_ERR_BAD_ARGUMENT;
+    if (d->dtype != SNTL_DTYPE_BF16 && d->dtype != SNTL_DTYPE_F32) return SNTL_ERR_BAD_ARGUMENT;
+    if (d->layout != SNTL_LAYOUT_BHSD && d->layout != SNTL_LAYOUT_SENTINEL) return SNTL_ERR_BAD_ARGUMENT;
+    if (d->batch <= 0 || d->q_heads <= 0 || d->kv_heads <= 0 || d->seq_q <= 0 || d->seq_kv <= 0 || d->head_dim <= 0)
+        return SNTL_ERR_BAD_ARGUMENT;
+    if (d->q_heads % d->kv_heads != 0) return SNTL_ERR_BAD_ARGUMENT;
+    if (d->causal && d->seq_q != d->seq_kv) return SNTL_ERR_BAD_ARGUMENT;
+    if (!(d->scale > 0.0f)) return SNTL_ERR_BAD_ARGUMENT;
+    if (d->head_dim > 256) return SNTL_ERR_UNSUPPORTED;
+    if (d->batch > 65535 || d->q_heads > 65535) return SNTL_ERR_UNSUPPORTED;
+    if (d->layout == SNTL_LAYOUT_SENTINEL) {
+        if (d->dtype != SNTL_DTYPE_F32) return SNTL_ERR_UNSUPPORTED;
+        if (d->seq_q != d->seq_kv) return SNTL_ERR_BAD_ARGUMENT;
+        // window [column_start, column_start + batch*seq) must lie inside the matrix (CudaFlashAttention.cu:1533-1539)
+        if (d->column_start < 0 || d->stride_columns <= 0) return SNTL_ERR_BAD_ARGUMENT;
+        if ((long long)d->column_start + (long long)d->batch * d->seq_q > (long long)d->stride_columns) return SNTL_ERR_BAD_ARGUMENT;
+    }
+    return SNTL_OK;
+}
+
+AttnShape shape_of(const sntl_attn_desc* d)
+{
+    return AttnShape{d->batch, d->q_heads, d->kv_heads, d->seq_q, d->seq_kv, d->head_dim, d->scale, d->causal ? 1 : 0};
+}
+
+// tensor-core path is taken for bf16 tensors, or fp32 tensors when the caller allows bf16 operands
+bool wants_tc(const sntl_attn_desc* d, bool backward)
+{
+    if (d->flags & SNTL_FLAG_FORCE_SIMT) return false;
+    if (d->dtype == SNTL_DTYPE_F32 && !(d->flags & SNTL_FLAG_ALLOW_BF16_COMPUTE)) return false;
+    return backward ? tc_bwd_supported(shape_of(d)) : tc_fwd_supported(shape_of(d));
+}
+
+bool needs_staging(const sntl_attn_desc* d) { return d->dtype == SNTL_DTYPE_F32 || d->layout == SNTL_LAYOUT_SENTINEL; }
+
+void views(const sntl_attn_desc* d, View4& vq, View4& vkv, View3& vlse)
+{
+    const long long D = d->head_dim;
+    if (d->layout == SNTL_LAYOUT_BHSD) {
+        vq = View4{(long long)d->q_heads * d->seq_q * D, (long long)d->seq_q * D, D, 1};
+        vkv = View4{(long long)d->kv_heads * d->seq_kv * D, (long long)d->seq_kv * D, D, 1};
+        vlse = View3{(long long)d->q_heads * d->seq_q, (long long)d->seq_q, 1};
+    } else {
+        const long long C = d->stride_columns;
+        vq = View4{(long long)d->seq_q, D * C, 1, C};
+        vkv = View4{(long long)d->seq_kv, D * C, 1, C};
+        vlse = View3{(long long)d->seq_q, C, 1};
+    }
+}
+
+struct Carve {
+    char* p;
+    size_t left;
+    bool ok = true;
+    void* take(size_t bytes)
+    {
+        bytes = align_up(bytes);
+        if (bytes > left) { ok = false; return nullptr; }
+        void* r = p;
+        p += bytes;
+        left -= bytes;
+        return r;
+    }
+};
+
+size_t nq_elems(const sntl_attn_desc* d) { return (size_t)d->batch * d->q_heads * d->seq_q * d->head_dim; }
+size_t nkv_elems(const sntl_attn_desc* d) { return (size_t)d->batch * d->kv_heads * d->seq_kv * d->head_dim; }
+size_t nlse(const sntl_attn_desc* d) { return (size_t)d->batch * d->q_heads * d->seq_q; }
+
+int cuda_status(cudaError_t e) { return e == cudaSuccess ? SNTL_OK : SNTL_ERR_CUDA; }
+
+bool device_ok()
+{
+    int dev = 0, major = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return false;
+    if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess) return false;
+    return major == 10;
+}
+
+// Stage one tensor of `heads` heads into bf16 BHSD.
+cudaError_t stage_in(const sntl_attn_desc* d, const void* src, __nv_bfloat16* dst, int heads, int S, cudaStream_t st)
+{
+    if (d->layout == SNTL_LAYOUT_SENTINEL)
+        return sentinel_to_bhsd_bf16((const float*)src, dst, d->batch, heads, S, d->head_dim, d->stride_columns, d->column_start, st);
+    return f32_to_bf16((const float*)src, dst, (size_t)d->batch * heads * S * d->head_dim, st);
+}
+cudaError_t stage_out(const sntl_attn_desc* d, const __nv_bfloat16* src, void* dst, int heads, int S, cudaStream_t st)
+{
+    if (d->layout == SNTL_LAYOUT_SENTINEL)
+        return bhsd_bf16_to_sentinel(src, (float*)dst, d->batch, heads, S, d->head_dim, d->stride_columns, d->column_start, st);
+    return bf16_to_f32(src, (float*)dst, (size_t)d->batch * heads * S * d->head_dim, st);
+}
+
+}  // namespace
+}  // namespace sntl
+
+using namespace sntl;
+
+extern "C" {
+
+int sntl_attn_version(void) { return 100; }
+
+const char* sntl_status_string(int status)
+{
+    switch (status) {
+        case SNTL_OK: return "ok";
+        case SNTL_ERR_BAD_ARGUMENT: return "bad argument";
+        case SNTL_ERR_UNSUPPORTED: return "unsupported shape, dtype or layout";
+        case SNTL_ERR_WORKSPACE: return "workspace missing or too small";
+        case SNTL_ERR_CUDA: return "CUDA call or kernel launch failed";
+        case SNTL_ERR_NO_DEVICE: return "no compute-capability-10.x device is current";
+        case SNTL_ERR_DEVICE_TIMEOUT: return "a bounded device-side wait ran out";
+        default: return "unknown status";
+    }
+}
+
+const char* sntl_attn_last_path(void) { return g_last_path; }
+
+uint64_t sntl_attn_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+size_t sntl_attn_fwd_workspace_bytes(const sntl_attn_desc* d)
+{
+    if (validate(d) != SNTL_OK) return 0;
+    if (!wants_tc(d, false) || !needs_staging(d)) return 0;
+    // bf16 copies of Q, K, V, O and a [B][Hq][S] LSE when the caller's LSE is feature-major
+    return align_up(2 * nq_elems(d)) * 2 + align_up(2 * nkv_elems(d)) * 2 + align_up(4 * nlse(d));
+}
+
+size_t sntl_attn_bwd_workspace_bytes(const sntl_attn_desc* d)
+{
+    if (validate(d) != SNTL_OK) return 0;
+    size_t bytes = align_up(4 * nlse(d));  // delta (exact path) -- the tensor-core path sizes its own below
+    if (!wants_tc(d, true)) return bytes;
+    bytes = align_up(tc_backward_workspace_bytes(shape_of(d)));
+    if (needs_staging(d))  // bf16 Q,O,dO,dQ + K,V,dK,dV + LSE
+        bytes += align_up(2 * nq_elems(d)) * 4 + align_up(2 * nkv_elems(d)) * 4 + align_up(4 * nlse(d));
+    return bytes;
+}
+
+int sntl_attn_fwd(const sntl_attn_desc* d, const void* q, const void* k, const void* v, void* o, float* lse,
+                  void* workspace, size_t workspace_bytes, void* stream)
+{
+    int rc = validate(d);
+    if (rc != SNTL_OK) return rc;
+    if (!q || !k || !v || !o || !lse) return SNTL_ERR_BAD_ARGUMENT;
+    if (!device_ok()) return SNTL_ERR_NO_DEVICE;
+    cudaStream_t st = (cudaStream_t)stream;
+    const size_t need = sntl_attn_fwd_workspace_bytes(d);
+    if (need && (!workspace || workspace_bytes < need)) return SNTL_ERR_WORKSPACE;
+
+    if (!wants_tc(d, false)) {
+        if (d->head_dim % 2 != 0) return SNTL_ERR_UNSUPPORTED;
+        SimtArgs a{};
+        a.s = shape_of(d);
+        a.is_bf16 = d->dtype == SNTL_DTYPE_BF16;
+        a.q = q; a.k = k; a.v = v; a.o_out = o; a.lse_out = lse;
+        views(d, a.vq, a.vkv, a.vlse);
+        g_last_path = a.is_bf16 ? "simt_bf16" : "simt_f32";
+        return cuda_status(simt_forward(a, st));
+    }
+
+    TcArgs t{};
+    t.s = shape_of(d);
+    g_last_path = "tcgen05";
+    if (!needs_staging(d)) {
+        t.q = (const __nv_bfloat16*)q; t.k = (const __nv_bfloat16*)k; t.v = (const __nv_bfloat16*)v;
+        t.o_out = (__nv_bfloat16*)o; t.lse_out = lse;
+        return cuda_status(tc_forward(t, st));
+    }
+    g_last_path = "tcgen05_staged";
+    Carve c{(char*)workspace, workspace_bytes};
+    auto* qb = (__nv_bfloat16*)c.take(2 * nq_elems(d));
+    auto* ob = (__nv_bfloat16*)c.take(2 * nq_elems(d));
+    auto* kb = (__nv_bfloat16*)c.take(2 * nkv_elems(d));
+    auto* vb = (__nv_bfloat16*)c.take(2 * nkv_elems(d));
+    auto* lb = (float*)c.take(4 * nlse(d));
+    if (!c.ok) return SNTL_ERR_WORKSPACE;
+    cudaError_t e;
+    if ((e = stage_in(d, q, qb, d->q_heads, d->seq_q, st)) != cudaSuccess) return SNTL_ERR_CUDA;
+    if ((e = stage_in(d, k, kb, d->kv_heads, d->seq_kv, st)) != cudaSuccess) return SNTL_ERR_CUDA;
+    if ((e = stage_in(d, v, vb, d->kv_heads, d->seq_kv, st)) != cudaSuccess) return SNTL_ERR_CUDA;
+    t.q = qb; t.k = kb; t.v = vb; t.o_out = ob;
+    t.lse_out = d->layout == SNTL_LAYOUT_SENTINEL ? lb : lse;
+    if ((e = tc_forward(t, st)) != cudaSuccess) return SNTL_ERR_CUDA;
+    if ((e = stage_out(d, ob, o, d->q_heads, d->seq_q, st)) != cudaSuccess) return SNTL_ERR_CUDA;
+    if (d->layout == SNTL_LAYOUT_SENTINEL &&
+        (e = lse_bhs_to_sentinel(lb, lse, d->batch, d->q_heads, d->seq_q, d->stride_columns, d->column_start, st)) != cudaSuccess)
+        return SNTL_ERR_CUDA;
+    return SNTL_OK;
+}
+
+int sntl_attn_bwd(const sntl_attn_desc* d, const void* q, const void* k, const void* v, const void* o,
+                  const float* lse, const void* dout, void* dq, void* dk, void* dv, void* workspace,
+                  size_t workspace_bytes, void* stream)
+{
+    int rc = validate(d);
+    if (rc != SNTL_OK) return rc;
+    if (!q || !k || !v || !o || !lse || !dout || !dq || !dk || !dv) return SNTL_ERR_BAD_ARGUMENT;
+    if (!device_ok()) return SNTL_ERR_NO_DEVICE;
+    cudaStream_t st = (cudaStream_t)stream;
+    const size_t need = sntl_attn_bwd_workspace_bytes(d);
+    if (!workspace || workspace_bytes < need) return SNTL_ERR_WORKSPACE;
+    Carve c{(char*)workspace, workspace_bytes};
+
+    if (!wants_tc(d, true)) {
+        if (d->head_dim % 2 != 0) return SNTL_ERR_UNSUPPORTED;
+        SimtArgs a{};
+        a.s = shape_of(d);
+        a.is_bf16 = d->dtype == SNTL_DTYPE_BF16;
+        a.q = q; a.k = k; a.v = v; a.o = o; a.dout = dout; a.lse = lse;
+        a.dq = dq; a.dk = dk; a.dv = dv;
+        a.delta = (float*)c.take(4 * nlse(d));
+        if (!c.ok) return SNTL_ERR_WORKSPACE;
+        views(d, a.vq, a.vkv, a.vlse);
+        a.vdelta = View3{(long long)d->q_heads * d->seq_q, (long long)d->seq_q, 1};
+        g_last_path = a.is_bf16 ? "simt_bf16" : "simt_f32";
+        return cuda_status(simt_backward(a, st));
+    }
+
+    TcArgs t{};
+    t.s = shape_of(d);
+    char* tcws = (char*)c.take(tc_backward_workspace_bytes(t.s));
+    if (!c.ok) return SNTL_ERR_WORKSPACE;
+    const size_t sq_pad = ((size_t)d->seq_q + 127) / 128 * 128;
+    t.delta = (float*)tcws;
+    t.dq_accum = (float*)(tcws + align_up(4 * (size_t)d->batch * d->q_heads * sq_pad));
+    g_last_path = "tcgen05";
+    if (!needs_staging(d)) {
+        t.q = (const __nv_bfloat16*)q; t.k = (const __nv_bfloat16*)k; t.v = (const __nv_bfloat16*)v;
+        t.o = (const __nv_bfloat16*)o; t.dout = (const __nv_bfloat16*)dout; t.lse = lse;
+        t.dq = (__nv_bfloat16*)dq; t.dk = (__nv_bfloat16*)dk; t.dv = (__nv_bfloat16*)dv;
+        return cuda_status(tc_backward(t, st));
+    }
+    g_last_path = "tcgen05_staged";
+    auto* qb = (__nv_bfloat16*)c.take(2 * nq_elems(d));
+    auto* ob = (__nv_bfloat16*)c.take(2 * nq_elems(d));
+    auto* gb = (__nv_bfloat16*)c.take(2 * nq_elems(d));
+    auto* dqb = (__nv_bfloat16*)c.take(2 * nq_elems(d));
+    auto* kb = (__nv_bfloat16*)c.take(2 * nkv_elems(d));
+    auto* vb = (__nv_bfloat16*)c.take(2 * nkv_elems(d));
+    auto* dkb = (__nv_bfloat16*)c.take(2 * nkv_elems(d));
+    auto* dvb = (__nv_bfloat16*)c.take(2 * nkv_elems(d));
+    auto* lb = (float*)c.take(4 * nlse(d));
+    if (!c.ok) return SNTL_ERR_WORKSPACE;
+    if (stage_in(d, q, qb, d->q_heads, d->seq_q, st) != cudaSuccess) return SNTL_ERR_CUDA;
+    if (stage_in(d, o, ob, d->q_heads, d->seq_q, st) != cudaSuccess) return SNTL_ERR_CUDA;
+    if (stage_in(d, dout, gb, d->q_heads, d->seq_q, st) != cudaSuccess) return SNTL_ERR_CUDA;
+    if (stage_in(d, k, kb, d->kv_heads, d->seq_kv, st) != cudaSuccess) return SNTL_ERR_CUDA;
+    if (stage_in(d, v, vb, d->kv_heads, d->seq_kv, st) != cudaSuccess) return SNTL_ERR_CUDA;
+    t.lse = lse;
+    if (d->layout == SNTL_LAYOUT_SENTINEL) {
+        if (lse_sentinel_to_bhs(lse, lb, d->batch, d->q_heads, d->seq_q, d->stride_columns, d->column_start, st) != cudaSuccess)
+            return SNTL_ERR_CUDA;
+        t.lse = lb;
+    }
+    t.q = qb; t.k = kb; t.v = vb; t.o = ob; t.dout = gb; t.dq = dqb; t.dk = dkb; t.dv = dvb;
+    if (tc_backward(t, st) != cudaSuccess) return SNTL_ERR_CUDA;
+    if (stage_out(d, dqb, dq, d->q_heads, d->seq_q, st) != cudaSuccess) return SNTL_ERR_CUDA;
+    if (stage_out(d, dkb, dk, d->kv_heads, d->seq_kv, st) != cudaSuccess) return SNTL_ERR_CUDA;
+    if (stage_out(d, dvb, dv, d->kv_heads, d->seq_kv, st) != cudaSuccess) return SNTL_ERR_CUDA;
+    return SNTL_OK;
+}
+
+int sntl_attn_merge(int32_t acc_dtype, int32_t part_dtype, int64_t rows, int32_t head_dim, void* o_acc, float* lse_acc,
+                    const void* o_part, const float* lse_part, void* stream)
+{
+    if (rows < 0 || head_dim <= 0 || !o_acc || !lse_acc || !o_part || !lse_part) return SNTL_ERR_BAD_ARGUMENT;
+    if ((acc_dtype != SNTL_DTYPE_BF16 && acc_dtype != SNTL_DTYPE_F32) ||
+        (part_dtype != SNTL_DTYPE_BF16 && part_dtype != SNTL_DTYPE_F32))
+        return SNTL_ERR_BAD_ARGUMENT;
+    return cuda_status(merge_partials(acc_dtype, part_dtype, rows, head_dim, o_acc, lse_acc, o_part, lse_part, (cudaStream_t)stream));
+}
+
+int sntl_attn_poll_device_status(void* stream, uint32_t* detail)
+{
+    uint32_t word = 0, word_bwd = 0;
+    if (read_and_clear_fwd_status((cudaStream_t)stream, &word) != cudaSuccess) return SNTL_ERR_CUDA;
+    if (read_and_clear_bwd_status((cudaStream_t)stream, &word_bwd) != cudaSuccess) return SNTL_ERR_CUDA;
+    if (word == 0) word = word_bwd;
+    if (detail) *detail = word;
+    return word == 0 ? SNTL_OK : SNTL_ERR_DEVICE_TIMEOUT;
+}
+
+}  // extern "C"

@@ -1,0 +1,398 @@
+// Causal attention forward for sm_100a: tcgen05 MMA with accumulators in TMEM, TMA-staged operands,
+// warp-specialised producer / MMA / softmax roles.
+//
+// Replaces the reference's CudaFlashAttentionForwardWmma64Entry
+// (sentinel/NeuralNet/Cuda/CudaFlashAttention.cu:1105-1266): same math -- S = scale*Q K^T, causal mask,
+// online softmax, O = P V, LSE = m + ln(l) -- re-designed for Blackwell:
+//
+//   * one CTA owns 256 consecutive query rows of one (batch, head) as two 128-row tiles; each tile has its
+//     own softmax warpgroup (one thread per query row: tcgen05.ld's 32x32b shape hands thread i row i, so the
+//     row max / row sum need no shuffles) while a single MMA-issuing thread feeds the tensor core for both,
+//     so one tile's softmax overlaps the other tile's MMAs;
+//   * S (fp32, 128 columns) and O (fp32, D columns) live in TMEM; P is written back over S as packed bf16 and
+//     consumed by the PV MMA straight from TMEM (A operand in TMEM), V is consumed from shared memory as an
+//     MN-major operand, so nothing is transposed and P never touches shared memory;
+//   * Q/K/V tiles arrive by per-CTA TMA (128-byte swizzle, no multicast) into two-stage K and V rings
+//     guarded by mbarriers; stages are released by tcgen05.commit;
+//   * the softmax works in the exp2 domain with scale*log2(e) folded into one FMA, and rescales O lazily:
+//     only when a row's running max grew by more than 2^8 since the last rescale;
+//   * grouped-query heads index their shared K/V head directly (no repeated K/V as at
+//     sentinel/NeuralNet/Cuda/CudaCausalSelfAttention.cu:27-34); CTAs are ordered heaviest-first and the query
+//     heads of one group are adjacent in launch order so they share K/V tiles in L2.
+//
+// Layout: bf16 token-major [B][H][S][D], D in {64,128}; LSE [B][Hq][Sq] fp32 (natural log).
+// TMEM map (512 columns): S0 [0,128) S1 [128,256) O0 [256,256+D) O1 [384,384+D).
+#include "common.cuh"
+#include "sm100_ptx.cuh"
+
+#include <mutex>
+
+namespace sntl {
+
+using namespace ptx;
+
+namespace {
+
+constexpr int kM = 128;          // query rows per tile
+constexpr int kN = 128;          // keys per tile
+constexpr int kFwdThreads = 320; // 2 softmax warpgroups + MMA warp + TMA warp
+constexpr uint32_t kTmemCols = 512;
+constexpr float kRescaleThreshold = 8.0f;  // log2 units
+
+enum WaitSite : uint32_t {
+    kSiteQ = 1, kSiteKFull, kSiteVFull, kSiteKEmpty, kSiteVEmpty, kSiteSReady, kSitePReady, kSiteOReady, kSiteFinal
+};
+
+struct FwdParams {
+    __nv_bfloat16* o;
+    float* lse;
+    int B, Hq, Hkv, Sq, Skv;
+    int causal;
+    int n_qblk;       // 256-row query blocks per (b, h)
+    float scale_log2; // scale * log2(e)
+};
+
+struct FwdBarriers {
+    uint64_t q_full;
+    uint64_t k_full[2], k_empty[2], v_full[2], v_empty[2];
+    uint64_t s_ready[2], p_ready[2], o_ready[2];
+    uint64_t final_bar;
+    uint32_t tmem_base;
+    uint32_t abort_flag;
+};
+
+template <int D>
+__global__ void __launch_bounds__(kFwdThreads, 1)
+attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+                   const __grid_constant__ CUtensorMap tmap_v, const FwdParams p)
+{
+    constexpr int kTileBytes = 128 * D * 2;          // one 128-row tile of Q, K or V
+    constexpr int kChunkBytes = 128 * 128;           // one 64-element-wide TMA box (128 rows x 128 B)
+    constexpr int kChunks = D / 64;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t* sQ = smem;                               // [2][kTileBytes]
+    uint8_t* sK = sQ + 2 * kTileBytes;                // [2][kTileBytes]
+    uint8_t* sV = sK + 2 * kTileBytes;                // [2][kTileBytes]
+    FwdBarriers* bars = (FwdBarriers*)(sV + 2 * kTileBytes);
+    volatile uint32_t* abort_flag = &bars->abort_flag;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    // ---- work decode: heaviest query blocks first; the heads of one KV group are adjacent ----
+    const int bh_count = p.B * p.Hq;
+    const int qblk_rank = blockIdx.x / bh_count;
+    const int bh = blockIdx.x - qblk_rank * bh_count;
+    const int qblk = p.causal ? (p.n_qblk - 1 - qblk_rank) : qblk_rank;
+    const int b = bh / p.Hq, h = bh - b * p.Hq;
+    const int bh_kv = b * p.Hkv + h / (p.Hq / p.Hkv);
+    const int q0 = qblk * 2 * kM;
+    const int n_ktiles_all = (p.Skv + kN - 1) / kN;
+    int n_t[2];
+#pragma unroll
+    for (int t = 0; t < 2; ++t) {
+        const int row0 = q0 + t * kM;
+        if (row0 >= p.Sq) n_t[t] = 0;
+        else if (p.causal) n_t[t] = min(n_ktiles_all, row0 / kN + 1);
+        else n_t[t] = n_ktiles_all;
+    }
+    const int n_max = max(n_t[0], n_t[1]);
+
+    // ---- setup ----
+    if (warp == 9 && lane == 0) {
+        prefetch_tensormap(&tmap_q);
+        prefetch_tensormap(&tmap_k);
+        prefetch_tensormap(&tmap_v);
+        mbar_init(&bars->q_full, 1);
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&bars->k_full[i], 1);
+            mbar_init(&bars->k_empty[i], 1);
+            mbar_init(&bars->v_full[i], 1);
+            mbar_init(&bars->v_empty[i], 1);
+            mbar_init(&bars->s_ready[i], 1);
+            mbar_init(&bars->p_ready[i], 128);
+            mbar_init(&bars->o_ready[i], 1);
+        }
+        mbar_init(&bars->final_bar, 1);
+        bars->abort_flag = 0;
+        fence_mbar_init();
+    }
+    if (warp == 8) {
+        tmem_alloc(&bars->tmem_base, kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = bars->tmem_base;
+    const uint32_t tmem_S[2] = {tmem + 0u, tmem + 128u};
+    const uint32_t tmem_O[2] = {tmem + 256u, tmem + 384u};
+
+    if (warp == 9) {
+        // =========================== TMA producer ===========================
+        if (lane == 0) {
+            int n_valid = (n_t[0] > 0) + (n_t[1] > 0);
+            mbar_arrive_expect_tx(&bars->q_full, (uint32_t)(n_valid * kTileBytes));
+            for (int t = 0; t < 2; ++t)
+                if (n_t[t] > 0)
+                    for (int c = 0; c < kChunks; ++c)
+                        tma_load_3d(sQ + t * kTileBytes + c * kChunkBytes, &tmap_q, &bars->q_full, c * 64, q0 + t * kM, bh);
+            for (int j = 0; j < n_max; ++j) {
+                const int st = j & 1;
+                if (j >= 2 && !mbar_wait(&bars->k_empty[st], ((j >> 1) - 1) & 1, abort_flag, kSiteKEmpty)) break;
+                mbar_arrive_expect_tx(&bars->k_full[st], (uint32_t)kTileBytes);
+                for (int c = 0; c < kChunks; ++c)
+                    tma_load_3d(sK + st * kTileBytes + c * kChunkBytes, &tmap_k, &bars->k_full[st], c * 64, j * kN, bh_kv);
+                if (j >= 2 && !mbar_wait(&bars->v_empty[st], ((j >> 1) - 1) & 1, abort_flag, kSiteVEmpty)) break;
+                mbar_arrive_expect_tx(&bars->v_full[st], (uint32_t)kTileBytes);
+                for (int c = 0; c < kChunks; ++c)
+                    tma_load_3d(sV + st * kTileBytes + c * kChunkBytes, &tmap_v, &bars->v_full[st], c * 64, j * kN, bh_kv);
+            }
+        }
+    } else if (warp == 8) {
+        // =========================== MMA issuer ===========================
+        if (lane == 0) {
+            constexpr uint32_t idesc_s = make_idesc(kM, kN, false, false);
+            constexpr uint32_t idesc_pv = make_idesc(kM, D, false, true);
+            const uint32_t q_base = smem_u32(sQ), k_base = smem_u32(sK), v_base = smem_u32(sV);
+            auto issue_s = [&](int t, int st) {
+#pragma unroll
+                for (int ks = 0; ks < D / 16; ++ks) {
+                    const uint32_t off = (uint32_t)((ks >> 2) * kChunkBytes + (ks & 3) * 32);
+                    mma_ss(tmem_S[t], make_sdesc(q_base + t * kTileBytes + off, 16, 1024),
+                           make_sdesc(k_base + st * kTileBytes + off, 16, 1024), idesc_s, ks > 0 ? 1u : 0u);
+                }
+                tc_commit(&bars->s_ready[t]);
+            };
+            auto issue_pv = [&](int t, int st, bool accumulate) {
+#pragma unroll
+                for (int ks = 0; ks < kN / 16; ++ks) {
+                    mma_ts(tmem_O[t], tmem_S[t] + (uint32_t)(ks * 8), make_sdesc(v_base + st * kTileBytes + ks * 2048, kChunkBytes, 1024),
+                           idesc_pv, (accumulate || ks > 0) ? 1u : 0u);
+                }
+                tc_commit(&bars->o_ready[t]);
+            };
+            bool ok = n_max > 0 && mbar_wait(&bars->q_full, 0, abort_flag, kSiteQ) &&
+                      mbar_wait(&bars->k_full[0], 0, abort_flag, kSiteKFull);
+            if (ok) {
+                tc_fence_after();
+                if (n_t[0] > 0) issue_s(0, 0);
+                if (n_t[1] > 0) issue_s(1, 0);
+                tc_commit(&bars->k_empty[0]);
+            }
+            for (int j = 0; ok && j < n_max; ++j) {
+                const int st = j & 1, nst = st ^ 1;
+                const uint32_t ph = (uint32_t)((j >> 1) & 1), nph = (uint32_t)(((j + 1) >> 1) & 1);
+                if (!(ok = mbar_wait(&bars->v_full[st], ph, abort_flag, kSiteVFull))) break;
+                bool next_k_ready = false;
+                for (int t = 0; t < 2 && ok; ++t) {
+                    if (j >= n_t[t]) continue;
+                    if (!(ok = mbar_wait(&bars->p_ready[t], (uint32_t)(j & 1), abort_flag, kSitePReady))) break;
+                    tc_fence_after();
+                    issue_pv(t, st, j > 0);
+                    if (j + 1 < n_t[t]) {
+                        if (!next_k_ready) {
+                            if (!(ok = mbar_wait(&bars->k_full[nst], nph, abort_flag, kSiteKFull))) break;
+                            tc_fence_after();
+                            next_k_ready = true;
+                        }
+                        issue_s(t, nst);
+                    }
+                }
+                if (!ok) break;
+                if (j + 1 < n_max) tc_commit(&bars->k_empty[nst]);
+                tc_commit(&bars->v_empty[st]);
+            }
+            // every MMA issued above must have retired before shared memory / TMEM are given up
+            tc_commit(&bars->final_bar);
+            mbar_wait(&bars->final_bar, 0, abort_flag, kSiteFinal);
+        }
+    } else {
+        // =========================== softmax + epilogue warpgroups ===========================
+        const int t = warp >> 2;                       // tile 0 or 1
+        const int row = (warp & 3) * 32 + lane;        // row inside the tile == TMEM lane
+        const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;
+        const int grow = q0 + t * kM + row;            // global query index
+        const int n_mine = n_t[t];
+        float m_ref = -INFINITY, l = 0.0f;
+        bool ok = true;
+        for (int j = 0; j < n_mine; ++j) {
+            if (!(ok = mbar_wait(&bars->s_ready[t], (uint32_t)(j & 1), abort_flag, kSiteSReady))) break;
+            tc_fence_after();
+            uint32_t s[128];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) tmem_ld32(tmem_S[t] + lane_off + (uint32_t)(c * 32), s + c * 32);
+            tmem_ld_wait();
+            // number of visible keys of this row inside this tile
+            int limit = (p.causal ? min(p.Skv, grow + 1) : p.Skv) - j * kN;
+            if (limit < kN) {
+#pragma unroll
+                for (int c = 0; c < kN; ++c)
+                    if (c >= limit) s[c] = 0xff800000u;  // -inf
+            }
+            float mx = -INFINITY;
+#pragma unroll
+            for (int c = 0; c < kN; ++c) mx = fmaxf(mx, __uint_as_float(s[c]));
+            const float m_new = fmaxf(m_ref, mx * p.scale_log2);
+            const bool need = (m_new - m_ref) > kRescaleThreshold;   // false when both are -inf (NaN compare)
+            if (j == 0) {
+                m_ref = m_new;
+            } else if (__any_sync(0xffffffffu, need)) {
+                if (!(ok = mbar_wait(&bars->o_ready[t], (uint32_t)((j - 1) & 1), abort_flag, kSiteOReady))) break;
+                tc_fence_after();
+                const float factor = need ? ex2(m_ref - m_new) : 1.0f;
+                if (need) m_ref = m_new;
+                l *= factor;
+#pragma unroll
+                for (int c = 0; c < D / 32; ++c) {
+                    uint32_t o[32];
+                    tmem_ld32(tmem_O[t] + lane_off + (uint32_t)(c * 32), o);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * factor);
+                    tmem_st32(tmem_O[t] + lane_off + (uint32_t)(c * 32), o);
+                }
+                tmem_st_wait();
+            }
+            const float neg_m = (m_ref == -INFINITY) ? 0.0f : -m_ref;
+            uint32_t pk[64];
+#pragma unroll
+            for (int c = 0; c < 64; ++c) {
+                const float p0 = ex2(fmaf(__uint_as_float(s[2 * c]), p.scale_log2, neg_m));
+                const float p1 = ex2(fmaf(__uint_as_float(s[2 * c + 1]), p.scale_log2, neg_m));
+                l += p0 + p1;
+                pk[c] = pack_bf16(p0, p1);
+            }
+            tmem_st32(tmem_S[t] + lane_off, pk);
+            tmem_st32(tmem_S[t] + lane_off + 32u, pk + 32);
+            tmem_st_wait();
+            tc_fence_before();
+            mbar_arrive(&bars->p_ready[t]);
+        }
+        if (ok && n_mine > 0 && mbar_wait(&bars->o_ready[t], (uint32_t)((n_mine - 1) & 1), abort_flag, kSiteOReady)) {
+            tc_fence_after();
+            const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+            const bool store = grow < p.Sq;
+            __nv_bfloat16* orow = p.o + ((size_t)bh * p.Sq + (size_t)(store ? grow : 0)) * D;
+#pragma unroll
+            for (int c = 0; c < D / 32; ++c) {
+                uint32_t o[32];
+                tmem_ld32(tmem_O[t] + lane_off + (uint32_t)(c * 32), o);
+                tmem_ld_wait();
+                if (store) {
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        uint4 w;
+                        w.x = pack_bf16(__uint_as_float(o[8 * i + 0]) * inv, __uint_as_float(o[8 * i + 1]) * inv);
+                        w.y = pack_bf16(__uint_as_float(o[8 * i + 2]) * inv, __uint_as_float(o[8 * i + 3]) * inv);
+                        w.z = pack_bf16(__uint_as_float(o[8 * i + 4]) * inv, __uint_as_float(o[8 * i + 5]) * inv);
+                        w.w = pack_bf16(__uint_as_float(o[8 * i + 6]) * inv, __uint_as_float(o[8 * i + 7]) * inv);
+                        *reinterpret_cast<uint4*>(orow + c * 32 + i * 8) = w;
+                    }
+                }
+            }
+            if (store)
+                p.lse[(size_t)bh * p.Sq + grow] = l > 0.0f ? (m_ref + log2f(l)) * 0.6931471805599453f : -INFINITY;
+        }
+    }
+
+    // ---- teardown ----
+    if (*abort_flag) {
+        // a wait gave up: let TMA copies that may still be in flight land before the CTA's memory is released
+        for (int i = 0; i < 64; ++i) __nanosleep(2000);
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 8) {
+        tc_fence_after();
+        tmem_dealloc(tmem, kTmemCols);
+    }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn()
+{
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)sym;
+    });
+    return fn;
+}
+
+template <int D>
+cudaError_t launch_fwd(const TcArgs& a, cudaStream_t st)
+{
+    const AttnShape& s = a.s;
+    CUtensorMap tq, tk, tv;
+    cudaError_t e;
+    if ((e = encode_tmap_bf16_3d(&tq, a.q, D, s.Sq, s.B * s.Hq, 128)) != cudaSuccess) return e;
+    if ((e = encode_tmap_bf16_3d(&tk, a.k, D, s.Skv, s.B * s.Hkv, 128)) != cudaSuccess) return e;
+    if ((e = encode_tmap_bf16_3d(&tv, a.v, D, s.Skv, s.B * s.Hkv, 128)) != cudaSuccess) return e;
+    FwdParams p{};
+    p.o = a.o_out;
+    p.lse = a.lse_out;
+    p.B = s.B; p.Hq = s.Hq; p.Hkv = s.Hkv; p.Sq = s.Sq; p.Skv = s.Skv;
+    p.causal = s.causal;
+    p.n_qblk = (s.Sq + 2 * kM - 1) / (2 * kM);
+    p.scale_log2 = s.scale * 1.4426950408889634f;
+    const size_t smem = 6 * (size_t)(128 * D * 2) + sizeof(FwdBarriers) + 1024;
+    static bool configured = false;  // per instantiation
+    if (!configured) {
+        if ((e = cudaFuncSetAttribute(attn_fwd_tc_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)) != cudaSuccess)
+            return e;
+        configured = true;
+    }
+    const long long ctas = (long long)p.n_qblk * s.B * s.Hq;
+    if (ctas > 0x7fffffffLL) return cudaErrorInvalidConfiguration;
+    attn_fwd_tc_kernel<D><<<(unsigned)ctas, kFwdThreads, smem, st>>>(tq, tk, tv, p);
+    count_launch();
+    return cudaGetLastError();
+}
+
+}  // namespace
+
+cudaError_t encode_tmap_bf16_3d(CUtensorMap* out, const void* base, int D, int rows, int slabs, int box_rows)
+{
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return cudaErrorNotSupported;
+    if (((uintptr_t)base & 15u) != 0) return cudaErrorMisalignedAddress;
+    cuuint64_t dims[3] = {(cuuint64_t)D, (cuuint64_t)rows, (cuuint64_t)slabs};
+    cuuint64_t strides[2] = {(cuuint64_t)D * 2, (cuuint64_t)rows * D * 2};
+    cuuint32_t box[3] = {64u, (cuuint32_t)box_rows, 1u};
+    cuuint32_t estr[3] = {1u, 1u, 1u};
+    CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
+}
+
+bool tc_fwd_supported(const AttnShape& s)
+{
+    return (s.D == 64 || s.D == 128) && (!s.causal || s.Sq == s.Skv);
+}
+
+cudaError_t tc_forward(const TcArgs& a, cudaStream_t st)
+{
+    return a.s.D == 64 ? launch_fwd<64>(a, st) : launch_fwd<128>(a, st);
+}
+
+cudaError_t read_and_clear_fwd_status(cudaStream_t st, uint32_t* word)
+{
+    cudaError_t e = cudaStreamSynchronize(st);
+    if (e != cudaSuccess) return e;
+    unsigned int w = 0, zero = 0;
+    if ((e = cudaMemcpyFromSymbol(&w, ptx::g_device_status, sizeof(w))) != cudaSuccess) return e;
+    if (w != 0 && (e = cudaMemcpyToSymbol(ptx::g_device_status, &zero, sizeof(zero))) != cudaSuccess) return e;
+    *word = w;
+    return cudaSuccess;
+}
+
+}  // namespace sntl

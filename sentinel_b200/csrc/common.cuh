@@ -1,0 +1,78 @@
+// Shared declarations of the attention library's translation units.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "sntl_attn.h"
+
+namespace sntl {
+
+// Element strides of a [B][H][S][D]-indexed tensor; covers both layouts of the C ABI.
+struct View4 {
+    long long sb, sh, ss, sd;
+};
+// Element strides of a [B][H][S]-indexed fp32 tensor (LSE, delta).
+struct View3 {
+    long long sb, sh, ss;
+};
+
+struct AttnShape {
+    int B, Hq, Hkv, Sq, Skv, D;
+    float scale;
+    int causal;
+};
+
+// Exact-fp32 SIMT kernels (attn_simt.cu).  T = float or __nv_bfloat16 element type.
+struct SimtArgs {
+    AttnShape s;
+    int is_bf16;
+    const void *q, *k, *v, *o, *dout;
+    void *o_out, *dq, *dk, *dv;
+    float *lse_out, *delta;
+    const float* lse;
+    View4 vq, vkv;     // q-like tensors (Q, O, dO, dQ) and kv-like tensors (K, V, dK, dV)
+    View3 vlse, vdelta;
+};
+cudaError_t simt_forward(const SimtArgs& a, cudaStream_t st);
+cudaError_t simt_backward(const SimtArgs& a, cudaStream_t st);  // delta pass + dQ kernel + dK/dV kernel
+
+// Tensor-core kernels (attn_fwd_sm100.cu / attn_bwd_sm100.cu): bf16, BHSD contiguous, D in {64,128}.
+struct TcArgs {
+    AttnShape s;
+    const __nv_bfloat16 *q, *k, *v, *o, *dout;
+    __nv_bfloat16 *o_out, *dq, *dk, *dv;
+    float* lse_out;
+    const float* lse;
+    float* delta;      // [B][Hq][Sq_pad]
+    float* dq_accum;   // [B][Hq][Sq_pad][D] fp32
+};
+bool tc_fwd_supported(const AttnShape& s);
+bool tc_bwd_supported(const AttnShape& s);
+cudaError_t tc_forward(const TcArgs& a, cudaStream_t st);
+cudaError_t tc_backward(const TcArgs& a, cudaStream_t st);
+size_t tc_backward_workspace_bytes(const AttnShape& s);
+
+// Layout / dtype staging (layout_convert.cu): SENTINEL fp32 feature-major <-> bf16 BHSD.
+cudaError_t sentinel_to_bhsd_bf16(const float* src, __nv_bfloat16* dst, int B, int H, int S, int D, int stride_columns,
+                                  int column_start, cudaStream_t st);
+cudaError_t bhsd_bf16_to_sentinel(const __nv_bfloat16* src, float* dst, int B, int H, int S, int D, int stride_columns,
+                                  int column_start, cudaStream_t st);
+cudaError_t f32_to_bf16(const float* src, __nv_bfloat16* dst, size_t n, cudaStream_t st);
+cudaError_t bf16_to_f32(const __nv_bfloat16* src, float* dst, size_t n, cudaStream_t st);
+cudaError_t lse_bhs_to_sentinel(const float* src, float* dst, int B, int H, int S, int stride_columns, int column_start,
+                                cudaStream_t st);
+cudaError_t lse_sentinel_to_bhs(const float* src, float* dst, int B, int H, int S, int stride_columns, int column_start,
+                                cudaStream_t st);
+cudaError_t merge_partials(int acc_dtype, int part_dtype, long long rows, int D, void* o_acc, float* lse_acc,
+                           const void* o_part, const float* lse_part, cudaStream_t st);
+
+// Launch accounting (attn_api.cu).
+void count_launch(int n = 1);
+
+// Device status words written by bounded waits (one per tensor-core translation unit).
+cudaError_t read_and_clear_fwd_status(cudaStream_t st, uint32_t* word);
+cudaError_t read_and_clear_bwd_status(cudaStream_t st, uint32_t* word);
+
+}  // namespace sntl

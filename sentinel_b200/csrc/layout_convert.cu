@@ -1,0 +1,177 @@
+// HBM-bound staging kernels: the reference's fp32 feature-major matrices <-> bf16 token-major tensors,
+// plain dtype casts, LSE re-indexing, and the log-sum-exp merge of two partial attention results.
+//
+// Feature-major ("SENTINEL") addressing follows sentinel/NeuralNet/Cuda/CudaFlashAttention.cu:129-131:
+// element (b,h,s,d) lives at (h*D + d)*stride_columns + column_start + b*S + s.
+#include "common.cuh"
+
+namespace sntl {
+namespace {
+
+// 32x32 transposing tile: reads are contiguous along tokens (source rows), writes along d (destination rows).
+__global__ void sentinel_to_bhsd_kernel(const float* __restrict__ src, __nv_bfloat16* __restrict__ dst, int H, int S, int D,
+                                        int stride_columns, int column_start)
+{
+    __shared__ float tile[32][33];
+    const int bh = blockIdx.z, b = bh / H, h = bh % H;
+    const int s0 = blockIdx.x * 32, d0 = blockIdx.y * 32;
+    const int tx = threadIdx.x, ty = threadIdx.y;  // 32 x 8
+    for (int r = ty; r < 32; r += 8) {
+        const int d = d0 + r, s = s0 + tx;
+        tile[r][tx] = (d < D && s < S) ? src[(long long)(h * D + d) * stride_columns + column_start + (long long)b * S + s] : 0.0f;
+    }
+    __syncthreads();
+    for (int r = ty; r < 32; r += 8) {
+        const int s = s0 + r, d = d0 + tx;
+        if (s < S && d < D) dst[((long long)bh * S + s) * D + d] = __float2bfloat16_rn(tile[tx][r]);
+    }
+}
+
+__global__ void bhsd_to_sentinel_kernel(const __nv_bfloat16* __restrict__ src, float* __restrict__ dst, int H, int S, int D,
+                                        int stride_columns, int column_start)
+{
+    __shared__ float tile[32][33];
+    const int bh = blockIdx.z, b = bh / H, h = bh % H;
+    const int s0 = blockIdx.x * 32, d0 = blockIdx.y * 32;
+    const int tx = threadIdx.x, ty = threadIdx.y;
+    for (int r = ty; r < 32; r += 8) {
+        const int s = s0 + r, d = d0 + tx;
+        tile[r][tx] = (s < S && d < D) ? __bfloat162float(src[((long long)bh * S + s) * D + d]) : 0.0f;
+    }
+    __syncthreads();
+    for (int r = ty; r < 32; r += 8) {
+        const int d = d0 + r, s = s0 + tx;
+        if (d < D && s < S) dst[(long long)(h * D + d) * stride_columns + column_start + (long long)b * S + s] = tile[tx][r];
+    }
+}
+
+__global__ void f32_to_bf16_kernel(const float* __restrict__ src, __nv_bfloat16* __restrict__ dst, size_t n)
+{
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+        dst[i] = __float2bfloat16_rn(src[i]);
+}
+__global__ void bf16_to_f32_kernel(const __nv_bfloat16* __restrict__ src, float* __restrict__ dst, size_t n)
+{
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+        dst[i] = __bfloat162float(src[i]);
+}
+
+// dir 0: [B][H][S] -> H x stride_columns ; dir 1: the reverse
+__global__ void lse_reindex_kernel(const float* __restrict__ src, float* __restrict__ dst, int B, int H, int S,
+                                   int stride_columns, int column_start, int dir)
+{
+    const long long n = (long long)B * H * S;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+        const int s = (int)(i % S);
+        const int h = (int)((i / S) % H);
+        const int b = (int)(i / ((long long)S * H));
+        const long long j = (long long)h * stride_columns + column_start + (long long)b * S + s;
+        if (dir == 0) dst[j] = src[i];
+        else dst[i] = src[j];
+    }
+}
+
+template <typename T> __device__ __forceinline__ float ldf(const T* p);
+template <> __device__ __forceinline__ float ldf<float>(const float* p) { return *p; }
+template <> __device__ __forceinline__ float ldf<__nv_bfloat16>(const __nv_bfloat16* p) { return __bfloat162float(*p); }
+template <typename T> __device__ __forceinline__ void stf(T* p, float x);
+template <> __device__ __forceinline__ void stf<float>(float* p, float x) { *p = x; }
+template <> __device__ __forceinline__ void stf<__nv_bfloat16>(__nv_bfloat16* p, float x) { *p = __float2bfloat16_rn(x); }
+
+// One warp per row: (o_acc, lse_acc) <- the softmax-weighted combination with (o_part, lse_part).
+template <typename T, typename P>
+__global__ void merge_kernel(long long rows, int D, T* __restrict__ o_acc, float* __restrict__ lse_acc,
+                             const P* __restrict__ o_part, const float* __restrict__ lse_part)
+{
+    const int lane = threadIdx.x & 31;
+    const long long row = blockIdx.x * (long long)(blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (row >= rows) return;
+    const float la = lse_acc[row], lb = lse_part[row];
+    const float m = fmaxf(la, lb);
+    if (m == -INFINITY) return;  // both empty: keep zeros / -inf
+    const float wa = expf(la - m), wb = expf(lb - m);
+    const float inv = 1.0f / (wa + wb);
+    for (int d = lane; d < D; d += 32) {
+        const float x = ldf(o_acc + row * D + d) * wa + ldf(o_part + row * D + d) * wb;
+        stf(o_acc + row * D + d, x * inv);
+    }
+    if (lane == 0) lse_acc[row] = m + logf(wa + wb);
+}
+
+inline int blocks_for(size_t n, int threads)
+{
+    size_t b = (n + threads - 1) / threads;
+    return (int)(b > 148 * 16 ? 148 * 16 : (b ? b : 1));
+}
+
+}  // namespace
+
+cudaError_t sentinel_to_bhsd_bf16(const float* src, __nv_bfloat16* dst, int B, int H, int S, int D, int stride_columns,
+                                  int column_start, cudaStream_t st)
+{
+    dim3 grid((S + 31) / 32, (D + 31) / 32, B * H), block(32, 8);
+    sentinel_to_bhsd_kernel<<<grid, block, 0, st>>>(src, dst, H, S, D, stride_columns, column_start);
+    count_launch();
+    return cudaGetLastError();
+}
+
+cudaError_t bhsd_bf16_to_sentinel(const __nv_bfloat16* src, float* dst, int B, int H, int S, int D, int stride_columns,
+                                  int column_start, cudaStream_t st)
+{
+    dim3 grid((S + 31) / 32, (D + 31) / 32, B * H), block(32, 8);
+    bhsd_to_sentinel_kernel<<<grid, block, 0, st>>>(src, dst, H, S, D, stride_columns, column_start);
+    count_launch();
+    return cudaGetLastError();
+}
+
+cudaError_t f32_to_bf16(const float* src, __nv_bfloat16* dst, size_t n, cudaStream_t st)
+{
+    f32_to_bf16_kernel<<<blocks_for(n, 256), 256, 0, st>>>(src, dst, n);
+    count_launch();
+    return cudaGetLastError();
+}
+
+cudaError_t bf16_to_f32(const __nv_bfloat16* src, float* dst, size_t n, cudaStream_t st)
+{
+    bf16_to_f32_kernel<<<blocks_for(n, 256), 256, 0, st>>>(src, dst, n);
+    count_launch();
+    return cudaGetLastError();
+}
+
+cudaError_t lse_bhs_to_sentinel(const float* src, float* dst, int B, int H, int S, int stride_columns, int column_start,
+                                cudaStream_t st)
+{
+    lse_reindex_kernel<<<blocks_for((size_t)B * H * S, 256), 256, 0, st>>>(src, dst, B, H, S, stride_columns, column_start, 0);
+    count_launch();
+    return cudaGetLastError();
+}
+
+cudaError_t lse_sentinel_to_bhs(const float* src, float* dst, int B, int H, int S, int stride_columns, int column_start,
+                                cudaStream_t st)
+{
+    lse_reindex_kernel<<<blocks_for((size_t)B * H * S, 256), 256, 0, st>>>(src, dst, B, H, S, stride_columns, column_start, 1);
+    count_launch();
+    return cudaGetLastError();
+}
+
+cudaError_t merge_partials(int acc_dtype, int part_dtype, long long rows, int D, void* o_acc, float* lse_acc,
+                           const void* o_part, const float* lse_part, cudaStream_t st)
+{
+    const int warps = 8;
+    const long long blocks = (rows + warps - 1) / warps;
+    if (blocks <= 0) return cudaSuccess;
+    const unsigned g = (unsigned)blocks;
+    const bool ab = acc_dtype == SNTL_DTYPE_BF16, pb = part_dtype == SNTL_DTYPE_BF16;
+    if (ab && pb)
+        merge_kernel<<<g, warps * 32, 0, st>>>(rows, D, (__nv_bfloat16*)o_acc, lse_acc, (const __nv_bfloat16*)o_part, lse_part);
+    else if (!ab && pb)
+        merge_kernel<<<g, warps * 32, 0, st>>>(rows, D, (float*)o_acc, lse_acc, (const __nv_bfloat16*)o_part, lse_part);
+    else if (ab && !pb)
+        merge_kernel<<<g, warps * 32, 0, st>>>(rows, D, (__nv_bfloat16*)o_acc, lse_acc, (const float*)o_part, lse_part);
+    else
+        merge_kernel<<<g, warps * 32, 0, st>>>(rows, D, (float*)o_acc, lse_acc, (const float*)o_part, lse_part);
+    count_launch();
+    return cudaGetLastError();
+}
+
+}  // namespace sntl

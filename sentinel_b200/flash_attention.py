@@ -1,0 +1,246 @@
+"""Python host side of the attention path: ctypes calls into the C ABI on torch-owned device memory.
+
+Two levels:
+
+* ``attention_forward`` / ``attention_backward`` -- the native interface: bf16 (or fp32) token-major
+  ``[B, H, S, D]`` CUDA tensors, grouped-query heads native.
+* ``CudaFlashAttention`` -- the reference's operator interface (same method names, argument order, defaults
+  and error behaviour as ``sentinel/NeuralNet/Cuda/CudaFlashAttention.hpp:10-41``) on fp32 feature-major
+  ``(H*D) x strideColumns`` CUDA tensors, so the reference's parity procedures can be replayed against it.
+
+Nothing here computes attention: every result comes from ``lib/libsntl_attn.so``.  torch supplies memory and
+the current stream.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from . import _lib
+
+_ws_cache: dict = {}
+
+
+def _stream_ptr() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _workspace(nbytes: int, device) -> torch.Tensor | None:
+    """Grow-only scratch per device (the reference grows its buffers the same way, CudaMatmul.cu:119-136)."""
+    if nbytes == 0:
+        return None
+    key = (device.type, device.index)
+    buf = _ws_cache.get(key)
+    if buf is None or buf.numel() < nbytes:
+        buf = torch.empty(nbytes, dtype=torch.uint8, device=device)
+        _ws_cache[key] = buf
+    return buf
+
+
+def _dtype_code(t: torch.Tensor) -> int:
+    if t.dtype == torch.bfloat16:
+        return _lib.DTYPE_BF16
+    if t.dtype == torch.float32:
+        return _lib.DTYPE_F32
+    raise ValueError(f"unsupported dtype {t.dtype}: bf16 or fp32 expected")
+
+
+def _require(t: torch.Tensor, name: str) -> None:
+    if not t.is_cuda:
+        raise ValueError(f"{name} must be a CUDA tensor (there is no CPU path)")
+    if not t.is_contiguous():
+        raise ValueError(f"{name} must be contiguous")
+
+
+def _bhsd_desc(q, k, causal, scale, flags) -> _lib.Desc:
+    if q.dim() != 4 or k.dim() != 4:
+        raise ValueError("expected [B, H, S, D] tensors")
+    B, Hq, Sq, D = q.shape
+    Bk, Hkv, Skv, Dk = k.shape
+    if Bk != B or Dk != D:
+        raise ValueError("q and k disagree on batch or head_dim")
+    if scale is None:
+        scale = D ** -0.5
+    return _lib.Desc(_dtype_code(q), _lib.LAYOUT_BHSD, B, Hq, Hkv, Sq, Skv, D, float(scale), int(bool(causal)), 0, 0,
+                     int(flags))
+
+
+def attention_forward(q, k, v, *, causal=True, scale=None, flags=0, out=None, lse=None):
+    """O, LSE = attention(Q, K, V).  q: [B,Hq,Sq,D]; k, v: [B,Hkv,Skv,D]; LSE: [B,Hq,Sq] fp32 (natural log)."""
+    lib = _lib.load()
+    for t, n in ((q, "q"), (k, "k"), (v, "v")):
+        _require(t, n)
+    if k.shape != v.shape or k.dtype != q.dtype or v.dtype != q.dtype:
+        raise ValueError("k and v must share shape; q, k, v must share dtype")
+    d = _bhsd_desc(q, k, causal, scale, flags)
+    o = torch.empty_like(q) if out is None else out
+    lse = torch.empty(q.shape[:3], dtype=torch.float32, device=q.device) if lse is None else lse
+    nbytes = lib.sntl_attn_fwd_workspace_bytes(C.byref(d))
+    ws = _workspace(nbytes, q.device)
+    rc = lib.sntl_attn_fwd(C.byref(d), q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(),
+                           ws.data_ptr() if ws is not None else None, nbytes, _stream_ptr())
+    _lib.check(rc, "sntl_attn_fwd")
+    return o, lse
+
+
+def attention_backward(q, k, v, o, lse, dout, *, causal=True, scale=None, flags=0, dq=None, dk=None, dv=None):
+    """dQ, dK, dV from dO (P recomputed from LSE).  Shapes as in attention_forward."""
+    lib = _lib.load()
+    for t, n in ((q, "q"), (k, "k"), (v, "v"), (o, "o"), (lse, "lse"), (dout, "dout")):
+        _require(t, n)
+    if o.shape != q.shape or dout.shape != q.shape or lse.shape != q.shape[:3] or lse.dtype != torch.float32:
+        raise ValueError("o/dout must match q; lse must be fp32 [B,Hq,Sq]")
+    d = _bhsd_desc(q, k, causal, scale, flags)
+    dq = torch.empty_like(q) if dq is None else dq
+    dk = torch.empty_like(k) if dk is None else dk
+    dv = torch.empty_like(v) if dv is None else dv
+    nbytes = lib.sntl_attn_bwd_workspace_bytes(C.byref(d))
+    ws = _workspace(nbytes, q.device)
+    rc = lib.sntl_attn_bwd(C.byref(d), q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(),
+                           dout.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
+                           ws.data_ptr() if ws is not None else None, nbytes, _stream_ptr())
+    _lib.check(rc, "sntl_attn_bwd")
+    return dq, dk, dv
+
+
+def attention_forward_backward_host(q, k, v, dout, *, causal=True, scale=None, flags=0, device="cuda"):
+    """End-to-end call on HOST tensors (pinned memory recommended): uploads Q, K, V, dO, runs forward and
+    backward on the device, downloads O, LSE, dQ, dK, dV.  This is the path the benchmark's ``e2e`` times."""
+    dev = torch.device(device)
+    dq_, dk_, dv_, do_ = (t.to(dev, non_blocking=True) for t in (q, k, v, dout))
+    o, lse = attention_forward(dq_, dk_, dv_, causal=causal, scale=scale, flags=flags)
+    gq, gk, gv = attention_backward(dq_, dk_, dv_, o, lse, do_, causal=causal, scale=scale, flags=flags)
+    outs = [t.to("cpu", non_blocking=True) for t in (o, lse, gq, gk, gv)]
+    torch.cuda.current_stream().synchronize()
+    return tuple(outs)
+
+
+def merge_partials(o_acc, lse_acc, o_part, lse_part):
+    """In-place log-sum-exp merge of two partial results over disjoint key sets (ring combine step)."""
+    lib = _lib.load()
+    for t, n in ((o_acc, "o_acc"), (lse_acc, "lse_acc"), (o_part, "o_part"), (lse_part, "lse_part")):
+        _require(t, n)
+    D = o_acc.shape[-1]
+    rows = o_acc.numel() // D
+    rc = lib.sntl_attn_merge(_dtype_code(o_acc), _dtype_code(o_part), rows, D, o_acc.data_ptr(), lse_acc.data_ptr(),
+                             o_part.data_ptr(), lse_part.data_ptr(), _stream_ptr())
+    _lib.check(rc, "sntl_attn_merge")
+    return o_acc, lse_acc
+
+
+def last_path() -> str:
+    return _lib.load().sntl_attn_last_path().decode()
+
+
+def launch_count() -> int:
+    return int(_lib.load().sntl_attn_launch_count())
+
+
+def poll_device_status() -> int:
+    """Synchronises the current stream and returns the device status word (0 = no bounded wait ran out)."""
+    word = C.c_uint32(0)
+    rc = _lib.load().sntl_attn_poll_device_status(_stream_ptr(), C.byref(word))
+    if rc not in (_lib.OK, _lib.ERR_DEVICE_TIMEOUT):
+        _lib.check(rc, "sntl_attn_poll_device_status")
+    return int(word.value)
+
+
+class CudaFlashAttention:
+    """The reference's operator interface (CudaFlashAttention.hpp:10-41) over fp32 feature-major CUDA tensors.
+
+    ``query`` is ``(headCount*headDimension) x strideColumns``; ``key``/``value`` are
+    ``(kvHeads*headDimension) x strideColumns`` (kvHeads == headCount reproduces the reference call, fewer
+    heads = grouped-query attention without repeating K/V); ``logSumExp`` is ``headCount x strideColumns``.
+    Outputs are allocated by the callee when not passed, as the reference's ensureSize does.
+    """
+    queryTileSize = 128
+    keyTileSize = 128
+    maxHeadDimension = 128
+    allow_reduced_precision = False
+
+    @staticmethod
+    def _desc(query, key, headCount, headDimension, scale, causal, columnStart, columnCount, packCount):
+        op = "CudaFlashAttention"
+        if query.numel() == 0 or key.numel() == 0:
+            raise ValueError(f"{op} empty input")
+        if headCount <= 0 or headDimension <= 0:
+            raise ValueError(f"{op} invalid head geometry")
+        if query.shape[0] != headCount * headDimension:
+            raise ValueError(f"{op} query rows mismatch headCount*headDim")
+        if key.shape[0] % headDimension != 0 or headCount % (key.shape[0] // headDimension) != 0:
+            raise ValueError(f"{op} key/value rows mismatch")
+        if query.shape[1] != key.shape[1]:
+            raise ValueError(f"{op} sequenceLength mismatch")
+        if packCount <= 0:
+            packCount = 1
+        stride = query.shape[1]
+        if columnCount <= 0:                      # resolveColumnWindow, CudaFlashAttention.cu:1533-1539
+            columnCount = stride - columnStart
+        if columnStart < 0 or columnCount <= 0 or columnStart + columnCount > stride:
+            raise ValueError(f"{op} invalid column window")
+        if columnStart + packCount * columnCount > stride:
+            raise ValueError(f"{op} pack window exceeds columns")
+        flags = _lib.FLAG_ALLOW_BF16_COMPUTE if CudaFlashAttention.allow_reduced_precision else 0
+        return _lib.Desc(_lib.DTYPE_F32, _lib.LAYOUT_SENTINEL, packCount, headCount, key.shape[0] // headDimension,
+                         columnCount, columnCount, headDimension, float(scale), int(bool(causal)), stride, columnStart,
+                         flags)
+
+    @staticmethod
+    def forwardMultiHead(query, key, value, out, logSumExp, headCount, headDimension, scale, causal=True, columnStart=0,
+                         columnCount=0, packCount=1):
+        lib = _lib.load()
+        if key.shape != value.shape:
+            raise ValueError("CudaFlashAttention key/value rows mismatch")
+        d = CudaFlashAttention._desc(query, key, headCount, headDimension, scale, causal, columnStart, columnCount, packCount)
+        for t, n in ((query, "query"), (key, "key"), (value, "value")):
+            _require(t, n)
+        if out is None:
+            out = torch.zeros_like(query)
+        if logSumExp is None:
+            logSumExp = torch.zeros(headCount, query.shape[1], dtype=torch.float32, device=query.device)
+        nbytes = lib.sntl_attn_fwd_workspace_bytes(C.byref(d))
+        ws = _workspace(nbytes, query.device)
+        rc = lib.sntl_attn_fwd(C.byref(d), query.data_ptr(), key.data_ptr(), value.data_ptr(), out.data_ptr(),
+                               logSumExp.data_ptr(), ws.data_ptr() if ws is not None else None, nbytes, _stream_ptr())
+        _lib.check(rc, "CudaFlashAttention::forwardMultiHead")
+        return out, logSumExp
+
+    @staticmethod
+    def forward(query, key, value, out, logSumExp, scale, causal=True):
+        return CudaFlashAttention.forwardMultiHead(query, key, value, out, logSumExp, 1, query.shape[0], scale, causal, 0,
+                                                   query.shape[1])
+
+    @staticmethod
+    def backwardMultiHead(query, key, value, out, logSumExp, outGradient, queryGradient, keyGradient, valueGradient,
+                          deltaWorkspace, headCount, headDimension, scale, causal=True, columnStart=0, columnCount=0,
+                          packCount=1):
+        lib = _lib.load()
+        d = CudaFlashAttention._desc(query, key, headCount, headDimension, scale, causal, columnStart, columnCount, packCount)
+        if out.shape != query.shape:
+            raise ValueError("CudaFlashAttention::backwardMultiHead out shape mismatch")
+        if outGradient.shape != query.shape:
+            raise ValueError("CudaFlashAttention::backwardMultiHead outGradient shape mismatch")
+        if tuple(logSumExp.shape) != (headCount, query.shape[1]):
+            raise ValueError("CudaFlashAttention::backwardMultiHead logSumExp shape mismatch")
+        for t, n in ((query, "query"), (key, "key"), (value, "value"), (out, "out"), (logSumExp, "logSumExp"),
+                     (outGradient, "outGradient")):
+            _require(t, n)
+        queryGradient = torch.zeros_like(query) if queryGradient is None else queryGradient
+        keyGradient = torch.zeros_like(key) if keyGradient is None else keyGradient
+        valueGradient = torch.zeros_like(value) if valueGradient is None else valueGradient
+        nbytes = lib.sntl_attn_bwd_workspace_bytes(C.byref(d))
+        ws = _workspace(nbytes, query.device)
+        rc = lib.sntl_attn_bwd(C.byref(d), query.data_ptr(), key.data_ptr(), value.data_ptr(), out.data_ptr(),
+                               logSumExp.data_ptr(), outGradient.data_ptr(), queryGradient.data_ptr(),
+                               keyGradient.data_ptr(), valueGradient.data_ptr(),
+                               ws.data_ptr() if ws is not None else None, nbytes, _stream_ptr())
+        _lib.check(rc, "CudaFlashAttention::backwardMultiHead")
+        return queryGradient, keyGradient, valueGradient
+
+    @staticmethod
+    def backward(query, key, value, out, logSumExp, outGradient, queryGradient, keyGradient, valueGradient, scale,
+                 causal=True):
+        return CudaFlashAttention.backwardMultiHead(query, key, value, out, logSumExp, outGradient, queryGradient,
+                                                    keyGradient, valueGradient, None, 1, query.shape[0], scale, causal, 0,
+                                                    query.shape[1])

@@ -1,0 +1,62 @@
+"""Generates the golden fixtures of this directory by running the reference's OWN CPU attention layer
+(compiled from the reference sources into oracle/_ref by oracle/Makefile) on seeded inputs.
+
+The reference stores no golden vectors for this path; its tests are parity procedures between two of its own
+implementations on LCG/seeded inputs.  These fixtures freeze the outputs of its CPU layer
+(CausalSelfAttention::forward/backward through the public API, see oracle/ref_harness.cpp) so that the fp64
+restatement and the CUDA kernels can be checked where the reference sources are not available.
+
+Run from the repository root, where the reference is mounted:   python tests/golden/make_golden.py
+Each case is stored as <name>.npz with inputs (q, k, v, dout) and reference outputs (o, lse, dq, dk, dv), fp32,
+token-major [B, H, S, D].
+"""
+import os
+import sys
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+sys.path.insert(0, ROOT)
+
+from oracle import cpu  # noqa: E402
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+# name: (B, Hq, Hkv, S, D, input std, seed, round inputs to bf16)
+CASES = {
+    # BASELINE config 1: the repo-default toy LM attention, fp32
+    "toy_f32_b4_h4_s64_d16": (4, 4, 4, 64, 16, 1.0, 101, False),
+    # shape of the reference's runGqaHostSmokeDemo (E=64, 8 heads, 2 KV heads, S=16)
+    "gqa_h8_kv2_s16_d8": (1, 8, 2, 16, 8, 1.0, 102, False),
+    # shape of runFlashParitySmokeDemo(64, 4, 48, 64): S not a multiple of any tile size
+    "mha_h4_s48_d16": (2, 4, 4, 48, 16, 1.0, 103, False),
+    # tensor-core head sizes at ragged lengths, inputs pre-rounded to bf16 (what the bf16 kernels see)
+    "gqa_h4_kv1_s200_d64_bf16in": (1, 4, 1, 200, 64, 0.5, 104, True),
+    "gqa_h4_kv2_s136_d128_bf16in": (1, 4, 2, 136, 128, 0.5, 105, True),
+}
+
+
+def make_case(B, Hq, Hkv, S, D, std, seed, bf16_inputs):
+    rng = np.random.default_rng(seed)
+    q = (rng.standard_normal((B, Hq, S, D)) * std).astype(np.float32)
+    k = (rng.standard_normal((B, Hkv, S, D)) * std).astype(np.float32)
+    v = rng.standard_normal((B, Hkv, S, D)).astype(np.float32)
+    dout = rng.standard_normal((B, Hq, S, D)).astype(np.float32)
+    if bf16_inputs:
+        q, k, v, dout = (cpu.round_bf16(t) for t in (q, k, v, dout))
+    return q, k, v, dout
+
+
+def main():
+    if not cpu.ref_available():
+        cpu.build()
+    for name, spec in CASES.items():
+        q, k, v, dout = make_case(*spec)
+        o, lse, dq, dk, dv = cpu.ref_layer_fwd_bwd(q, k, v, dout)
+        path = os.path.join(HERE, name + ".npz")
+        np.savez_compressed(path, q=q, k=k, v=v, dout=dout, o=o, lse=lse, dq=dq, dk=dk, dv=dv)
+        print(f"{name}: wrote {os.path.getsize(path) / 1024:.0f} KiB")
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,143 @@
+"""CPU tests of the boundary: the C-ABI library loads, exports every symbol the header declares, validates
+arguments like the reference's host code, and the Python/C++ mirrors raise the reference's error kinds.
+No compute entry point runs a kernel here (there is no GPU in this suite)."""
+import ctypes as C
+import os
+import re
+
+import pytest
+
+from sentinel_b200 import _lib
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def lib():
+    if not os.path.exists(_lib.LIB_PATH):
+        from sentinel_b200 import build
+        build.build()
+    return _lib.load()
+
+
+def _declared_symbols():
+    text = open(os.path.join(ROOT, "include", "sntl_attn.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(sntl_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_every_declared_symbol_is_exported(lib):
+    names = _declared_symbols()
+    assert set(names) == set(_lib.EXPORTS), "header and loader disagree on the ABI surface"
+    for n in names:
+        assert hasattr(lib, n), f"{n} declared in include/sntl_attn.h but not exported"
+
+
+def test_version_and_status_strings(lib):
+    assert lib.sntl_attn_version() >= 100
+    seen = {lib.sntl_status_string(i).decode() for i in range(7)}
+    assert len(seen) == 7 and lib.sntl_status_string(99).decode() == "unknown status"
+
+
+def _desc(**kw):
+    base = dict(dtype=_lib.DTYPE_BF16, layout=_lib.LAYOUT_BHSD, batch=2, q_heads=8, kv_heads=2, seq_q=256, seq_kv=256,
+                head_dim=128, scale=0.088, causal=1, stride_columns=0, column_start=0, flags=0)
+    base.update(kw)
+    return _lib.Desc(**base)
+
+
+def test_workspace_sizes(lib):
+    d = _desc()
+    assert lib.sntl_attn_fwd_workspace_bytes(C.byref(d)) == 0          # native bf16 needs no forward scratch
+    bwd = lib.sntl_attn_bwd_workspace_bytes(C.byref(d))
+    assert bwd >= 4 * 2 * 8 * 256                                      # at least delta
+    f32 = _desc(dtype=_lib.DTYPE_F32, head_dim=16)
+    assert lib.sntl_attn_fwd_workspace_bytes(C.byref(f32)) == 0        # exact fp32 path: no staging
+    assert lib.sntl_attn_bwd_workspace_bytes(C.byref(f32)) >= 4 * 2 * 8 * 256
+    staged = _desc(dtype=_lib.DTYPE_F32, flags=_lib.FLAG_ALLOW_BF16_COMPUTE)
+    assert lib.sntl_attn_fwd_workspace_bytes(C.byref(staged)) >= 2 * (2 * 2 * 8 * 256 * 128)
+    assert lib.sntl_attn_bwd_workspace_bytes(C.byref(_desc(batch=0))) == 0
+
+
+@pytest.mark.parametrize("kw,status", [
+    (dict(batch=0), _lib.ERR_BAD_ARGUMENT),
+    (dict(q_heads=7), _lib.ERR_BAD_ARGUMENT),                 # not divisible by kv_heads
+    (dict(seq_kv=128), _lib.ERR_BAD_ARGUMENT),                # causal needs seq_q == seq_kv
+    (dict(scale=0.0), _lib.ERR_BAD_ARGUMENT),
+    (dict(dtype=5), _lib.ERR_BAD_ARGUMENT),
+    (dict(head_dim=512), _lib.ERR_UNSUPPORTED),
+    (dict(layout=_lib.LAYOUT_SENTINEL), _lib.ERR_UNSUPPORTED),            # feature-major is fp32 only
+    (dict(layout=_lib.LAYOUT_SENTINEL, dtype=_lib.DTYPE_F32, stride_columns=500, column_start=0), _lib.ERR_BAD_ARGUMENT),  # 2*256 > 500
+    (dict(layout=_lib.LAYOUT_SENTINEL, dtype=_lib.DTYPE_F32, stride_columns=600, column_start=-1), _lib.ERR_BAD_ARGUMENT),
+])
+def test_argument_validation_status_codes(lib, kw, status):
+    d = _desc(**kw)
+    dummy = C.c_void_p(16)   # never dereferenced: validation fails first
+    assert lib.sntl_attn_fwd(C.byref(d), dummy, dummy, dummy, dummy, dummy, None, 0, None) == status
+    assert lib.sntl_attn_bwd(C.byref(d), dummy, dummy, dummy, dummy, dummy, dummy, dummy, dummy, dummy, dummy, 1 << 30,
+                             None) == status
+
+
+def test_null_pointers_and_missing_device(lib):
+    d = _desc()
+    dummy = C.c_void_p(16)
+    assert lib.sntl_attn_fwd(C.byref(d), None, dummy, dummy, dummy, dummy, None, 0, None) == _lib.ERR_BAD_ARGUMENT
+    assert lib.sntl_attn_fwd(None, dummy, dummy, dummy, dummy, dummy, None, 0, None) == _lib.ERR_BAD_ARGUMENT
+    import torch
+    if not torch.cuda.is_available():
+        # no fallback of any kind: without an sm_100 device the call reports it and does nothing
+        assert lib.sntl_attn_fwd(C.byref(d), dummy, dummy, dummy, dummy, dummy, None, 0, None) == _lib.ERR_NO_DEVICE
+    assert lib.sntl_attn_merge(0, 0, -1, 64, dummy, dummy, dummy, dummy, None) == _lib.ERR_BAD_ARGUMENT
+
+
+def test_status_to_exception_mapping():
+    with pytest.raises(ValueError):
+        _lib.check(_lib.ERR_BAD_ARGUMENT, "x")
+    with pytest.raises(ValueError):
+        _lib.check(_lib.ERR_UNSUPPORTED, "x")
+    with pytest.raises(RuntimeError):
+        _lib.check(_lib.ERR_CUDA, "x")
+    _lib.check(_lib.OK, "x")
+
+
+@pytest.mark.parametrize("args,ok", [
+    ((64, 64, 96, 4, 16, 0, 48, 2), True),      # two packs of 48 fill the matrix
+    ((64, 32, 96, 4, 16, 0, 48, 2), True),      # grouped-query: 2 KV heads
+    ((64, 64, 96, 4, 16, 0, 0, 1), True),       # columnCount <= 0 means "to the end"
+    ((64, 64, 96, 4, 16, 8, 48, 2), False),     # pack window exceeds columns
+    ((64, 64, 96, 4, 16, -1, 48, 1), False),    # invalid column window
+    ((64, 64, 96, 3, 16, 0, 48, 1), False),     # rows != headCount*headDim
+    ((64, 48, 96, 4, 16, 0, 48, 1), False),     # 3 KV heads do not divide 4
+])
+def test_compat_class_argument_checks(lib, args, ok):
+    """The C++ operator class validates like validateMultiHeadShape/resolveColumnWindow
+    (CudaFlashAttention.cu:1458-1471, :1533-1539) and reports std::invalid_argument."""
+    err = C.create_string_buffer(256)
+    rc = lib.sntl_compat_validate(*args, err, 256)
+    assert (rc == 0) == ok, err.value
+    if not ok:
+        assert err.value.startswith(b"CudaFlashAttention")
+
+
+def test_python_mirror_raises_reference_error_kinds():
+    import torch
+    from sentinel_b200 import CudaFlashAttention as FA
+    q = torch.zeros(64, 96)
+    k = torch.zeros(64, 96)
+    with pytest.raises(ValueError, match="query rows mismatch"):
+        FA.forwardMultiHead(q, k, k, None, None, 3, 16, 0.25)
+    with pytest.raises(ValueError, match="pack window exceeds columns"):
+        FA.forwardMultiHead(q, k, k, None, None, 4, 16, 0.25, True, 8, 48, 2)
+    with pytest.raises(ValueError, match="invalid column window"):
+        FA.forwardMultiHead(q, k, k, None, None, 4, 16, 0.25, True, 90, 48, 1)
+    with pytest.raises(ValueError, match="CUDA tensor"):   # host tensors are refused: there is no CPU path
+        FA.forwardMultiHead(q, k, k, None, None, 4, 16, 0.25)
+    with pytest.raises(ValueError, match="logSumExp shape mismatch"):
+        FA.backwardMultiHead(q, k, k, q, torch.zeros(3, 96), q, None, None, None, None, 4, 16, 0.25)
+
+
+def test_missing_library_fails_loudly(monkeypatch, tmp_path):
+    monkeypatch.setattr(_lib, "_lib", None)
+    monkeypatch.setattr(_lib, "LIB_PATH", str(tmp_path / "nope.so"))
+    with pytest.raises(_lib.LibraryMissing, match="no CPU or PyTorch fallback"):
+        _lib.load()

@@ -1,0 +1,299 @@
+"""GPU parity tests (run with -m gpu on a B200): every result comes through the C ABI and is compared with the
+reference's frozen CPU outputs (tests/golden) and the fp64 oracle on the same seeded inputs.
+
+Tolerances (from the acceptance rule of this path):
+  fp32 tensors, exact kernels:      max abs error <= 1e-4 versus the reference CPU path
+  bf16 tensors, tensor-core kernels: max abs error <= 2e-2 and relative L2 <= 5e-3 versus the fp64 oracle
+"""
+import numpy as np
+import pytest
+import torch
+
+from conftest import GOLDEN_CASES, load_golden, max_abs, rel_l2
+
+pytestmark = pytest.mark.gpu
+
+F32_TOL = 1e-4
+BF16_ABS, BF16_REL = 2e-2, 5e-3
+
+
+@pytest.fixture(scope="module")
+def sb():
+    import sentinel_b200
+    sentinel_b200._lib.load()          # fails loudly when the CUDA library is missing
+    assert torch.cuda.is_available()
+    return sentinel_b200
+
+
+def _dev(a, dtype=torch.float32):
+    return torch.from_numpy(np.ascontiguousarray(a)).to("cuda").to(dtype)
+
+
+def _np(t):
+    return t.detach().to(torch.float32).cpu().numpy()
+
+
+def _check_bf16(got, want, what):
+    assert np.isfinite(got).all(), what
+    assert max_abs(got, want) <= BF16_ABS, (what, max_abs(got, want))
+    assert rel_l2(got, want) <= BF16_REL, (what, rel_l2(got, want))
+
+
+# ---------------------------------------------------------------------------------------------- exact fp32 path
+@pytest.mark.parametrize("name", GOLDEN_CASES)
+def test_f32_exact_path_matches_reference_golden(sb, name):
+    g = load_golden(name)
+    q, k, v, do = (_dev(g[x]) for x in ("q", "k", "v", "dout"))
+    o, lse = sb.attention_forward(q, k, v)
+    assert sb.last_path() == "simt_f32"
+    dq, dk, dv = sb.attention_backward(q, k, v, o, lse, do)
+    assert sb.poll_device_status() == 0
+    for got, key in ((o, "o"), (lse, "lse"), (dq, "dq"), (dk, "dk"), (dv, "dv")):
+        assert max_abs(_np(got), g[key]) <= F32_TOL, (key, max_abs(_np(got), g[key]))
+
+
+@pytest.mark.parametrize("shape", [(1, 1, 1, 1, 2), (1, 2, 1, 5, 6), (2, 6, 3, 97, 40), (1, 4, 4, 300, 64), (1, 2, 2, 130, 256)])
+def test_f32_exact_path_edge_shapes_vs_oracle(sb, oracle, shape):
+    """S = 1, S not a multiple of any tile, odd group sizes, the largest head_dim."""
+    B, Hq, Hkv, S, D = shape
+    rng = np.random.default_rng(S * 7 + D)
+    q = rng.standard_normal((B, Hq, S, D), dtype=np.float32)
+    k = rng.standard_normal((B, Hkv, S, D), dtype=np.float32)
+    v = rng.standard_normal((B, Hkv, S, D), dtype=np.float32)
+    do = rng.standard_normal((B, Hq, S, D), dtype=np.float32)
+    o, lse = sb.attention_forward(_dev(q), _dev(k), _dev(v))
+    dq, dk, dv = sb.attention_backward(_dev(q), _dev(k), _dev(v), o, lse, _dev(do))
+    wo, wl = oracle.attn_fwd(q, k, v)
+    wdq, wdk, wdv, _ = oracle.attn_bwd(q, k, v, do)
+    for got, want, key in ((o, wo, "o"), (lse, wl, "lse"), (dq, wdq, "dq"), (dk, wdk, "dk"), (dv, wdv, "dv")):
+        assert max_abs(_np(got), want) <= F32_TOL, (key, max_abs(_np(got), want))
+
+
+def test_f32_noncausal_rectangular_and_merge(sb, oracle):
+    """Ring building blocks: non-causal attention with Sq != Skv, and the LSE merge of two key halves."""
+    rng = np.random.default_rng(21)
+    B, Hq, Hkv, Sq, Skv, D = 1, 4, 2, 50, 90, 32
+    q = rng.standard_normal((B, Hq, Sq, D), dtype=np.float32)
+    k = rng.standard_normal((B, Hkv, Skv, D), dtype=np.float32)
+    v = rng.standard_normal((B, Hkv, Skv, D), dtype=np.float32)
+    do = rng.standard_normal((B, Hq, Sq, D), dtype=np.float32)
+    wo, wl = oracle.attn_fwd(q, k, v, causal=False)
+    wdq, wdk, wdv, _ = oracle.attn_bwd(q, k, v, do, causal=False)
+    o, lse = sb.attention_forward(_dev(q), _dev(k), _dev(v), causal=False)
+    dq, dk, dv = sb.attention_backward(_dev(q), _dev(k), _dev(v), o, lse, _dev(do), causal=False)
+    for got, want in ((o, wo), (lse, wl), (dq, wdq), (dk, wdk), (dv, wdv)):
+        assert max_abs(_np(got), want) <= F32_TOL
+    oa, la = sb.attention_forward(_dev(q), _dev(k[:, :, :40]), _dev(v[:, :, :40]), causal=False)
+    ob, lb = sb.attention_forward(_dev(q), _dev(k[:, :, 40:]), _dev(v[:, :, 40:]), causal=False)
+    sb.merge_partials(oa, la, ob, lb)
+    assert max_abs(_np(oa), wo) <= F32_TOL and max_abs(_np(la), wl) <= F32_TOL
+
+
+# -------------------------------------------------------------------- the reference's operator interface / layout
+def _to_feature_major(x, stride, col0):
+    """[B,H,S,D] -> (H*D) x stride with sequences at columns col0 + b*S (other columns hold a sentinel value)."""
+    B, H, S, D = x.shape
+    m = np.full((H * D, stride), 3.25, np.float32)
+    for b in range(B):
+        m[:, col0 + b * S: col0 + (b + 1) * S] = x[b].transpose(0, 2, 1).reshape(H * D, S)
+    return m
+
+
+def _from_feature_major(m, B, H, S, D, col0):
+    out = np.empty((B, H, S, D), np.float32)
+    for b in range(B):
+        out[b] = m[:, col0 + b * S: col0 + (b + 1) * S].reshape(H, D, S).transpose(0, 2, 1)
+    return out
+
+
+@pytest.mark.parametrize("name,col0,extra", [("toy_f32_b4_h4_s64_d16", 0, 0), ("mha_h4_s48_d16", 8, 16), ("gqa_h8_kv2_s16_d8", 4, 4)])
+def test_reference_operator_interface_python_mirror(sb, name, col0, extra):
+    """CudaFlashAttention.forwardMultiHead/backwardMultiHead on fp32 feature-major matrices with a pack window
+    (columnStart, columnCount, packCount), against the reference CPU outputs; columns outside the window stay untouched."""
+    g = load_golden(name)
+    B, Hq, S, D = g["q"].shape
+    Hkv = g["k"].shape[1]
+    stride = col0 + B * S + extra
+    FA = sb.CudaFlashAttention
+    q, k, v, do = (torch.from_numpy(_to_feature_major(g[x], stride, col0)).cuda() for x in ("q", "k", "v", "dout"))
+    out = torch.full_like(q, -777.0)
+    lse = torch.full((Hq, stride), -777.0, device="cuda")
+    FA.forwardMultiHead(q, k, v, out, lse, Hq, D, D ** -0.5, True, col0, S, B)
+    dq, dk, dv = torch.full_like(q, -777.0), torch.full_like(k, -777.0), torch.full_like(v, -777.0)
+    FA.backwardMultiHead(q, k, v, out, lse, do, dq, dk, dv, None, Hq, D, D ** -0.5, True, col0, S, B)
+    assert max_abs(_from_feature_major(_np(out), B, Hq, S, D, col0), g["o"]) <= F32_TOL
+    assert max_abs(_from_feature_major(_np(dq), B, Hq, S, D, col0), g["dq"]) <= F32_TOL
+    assert max_abs(_from_feature_major(_np(dk), B, Hkv, S, D, col0), g["dk"]) <= F32_TOL
+    assert max_abs(_from_feature_major(_np(dv), B, Hkv, S, D, col0), g["dv"]) <= F32_TOL
+    lse_np = _np(lse)
+    for b in range(B):
+        assert max_abs(lse_np[:, col0 + b * S: col0 + (b + 1) * S], g["lse"][b]) <= F32_TOL
+    for t in (out, dq, dk, dv):   # nothing outside the window was written
+        tn = _np(t)
+        assert (tn[:, :col0] == -777.0).all() and (tn[:, col0 + B * S:] == -777.0).all()
+
+
+def test_reference_operator_interface_cpp_class(sb):
+    """Same check through the C++ class a Sentinel build would link (sentinel_compat.cu), driven by its test hook."""
+    import ctypes as C
+    lib = sb._lib.load()
+    g = load_golden("mha_h4_s48_d16")
+    B, Hq, S, D = g["q"].shape
+    stride = B * S
+    q, k, v, do = (_to_feature_major(g[x], stride, 0) for x in ("q", "k", "v", "dout"))
+    out, dq, dk, dv = (np.empty_like(q) for _ in range(4))
+    lse = np.empty((Hq, stride), np.float32)
+    path, err = C.create_string_buffer(64), C.create_string_buffer(256)
+    fp = lambda a: a.ctypes.data_as(C.POINTER(C.c_float))
+    rc = lib.sntl_compat_forward_backward(fp(q), fp(k), fp(v), fp(do), Hq, Hq, D, stride, D ** -0.5, 1, 0, S, B, 0, fp(out),
+                                          fp(lse), fp(dq), fp(dk), fp(dv), path, 64, err, 256)
+    assert rc == 0, err.value
+    assert path.value == b"simt_f32"
+    assert max_abs(_from_feature_major(out, B, Hq, S, D, 0), g["o"]) <= F32_TOL
+    assert max_abs(_from_feature_major(dq, B, Hq, S, D, 0), g["dq"]) <= F32_TOL
+    assert max_abs(_from_feature_major(dk, B, Hq, S, D, 0), g["dk"]) <= F32_TOL
+    assert max_abs(_from_feature_major(dv, B, Hq, S, D, 0), g["dv"]) <= F32_TOL
+    # error behaviour: a pack window that leaves the matrix is std::invalid_argument (rc 1), as in the reference
+    rc = lib.sntl_compat_forward_backward(fp(q), fp(k), fp(v), None, Hq, Hq, D, stride, D ** -0.5, 1, 8, S, B, 0, fp(out),
+                                          fp(lse), None, None, None, path, 64, err, 256)
+    assert rc == 1 and b"pack window exceeds columns" in err.value
+
+
+# ---------------------------------------------------------------------------------------------- tensor-core path
+def _bf16_case(w, **kw):
+    from sentinel_b200 import make_inputs
+    q, k, v, do = make_inputs(w, **kw)
+    return q, k, v, do
+
+
+def _oracle_full(oracle, q, k, v, do, causal=True):
+    qf, kf, vf, dof = (t.to(torch.float32).numpy() for t in (q, k, v, do))
+    o, lse = oracle.attn_fwd(qf, kf, vf, causal=causal)
+    dq, dk, dv, _ = oracle.attn_bwd(qf, kf, vf, dof, causal=causal)
+    return o, lse, dq, dk, dv
+
+
+@pytest.mark.parametrize("wname,kw", [
+    ("gpt2_small", dict(batch=1, q_heads=2, kv_heads=2, seq=256)),
+    ("gpt2_small", dict(batch=2, q_heads=3, kv_heads=3, seq=1024)),
+    ("llama1b_gqa", dict(batch=1, q_heads=8, kv_heads=2, seq=640)),
+    ("gqa7b_d128", dict(batch=1, q_heads=7, kv_heads=1, seq=512)),
+    ("gqa7b_d128", dict(batch=2, q_heads=4, kv_heads=2, seq=384)),
+    ("gqa7b_d128", dict(batch=1, q_heads=2, kv_heads=1, seq=200)),     # ragged: not a multiple of 128
+    ("gpt2_small", dict(batch=1, q_heads=2, kv_heads=1, seq=77)),      # shorter than one tile
+])
+def test_bf16_tensor_core_path_vs_oracle(sb, oracle, wname, kw):
+    w = sb.WORKLOADS[wname]
+    q, k, v, do = _bf16_case(w, **kw)
+    wo, wl, wdq, wdk, wdv = _oracle_full(oracle, q, k, v, do)
+    qd, kd, vd, dod = (t.cuda() for t in (q, k, v, do))
+    o, lse = sb.attention_forward(qd, kd, vd)
+    assert sb.last_path() == "tcgen05", sb.last_path()
+    dq, dk, dv = sb.attention_backward(qd, kd, vd, o, lse, dod)
+    assert sb.poll_device_status() == 0
+    _check_bf16(_np(o), wo, "o")
+    assert max_abs(_np(lse), wl) <= BF16_ABS
+    _check_bf16(_np(dq), wdq, "dq")
+    _check_bf16(_np(dk), wdk, "dk")
+    _check_bf16(_np(dv), wdv, "dv")
+
+
+def test_bf16_tensor_core_noncausal_rectangular(sb, oracle):
+    w = sb.WORKLOADS["gqa7b_d128"]
+    q, _, _, do = _bf16_case(w, batch=1, q_heads=4, kv_heads=2, seq=256)
+    _, k, v, _ = _bf16_case(w, batch=1, q_heads=4, kv_heads=2, seq=384, seed_offset=1)
+    wo, wl, wdq, wdk, wdv = _oracle_full(oracle, q, k, v, do, causal=False)
+    qd, kd, vd, dod = (t.cuda() for t in (q, k, v, do))
+    o, lse = sb.attention_forward(qd, kd, vd, causal=False)
+    dq, dk, dv = sb.attention_backward(qd, kd, vd, o, lse, dod, causal=False)
+    assert sb.poll_device_status() == 0
+    _check_bf16(_np(o), wo, "o")
+    _check_bf16(_np(dq), wdq, "dq")
+    _check_bf16(_np(dk), wdk, "dk")
+    _check_bf16(_np(dv), wdv, "dv")
+
+
+def test_bf16_golden_inputs_tensor_core_vs_reference_cpu(sb):
+    """Golden fixtures whose inputs are bf16-exact: the tensor-core path against the reference CPU outputs."""
+    for name in ("gqa_h4_kv1_s200_d64_bf16in", "gqa_h4_kv2_s136_d128_bf16in"):
+        g = load_golden(name)
+        q, k, v, do = (_dev(g[x], torch.bfloat16) for x in ("q", "k", "v", "dout"))
+        o, lse = sb.attention_forward(q, k, v)
+        dq, dk, dv = sb.attention_backward(q, k, v, o, lse, do)
+        assert sb.poll_device_status() == 0
+        # dO here is N(0,1), so gradients are O(1-10): compare relative L2 and a scaled abs bound
+        _check_bf16(_np(o), g["o"], name)
+        for got, key in ((dq, "dq"), (dk, "dk"), (dv, "dv")):
+            assert rel_l2(_np(got), g[key]) <= BF16_REL, (name, key, rel_l2(_np(got), g[key]))
+
+
+def test_staged_fp32_sentinel_layout_on_tensor_cores(sb, oracle):
+    """fp32 feature-major matrices with reduced precision allowed: staged through bf16 onto the tensor-core kernels."""
+    FA = sb.CudaFlashAttention
+    w = sb.WORKLOADS["gpt2_small"]
+    q, k, v, do = _bf16_case(w, batch=2, q_heads=4, kv_heads=2, seq=256)
+    wo, wl, wdq, wdk, wdv = _oracle_full(oracle, q, k, v, do)
+    B, Hq, S, D = q.shape
+    Hkv = k.shape[1]
+    stride, col0 = B * S + 64, 32
+    fm = lambda t: torch.from_numpy(_to_feature_major(t.to(torch.float32).numpy(), stride, col0)).cuda()
+    FA.allow_reduced_precision = True
+    try:
+        out, lse = FA.forwardMultiHead(fm(q), fm(k), fm(v), None, None, Hq, D, D ** -0.5, True, col0, S, B)
+        assert sb.last_path() == "tcgen05_staged"
+        dq, dk, dv = FA.backwardMultiHead(fm(q), fm(k), fm(v), out, lse, fm(do), None, None, None, None, Hq, D, D ** -0.5,
+                                          True, col0, S, B)
+    finally:
+        FA.allow_reduced_precision = False
+    assert sb.poll_device_status() == 0
+    _check_bf16(_from_feature_major(_np(out), B, Hq, S, D, col0), wo, "o")
+    _check_bf16(_from_feature_major(_np(dq), B, Hq, S, D, col0), wdq, "dq")
+    _check_bf16(_from_feature_major(_np(dk), B, Hkv, S, D, col0), wdk, "dk")
+    _check_bf16(_from_feature_major(_np(dv), B, Hkv, S, D, col0), wdv, "dv")
+
+
+def test_forward_is_deterministic_and_recompute_stable(sb):
+    """Activation checkpointing re-runs the forward inside backward (CudaTransformerBlock.cu:277-284): two runs
+    must agree bit for bit, and so must two backward runs of dK/dV (each is owned by one CTA)."""
+    w = sb.WORKLOADS["gqa7b_d128"]
+    q, k, v, do = (t.cuda() for t in _bf16_case(w, batch=1, q_heads=4, kv_heads=1, seq=512))
+    o1, l1 = sb.attention_forward(q, k, v)
+    o2, l2 = sb.attention_forward(q, k, v)
+    assert torch.equal(o1, o2) and torch.equal(l1, l2)
+    _, dk1, dv1 = sb.attention_backward(q, k, v, o1, l1, do)
+    _, dk2, dv2 = sb.attention_backward(q, k, v, o1, l1, do)
+    assert torch.equal(dk1, dk2) and torch.equal(dv1, dv2)
+
+
+@pytest.mark.parametrize("wname", ["gpt2_small", "llama1b_gqa", "gqa7b_d128"])
+def test_full_size_workloads_sampled_oracle_and_cross_check(sb, oracle, wname):
+    """At the benchmark's full sizes: sampled fp64-oracle rows/columns, plus size-independent properties
+    (softmax rows sum to one => O of constant V is that constant; dV linear in dO; sum_d O*dO == delta)."""
+    w = sb.WORKLOADS[wname]
+    q, k, v, do = _bf16_case(w)
+    qd, kd, vd, dod = (t.cuda() for t in (q, k, v, do))
+    o, lse = sb.attention_forward(qd, kd, vd)
+    dq, dk, dv = sb.attention_backward(qd, kd, vd, o, lse, dod)
+    assert sb.poll_device_status() == 0
+    qf, kf, vf, dof = (t.to(torch.float32).numpy() for t in (q, k, v, do))
+    S = w.seq
+    rows = np.array([0, 1, 127, 128, 255, S // 2 - 1, S // 2, S - 129, S - 1])
+    group = w.q_heads // w.kv_heads
+    for (b, h) in ((0, 0), (w.batch - 1, w.q_heads - 1)):
+        wo, wl, wdq = oracle.attn_rows(qf, kf, vf, dof, b, h, rows)
+        _check_bf16(_np(o[b, h, rows]), wo, "o rows")
+        assert max_abs(_np(lse[b, h, rows]), wl) <= BF16_ABS
+        _check_bf16(_np(dq[b, h, rows]), wdq, "dq rows")
+    cols = np.array([0, 127, 128, S // 2, S - 200, S - 1])
+    if S <= 4096 or group <= 7:
+        b, hk = w.batch - 1, w.kv_heads - 1
+        wdk, wdv = oracle.attn_cols(qf, kf, vf, dof, b, hk, cols)
+        _check_bf16(_np(dk[b, hk, cols]), wdk, "dk cols")
+        _check_bf16(_np(dv[b, hk, cols]), wdv, "dv cols")
+    # property: constant V => O equals that constant wherever it is defined
+    ones = torch.ones_like(vd)
+    o1, _ = sb.attention_forward(qd, kd, ones)
+    assert float((o1.float() - 1.0).abs().max()) <= 1e-2
+    # property: dV is linear in dO
+    _, _, dv2 = sb.attention_backward(qd, kd, vd, o, lse, dod * 2)
+    assert rel_l2(_np(dv2), 2 * _np(dv)) <= 2e-3

@@ -1,0 +1,123 @@
+"""CPU tests of the checker itself: the fp64 restatement against the reference's frozen outputs (golden
+fixtures), against the live reference where it is built, and against the invariants the reference's own
+smokes assert (GQA == MHA with repeated K/V, finite differences)."""
+import numpy as np
+import pytest
+
+from conftest import GOLDEN_CASES, load_golden, max_abs
+
+
+@pytest.mark.parametrize("name", GOLDEN_CASES)
+def test_oracle_matches_reference_golden(oracle, name):
+    g = load_golden(name)
+    o, lse = oracle.attn_fwd(g["q"], g["k"], g["v"])
+    dq, dk, dv, _ = oracle.attn_bwd(g["q"], g["k"], g["v"], g["dout"])
+    # the reference computes in fp32 (blocked GEMM, S-long sums); the oracle in fp64
+    assert max_abs(o, g["o"]) < 5e-6
+    assert max_abs(lse, g["lse"]) < 5e-6
+    assert max_abs(dq, g["dq"]) < 2e-5
+    assert max_abs(dk, g["dk"]) < 2e-5
+    assert max_abs(dv, g["dv"]) < 2e-5
+
+
+def test_reference_live_matches_golden_and_core_route(oracle):
+    """Where the reference CPU path is built: it reproduces its own fixtures bit for bit, and the primitive
+    route used for timing is bit-identical to the public layer route."""
+    if not oracle.ref_available():
+        pytest.skip("oracle/_ref not built (reference sources absent)")
+    g = load_golden("mha_h4_s48_d16")
+    o, lse, dq, dk, dv = oracle.ref_layer_fwd_bwd(g["q"], g["k"], g["v"], g["dout"])
+    for got, key in ((o, "o"), (lse, "lse"), (dq, "dq"), (dk, "dk"), (dv, "dv")):
+        assert np.array_equal(got, g[key]), key
+    co, cdq, cdk, cdv, secs = oracle.ref_core_fwd_bwd(g["q"], g["k"], g["v"], g["dout"])
+    assert np.array_equal(co, o) and np.array_equal(cdq, dq) and np.array_equal(cdk, dk) and np.array_equal(cdv, dv)
+    assert secs[0] > 0 and secs[1] > 0
+
+
+def test_gqa_equals_mha_with_repeated_kv(oracle):
+    """The reference's runGqaHostSmokeDemo invariant (CausalSelfAttention.cpp:549-684): GQA == MHA with K/V
+    repeated per group, and K/V grads are the sums over the group."""
+    rng = np.random.default_rng(7)
+    B, Hq, Hkv, S, D = 1, 8, 2, 16, 8
+    q = rng.standard_normal((B, Hq, S, D), dtype=np.float32)
+    k = rng.standard_normal((B, Hkv, S, D), dtype=np.float32)
+    v = rng.standard_normal((B, Hkv, S, D), dtype=np.float32)
+    do = rng.standard_normal((B, Hq, S, D), dtype=np.float32)
+    g = Hq // Hkv
+    kr, vr = np.repeat(k, g, axis=1), np.repeat(v, g, axis=1)
+    o1, l1 = oracle.attn_fwd(q, k, v)
+    o2, l2 = oracle.attn_fwd(q, kr, vr)
+    assert max_abs(o1, o2) < 1e-6 and max_abs(l1, l2) < 1e-6
+    dq1, dk1, dv1, _ = oracle.attn_bwd(q, k, v, do)
+    dq2, dk2, dv2, _ = oracle.attn_bwd(q, kr, vr, do)
+    assert max_abs(dq1, dq2) < 1e-5
+    assert max_abs(dk1, dk2.reshape(B, Hkv, g, S, D).sum(2)) < 1e-5
+    assert max_abs(dv1, dv2.reshape(B, Hkv, g, S, D).sum(2)) < 1e-5
+
+
+def test_backward_finite_difference(oracle):
+    """Finite-difference check of dQ, dK, dV as in the reference's sparse-backward smoke
+    (CausalSelfAttention.cpp:420-500, eps = 1e-3)."""
+    rng = np.random.default_rng(11)
+    B, Hq, Hkv, S, D = 1, 2, 1, 12, 8
+    q = rng.standard_normal((B, Hq, S, D), dtype=np.float32)
+    k = rng.standard_normal((B, Hkv, S, D), dtype=np.float32)
+    v = rng.standard_normal((B, Hkv, S, D), dtype=np.float32)
+    do = rng.standard_normal((B, Hq, S, D), dtype=np.float32)
+    dq, dk, dv, _ = oracle.attn_bwd(q, k, v, do)
+
+    def loss(q_, k_, v_):
+        o, _ = oracle.attn_fwd(q_, k_, v_)
+        return float((o.astype(np.float64) * do).sum())
+
+    eps = 1e-3
+    for arr, grad, idx in ((q, dq, (0, 1, 7, 3)), (k, dk, (0, 0, 2, 5)), (v, dv, (0, 0, 4, 1))):
+        hi, lo = arr.copy(), arr.copy()
+        hi[idx] += eps
+        lo[idx] -= eps
+        args_hi = [hi if a is arr else a for a in (q, k, v)]
+        args_lo = [lo if a is arr else a for a in (q, k, v)]
+        fd = (loss(*args_hi) - loss(*args_lo)) / (2 * eps)
+        assert abs(fd - float(grad[idx])) < 5e-3 * max(1.0, abs(fd))
+
+
+def test_sampled_rows_and_cols_equal_full(oracle):
+    rng = np.random.default_rng(3)
+    B, Hq, Hkv, S, D = 2, 4, 2, 70, 16
+    q = rng.standard_normal((B, Hq, S, D), dtype=np.float32)
+    k = rng.standard_normal((B, Hkv, S, D), dtype=np.float32)
+    v = rng.standard_normal((B, Hkv, S, D), dtype=np.float32)
+    do = rng.standard_normal((B, Hq, S, D), dtype=np.float32)
+    o, lse = oracle.attn_fwd(q, k, v)
+    dq, dk, dv, _ = oracle.attn_bwd(q, k, v, do)
+    rows = np.array([0, 1, 33, 69])
+    orow, lrow, dqrow = oracle.attn_rows(q, k, v, do, 1, 3, rows)
+    assert np.array_equal(orow, o[1, 3, rows]) and np.array_equal(lrow, lse[1, 3, rows])
+    assert max_abs(dqrow, dq[1, 3, rows]) < 1e-6
+    cols = np.array([0, 31, 69])
+    dkc, dvc = oracle.attn_cols(q, k, v, do, 1, 1, cols)
+    assert max_abs(dkc, dk[1, 1, cols]) < 1e-6 and max_abs(dvc, dv[1, 1, cols]) < 1e-6
+
+
+def test_noncausal_rectangular_and_empty_rows(oracle):
+    """Off-diagonal ring blocks are non-causal with Sq != Skv; LSE merge of two key halves equals the full result."""
+    rng = np.random.default_rng(5)
+    B, H, Sq, Skv, D = 1, 2, 9, 20, 8
+    q = rng.standard_normal((B, H, Sq, D), dtype=np.float32)
+    k = rng.standard_normal((B, H, Skv, D), dtype=np.float32)
+    v = rng.standard_normal((B, H, Skv, D), dtype=np.float32)
+    o, lse = oracle.attn_fwd(q, k, v, causal=False)
+    oa, la = oracle.attn_fwd(q, k[:, :, :8], v[:, :, :8], causal=False)
+    ob, lb = oracle.attn_fwd(q, k[:, :, 8:], v[:, :, 8:], causal=False)
+    m = np.maximum(la, lb)
+    wa, wb = np.exp(la - m), np.exp(lb - m)
+    merged = (oa * wa[..., None] + ob * wb[..., None]) / (wa + wb)[..., None]
+    assert max_abs(merged, o) < 1e-6
+    assert max_abs(m + np.log(wa + wb), lse) < 1e-6
+
+
+def test_bf16_rounding_matches_torch(oracle):
+    torch = pytest.importorskip("torch")
+    x = np.random.default_rng(1).standard_normal(4096).astype(np.float32) * 3
+    want = torch.from_numpy(x).to(torch.bfloat16).to(torch.float32).numpy()
+    assert np.array_equal(oracle.round_bf16(x), want)
