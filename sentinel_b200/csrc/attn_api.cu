@@ -176,7 +176,10 @@ int sntl_attn_fwd(const sntl_attn_desc* d, const void* q, const void* k, const v
         SimtArgs a{};
         a.s = shape_of(d);
         a.is_bf16 = d->dtype == SNTL_DTYPE_BF16;
-        a.q = q; a.k = k; a.v = v; a.o_out = o; a.lse_out = lse;
+        // feature-major matrices: the window starts column_start elements into every row
+        const size_t off = d->layout == SNTL_LAYOUT_SENTINEL ? (size_t)d->column_start * sizeof(float) : 0;
+        a.q = (const char*)q + off; a.k = (const char*)k + off; a.v = (const char*)v + off;
+        a.o_out = (char*)o + off; a.lse_out = (float*)((char*)lse + off);
         views(d, a.vq, a.vkv, a.vlse);
         g_last_path = a.is_bf16 ? "simt_bf16" : "simt_f32";
         return cuda_status(simt_forward(a, st));
@@ -230,8 +233,10 @@ int sntl_attn_bwd(const sntl_attn_desc* d, const void* q, const void* k, const v
         SimtArgs a{};
         a.s = shape_of(d);
         a.is_bf16 = d->dtype == SNTL_DTYPE_BF16;
-        a.q = q; a.k = k; a.v = v; a.o = o; a.dout = dout; a.lse = lse;
-        a.dq = dq; a.dk = dk; a.dv = dv;
+        const size_t off = d->layout == SNTL_LAYOUT_SENTINEL ? (size_t)d->column_start * sizeof(float) : 0;
+        a.q = (const char*)q + off; a.k = (const char*)k + off; a.v = (const char*)v + off;
+        a.o = (const char*)o + off; a.dout = (const char*)dout + off; a.lse = (const float*)((const char*)lse + off);
+        a.dq = (char*)dq + off; a.dk = (char*)dk + off; a.dv = (char*)dv + off;
         a.delta = (float*)c.take(4 * nlse(d));
         if (!c.ok) return SNTL_ERR_WORKSPACE;
         views(d, a.vq, a.vkv, a.vlse);
@@ -246,7 +251,7 @@ int sntl_attn_bwd(const sntl_attn_desc* d, const void* q, const void* k, const v
     if (!c.ok) return SNTL_ERR_WORKSPACE;
     const size_t sq_pad = ((size_t)d->seq_q + 127) / 128 * 128;
     t.delta = (float*)tcws;
-    t.dq_accum = (float*)(tcws + align_up(4 * (size_t)d->batch * d->q_heads * sq_pad));
+    t.dq_accum = (float*)(tcws + align_up(2 * 4 * (size_t)d->batch * d->q_heads * sq_pad));  // after [delta | lse*log2e]
     g_last_path = "tcgen05";
     if (!needs_staging(d)) {
         t.q = (const __nv_bfloat16*)q; t.k = (const __nv_bfloat16*)k; t.v = (const __nv_bfloat16*)v;

@@ -1,9 +1,541 @@
-// placeholder until the tcgen05 backward lands
+// Causal attention backward for sm_100a: dQ, dK, dV with P recomputed from the saved log-sum-exp.
+//
+// Replaces the reference's CudaFlashAttentionDeltaEntry + CudaFlashAttentionBackwardQueryWmma64Entry
+// (sentinel/NeuralNet/Cuda/CudaFlashAttention.cu:576-596, :1269-1456).  The reference walks query tiles and
+// pushes dK/dV out with global atomics after scalar FMA loops; here all five products run on tcgen05 tensor
+// cores and the loop is key-tile-outer:
+//
+//   * one CTA owns one 128-key tile of one (batch, KV head) and walks every 128-query tile that can see it,
+//     for every query head of the group, so dK and dV accumulate in TMEM for the whole CTA lifetime and are
+//     written exactly once: deterministic, no atomics, grouped-query sums done in place (the reference
+//     materialises repeated K/V and reduces afterwards, CudaCausalSelfAttention.cu:27-44);
+//   * everything is computed transposed (rows = keys) so that both P^T and dS^T are consumed by the next MMA
+//     straight from TMEM as the A operand:
+//         S^T  = K  Q^T          (K, Q  K-major from shared memory)      -> TMEM
+//         dP^T = V  dO^T         (V, dO K-major from shared memory)      -> TMEM
+//         P^T  = exp2(S^T*scale*log2e - LSE*log2e), causal mask on the diagonal tile, bf16 back over S^T
+//         dV  += P^T  dO         (A = P^T in TMEM,  B = dO tile MN-major)
+//         dS^T = P^T o (dP^T - delta), bf16 back over dP^T and also into shared memory
+//         dK  += dS^T Q          (A = dS^T in TMEM, B = Q tile MN-major)
+//         dQ_i = dS   K          (A = dS^T tile in shared memory read MN-major, B = K tile MN-major)
+//     the softmax scale is folded into the final dK store and the dQ conversion pass;
+//   * dQ_i lands in TMEM (over the dP^T columns, which are dead by then) and a drain warpgroup adds it into an
+//     fp32 accumulator in global memory with coalesced 16-byte vector reductions; the accumulator uses a
+//     per-tile [d/4][row][4] order so that the 32 rows of a warp hit consecutive addresses;
+//   * warp roles: 2 compute warpgroups (each owns 64 of the 128 query columns, one thread per key row),
+//     1 drain warpgroup, 1 MMA-issuing warp, 1 TMA-producer warp.  Q (+LSE, delta) is double-buffered; dO is
+//     double-buffered for D=64 and single-buffered for D=128 (shared-memory budget).
+//
+// A pre-pass computes delta = rowsum(dO o O), LSE*log2e (padded rows get +inf so they produce P = 0) and
+// zeroes the dQ accumulator; a post-pass converts the accumulator to bf16 dQ (times scale).
+// TMEM map (512 columns): S^T/P^T [0,128)  dP^T/dS^T/dQ [128,256)  dV [256,256+D)  dK [384,384+D).
 #include "common.cuh"
 #include "sm100_ptx.cuh"
+
 namespace sntl {
-bool tc_bwd_supported(const AttnShape&) { return false; }
-size_t tc_backward_workspace_bytes(const AttnShape&) { return 0; }
-cudaError_t tc_backward(const TcArgs&, cudaStream_t) { return cudaErrorNotSupported; }
-cudaError_t read_and_clear_bwd_status(cudaStream_t, uint32_t* w) { *w = 0; return cudaSuccess; }
+
+using namespace ptx;
+
+namespace {
+
+constexpr int kT = 128;                 // tile edge: keys per CTA, queries per step
+constexpr int kBwdThreads = 448;        // 2 compute WGs + drain WG + MMA warp + producer warp
+constexpr uint32_t kTmemCols = 512;
+
+enum BwdSite : uint32_t {
+    kSiteKV = 0x21, kSiteQFull, kSiteQEmpty, kSiteDoFull, kSiteDoEmpty, kSiteS, kSiteP, kSiteDP, kSiteDS, kSiteDQ,
+    kSiteDrained, kSiteFinal
+};
+
+struct BwdParams {
+    __nv_bfloat16 *dk, *dv;
+    const float* lse2;     // [B][Hq][Sq_pad]  LSE * log2(e), +inf on padded rows
+    const float* delta;    // [B][Hq][Sq_pad]
+    float* dq_accum;       // [B*Hq][n_qt][D/4][128][4]
+    int B, Hq, Hkv, Sq, Skv, Sq_pad;
+    int causal;
+    int n_qt, n_kt;
+    float scale, scale_log2;
+};
+
+struct BwdBarriers {
+    uint64_t kv_full;
+    uint64_t q_full[2], q_empty[2], do_full[2], do_empty[2];
+    uint64_t s_ready, p_ready, dp_ready, ds_ready, dq_ready, dq_drained, final_bar;
+    uint32_t tmem_base;
+    uint32_t abort_flag;
+};
+
+template <int D>
+__global__ void __launch_bounds__(kBwdThreads, 1)
+attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+                   const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_do, const BwdParams p)
+{
+    constexpr int kTileBytes = kT * D * 2;
+    constexpr int kChunkBytes = kT * 128;          // 128 rows x 128 B
+    constexpr int kChunks = D / 64;
+    constexpr int kDoStages = (D == 128) ? 1 : 2;
+    constexpr int kDsBytes = kT * kT * 2;          // dS^T tile: [128 keys][128 queries] bf16 as two 64-query chunks
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t* sK = smem;
+    uint8_t* sV = sK + kTileBytes;
+    uint8_t* sQ = sV + kTileBytes;                 // [2]
+    uint8_t* sDo = sQ + 2 * kTileBytes;            // [kDoStages]
+    uint8_t* sDs = sDo + kDoStages * kTileBytes;
+    float* sLse = (float*)(sDs + kDsBytes);        // [2][128]
+    float* sDelta = sLse + 2 * kT;                 // [2][128]
+    BwdBarriers* bars = (BwdBarriers*)(sDelta + 2 * kT);
+    volatile uint32_t* abort_flag = &bars->abort_flag;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    // ---- work decode: key tile 0 sees every query tile, so low key tiles go first ----
+    const int slabs = p.B * p.Hkv;
+    const int kt = blockIdx.x / slabs;
+    const int slab = blockIdx.x - kt * slabs;           // b * Hkv + hk
+    const int b = slab / p.Hkv, hk = slab - b * p.Hkv;
+    const int group = p.Hq / p.Hkv;
+    const int k0 = kt * kT;
+    const int qt_first = p.causal ? kt : 0;
+    const int per_head = p.n_qt - qt_first;             // query tiles per head this CTA visits
+    const int n_iter = per_head > 0 ? per_head * group : 0;
+
+    if (warp == 13 && lane == 0) {
+        prefetch_tensormap(&tmap_q);
+        prefetch_tensormap(&tmap_k);
+        prefetch_tensormap(&tmap_v);
+        prefetch_tensormap(&tmap_do);
+        mbar_init(&bars->kv_full, 1);
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&bars->q_full[i], 1);
+            mbar_init(&bars->q_empty[i], 1);
+            mbar_init(&bars->do_full[i], 1);
+            mbar_init(&bars->do_empty[i], 1);
+        }
+        mbar_init(&bars->s_ready, 1);
+        mbar_init(&bars->p_ready, 256);
+        mbar_init(&bars->dp_ready, 1);
+        mbar_init(&bars->ds_ready, 256);
+        mbar_init(&bars->dq_ready, 1);
+        mbar_init(&bars->dq_drained, 128);
+        mbar_init(&bars->final_bar, 1);
+        bars->abort_flag = 0;
+        fence_mbar_init();
+    }
+    if (warp == 12) {
+        tmem_alloc(&bars->tmem_base, kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = bars->tmem_base;
+    const uint32_t tm_S = tmem, tm_dP = tmem + 128u, tm_dV = tmem + 256u, tm_dK = tmem + 384u;
+
+    if (warp == 13) {
+        // =========================== TMA producer ===========================
+        if (lane == 0 && n_iter > 0) {
+            mbar_arrive_expect_tx(&bars->kv_full, (uint32_t)(2 * kTileBytes));
+            for (int c = 0; c < kChunks; ++c) {
+                tma_load_3d(sK + c * kChunkBytes, &tmap_k, &bars->kv_full, c * 64, k0, slab);
+                tma_load_3d(sV + c * kChunkBytes, &tmap_v, &bars->kv_full, c * 64, k0, slab);
+            }
+            for (int i = 0; i < n_iter; ++i) {
+                const int g = i / per_head, qt = qt_first + (i - g * per_head);
+                const int bh = b * p.Hq + hk * group + g;
+                const int sq = i & 1;
+                if (i >= 2 && !mbar_wait(&bars->q_empty[sq], (uint32_t)(((i >> 1) - 1) & 1), abort_flag, kSiteQEmpty)) break;
+                mbar_arrive_expect_tx(&bars->q_full[sq], (uint32_t)(kTileBytes + 2 * kT * 4));
+                for (int c = 0; c < kChunks; ++c)
+                    tma_load_3d(sQ + sq * kTileBytes + c * kChunkBytes, &tmap_q, &bars->q_full[sq], c * 64, qt * kT, bh);
+                bulk_load_1d(sLse + sq * kT, p.lse2 + (size_t)bh * p.Sq_pad + (size_t)qt * kT, kT * 4, &bars->q_full[sq]);
+                bulk_load_1d(sDelta + sq * kT, p.delta + (size_t)bh * p.Sq_pad + (size_t)qt * kT, kT * 4, &bars->q_full[sq]);
+                const int sd = i % kDoStages;
+                if (i >= kDoStages &&
+                    !mbar_wait(&bars->do_empty[sd], (uint32_t)(((i / kDoStages) - 1) & 1), abort_flag, kSiteDoEmpty))
+                    break;
+                mbar_arrive_expect_tx(&bars->do_full[sd], (uint32_t)kTileBytes);
+                for (int c = 0; c < kChunks; ++c)
+                    tma_load_3d(sDo + sd * kTileBytes + c * kChunkBytes, &tmap_do, &bars->do_full[sd], c * 64, qt * kT, bh);
+            }
+        }
+    } else if (warp == 12) {
+        // =========================== MMA issuer ===========================
+        if (lane == 0 && n_iter > 0) {
+            constexpr uint32_t idesc_st = make_idesc(kT, kT, false, false);   // S^T, dP^T
+            constexpr uint32_t idesc_kv = make_idesc(kT, D, false, true);     // dV, dK: A in TMEM, B MN-major
+            constexpr uint32_t idesc_dq = make_idesc(kT, D, true, true);      // dQ: both operands MN-major
+            const uint32_t k_base = smem_u32(sK), v_base = smem_u32(sV), q_base = smem_u32(sQ), do_base = smem_u32(sDo),
+                           ds_base = smem_u32(sDs);
+            // C[128 x 128] = A[128 x D] * B[128 x D]^T, both K-major tiles
+            auto issue_kmajor = [&](uint32_t d_tmem, uint32_t a_tile, uint32_t b_tile) {
+#pragma unroll
+                for (int ks = 0; ks < D / 16; ++ks) {
+                    const uint32_t off = (uint32_t)((ks >> 2) * kChunkBytes + (ks & 3) * 32);
+                    mma_ss(d_tmem, make_sdesc(a_tile + off, 16, 1024), make_sdesc(b_tile + off, 16, 1024), idesc_st, ks > 0 ? 1u : 0u);
+                }
+            };
+            // C[128 keys x D] (+)= A^T[128 keys x 128 q] (packed bf16 in TMEM) * B[128 q x D] (MN-major tile)
+            auto issue_from_tmem = [&](uint32_t d_tmem, uint32_t a_tmem, uint32_t b_tile, bool accumulate) {
+#pragma unroll
+                for (int ks = 0; ks < kT / 16; ++ks) {
+                    const uint32_t a = a_tmem + (uint32_t)((ks >> 2) * 64 + (ks & 3) * 8);
+                    mma_ts(d_tmem, a, make_sdesc(b_tile + ks * 2048, kChunkBytes, 1024), idesc_kv, (accumulate || ks > 0) ? 1u : 0u);
+                }
+            };
+            bool ok = mbar_wait(&bars->kv_full, 0, abort_flag, kSiteKV) && mbar_wait(&bars->q_full[0], 0, abort_flag, kSiteQFull);
+            if (ok) {
+                tc_fence_after();
+                issue_kmajor(tm_S, k_base, q_base);
+                tc_commit(&bars->s_ready);
+                ok = mbar_wait(&bars->do_full[0], 0, abort_flag, kSiteDoFull);
+            }
+            if (ok) {
+                tc_fence_after();
+                issue_kmajor(tm_dP, v_base, do_base);
+                tc_commit(&bars->dp_ready);
+            }
+            for (int i = 0; ok && i < n_iter; ++i) {
+                const uint32_t ph = (uint32_t)(i & 1);
+                const int sq = i & 1, sd = i % kDoStages;
+                const bool more = i + 1 < n_iter;
+                // dV += P^T dO
+                if (!(ok = mbar_wait(&bars->p_ready, ph, abort_flag, kSiteP))) break;
+                tc_fence_after();
+                issue_from_tmem(tm_dV, tm_S, do_base + sd * kTileBytes, i > 0);
+                tc_commit(&bars->do_empty[sd]);
+                // S^T of the next step (its P phase overlaps dK/dQ/drain of this step)
+                if (more) {
+                    const int nq = (i + 1) & 1;
+                    if (!(ok = mbar_wait(&bars->q_full[nq], (uint32_t)(((i + 1) >> 1) & 1), abort_flag, kSiteQFull))) break;
+                    tc_fence_after();
+                    issue_kmajor(tm_S, k_base, q_base + nq * kTileBytes);
+                    tc_commit(&bars->s_ready);
+                }
+                // dK += dS^T Q ; dQ_i = dS K
+                if (!(ok = mbar_wait(&bars->ds_ready, ph, abort_flag, kSiteDS))) break;
+                tc_fence_after();
+                issue_from_tmem(tm_dK, tm_dP, q_base + sq * kTileBytes, i > 0);
+                tc_commit(&bars->q_empty[sq]);
+#pragma unroll
+                for (int ks = 0; ks < kT / 16; ++ks)
+                    mma_ss(tm_dP, make_sdesc(ds_base + ks * 2048, kChunkBytes, 1024), make_sdesc(k_base + ks * 2048, kChunkBytes, 1024),
+                           idesc_dq, ks > 0 ? 1u : 0u);
+                tc_commit(&bars->dq_ready);
+                // dP^T of the next step needs the dQ columns drained
+                if (more) {
+                    const int nd = (i + 1) % kDoStages;
+                    if (!(ok = mbar_wait(&bars->dq_drained, ph, abort_flag, kSiteDrained))) break;
+                    if (!(ok = mbar_wait(&bars->do_full[nd], (uint32_t)(((i + 1) / kDoStages) & 1), abort_flag, kSiteDoFull))) break;
+                    tc_fence_after();
+                    issue_kmajor(tm_dP, v_base, do_base + nd * kTileBytes);
+                    tc_commit(&bars->dp_ready);
+                }
+            }
+            tc_commit(&bars->final_bar);
+            mbar_wait(&bars->final_bar, 0, abort_flag, kSiteFinal);
+        }
+    } else if (warp >= 8) {
+        // =========================== dQ drain warpgroup ===========================
+        const int row = (warp & 3) * 32 + lane;                 // query row inside the tile == TMEM lane
+        const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;
+        bool ok = true;
+        for (int i = 0; i < n_iter; ++i) {
+            const int g = i / per_head, qt = qt_first + (i - g * per_head);
+            const int bh = b * p.Hq + hk * group + g;
+            float* tile = p.dq_accum + ((size_t)bh * p.n_qt + qt) * (size_t)(kT * D);
+            ok = __all_sync(0xffffffffu, mbar_wait(&bars->dq_ready, (uint32_t)(i & 1), abort_flag, kSiteDQ));
+            if (!ok) break;
+            tc_fence_after();
+#pragma unroll
+            for (int c = 0; c < D / 32; ++c) {
+                uint32_t r[32];
+                tmem_ld32(tm_dP + lane_off + (uint32_t)(c * 32), r);
+                tmem_ld_wait();
+                if (c == D / 32 - 1) {   // every column has been read: the MMA warp may overwrite them
+                    tc_fence_before();
+                    mbar_arrive(&bars->dq_drained);
+                }
+#pragma unroll
+                for (int v = 0; v < 8; ++v)
+                    red_add_v4(tile + ((size_t)(c * 8 + v) * kT + row) * 4, __uint_as_float(r[4 * v]), __uint_as_float(r[4 * v + 1]),
+                               __uint_as_float(r[4 * v + 2]), __uint_as_float(r[4 * v + 3]));
+            }
+        }
+    } else {
+        // =========================== compute warpgroups ===========================
+        const int wg = warp >> 2;                                // owns query columns [64*wg, 64*wg+64)
+        const int row = (warp & 3) * 32 + lane;                  // key row inside the tile == TMEM lane
+        const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;
+        const uint32_t col0 = (uint32_t)(wg * 64);
+        uint8_t* ds_row = sDs + wg * kChunkBytes + row * 128;    // this thread's 128-byte row of its 64-query chunk
+        bool ok = true;
+        for (int i = 0; i < n_iter; ++i) {
+            const int qt = qt_first + (i % per_head);
+            const int sq = i & 1;
+            const uint32_t ph = (uint32_t)(i & 1);
+            // ---- P^T ----
+            ok = __all_sync(0xffffffffu, mbar_wait(&bars->q_full[sq], (uint32_t)((i >> 1) & 1), abort_flag, kSiteQFull) &&
+                                             mbar_wait(&bars->s_ready, ph, abort_flag, kSiteS));
+            if (!ok) break;
+            tc_fence_after();
+            uint32_t s[64];
+            tmem_ld32(tm_S + lane_off + col0, s);
+            tmem_ld32(tm_S + lane_off + col0 + 32u, s + 32);
+            tmem_ld_wait();
+            const float4* lse4 = reinterpret_cast<const float4*>(sLse + sq * kT + col0);
+            const bool diag = p.causal && (qt == kt);
+            uint32_t pk[32];
+#pragma unroll
+            for (int c = 0; c < 16; ++c) {
+                const float4 l = lse4[c];
+                float p0 = ex2(fmaf(__uint_as_float(s[4 * c + 0]), p.scale_log2, -l.x));
+                float p1 = ex2(fmaf(__uint_as_float(s[4 * c + 1]), p.scale_log2, -l.y));
+                float p2 = ex2(fmaf(__uint_as_float(s[4 * c + 2]), p.scale_log2, -l.z));
+                float p3 = ex2(fmaf(__uint_as_float(s[4 * c + 3]), p.scale_log2, -l.w));
+                if (diag) {   // key (row) > query (column) is masked
+                    const int q = (int)col0 + 4 * c;
+                    if (row > q + 0) p0 = 0.0f;
+                    if (row > q + 1) p1 = 0.0f;
+                    if (row > q + 2) p2 = 0.0f;
+                    if (row > q + 3) p3 = 0.0f;
+                }
+                pk[2 * c] = pack_bf16(p0, p1);
+                pk[2 * c + 1] = pack_bf16(p2, p3);
+            }
+            tmem_st32(tm_S + lane_off + col0, pk);
+            tmem_st_wait();
+            tc_fence_before();
+            mbar_arrive(&bars->p_ready);
+            // ---- dS^T ----
+            ok = __all_sync(0xffffffffu, mbar_wait(&bars->dp_ready, ph, abort_flag, kSiteDP));
+            if (!ok) break;
+            tc_fence_after();
+            tmem_ld32(tm_dP + lane_off + col0, s);
+            tmem_ld32(tm_dP + lane_off + col0 + 32u, s + 32);
+            tmem_ld_wait();
+            const float4* dl4 = reinterpret_cast<const float4*>(sDelta + sq * kT + col0);
+#pragma unroll
+            for (int c = 0; c < 16; ++c) {
+                const float4 dl = dl4[c];
+                const float p0 = __uint_as_float(pk[2 * c] << 16), p1 = __uint_as_float(pk[2 * c] & 0xffff0000u);
+                const float p2 = __uint_as_float(pk[2 * c + 1] << 16), p3 = __uint_as_float(pk[2 * c + 1] & 0xffff0000u);
+                const float d0 = p0 * (__uint_as_float(s[4 * c + 0]) - dl.x);
+                const float d1 = p1 * (__uint_as_float(s[4 * c + 1]) - dl.y);
+                const float d2 = p2 * (__uint_as_float(s[4 * c + 2]) - dl.z);
+                const float d3 = p3 * (__uint_as_float(s[4 * c + 3]) - dl.w);
+                pk[2 * c] = pack_bf16(d0, d1);
+                pk[2 * c + 1] = pack_bf16(d2, d3);
+            }
+            tmem_st32(tm_dP + lane_off + col0, pk);
+            // the same values into shared memory, rows of 128 bytes with the 128-byte swizzle the MMA expects
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                uint4 w = make_uint4(pk[4 * j], pk[4 * j + 1], pk[4 * j + 2], pk[4 * j + 3]);
+                *reinterpret_cast<uint4*>(ds_row + ((j ^ (row & 7)) << 4)) = w;
+            }
+            fence_proxy_async_smem();
+            tmem_st_wait();
+            tc_fence_before();
+            mbar_arrive(&bars->ds_ready);
+        }
+        // ---- epilogue: dV (warpgroup 0) and dK (warpgroup 1) ----
+        ok = __all_sync(0xffffffffu, ok && n_iter > 0 && mbar_wait(&bars->final_bar, 0, abort_flag, kSiteFinal));
+        if (ok) {
+            tc_fence_after();
+            const int key = k0 + row;
+            const bool store = key < p.Skv;
+            const float mul = wg == 0 ? 1.0f : p.scale;
+            __nv_bfloat16* dst = (wg == 0 ? p.dv : p.dk) + ((size_t)slab * p.Skv + (size_t)(store ? key : 0)) * D;
+            const uint32_t src = (wg == 0 ? tm_dV : tm_dK) + lane_off;
+#pragma unroll
+            for (int c = 0; c < D / 32; ++c) {
+                uint32_t r[32];
+                tmem_ld32(src + (uint32_t)(c * 32), r);
+                tmem_ld_wait();
+                if (store) {
+#pragma unroll
+                    for (int v = 0; v < 4; ++v) {
+                        uint4 w;
+                        w.x = pack_bf16(__uint_as_float(r[8 * v + 0]) * mul, __uint_as_float(r[8 * v + 1]) * mul);
+                        w.y = pack_bf16(__uint_as_float(r[8 * v + 2]) * mul, __uint_as_float(r[8 * v + 3]) * mul);
+                        w.z = pack_bf16(__uint_as_float(r[8 * v + 4]) * mul, __uint_as_float(r[8 * v + 5]) * mul);
+                        w.w = pack_bf16(__uint_as_float(r[8 * v + 6]) * mul, __uint_as_float(r[8 * v + 7]) * mul);
+                        *reinterpret_cast<uint4*>(dst + c * 32 + v * 8) = w;
+                    }
+                }
+            }
+        } else if (n_iter == 0) {
+            // a key tile no query can see (cannot happen for causal with Sq == Skv; kept for safety): zero grads
+            const int key = k0 + row;
+            if (key < p.Skv) {
+                __nv_bfloat16* dst = (wg == 0 ? p.dv : p.dk) + ((size_t)slab * p.Skv + key) * D;
+                for (int d = 0; d < D; d += 8) *reinterpret_cast<uint4*>(dst + d) = make_uint4(0, 0, 0, 0);
+            }
+        }
+    }
+
+    // ---- teardown ----
+    if (*abort_flag) {
+        for (int i = 0; i < 64; ++i) __nanosleep(2000);
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 12) {
+        tc_fence_after();
+        tmem_dealloc(tmem, kTmemCols);
+    }
 }
+
+// delta = rowsum(dO o O), lse2 = LSE * log2(e) (+inf for padded rows and for rows without visible keys), and the
+// dQ accumulator zeroed.  One warp per (b, h, padded row).
+template <int D>
+__global__ void bwd_pre_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ dout,
+                               const float* __restrict__ lse, float* __restrict__ lse2, float* __restrict__ delta,
+                               float* __restrict__ dq_accum, int Sq, int Sq_pad, long long rows_padded)
+{
+    const int lane = threadIdx.x & 31;
+    const long long r = blockIdx.x * (long long)(blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (r >= rows_padded) return;
+    const long long bh = r / Sq_pad;
+    const int s = (int)(r - bh * Sq_pad);
+    // the accumulator is tile-permuted but covers exactly D floats per padded row: zero it linearly
+    float4* z = reinterpret_cast<float4*>(dq_accum + r * D);
+    for (int i = lane; i < D / 4; i += 32) z[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (s >= Sq) {
+        if (lane == 0) { lse2[r] = INFINITY; delta[r] = 0.0f; }
+        return;
+    }
+    const size_t off = ((size_t)bh * Sq + s) * D;
+    float acc = 0.0f;
+    for (int d = lane * 2; d < D; d += 64) {
+        const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(o + off + d);
+        const __nv_bfloat162 g = *reinterpret_cast<const __nv_bfloat162*>(dout + off + d);
+        acc = fmaf(__bfloat162float(a.x), __bfloat162float(g.x), acc);
+        acc = fmaf(__bfloat162float(a.y), __bfloat162float(g.y), acc);
+    }
+#pragma unroll
+    for (int m = 16; m > 0; m >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, m);
+    if (lane == 0) {
+        const float l = lse[(size_t)bh * Sq + s];
+        lse2[r] = (l == -INFINITY) ? INFINITY : l * 1.4426950408889634f;
+        delta[r] = acc;
+    }
+}
+
+// dQ (bf16, [B][Hq][Sq][D]) = scale * accumulator, undoing the per-tile [d/4][row][4] order.
+// One CTA per (tile, 32-row group): for a fixed d/4 chunk its 32 rows are 512 contiguous bytes of the accumulator.
+template <int D>
+__global__ void __launch_bounds__(256) bwd_post_kernel(const float* __restrict__ dq_accum, __nv_bfloat16* __restrict__ dq, int Sq,
+                                                       int n_qt, float scale)
+{
+    constexpr int kRows = 32;
+    __shared__ float tile[kRows][D + 4];
+    const size_t t = blockIdx.x >> 2;
+    const int r0 = (int)(blockIdx.x & 3) * kRows;
+    const size_t bh = t / n_qt;
+    const int qt = (int)(t - bh * n_qt);
+    const float4* src = reinterpret_cast<const float4*>(dq_accum + t * (size_t)(kT * D));
+    for (int e = threadIdx.x; e < kRows * D / 4; e += blockDim.x) {
+        const int chunk = e / kRows, row = e - chunk * kRows;   // consecutive threads -> consecutive 16-byte units
+        const float4 v = src[(size_t)chunk * kT + r0 + row];
+        *reinterpret_cast<float4*>(&tile[row][chunk * 4]) = v;
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < kRows * D / 8; e += blockDim.x) {
+        const int row = e / (D / 8), d8 = (e - row * (D / 8)) * 8;
+        const int s = qt * kT + r0 + row;
+        if (s >= Sq) continue;
+        const float* x = &tile[row][d8];
+        uint4 w;
+        w.x = pack_bf16(x[0] * scale, x[1] * scale);
+        w.y = pack_bf16(x[2] * scale, x[3] * scale);
+        w.z = pack_bf16(x[4] * scale, x[5] * scale);
+        w.w = pack_bf16(x[6] * scale, x[7] * scale);
+        *reinterpret_cast<uint4*>(dq + (bh * Sq + s) * D + d8) = w;
+    }
+}
+
+inline size_t align256(size_t x) { return (x + 255) / 256 * 256; }
+
+template <int D>
+cudaError_t launch_bwd(const TcArgs& a, cudaStream_t st)
+{
+    const AttnShape& s = a.s;
+    const int n_qt = (s.Sq + kT - 1) / kT, n_kt = (s.Skv + kT - 1) / kT;
+    const int Sq_pad = n_qt * kT;
+    const long long rows_padded = (long long)s.B * s.Hq * Sq_pad;
+    float* lse2 = a.delta + rows_padded;   // workspace: [delta | lse2] then the accumulator (see tc_backward_workspace_bytes)
+    cudaError_t e;
+    {
+        const int warps = 8;
+        const long long blocks = (rows_padded + warps - 1) / warps;
+        bwd_pre_kernel<D><<<(unsigned)blocks, warps * 32, 0, st>>>(a.o, a.dout, a.lse, lse2, a.delta, a.dq_accum, s.Sq, Sq_pad,
+                                                                    rows_padded);
+        count_launch();
+        if ((e = cudaGetLastError()) != cudaSuccess) return e;
+    }
+    CUtensorMap tq, tk, tv, tdo;
+    if ((e = encode_tmap_bf16_3d(&tq, a.q, D, s.Sq, s.B * s.Hq, 128)) != cudaSuccess) return e;
+    if ((e = encode_tmap_bf16_3d(&tdo, a.dout, D, s.Sq, s.B * s.Hq, 128)) != cudaSuccess) return e;
+    if ((e = encode_tmap_bf16_3d(&tk, a.k, D, s.Skv, s.B * s.Hkv, 128)) != cudaSuccess) return e;
+    if ((e = encode_tmap_bf16_3d(&tv, a.v, D, s.Skv, s.B * s.Hkv, 128)) != cudaSuccess) return e;
+    BwdParams p{};
+    p.dk = a.dk; p.dv = a.dv;
+    p.lse2 = lse2; p.delta = a.delta; p.dq_accum = a.dq_accum;
+    p.B = s.B; p.Hq = s.Hq; p.Hkv = s.Hkv; p.Sq = s.Sq; p.Skv = s.Skv; p.Sq_pad = Sq_pad;
+    p.causal = s.causal;
+    p.n_qt = n_qt; p.n_kt = n_kt;
+    p.scale = s.scale;
+    p.scale_log2 = s.scale * 1.4426950408889634f;
+    constexpr int kDoStages = (D == 128) ? 1 : 2;
+    const size_t smem = (size_t)(128 * D * 2) * (4 + kDoStages) + 128 * 128 * 2 + 4 * 128 * 4 + sizeof(BwdBarriers) + 1024;
+    static bool configured = false;
+    if (!configured) {
+        if ((e = cudaFuncSetAttribute(attn_bwd_tc_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)) != cudaSuccess)
+            return e;
+        configured = true;
+    }
+    const long long ctas = (long long)n_kt * s.B * s.Hkv;
+    if (ctas > 0x7fffffffLL) return cudaErrorInvalidConfiguration;
+    attn_bwd_tc_kernel<D><<<(unsigned)ctas, kBwdThreads, smem, st>>>(tq, tk, tv, tdo, p);
+    count_launch();
+    if ((e = cudaGetLastError()) != cudaSuccess) return e;
+    bwd_post_kernel<D><<<(unsigned)((long long)s.B * s.Hq * n_qt * 4), 256, 0, st>>>(a.dq_accum, a.dq, s.Sq, n_qt, s.scale);
+    count_launch();
+    return cudaGetLastError();
+}
+
+}  // namespace
+
+bool tc_bwd_supported(const AttnShape& s)
+{
+    return (s.D == 64 || s.D == 128) && (!s.causal || s.Sq == s.Skv);
+}
+
+// [delta: B*Hq*Sq_pad fp32][lse2: same], 256-byte aligned, then the fp32 dQ accumulator B*Hq*Sq_pad*D
+size_t tc_backward_workspace_bytes(const AttnShape& s)
+{
+    const size_t sq_pad = ((size_t)s.Sq + kT - 1) / kT * kT;
+    const size_t rows = (size_t)s.B * s.Hq * sq_pad;
+    return align256(2 * 4 * rows) + align256(4 * rows * (size_t)s.D);
+}
+
+cudaError_t tc_backward(const TcArgs& a, cudaStream_t st)
+{
+    return a.s.D == 64 ? launch_bwd<64>(a, st) : launch_bwd<128>(a, st);
+}
+
+cudaError_t read_and_clear_bwd_status(cudaStream_t st, uint32_t* word)
+{
+    cudaError_t e = cudaStreamSynchronize(st);
+    if (e != cudaSuccess) return e;
+    unsigned int w = 0, zero = 0;
+    if ((e = cudaMemcpyFromSymbol(&w, ptx::g_device_status, sizeof(w))) != cudaSuccess) return e;
+    if (w != 0 && (e = cudaMemcpyToSymbol(ptx::g_device_status, &zero, sizeof(zero))) != cudaSuccess) return e;
+    *word = w;
+    return cudaSuccess;
+}
+
+}  // namespace sntl

@@ -217,7 +217,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
         float m_ref = -INFINITY, l = 0.0f;
         bool ok = true;
         for (int j = 0; j < n_mine; ++j) {
-            if (!(ok = mbar_wait(&bars->s_ready[t], (uint32_t)(j & 1), abort_flag, kSiteSReady))) break;
+            if (!(ok = __all_sync(0xffffffffu, mbar_wait(&bars->s_ready[t], (uint32_t)(j & 1), abort_flag, kSiteSReady)))) break;
             tc_fence_after();
             uint32_t s[128];
 #pragma unroll
@@ -238,7 +238,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
             if (j == 0) {
                 m_ref = m_new;
             } else if (__any_sync(0xffffffffu, need)) {
-                if (!(ok = mbar_wait(&bars->o_ready[t], (uint32_t)((j - 1) & 1), abort_flag, kSiteOReady))) break;
+                if (!(ok = __all_sync(0xffffffffu, mbar_wait(&bars->o_ready[t], (uint32_t)((j - 1) & 1), abort_flag, kSiteOReady)))) break;
                 tc_fence_after();
                 const float factor = need ? ex2(m_ref - m_new) : 1.0f;
                 if (need) m_ref = m_new;
@@ -269,7 +269,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
             tc_fence_before();
             mbar_arrive(&bars->p_ready[t]);
         }
-        if (ok && n_mine > 0 && mbar_wait(&bars->o_ready[t], (uint32_t)((n_mine - 1) & 1), abort_flag, kSiteOReady)) {
+        if (__all_sync(0xffffffffu, ok && n_mine > 0 && mbar_wait(&bars->o_ready[t], (uint32_t)((n_mine - 1) & 1), abort_flag, kSiteOReady))) {
             tc_fence_after();
             const float inv = l > 0.0f ? 1.0f / l : 0.0f;
             const bool store = grow < p.Sq;
