@@ -277,13 +277,31 @@ def test_full_size_workloads_sampled_oracle_and_cross_check(sb, oracle, wname):
     assert sb.poll_device_status() == 0
     qf, kf, vf, dof = (t.to(torch.float32).numpy() for t in (q, k, v, do))
     S = w.seq
-    rows = np.array([0, 1, 127, 128, 255, S // 2 - 1, S // 2, S - 129, S - 1])
+    # Rows with only a handful of visible keys (0, 1) are held to the absolute bound only: their dQ is a single
+    # rounded dS value times a key difference, so the bf16 rounding of P and dS does not average out over keys
+    # and a relative L2 over so few rows is not the whole-tensor figure the 5e-3 bound is stated for.
+    first = np.array([0, 1])
+    rows = np.array([127, 128, 255, S // 2 - 1, S // 2, S - 129, S - 1])
     group = w.q_heads // w.kv_heads
     for (b, h) in ((0, 0), (w.batch - 1, w.q_heads - 1)):
         wo, wl, wdq = oracle.attn_rows(qf, kf, vf, dof, b, h, rows)
         _check_bf16(_np(o[b, h, rows]), wo, "o rows")
-        assert max_abs(_np(lse[b, h, rows]), wl) <= BF16_ABS
+        assert max_abs(_np(lse[b, h, rows]), wl) <= 1e-3
         _check_bf16(_np(dq[b, h, rows]), wdq, "dq rows")
+        wo, wl, wdq = oracle.attn_rows(qf, kf, vf, dof, b, h, first)
+        assert max_abs(_np(o[b, h, first]), wo) <= BF16_ABS and max_abs(_np(dq[b, h, first]), wdq) <= BF16_ABS
+    # whole-tensor relative L2 of one (batch, KV group) slice against the exact-fp32 kernels on the same inputs
+    # (those kernels are themselves pinned to the oracle and the reference above)
+    b, hk = w.batch - 1, w.kv_heads - 1
+    hs = slice(hk * group, (hk + 1) * group)
+    q1, k1, v1, do1 = qd[b:b + 1, hs].float(), kd[b:b + 1, hk:hk + 1].float(), vd[b:b + 1, hk:hk + 1].float(), dod[b:b + 1, hs].float()
+    o1, l1 = sb.attention_forward(q1, k1, v1)
+    assert sb.last_path() == "simt_f32"
+    dq1, dk1, dv1 = sb.attention_backward(q1, k1, v1, o1, l1, do1)
+    for got, want, what in ((o[b:b + 1, hs], o1, "O"), (dq[b:b + 1, hs], dq1, "dQ"), (dk[b:b + 1, hk:hk + 1], dk1, "dK"),
+                            (dv[b:b + 1, hk:hk + 1], dv1, "dV")):
+        _check_bf16(_np(got), _np(want), what + " slice vs exact kernels")
+    assert max_abs(_np(lse[b:b + 1, hs]), _np(l1)) <= 1e-4
     cols = np.array([0, 127, 128, S // 2, S - 200, S - 1])
     if S <= 4096 or group <= 7:
         b, hk = w.batch - 1, w.kv_heads - 1
