@@ -44,7 +44,8 @@ enum {
     SNTL_ERR_WORKSPACE = 3,      /* workspace missing or smaller than *_workspace_bytes() */
     SNTL_ERR_CUDA = 4,           /* a CUDA runtime/driver call or a launch failed */
     SNTL_ERR_NO_DEVICE = 5,      /* current device is not compute capability 10.x */
-    SNTL_ERR_DEVICE_TIMEOUT = 6  /* a bounded device-side wait ran out (reported by sntl_attn_poll_device_status) */
+    SNTL_ERR_DEVICE_TIMEOUT = 6, /* a bounded device-side wait ran out (reported by sntl_attn_poll_device_status) */
+    SNTL_ERR_SCRATCH_LIMIT = 7   /* sntl_attn_bwd_static_scratch: the problem needs more than the built-in scratch */
 };
 
 enum { SNTL_DTYPE_BF16 = 0, SNTL_DTYPE_F32 = 1 };
@@ -109,6 +110,20 @@ int sntl_attn_fwd(const sntl_attn_desc* desc, const void* q, const void* k, cons
 int sntl_attn_bwd(const sntl_attn_desc* desc, const void* q, const void* k, const void* v, const void* o,
                   const float* lse, const void* dout, void* dq, void* dk, void* dv, void* workspace,
                   size_t workspace_bytes, void* stream);
+
+/* The same backward for callers that cannot allocate device memory and so cannot bring a workspace (a plugin
+ * running inside another component's stream capture, a host that bans cudaMalloc in its hot loop, a binding with
+ * no allocator to lend).  The scratch is a fixed array inside the library image, sntl_attn_static_scratch_capacity()
+ * bytes (32 MiB) on every GPU that loads the library; a problem whose sntl_attn_bwd_workspace_bytes() exceeds it
+ * returns SNTL_ERR_SCRATCH_LIMIT and launches nothing.  The first call on a device resolves the array's device
+ * address and should be made before any stream capture.  All calls on a device share the array (each call rewrites
+ * what it reads, so nothing needs clearing), hence calls that can overlap on one GPU race and must be ordered by
+ * the caller.  Allocates nothing.  This entry point has no counterpart in the reference. */
+int sntl_attn_bwd_static_scratch(const sntl_attn_desc* desc, const void* q, const void* k, const void* v, const void* o,
+                                 const float* lse, const void* dout, void* dq, void* dk, void* dv, void* stream);
+
+/* Size in bytes of the built-in scratch used by sntl_attn_bwd_static_scratch.  No counterpart in the reference. */
+size_t sntl_attn_static_scratch_capacity(void);
 
 /* Log-sum-exp merge of two partial attention results over disjoint key sets (the ring schedule's
  * combine step): o_acc,lse_acc <- merge((o_acc,lse_acc),(o_part,lse_part)).  BHSD layout, `rows` =

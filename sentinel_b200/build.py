@@ -19,7 +19,7 @@ LIB = os.path.join(LIB_DIR, "libsntl_attn.so")
 OBJ_DIR = os.path.join(HERE, "build")
 
 SOURCES = ["attn_api.cu", "attn_simt.cu", "layout_convert.cu", "attn_fwd_sm100.cu", "attn_bwd_sm100.cu",
-           "sentinel_compat.cu"]
+           "sentinel_compat.cu", "attn_bwd_static_scratch.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "-I", os.path.join(ROOT, "include"), "-I", CSRC]
 
