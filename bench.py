@@ -153,11 +153,16 @@ def main():
     ap.add_argument("--workload", default="gqa7b_d128")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--batch", type=int, default=0, help="override the workload's per-GPU batch (profiling captures)")
+    ap.add_argument("--skip-e2e", action="store_true", help="skip the host-buffer leg (profiling captures)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
     from sentinel_b200.workloads import WORKLOADS, make_inputs
     w = WORKLOADS[args.workload]
+    if args.batch > 0:
+        import dataclasses
+        w = dataclasses.replace(w, batch=args.batch)
     if args.impl == "reference":
         run_reference_arm(args, w)
         return
@@ -235,14 +240,17 @@ def main():
     def e2e_step():
         sb.attention_forward_backward_host(q, k, v, do, device=dev)
 
-    for _ in range(2):
-        e2e_step()
-    e2e_steps = max(3, min(args.steps, 10))
-    e2e_ms = timed(e2e_step, e2e_steps) / e2e_steps
+    if args.skip_e2e:
+        e2e_ms = float("nan")
+    else:
+        for _ in range(2):
+            e2e_step()
+        e2e_steps = max(3, min(args.steps, 10))
+        e2e_ms = timed(e2e_step, e2e_steps) / e2e_steps
     esz = q.element_size()
     h2d = esz * (2 * q.numel() + 2 * k.numel())
     d2h = esz * (2 * q.numel() + 2 * k.numel()) + 4 * lse.numel()
-    e2e_value = flops_rank * world / (e2e_ms * 1e-3) / 1e12
+    e2e_value = None if args.skip_e2e else flops_rank * world / (e2e_ms * 1e-3) / 1e12
     status = sb.poll_device_status()
 
     peaks = load_peaks()
@@ -274,7 +282,7 @@ def main():
                            "l2": "per-step working set (Q,K,V,O,dO,dQ,dK,dV,dQ-accumulator) > 0.8 GB, larger than the 126 MB L2",
                            "kernel_path": sb.last_path()},
                 "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                        "ms_per_step": e2e_ms},
+                        "ms_per_step": None if args.skip_e2e else e2e_ms},
                 "gpu_launches": int(launches), "clocks": clocks.summary(), "roofline": roofline,
                 "device_status": status}
         if cpu_base is not None:

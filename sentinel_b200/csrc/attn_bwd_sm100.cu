@@ -15,16 +15,17 @@
 //         dP^T = V  dO^T         (V, dO K-major from shared memory)      -> TMEM
 //         P^T  = exp2(S^T*scale*log2e - LSE*log2e), causal mask on the diagonal tile, bf16 back over S^T
 //         dV  += P^T  dO         (A = P^T in TMEM,  B = dO tile MN-major)
-//         dS^T = P^T o (dP^T - delta), bf16 back over dP^T and also into shared memory
-//         dK  += dS^T Q          (A = dS^T in TMEM, B = Q tile MN-major)
-//         dQ_i = dS   K          (A = dS^T tile in shared memory read MN-major, B = K tile MN-major)
+//         dS^T = P^T o (dP^T - delta), bf16 into a shared-memory tile [key][query]
+//         dQ_i = dS   K          (A = that tile read MN-major, B = K tile MN-major)
+//         dK  += dS^T Q          (A = the same tile read K-major, B = Q tile MN-major)
 //     the softmax scale is folded into the final dK store and the dQ conversion pass;
 //   * dQ_i lands in TMEM (over the dP^T columns, which are dead by then) and a drain warpgroup adds it into an
 //     fp32 accumulator in global memory with coalesced 16-byte vector reductions; the accumulator uses a
 //     per-tile [d/4][row][4] order so that the 32 rows of a warp hit consecutive addresses;
 //   * warp roles: 2 compute warpgroups (each owns 64 of the 128 query columns, one thread per key row),
-//     1 drain warpgroup, 1 MMA-issuing warp, 1 TMA-producer warp.  Q (+LSE, delta) is double-buffered; dO is
-//     double-buffered for D=64 and single-buffered for D=128 (shared-memory budget).
+//     1 drain warpgroup, 2 MMA-issuing warps, 1 TMA-producer warp; registers are re-allocated per role
+//     (setmaxnreg).  Q (+LSE, delta) is double-buffered; dO is double-buffered for D=64 and single-buffered for
+//     D=128 (shared-memory budget).
 //
 // A pre-pass computes delta = rowsum(dO o O), LSE*log2e (padded rows get +inf so they produce P = 0) and
 // zeroes the dQ accumulator; a post-pass converts the accumulator to bf16 dQ (times scale).
@@ -39,7 +40,7 @@ using namespace ptx;
 namespace {
 
 constexpr int kT = 128;                 // tile edge: keys per CTA, queries per step
-constexpr int kBwdThreads = 448;        // 2 compute WGs + drain WG + MMA warp + producer warp
+constexpr int kBwdThreads = 512;        // 2 compute WGs + drain WG + 1 WG holding the MMA warp and the producer warp
 constexpr uint32_t kTmemCols = 512;
 
 enum BwdSite : uint32_t {
@@ -74,21 +75,30 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
     constexpr int kTileBytes = kT * D * 2;
     constexpr int kChunkBytes = kT * 128;          // 128 rows x 128 B
     constexpr int kChunks = D / 64;
-    constexpr int kDoStages = (D == 128) ? 1 : 2;
+    constexpr int kDoStages = (D == 128) ? 1 : 2;  // shared-memory budget: 227 KB
+    constexpr int kStageBytes = 32 * kT * 4;       // dQ staging: 32 columns x 128 rows fp32 = one bulk reduction
     constexpr int kDsBytes = kT * kT * 2;          // dS^T tile: [128 keys][128 queries] bf16 as two 64-query chunks
-    extern __shared__ uint8_t smem_raw[];
-    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    // The layout uses every byte of the 227 KB a CTA may have (D = 128), so there is no room for an alignment
+    // pad: the kernel has no static shared memory, which puts the dynamic window at the 1024-byte aligned start
+    // of the CTA's shared memory; that is verified below instead of assumed.
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    uint8_t* smem = smem_raw;
     uint8_t* sK = smem;
     uint8_t* sV = sK + kTileBytes;
     uint8_t* sQ = sV + kTileBytes;                 // [2]
     uint8_t* sDo = sQ + 2 * kTileBytes;            // [kDoStages]
     uint8_t* sDs = sDo + kDoStages * kTileBytes;
-    float* sLse = (float*)(sDs + kDsBytes);        // [2][128]
+    uint8_t* sStage = sDs + kDsBytes;              // [2][kStageBytes]
+    float* sLse = (float*)(sStage + 2 * kStageBytes);   // [2][128]
     float* sDelta = sLse + 2 * kT;                 // [2][128]
     BwdBarriers* bars = (BwdBarriers*)(sDelta + 2 * kT);
     volatile uint32_t* abort_flag = &bars->abort_flag;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if ((smem_u32(smem_raw) & 1023u) != 0u) {      // uniform over the CTA: nothing has been set up yet
+        if (threadIdx.x == 0) atomicCAS(&g_device_status, 0u, (0x3fu << 24) | (blockIdx.x & 0xffffffu));
+        return;
+    }
 
     // ---- work decode: key tile 0 sees every query tile, so low key tiles go first ----
     const int slabs = p.B * p.Hkv;
@@ -109,9 +119,9 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
         mbar_init(&bars->kv_full, 1);
         for (int i = 0; i < 2; ++i) {
             mbar_init(&bars->q_full[i], 1);
-            mbar_init(&bars->q_empty[i], 1);
+            mbar_init(&bars->q_empty[i], 2);
             mbar_init(&bars->do_full[i], 1);
-            mbar_init(&bars->do_empty[i], 1);
+            mbar_init(&bars->do_empty[i], 2);
         }
         mbar_init(&bars->s_ready, 1);
         mbar_init(&bars->p_ready, 256);
@@ -119,7 +129,7 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
         mbar_init(&bars->ds_ready, 256);
         mbar_init(&bars->dq_ready, 1);
         mbar_init(&bars->dq_drained, 128);
-        mbar_init(&bars->final_bar, 1);
+        mbar_init(&bars->final_bar, 2);
         bars->abort_flag = 0;
         fence_mbar_init();
     }
@@ -133,7 +143,15 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
     const uint32_t tmem = bars->tmem_base;
     const uint32_t tm_S = tmem, tm_dP = tmem + 128u, tm_dV = tmem + 256u, tm_dK = tmem + 384u;
 
-    if (warp == 13) {
+    // 512 threads start with 128 registers each; the issuing/producer warpgroup needs few, the others get the rest
+    // (each role re-allocates registers inside its own branch so that the compiler sees which budget applies where)
+
+
+    if (warp == 15) {
+        setmaxnreg_dec<56>();
+        // idle warps of the last warpgroup
+    } else if (warp == 13) {
+        setmaxnreg_dec<56>();
         // =========================== TMA producer ===========================
         if (lane == 0 && n_iter > 0) {
             mbar_arrive_expect_tx(&bars->kv_full, (uint32_t)(2 * kTileBytes));
@@ -160,113 +178,192 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
                     tma_load_3d(sDo + sd * kTileBytes + c * kChunkBytes, &tmap_do, &bars->do_full[sd], c * 64, qt * kT, bh);
             }
         }
-    } else if (warp == 12) {
-        // =========================== MMA issuer ===========================
+    } else if (warp == 12 || warp == 14) {
+        setmaxnreg_dec<56>();
+        // =========================== MMA issuers ===========================
+        // Two issuing threads on two different schedulers, because a lone issuing warp shares its scheduler with
+        // ALU-dense compute warps and gets too few issue slots to keep the tensor pipe fed:
+        //   warp 12 ("P side"):   dV_i += P^T dO_i ,  S^T_{i+1} = K Q_{i+1}^T
+        //   warp 14 ("dS side"):  dK_i += dS^T Q_i ,  dQ_i = dS K ,  dP^T_{i+1} = V dO_{i+1}^T
+        // Every TMEM region with a write-after-read hazard is touched by one of the two only (S^T/P^T by warp 12,
+        // dP^T/dS^T/dQ by warp 14), so the in-order execution of one thread's MMAs still covers those hazards.  The Q
+        // and dO stages are read by both and are released when both have committed (barrier count 2).
         if (lane == 0 && n_iter > 0) {
+            SNTL_TRACE_DECL(tn);
             constexpr uint32_t idesc_st = make_idesc(kT, kT, false, false);   // S^T, dP^T
             constexpr uint32_t idesc_kv = make_idesc(kT, D, false, true);     // dV, dK: A in TMEM, B MN-major
             constexpr uint32_t idesc_dq = make_idesc(kT, D, true, true);      // dQ: both operands MN-major
-            const uint32_t k_base = smem_u32(sK), v_base = smem_u32(sV), q_base = smem_u32(sQ), do_base = smem_u32(sDo),
-                           ds_base = smem_u32(sDs);
-            // C[128 x 128] = A[128 x D] * B[128 x D]^T, both K-major tiles
-            auto issue_kmajor = [&](uint32_t d_tmem, uint32_t a_tile, uint32_t b_tile) {
+            // C[128 x 128] = A[128 x D] * B[128 x D]^T, both K-major tiles; one descriptor per tile, advanced per k-step
+            // by a 64-bit add (the empty asm keeps the compiler from hoisting every advanced descriptor out of the main
+            // loop, which would cost this warp more registers than its budget)
+            auto issue_kmajor = [&](uint32_t d_tmem, uint64_t a, uint64_t b) {
+                asm volatile("" : "+l"(a), "+l"(b));
+                mma_ss_c<false>(d_tmem, a, b, idesc_st);
 #pragma unroll
-                for (int ks = 0; ks < D / 16; ++ks) {
+                for (int ks = 1; ks < D / 16; ++ks) {
                     const uint32_t off = (uint32_t)((ks >> 2) * kChunkBytes + (ks & 3) * 32);
-                    mma_ss(d_tmem, make_sdesc(a_tile + off, 16, 1024), make_sdesc(b_tile + off, 16, 1024), idesc_st, ks > 0 ? 1u : 0u);
+                    mma_ss_c<true>(d_tmem, sdesc_advance(a, off), sdesc_advance(b, off), idesc_st);
                 }
             };
             // C[128 keys x D] (+)= A^T[128 keys x 128 q] (packed bf16 in TMEM) * B[128 q x D] (MN-major tile)
-            auto issue_from_tmem = [&](uint32_t d_tmem, uint32_t a_tmem, uint32_t b_tile, bool accumulate) {
+            auto issue_from_tmem = [&](uint32_t d_tmem, uint32_t a_tmem, uint64_t b, bool accumulate) {
+                asm volatile("" : "+l"(b));
+                if (accumulate) mma_ts_c<true>(d_tmem, a_tmem, b, idesc_kv);
+                else mma_ts_c<false>(d_tmem, a_tmem, b, idesc_kv);
 #pragma unroll
-                for (int ks = 0; ks < kT / 16; ++ks) {
-                    const uint32_t a = a_tmem + (uint32_t)((ks >> 2) * 64 + (ks & 3) * 8);
-                    mma_ts(d_tmem, a, make_sdesc(b_tile + ks * 2048, kChunkBytes, 1024), idesc_kv, (accumulate || ks > 0) ? 1u : 0u);
-                }
+                for (int ks = 1; ks < kT / 16; ++ks)
+                    mma_ts_c<true>(d_tmem, a_tmem + (uint32_t)((ks >> 2) * 64 + (ks & 3) * 8), sdesc_advance(b, ks * 2048), idesc_kv);
             };
-            bool ok = mbar_wait(&bars->kv_full, 0, abort_flag, kSiteKV) && mbar_wait(&bars->q_full[0], 0, abort_flag, kSiteQFull);
-            if (ok) {
-                tc_fence_after();
-                issue_kmajor(tm_S, k_base, q_base);
-                tc_commit(&bars->s_ready);
-                ok = mbar_wait(&bars->do_full[0], 0, abort_flag, kSiteDoFull);
-            }
-            if (ok) {
-                tc_fence_after();
-                issue_kmajor(tm_dP, v_base, do_base);
-                tc_commit(&bars->dp_ready);
-            }
-            for (int i = 0; ok && i < n_iter; ++i) {
-                const uint32_t ph = (uint32_t)(i & 1);
-                const int sq = i & 1, sd = i % kDoStages;
-                const bool more = i + 1 < n_iter;
-                // dV += P^T dO
-                if (!(ok = mbar_wait(&bars->p_ready, ph, abort_flag, kSiteP))) break;
-                tc_fence_after();
-                issue_from_tmem(tm_dV, tm_S, do_base + sd * kTileBytes, i > 0);
-                tc_commit(&bars->do_empty[sd]);
-                // S^T of the next step (its P phase overlaps dK/dQ/drain of this step)
-                if (more) {
-                    const int nq = (i + 1) & 1;
-                    if (!(ok = mbar_wait(&bars->q_full[nq], (uint32_t)(((i + 1) >> 1) & 1), abort_flag, kSiteQFull))) break;
+            bool ok = mbar_wait(&bars->kv_full, 0, abort_flag, kSiteKV);
+            if (warp == 12) {
+                const uint64_t dK_k = make_sdesc(smem_u32(sK), 16, 1024);
+                const uint64_t dQ_k0 = make_sdesc(smem_u32(sQ), 16, 1024), dDo_mn0 = make_sdesc(smem_u32(sDo), kChunkBytes, 1024);
+                ok = ok && mbar_wait(&bars->q_full[0], 0, abort_flag, kSiteQFull);
+                if (ok) {
                     tc_fence_after();
-                    issue_kmajor(tm_S, k_base, q_base + nq * kTileBytes);
+                    issue_kmajor(tm_S, dK_k, dQ_k0);
                     tc_commit(&bars->s_ready);
                 }
-                // dK += dS^T Q ; dQ_i = dS K
-                if (!(ok = mbar_wait(&bars->ds_ready, ph, abort_flag, kSiteDS))) break;
-                tc_fence_after();
-                issue_from_tmem(tm_dK, tm_dP, q_base + sq * kTileBytes, i > 0);
-                tc_commit(&bars->q_empty[sq]);
-#pragma unroll
-                for (int ks = 0; ks < kT / 16; ++ks)
-                    mma_ss(tm_dP, make_sdesc(ds_base + ks * 2048, kChunkBytes, 1024), make_sdesc(k_base + ks * 2048, kChunkBytes, 1024),
-                           idesc_dq, ks > 0 ? 1u : 0u);
-                tc_commit(&bars->dq_ready);
-                // dP^T of the next step needs the dQ columns drained
-                if (more) {
-                    const int nd = (i + 1) % kDoStages;
-                    if (!(ok = mbar_wait(&bars->dq_drained, ph, abort_flag, kSiteDrained))) break;
-                    if (!(ok = mbar_wait(&bars->do_full[nd], (uint32_t)(((i + 1) / kDoStages) & 1), abort_flag, kSiteDoFull))) break;
+                for (int i = 0; ok && i < n_iter; ++i) {
+                    const int sq = i & 1, sd = i % kDoStages;
+                    if (!(ok = mbar_wait(&bars->p_ready, (uint32_t)(i & 1), abort_flag, kSiteP))) break;
+                    // dO_i has normally been consumed by the other issuer's dP^T_i already, but nothing orders the two
+                    // issuers, so this one checks the stage itself
+                    if (!(ok = mbar_wait(&bars->do_full[sd], (uint32_t)((i / kDoStages) & 1), abort_flag, kSiteDoFull))) break;
+                    SNTL_TRACE_EV(true, 0, tn, 1);
                     tc_fence_after();
-                    issue_kmajor(tm_dP, v_base, do_base + nd * kTileBytes);
+                    issue_from_tmem(tm_dV, tm_S, sdesc_advance(dDo_mn0, sd * kTileBytes), i > 0);
+                    tc_commit(&bars->do_empty[sd]);   // this warp's share: dV_i
+                    tc_commit(&bars->q_empty[sq]);    // this warp's share: S^T_i (issued one step earlier)
+                    SNTL_TRACE_EV(true, 0, tn, 2);
+                    if (i + 1 < n_iter) {
+                        const int nq = (i + 1) & 1;
+                        if (!(ok = mbar_wait(&bars->q_full[nq], (uint32_t)(((i + 1) >> 1) & 1), abort_flag, kSiteQFull))) break;
+                        tc_fence_after();
+                        issue_kmajor(tm_S, dK_k, sdesc_advance(dQ_k0, nq * kTileBytes));
+                        tc_commit(&bars->s_ready);
+                        SNTL_TRACE_EV(true, 0, tn, 9);
+                    }
+                }
+            } else {
+                const uint64_t dV_k = make_sdesc(smem_u32(sV), 16, 1024), dDo_k0 = make_sdesc(smem_u32(sDo), 16, 1024);
+                const uint64_t dK_mn = make_sdesc(smem_u32(sK), kChunkBytes, 1024), dDs_mn = make_sdesc(smem_u32(sDs), kChunkBytes, 1024);
+                const uint64_t dDs_k = make_sdesc(smem_u32(sDs), 16, 1024);
+                const uint64_t dQ_mn0 = make_sdesc(smem_u32(sQ), kChunkBytes, 1024);
+                ok = ok && mbar_wait(&bars->do_full[0], 0, abort_flag, kSiteDoFull);
+                if (ok) {
+                    tc_fence_after();
+                    issue_kmajor(tm_dP, dV_k, dDo_k0);
                     tc_commit(&bars->dp_ready);
                 }
+                for (int i = 0; ok && i < n_iter; ++i) {
+                    const uint32_t ph = (uint32_t)(i & 1);
+                    const int sq = i & 1, sd = i % kDoStages;
+                    if (!(ok = mbar_wait(&bars->ds_ready, ph, abort_flag, kSiteDS))) break;
+                    if (!(ok = mbar_wait(&bars->q_full[sq], (uint32_t)((i >> 1) & 1), abort_flag, kSiteQFull))) break;  // Q_i, see above
+                    SNTL_TRACE_EV(true, 4, tn, 3);
+                    tc_fence_after();
+                    // dQ first: it gates the drain and with it the next dP^T; dK only has to finish before the dS tile
+                    // is rewritten, which the in-order issue of this thread already guarantees
+                    {
+                        uint64_t a = dDs_mn, bq = dK_mn;
+                        asm volatile("" : "+l"(a), "+l"(bq));
+                        mma_ss_c<false>(tm_dP, a, bq, idesc_dq);
+#pragma unroll
+                        for (int ks = 1; ks < kT / 16; ++ks)
+                            mma_ss_c<true>(tm_dP, sdesc_advance(a, ks * 2048), sdesc_advance(bq, ks * 2048), idesc_dq);
+                    }
+                    tc_commit(&bars->dq_ready);
+                    SNTL_TRACE_EV(true, 4, tn, 4);
+                    // dK += dS^T Q with dS^T read from its shared-memory tile as a K-major A operand (rows = keys, the 64
+                    // contiguous elements run along the queries)
+                    {
+                        uint64_t a = dDs_k, bq = sdesc_advance(dQ_mn0, sq * kTileBytes);
+                        asm volatile("" : "+l"(a), "+l"(bq));
+                        if (i > 0) mma_ss_c<true>(tm_dK, a, bq, idesc_kv);
+                        else mma_ss_c<false>(tm_dK, a, bq, idesc_kv);
+#pragma unroll
+                        for (int ks = 1; ks < kT / 16; ++ks)
+                            mma_ss_c<true>(tm_dK, sdesc_advance(a, (ks >> 2) * kChunkBytes + (ks & 3) * 32), sdesc_advance(bq, ks * 2048), idesc_kv);
+                    }
+                    tc_commit(&bars->q_empty[sq]);    // this warp's share: dK_i
+                    tc_commit(&bars->do_empty[sd]);   // this warp's share: dP^T_i (issued one step earlier)
+                    if (i + 1 < n_iter) {
+                        const int nd = (i + 1) % kDoStages;
+                        if (!(ok = mbar_wait(&bars->dq_drained, ph, abort_flag, kSiteDrained))) break;
+                        SNTL_TRACE_EV(true, 4, tn, 5);
+                        if (!(ok = mbar_wait(&bars->do_full[nd], (uint32_t)(((i + 1) / kDoStages) & 1), abort_flag, kSiteDoFull))) break;
+                        tc_fence_after();
+                        issue_kmajor(tm_dP, dV_k, sdesc_advance(dDo_k0, nd * kTileBytes));
+                        tc_commit(&bars->dp_ready);
+                        SNTL_TRACE_EV(true, 4, tn, 6);
+                    }
+                }
             }
+            // every MMA of this thread has retired once its commit lands; the epilogue waits for both issuers
             tc_commit(&bars->final_bar);
             mbar_wait(&bars->final_bar, 0, abort_flag, kSiteFinal);
         }
     } else if (warp >= 8) {
+        setmaxnreg_inc<152>();
         // =========================== dQ drain warpgroup ===========================
         const int row = (warp & 3) * 32 + lane;                 // query row inside the tile == TMEM lane
+        SNTL_TRACE_DECL(tn);
+        const bool tw = warp == 8 && lane == 0;
+        (void)tw;
         const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;
+        const bool elected = warp == 8 && lane == 0;
         bool ok = true;
         for (int i = 0; i < n_iter; ++i) {
             const int g = i / per_head, qt = qt_first + (i - g * per_head);
             const int bh = b * p.Hq + hk * group + g;
             float* tile = p.dq_accum + ((size_t)bh * p.n_qt + qt) * (size_t)(kT * D);
             ok = __all_sync(0xffffffffu, mbar_wait(&bars->dq_ready, (uint32_t)(i & 1), abort_flag, kSiteDQ));
+            SNTL_TRACE_EV(tw, 3, tn, 1);
             if (!ok) break;
             tc_fence_after();
+            // The whole dQ tile goes to registers first so that the TMEM columns are handed back to the MMA warp at
+            // once; pushing 64 KB (D = 128) through the reduction path (~30 bytes/clock per SM) is the slow part and
+            // overlaps the next step.  The data leave through the TMA engine, not the load/store unit: reductions
+            // issued as instructions queue up in the unit that also carries the compute warps' shared-memory and
+            // TMEM traffic and stall them.  32 columns at a time: registers -> staging buffer -> one asynchronous
+            // bulk add-reduction of 16 KB (contiguous in the accumulator thanks to its [d/4][row][4] order).  Two
+            // staging buffers alternate; the elected thread makes sure a buffer's previous reduction has finished
+            // reading it before it is overwritten.
+            uint32_t r[D];
+#pragma unroll
+            for (int c = 0; c < D / 32; ++c) tmem_ld32(tm_dP + lane_off + (uint32_t)(c * 32), r + c * 32);
+            tmem_ld_wait();
+            tc_fence_before();
+            mbar_arrive(&bars->dq_drained);
+            SNTL_TRACE_EV(tw, 3, tn, 2);
 #pragma unroll
             for (int c = 0; c < D / 32; ++c) {
-                uint32_t r[32];
-                tmem_ld32(tm_dP + lane_off + (uint32_t)(c * 32), r);
-                tmem_ld_wait();
-                if (c == D / 32 - 1) {   // every column has been read: the MMA warp may overwrite them
-                    tc_fence_before();
-                    mbar_arrive(&bars->dq_drained);
-                }
+                uint8_t* stage = sStage + (c & 1) * kStageBytes;
+                if (elected) bulk_wait_read<1>();
+                named_barrier_sync(1, 128);
 #pragma unroll
                 for (int v = 0; v < 8; ++v)
-                    red_add_v4(tile + ((size_t)(c * 8 + v) * kT + row) * 4, __uint_as_float(r[4 * v]), __uint_as_float(r[4 * v + 1]),
-                               __uint_as_float(r[4 * v + 2]), __uint_as_float(r[4 * v + 3]));
+                    *reinterpret_cast<uint4*>(stage + ((size_t)v * kT + row) * 16) =
+                        make_uint4(r[c * 32 + 4 * v], r[c * 32 + 4 * v + 1], r[c * 32 + 4 * v + 2], r[c * 32 + 4 * v + 3]);
+                fence_proxy_async_smem();
+                named_barrier_sync(1, 128);
+                if (elected) {
+                    bulk_reduce_add_f32(tile + (size_t)c * 32 * kT, stage, (uint32_t)kStageBytes);
+                    bulk_commit();
+                }
             }
+            SNTL_TRACE_EV(tw, 3, tn, 3);
         }
+        if (elected) bulk_wait_all();   // the reductions read shared memory and must land before the CTA retires
     } else {
+        setmaxnreg_inc<152>();
         // =========================== compute warpgroups ===========================
         const int wg = warp >> 2;                                // owns query columns [64*wg, 64*wg+64)
         const int row = (warp & 3) * 32 + lane;                  // key row inside the tile == TMEM lane
+        SNTL_TRACE_DECL(tn);
+        const bool tw = (warp & 3) == 0 && lane == 0;
+        (void)tw;
         const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;
         const uint32_t col0 = (uint32_t)(wg * 64);
         uint8_t* ds_row = sDs + wg * kChunkBytes + row * 128;    // this thread's 128-byte row of its 64-query chunk
@@ -278,12 +375,14 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
             // ---- P^T ----
             ok = __all_sync(0xffffffffu, mbar_wait(&bars->q_full[sq], (uint32_t)((i >> 1) & 1), abort_flag, kSiteQFull) &&
                                              mbar_wait(&bars->s_ready, ph, abort_flag, kSiteS));
+            SNTL_TRACE_EV(tw, 1 + wg, tn, 1);
             if (!ok) break;
             tc_fence_after();
             uint32_t s[64];
             tmem_ld32(tm_S + lane_off + col0, s);
             tmem_ld32(tm_S + lane_off + col0 + 32u, s + 32);
             tmem_ld_wait();
+            SNTL_TRACE_EV(tw, 1 + wg, tn, 2);
             const float4* lse4 = reinterpret_cast<const float4*>(sLse + sq * kT + col0);
             const bool diag = p.causal && (qt == kt);
             uint32_t pk[32];
@@ -304,17 +403,21 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
                 pk[2 * c] = pack_bf16(p0, p1);
                 pk[2 * c + 1] = pack_bf16(p2, p3);
             }
+            SNTL_TRACE_EV(tw, 1 + wg, tn, 3);
             tmem_st32(tm_S + lane_off + col0, pk);
             tmem_st_wait();
             tc_fence_before();
             mbar_arrive(&bars->p_ready);
+            SNTL_TRACE_EV(tw, 1 + wg, tn, 4);
             // ---- dS^T ----
             ok = __all_sync(0xffffffffu, mbar_wait(&bars->dp_ready, ph, abort_flag, kSiteDP));
+            SNTL_TRACE_EV(tw, 1 + wg, tn, 5);
             if (!ok) break;
             tc_fence_after();
             tmem_ld32(tm_dP + lane_off + col0, s);
             tmem_ld32(tm_dP + lane_off + col0 + 32u, s + 32);
             tmem_ld_wait();
+            SNTL_TRACE_EV(tw, 1 + wg, tn, 6);
             const float4* dl4 = reinterpret_cast<const float4*>(sDelta + sq * kT + col0);
 #pragma unroll
             for (int c = 0; c < 16; ++c) {
@@ -328,17 +431,18 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
                 pk[2 * c] = pack_bf16(d0, d1);
                 pk[2 * c + 1] = pack_bf16(d2, d3);
             }
-            tmem_st32(tm_dP + lane_off + col0, pk);
-            // the same values into shared memory, rows of 128 bytes with the 128-byte swizzle the MMA expects
+            // into shared memory, rows of 128 bytes with the 128-byte swizzle the MMA expects (both the dQ and the dK
+            // product read this tile)
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
                 uint4 w = make_uint4(pk[4 * j], pk[4 * j + 1], pk[4 * j + 2], pk[4 * j + 3]);
                 *reinterpret_cast<uint4*>(ds_row + ((j ^ (row & 7)) << 4)) = w;
             }
             fence_proxy_async_smem();
-            tmem_st_wait();
-            tc_fence_before();
+            SNTL_TRACE_EV(tw, 1 + wg, tn, 7);
+            tc_fence_before();   // orders this thread's TMEM loads of dP^T before the MMA that overwrites those columns
             mbar_arrive(&bars->ds_ready);
+            SNTL_TRACE_EV(tw, 1 + wg, tn, 8);
         }
         // ---- epilogue: dV (warpgroup 0) and dK (warpgroup 1) ----
         ok = __all_sync(0xffffffffu, ok && n_iter > 0 && mbar_wait(&bars->final_bar, 0, abort_flag, kSiteFinal));
@@ -490,7 +594,7 @@ cudaError_t launch_bwd(const TcArgs& a, cudaStream_t st)
     p.scale = s.scale;
     p.scale_log2 = s.scale * 1.4426950408889634f;
     constexpr int kDoStages = (D == 128) ? 1 : 2;
-    const size_t smem = (size_t)(128 * D * 2) * (4 + kDoStages) + 128 * 128 * 2 + 4 * 128 * 4 + sizeof(BwdBarriers) + 1024;
+    const size_t smem = (size_t)(128 * D * 2) * (4 + kDoStages) + 128 * 128 * 2 + 2 * (32 * 128 * 4) + 4 * 128 * 4 + sizeof(BwdBarriers);
     static bool configured = false;
     if (!configured) {
         if ((e = cudaFuncSetAttribute(attn_bwd_tc_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)) != cudaSuccess)
@@ -526,6 +630,18 @@ cudaError_t tc_backward(const TcArgs& a, cudaStream_t st)
 {
     return a.s.D == 64 ? launch_bwd<64>(a, st) : launch_bwd<128>(a, st);
 }
+
+#ifdef SNTL_TRACE
+// trace build only: choose the CTA that records and read back what the last launch recorded
+extern "C" int sntl_debug_trace_bwd(unsigned long long* out, int n_words, int set_cta)
+{
+    if (out && cudaMemcpyFromSymbol(out, ptx::g_trace, sizeof(unsigned long long) * n_words) != cudaSuccess) return 1;
+    static unsigned long long zeros[ptx::kTraceRoles * ptx::kTraceDepth];
+    if (cudaMemcpyToSymbol(ptx::g_trace, zeros, sizeof(zeros)) != cudaSuccess) return 2;
+    unsigned int c = (unsigned int)set_cta;
+    return cudaMemcpyToSymbol(ptx::g_trace_cta, &c, sizeof(c)) == cudaSuccess ? 0 : 3;
+}
+#endif
 
 cudaError_t read_and_clear_bwd_status(cudaStream_t st, uint32_t* word)
 {

@@ -35,7 +35,7 @@ namespace {
 
 constexpr int kM = 128;          // query rows per tile
 constexpr int kN = 128;          // keys per tile
-constexpr int kFwdThreads = 320; // 2 softmax warpgroups + MMA warp + TMA warp
+constexpr int kFwdThreads = 384; // 2 softmax warpgroups + 1 warpgroup holding the MMA warp and the TMA warp
 constexpr uint32_t kTmemCols = 512;
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
 
@@ -128,7 +128,11 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
     const uint32_t tmem_S[2] = {tmem + 0u, tmem + 128u};
     const uint32_t tmem_O[2] = {tmem + 256u, tmem + 384u};
 
-    if (warp == 9) {
+    // 384 threads start with 168 registers each; each role re-allocates inside its own branch
+    if (warp >= 10) {
+        setmaxnreg_dec<72>();   // idle warps of the last warpgroup
+    } else if (warp == 9) {
+        setmaxnreg_dec<72>();
         // =========================== TMA producer ===========================
         if (lane == 0) {
             int n_valid = (n_t[0] > 0) + (n_t[1] > 0);
@@ -150,26 +154,36 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
             }
         }
     } else if (warp == 8) {
+        setmaxnreg_dec<72>();
         // =========================== MMA issuer ===========================
         if (lane == 0) {
+            SNTL_TRACE_DECL(tn);
             constexpr uint32_t idesc_s = make_idesc(kM, kN, false, false);
             constexpr uint32_t idesc_pv = make_idesc(kM, D, false, true);
-            const uint32_t q_base = smem_u32(sQ), k_base = smem_u32(sK), v_base = smem_u32(sV);
+            // one descriptor per tile, advanced per k-step by a 64-bit add
+            const uint64_t dq0 = make_sdesc(smem_u32(sQ), 16, 1024), dq1 = sdesc_advance(dq0, kTileBytes);
+            const uint64_t dk0 = make_sdesc(smem_u32(sK), 16, 1024), dk1 = sdesc_advance(dk0, kTileBytes);
+            const uint64_t dv0 = make_sdesc(smem_u32(sV), kChunkBytes, 1024), dv1 = sdesc_advance(dv0, kTileBytes);
             auto issue_s = [&](int t, int st) {
+                uint64_t a = t ? dq1 : dq0, b = st ? dk1 : dk0;
+                asm volatile("" : "+l"(a), "+l"(b));   // keeps the advanced descriptors from being hoisted into registers
+                const uint32_t d = tmem_S[t];
+                mma_ss_c<false>(d, a, b, idesc_s);
 #pragma unroll
-                for (int ks = 0; ks < D / 16; ++ks) {
+                for (int ks = 1; ks < D / 16; ++ks) {
                     const uint32_t off = (uint32_t)((ks >> 2) * kChunkBytes + (ks & 3) * 32);
-                    mma_ss(tmem_S[t], make_sdesc(q_base + t * kTileBytes + off, 16, 1024),
-                           make_sdesc(k_base + st * kTileBytes + off, 16, 1024), idesc_s, ks > 0 ? 1u : 0u);
+                    mma_ss_c<true>(d, sdesc_advance(a, off), sdesc_advance(b, off), idesc_s);
                 }
                 tc_commit(&bars->s_ready[t]);
             };
             auto issue_pv = [&](int t, int st, bool accumulate) {
+                uint64_t b = st ? dv1 : dv0;
+                asm volatile("" : "+l"(b));
+                const uint32_t d = tmem_O[t], a = tmem_S[t];
+                if (accumulate) mma_ts_c<true>(d, a, b, idesc_pv);
+                else mma_ts_c<false>(d, a, b, idesc_pv);
 #pragma unroll
-                for (int ks = 0; ks < kN / 16; ++ks) {
-                    mma_ts(tmem_O[t], tmem_S[t] + (uint32_t)(ks * 8), make_sdesc(v_base + st * kTileBytes + ks * 2048, kChunkBytes, 1024),
-                           idesc_pv, (accumulate || ks > 0) ? 1u : 0u);
-                }
+                for (int ks = 1; ks < kN / 16; ++ks) mma_ts_c<true>(d, a + (uint32_t)(ks * 8), sdesc_advance(b, ks * 2048), idesc_pv);
                 tc_commit(&bars->o_ready[t]);
             };
             bool ok = n_max > 0 && mbar_wait(&bars->q_full, 0, abort_flag, kSiteQ) &&
@@ -188,15 +202,20 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
                 for (int t = 0; t < 2 && ok; ++t) {
                     if (j >= n_t[t]) continue;
                     if (!(ok = mbar_wait(&bars->p_ready[t], (uint32_t)(j & 1), abort_flag, kSitePReady))) break;
+                    SNTL_TRACE_EV(true, 0, tn, 10 + t);
                     tc_fence_after();
                     issue_pv(t, st, j > 0);
+                    SNTL_TRACE_EV(true, 0, tn, 20 + t);
                     if (j + 1 < n_t[t]) {
                         if (!next_k_ready) {
+                            SNTL_TRACE_EV(true, 0, tn, 40);
                             if (!(ok = mbar_wait(&bars->k_full[nst], nph, abort_flag, kSiteKFull))) break;
                             tc_fence_after();
+                            SNTL_TRACE_EV(true, 0, tn, 41);
                             next_k_ready = true;
                         }
                         issue_s(t, nst);
+                        SNTL_TRACE_EV(true, 0, tn, 30 + t);
                     }
                 }
                 if (!ok) break;
@@ -209,20 +228,26 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
         }
     } else {
         // =========================== softmax + epilogue warpgroups ===========================
+        setmaxnreg_inc<216>();
         const int t = warp >> 2;                       // tile 0 or 1
         const int row = (warp & 3) * 32 + lane;        // row inside the tile == TMEM lane
         const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;
         const int grow = q0 + t * kM + row;            // global query index
         const int n_mine = n_t[t];
+        SNTL_TRACE_DECL(tn);
+        const bool tw = (warp & 3) == 0 && lane == 0;
+        (void)tw;
         float m_ref = -INFINITY, l = 0.0f;
         bool ok = true;
         for (int j = 0; j < n_mine; ++j) {
             if (!(ok = __all_sync(0xffffffffu, mbar_wait(&bars->s_ready[t], (uint32_t)(j & 1), abort_flag, kSiteSReady)))) break;
+            SNTL_TRACE_EV(tw, 1 + t, tn, 1);
             tc_fence_after();
             uint32_t s[128];
 #pragma unroll
             for (int c = 0; c < 4; ++c) tmem_ld32(tmem_S[t] + lane_off + (uint32_t)(c * 32), s + c * 32);
             tmem_ld_wait();
+            SNTL_TRACE_EV(tw, 1 + t, tn, 2);
             // number of visible keys of this row inside this tile
             int limit = (p.causal ? min(p.Skv, grow + 1) : p.Skv) - j * kN;
             if (limit < kN) {
@@ -230,10 +255,15 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
                 for (int c = 0; c < kN; ++c)
                     if (c >= limit) s[c] = 0xff800000u;  // -inf
             }
-            float mx = -INFINITY;
+            // row max with eight independent chains (a single 128-long dependent chain costs ~600 cycles)
+            float mx8[8];
 #pragma unroll
-            for (int c = 0; c < kN; ++c) mx = fmaxf(mx, __uint_as_float(s[c]));
+            for (int c = 0; c < 8; ++c) mx8[c] = __uint_as_float(s[c]);
+#pragma unroll
+            for (int c = 8; c < kN; ++c) mx8[c & 7] = fmaxf(mx8[c & 7], __uint_as_float(s[c]));
+            const float mx = fmaxf(fmaxf(fmaxf(mx8[0], mx8[1]), fmaxf(mx8[2], mx8[3])), fmaxf(fmaxf(mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7])));
             const float m_new = fmaxf(m_ref, mx * p.scale_log2);
+            SNTL_TRACE_EV(tw, 1 + t, tn, 3);
             const bool need = (m_new - m_ref) > kRescaleThreshold;   // false when both are -inf (NaN compare)
             if (j == 0) {
                 m_ref = m_new;
@@ -254,20 +284,30 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
                 }
                 tmem_st_wait();
             }
+            SNTL_TRACE_EV(tw, 1 + t, tn, 4);
             const float neg_m = (m_ref == -INFINITY) ? 0.0f : -m_ref;
-            uint32_t pk[64];
+            // exp2, row sum (four independent partial sums) and bf16 packing, 64 columns at a time so the packed half
+            // can be stored while the other half is computed
+            float l4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            const float2 sc2 = make_float2(p.scale_log2, p.scale_log2), nm2 = make_float2(neg_m, neg_m);
 #pragma unroll
-            for (int c = 0; c < 64; ++c) {
-                const float p0 = ex2(fmaf(__uint_as_float(s[2 * c]), p.scale_log2, neg_m));
-                const float p1 = ex2(fmaf(__uint_as_float(s[2 * c + 1]), p.scale_log2, neg_m));
-                l += p0 + p1;
-                pk[c] = pack_bf16(p0, p1);
+            for (int h = 0; h < 2; ++h) {
+                uint32_t pk[32];
+#pragma unroll
+                for (int c = 0; c < 32; ++c) {
+                    const float2 x = ffma2(make_float2(__uint_as_float(s[h * 64 + 2 * c]), __uint_as_float(s[h * 64 + 2 * c + 1])), sc2, nm2);
+                    const float p0 = ex2(x.x), p1 = ex2(x.y);
+                    l4[c & 3] += p0 + p1;
+                    pk[c] = pack_bf16(p0, p1);
+                }
+                tmem_st32(tmem_S[t] + lane_off + (uint32_t)(h * 32), pk);
             }
-            tmem_st32(tmem_S[t] + lane_off, pk);
-            tmem_st32(tmem_S[t] + lane_off + 32u, pk + 32);
+            l += (l4[0] + l4[1]) + (l4[2] + l4[3]);
+            SNTL_TRACE_EV(tw, 1 + t, tn, 5);
             tmem_st_wait();
             tc_fence_before();
             mbar_arrive(&bars->p_ready[t]);
+            SNTL_TRACE_EV(tw, 1 + t, tn, 6);
         }
         if (__all_sync(0xffffffffu, ok && n_mine > 0 && mbar_wait(&bars->o_ready[t], (uint32_t)((n_mine - 1) & 1), abort_flag, kSiteOReady))) {
             tc_fence_after();
@@ -383,6 +423,18 @@ cudaError_t tc_forward(const TcArgs& a, cudaStream_t st)
 {
     return a.s.D == 64 ? launch_fwd<64>(a, st) : launch_fwd<128>(a, st);
 }
+
+#ifdef SNTL_TRACE
+// trace build only: choose the CTA that records and read back what the last launch recorded
+extern "C" int sntl_debug_trace_fwd(unsigned long long* out, int n_words, int set_cta)
+{
+    if (out && cudaMemcpyFromSymbol(out, ptx::g_trace, sizeof(unsigned long long) * n_words) != cudaSuccess) return 1;
+    static unsigned long long zeros[ptx::kTraceRoles * ptx::kTraceDepth];
+    if (cudaMemcpyToSymbol(ptx::g_trace, zeros, sizeof(zeros)) != cudaSuccess) return 2;
+    unsigned int c = (unsigned int)set_cta;
+    return cudaMemcpyToSymbol(ptx::g_trace_cta, &c, sizeof(c)) == cudaSuccess ? 0 : 3;
+}
+#endif
 
 cudaError_t read_and_clear_fwd_status(cudaStream_t st, uint32_t* word)
 {

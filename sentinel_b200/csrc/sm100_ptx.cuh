@@ -17,6 +17,23 @@ namespace ptx {
 // ---------------------------------------------------------------------------------------------------
 static __device__ unsigned int g_device_status;  // one copy per translation unit; each exposes its own reader
 
+// Optional phase tracing (compile with -DSNTL_TRACE): one chosen CTA records (SM clock << 8 | event) per role, so
+// the length of each pipeline phase and each hand-off can be read back.  Compiles to nothing otherwise.
+#ifdef SNTL_TRACE
+constexpr int kTraceRoles = 8, kTraceDepth = 2048;
+static __device__ unsigned long long g_trace[kTraceRoles * kTraceDepth];
+static __device__ unsigned int g_trace_cta;
+__device__ __forceinline__ void trace_event(bool who, int role, int& n, uint32_t ev)
+{
+    if (who && blockIdx.x == g_trace_cta && n < kTraceDepth) g_trace[role * kTraceDepth + n++] = ((unsigned long long)clock64() << 8) | ev;
+}
+#define SNTL_TRACE_DECL(n) int n = 0
+#define SNTL_TRACE_EV(who, role, n, ev) ::sntl::ptx::trace_event(who, role, n, ev)
+#else
+#define SNTL_TRACE_DECL(n)
+#define SNTL_TRACE_EV(who, role, n, ev)
+#endif
+
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
 __device__ __forceinline__ uint64_t global_timer_ns()
@@ -110,6 +127,56 @@ __device__ __forceinline__ void red_add_v4(float* gptr, float a, float b, float 
     asm volatile("red.global.add.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(gptr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
 }
 
+// asynchronous fp32 add-reduction of a contiguous shared-memory block into global memory (both 16-byte aligned,
+// bytes a multiple of 16); tracked by bulk groups
+__device__ __forceinline__ void bulk_reduce_add_f32(float* gmem_dst, const void* smem_src, uint32_t bytes)
+{
+    asm volatile("cp.reduce.async.bulk.global.shared::cta.bulk_group.add.f32 [%0], [%1], %2;" ::"l"(gmem_dst), "r"(smem_u32(smem_src)),
+                 "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// returns once at most N of this thread's bulk groups are still reading their shared-memory source
+template <int N> __device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
+// barrier among a subset of the CTA's warps (id 1..15; `threads` a multiple of 32)
+__device__ __forceinline__ void named_barrier_sync(uint32_t id, uint32_t threads)
+{
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+
+// per-warpgroup register re-allocation (all four warps of the warpgroup must execute it)
+template <int N> __device__ __forceinline__ void setmaxnreg_inc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N)); }
+template <int N> __device__ __forceinline__ void setmaxnreg_dec() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N)); }
+
+// packed fp32x2 arithmetic (two independent fp32 lanes in one 64-bit register)
+__device__ __forceinline__ float2 ffma2(float2 a, float2 b, float2 c)
+{
+    float2 d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;"
+        : "=l"(reinterpret_cast<unsigned long long&>(d))
+        : "l"(reinterpret_cast<unsigned long long&>(a)), "l"(reinterpret_cast<unsigned long long&>(b)),
+          "l"(reinterpret_cast<unsigned long long&>(c)));
+    return d;
+}
+__device__ __forceinline__ float2 fmul2(float2 a, float2 b)
+{
+    float2 d;
+    asm("mul.rn.f32x2 %0, %1, %2;"
+        : "=l"(reinterpret_cast<unsigned long long&>(d))
+        : "l"(reinterpret_cast<unsigned long long&>(a)), "l"(reinterpret_cast<unsigned long long&>(b)));
+    return d;
+}
+__device__ __forceinline__ float2 fadd2(float2 a, float2 b)
+{
+    float2 d;
+    asm("add.rn.f32x2 %0, %1, %2;"
+        : "=l"(reinterpret_cast<unsigned long long&>(d))
+        : "l"(reinterpret_cast<unsigned long long&>(a)), "l"(reinterpret_cast<unsigned long long&>(b)));
+    return d;
+}
+
 // ---------------------------------------------------------------------------------------------------
 // tcgen05: TMEM allocation, fences, commit
 // ---------------------------------------------------------------------------------------------------
@@ -181,6 +248,36 @@ __device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_
         "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}" ::"r"(d_tmem),
         "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
         : "memory");
+}
+
+// Lean issue forms.  The single issuing thread shares its scheduler with busy softmax warps, so every instruction
+// it spends per MMA shows up as tensor-pipe idle time: descriptors are built once per tile and advanced with one
+// 64-bit add (the start-address field is in 16-byte units and never carries out of its 14 bits for addresses below
+// 256 KB), and the accumulate flag is a compile-time constant wherever the k-step is known.
+__device__ __forceinline__ uint64_t sdesc_advance(uint64_t desc, uint32_t bytes) { return desc + (uint64_t)(bytes >> 4); }
+template <bool kAccumulate>
+__device__ __forceinline__ void mma_ss_c(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc)
+{
+    if (kAccumulate)
+        asm volatile("{\n\t.reg .pred p;\n\tsetp.eq.u32 p, 0, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+                     "l"(a_desc), "l"(b_desc), "r"(idesc)
+                     : "memory");
+    else
+        asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.u32 p, 0, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+                     "l"(a_desc), "l"(b_desc), "r"(idesc)
+                     : "memory");
+}
+template <bool kAccumulate>
+__device__ __forceinline__ void mma_ts_c(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc)
+{
+    if (kAccumulate)
+        asm volatile("{\n\t.reg .pred p;\n\tsetp.eq.u32 p, 0, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}" ::"r"(d_tmem),
+                     "r"(a_tmem), "l"(b_desc), "r"(idesc)
+                     : "memory");
+    else
+        asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.u32 p, 0, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}" ::"r"(d_tmem),
+                     "r"(a_tmem), "l"(b_desc), "r"(idesc)
+                     : "memory");
 }
 
 // ---------------------------------------------------------------------------------------------------
