@@ -134,6 +134,10 @@ size_t sntl_attn_static_scratch_capacity(void);
 int sntl_attn_merge(int32_t acc_dtype, int32_t part_dtype, int64_t rows, int32_t head_dim, void* o_acc, float* lse_acc,
                     const void* o_part, const float* lse_part, void* stream);
 
+/* acc[i] += part[i] for `count` elements, acc fp32, part bf16 or fp32: the ring schedule's running sums of the
+ * dQ / dK / dV partials of successive key blocks.  Asynchronous on `stream`.  No counterpart in the reference. */
+int sntl_attn_accumulate(int32_t part_dtype, int64_t count, float* acc, const void* part, void* stream);
+
 /* Name of the kernel family the most recent sntl_attn_fwd / sntl_attn_bwd call on this thread dispatched to
  * ("simt_f32", "tcgen05", ...), so a test can assert the path taken, like the reference's
  * usedFlashAttention flag (CudaCausalSelfAttention.hpp:36). */

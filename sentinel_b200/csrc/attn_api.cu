@@ -300,6 +300,13 @@ int sntl_attn_merge(int32_t acc_dtype, int32_t part_dtype, int64_t rows, int32_t
     return cuda_status(merge_partials(acc_dtype, part_dtype, rows, head_dim, o_acc, lse_acc, o_part, lse_part, (cudaStream_t)stream));
 }
 
+int sntl_attn_accumulate(int32_t part_dtype, int64_t count, float* acc, const void* part, void* stream)
+{
+    if (count < 0 || !acc || !part) return SNTL_ERR_BAD_ARGUMENT;
+    if (part_dtype != SNTL_DTYPE_BF16 && part_dtype != SNTL_DTYPE_F32) return SNTL_ERR_BAD_ARGUMENT;
+    return cuda_status(accumulate_f32(part_dtype, acc, part, (size_t)count, (cudaStream_t)stream));
+}
+
 int sntl_attn_poll_device_status(void* stream, uint32_t* detail)
 {
     uint32_t word = 0, word_bwd = 0;

@@ -65,6 +65,7 @@ cudaError_t lse_bhs_to_sentinel(const float* src, float* dst, int B, int H, int 
                                 cudaStream_t st);
 cudaError_t lse_sentinel_to_bhs(const float* src, float* dst, int B, int H, int S, int stride_columns, int column_start,
                                 cudaStream_t st);
+cudaError_t accumulate_f32(int part_dtype, float* acc, const void* part, size_t n, cudaStream_t st);
 cudaError_t merge_partials(int acc_dtype, int part_dtype, long long rows, int D, void* o_acc, float* lse_acc,
                            const void* o_part, const float* lse_part, cudaStream_t st);
 

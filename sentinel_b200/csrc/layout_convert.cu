@@ -98,6 +98,13 @@ __global__ void merge_kernel(long long rows, int D, T* __restrict__ o_acc, float
     if (lane == 0) lse_acc[row] = m + logf(wa + wb);
 }
 
+template <typename P>
+__global__ void accumulate_kernel(float* __restrict__ acc, const P* __restrict__ part, size_t n)
+{
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+        acc[i] += ldf(part + i);
+}
+
 inline int blocks_for(size_t n, int threads)
 {
     size_t b = (n + threads - 1) / threads;
@@ -150,6 +157,17 @@ cudaError_t lse_sentinel_to_bhs(const float* src, float* dst, int B, int H, int 
                                 cudaStream_t st)
 {
     lse_reindex_kernel<<<blocks_for((size_t)B * H * S, 256), 256, 0, st>>>(src, dst, B, H, S, stride_columns, column_start, 1);
+    count_launch();
+    return cudaGetLastError();
+}
+
+cudaError_t accumulate_f32(int part_dtype, float* acc, const void* part, size_t n, cudaStream_t st)
+{
+    if (n == 0) return cudaSuccess;
+    if (part_dtype == SNTL_DTYPE_BF16)
+        accumulate_kernel<<<blocks_for(n, 256), 256, 0, st>>>(acc, (const __nv_bfloat16*)part, n);
+    else
+        accumulate_kernel<<<blocks_for(n, 256), 256, 0, st>>>(acc, (const float*)part, n);
     count_launch();
     return cudaGetLastError();
 }

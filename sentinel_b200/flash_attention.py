@@ -129,6 +129,18 @@ def merge_partials(o_acc, lse_acc, o_part, lse_part):
     return o_acc, lse_acc
 
 
+def accumulate(acc, part):
+    """acc (fp32) += part (bf16 or fp32), in place, on the library's kernel."""
+    lib = _lib.load()
+    _require(acc, "acc")
+    _require(part, "part")
+    if acc.dtype != torch.float32 or acc.numel() != part.numel():
+        raise ValueError("acc must be fp32 and match part in size")
+    rc = lib.sntl_attn_accumulate(_dtype_code(part), acc.numel(), acc.data_ptr(), part.data_ptr(), _stream_ptr())
+    _lib.check(rc, "sntl_attn_accumulate")
+    return acc
+
+
 def last_path() -> str:
     return _lib.load().sntl_attn_last_path().decode()
 

@@ -95,3 +95,12 @@ def make_inputs(w: Workload, *, batch: int | None = None, q_heads: int | None = 
     if w.dtype == "bf16":
         q, k, v, do = (t.to(torch.bfloat16) for t in (q, k, v, do))
     return q, k, v, do
+
+
+def shard_units(batch: int, kv_heads: int, rank: int, world: int):
+    """The (batch element, KV head) units rank ``rank`` of ``world`` owns: a contiguous, balanced slice of the
+    ``batch * kv_heads`` independent units.  A KV group is never split (that would need a dK/dV reduction)."""
+    units = [(b, hk) for b in range(batch) for hk in range(kv_heads)]
+    per, extra = divmod(len(units), world)
+    start = rank * per + min(rank, extra)
+    return units[start:start + per + (1 if rank < extra else 0)]
