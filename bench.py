@@ -182,19 +182,39 @@ def main():
         dist.init_process_group("nccl", device_id=dev)
     sb._lib.load()
 
-    # per-rank batch: the workload's own batch; each rank draws its own shard (different seed offset)
-    q, k, v, do = (t.pin_memory() for t in make_inputs(w, seed_offset=rank))
+    ring = None
+    if w.seq_shards > 1:
+        # sequence-sharded workload: every rank holds seq/seq_shards tokens; with N ranks the sequence is N shards long
+        # (the full 131072 tokens at N = 8) and K/V chunks travel round the ring over NCCL
+        import dataclasses
+        from sentinel_b200.ring import GpuBackend, RingAttention
+        shard = w.seq // w.seq_shards
+        ring = RingAttention(GpuBackend()) if world > 1 else None
+        w_local = dataclasses.replace(w, seq=shard, seq_shards=1)
+        w = dataclasses.replace(w, seq=shard * world)
+        q, k, v, do = (t.pin_memory() for t in make_inputs(w_local, seed_offset=rank))
+    else:
+        # per-rank batch: the workload's own batch; each rank draws its own shard (different seed offset)
+        q, k, v, do = (t.pin_memory() for t in make_inputs(w, seed_offset=rank))
     qd, kd, vd, dod = (t.to(dev, non_blocking=True) for t in (q, k, v, do))
     o = torch.empty_like(qd)
     lse = torch.empty(qd.shape[:3], dtype=torch.float32, device=dev)
     dq, dk, dv = torch.empty_like(qd), torch.empty_like(kd), torch.empty_like(vd)
     torch.cuda.synchronize()
 
+    state = {}
+
     def fwd():
-        sb.attention_forward(qd, kd, vd, out=o, lse=lse)
+        if ring is not None:
+            state["o"], state["lse"] = ring.forward(qd, kd, vd)
+        else:
+            sb.attention_forward(qd, kd, vd, out=o, lse=lse)
 
     def bwd():
-        sb.attention_backward(qd, kd, vd, o, lse, dod, dq=dq, dk=dk, dv=dv)
+        if ring is not None:
+            ring.backward(qd, kd, vd, state["o"], state["lse"], dod)
+        else:
+            sb.attention_backward(qd, kd, vd, o, lse, dod, dq=dq, dk=dk, dv=dv)
 
     def step():
         fwd()
@@ -233,12 +253,19 @@ def main():
         fwd_ms = timed(fwd, args.steps) / args.steps
         bwd_ms = timed(bwd, args.steps) / args.steps
     ms_per_step = total_ms / args.steps
-    flops_rank = w.flops
+    flops_rank = w.flops / world if ring is not None else w.flops     # the ring workload's FLOPs are for the whole sequence
     value = flops_rank * world / (ms_per_step * 1e-3) / 1e12
 
     # end to end through the host-buffer call: H2D of Q,K,V,dO, forward+backward, D2H of O,LSE,dQ,dK,dV
     def e2e_step():
-        sb.attention_forward_backward_host(q, k, v, do, device=dev)
+        if ring is not None:
+            sh = [t.to(dev, non_blocking=True) for t in (q, k, v, do)]
+            o_, lse_ = ring.forward(sh[0], sh[1], sh[2])
+            grads = ring.backward(sh[0], sh[1], sh[2], o_, lse_, sh[3])
+            outs = [t.to("cpu", non_blocking=True) for t in (o_, lse_) + tuple(grads)]
+            torch.cuda.current_stream().synchronize()
+        else:
+            sb.attention_forward_backward_host(q, k, v, do, device=dev)
 
     if args.skip_e2e:
         e2e_ms = float("nan")
@@ -278,7 +305,8 @@ def main():
                 "dtype": "bf16" if w.dtype == "bf16" else "f32", "data": "synthetic",
                 "config": {"workload": w.name, "B_per_gpu": w.batch, "global_batch": w.batch * world, "Hq": w.q_heads,
                            "Hkv": w.kv_heads, "S": w.seq, "D": w.head_dim, "causal": True,
-                           "parallelism": f"batch x KV-group sharding over {world} GPU(s), no communication",
+                           "parallelism": (f"sequence split into {world} contiguous shards, zigzag-balanced ring of K/V chunks over NCCL"
+                                           if ring is not None else f"batch x KV-group sharding over {world} GPU(s), no communication"),
                            "l2": "per-step working set (Q,K,V,O,dO,dQ,dK,dV,dQ-accumulator) > 0.8 GB, larger than the 126 MB L2",
                            "kernel_path": sb.last_path()},
                 "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
