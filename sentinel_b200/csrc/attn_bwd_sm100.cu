@@ -50,8 +50,8 @@ enum BwdSite : uint32_t {
 
 struct BwdParams {
     __nv_bfloat16 *dk, *dv;
-    const float* lse2;     // [B][Hq][Sq_pad]  LSE * log2(e), +inf on padded rows
-    const float* delta;    // [B][Hq][Sq_pad]
+    const float* lse2;     // [B][Hq][Sq_pad]  -LSE * log2(e), -inf on padded rows
+    const float* delta;    // [B][Hq][Sq_pad]  -rowsum(dO o O)
     float* dq_accum;       // [B*Hq][n_qt][D/4][128][4]
     int B, Hq, Hkv, Sq, Skv, Sq_pad;
     int causal;
@@ -260,9 +260,11 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
                     const uint32_t ph = (uint32_t)(i & 1);
                     const int sq = i & 1, sd = i % kDoStages;
                     if (!(ok = mbar_wait(&bars->ds_ready, ph, abort_flag, kSiteDS))) break;
-                    if (!(ok = mbar_wait(&bars->q_full[sq], (uint32_t)((i >> 1) & 1), abort_flag, kSiteQFull))) break;  // Q_i, see above
                     SNTL_TRACE_EV(true, 4, tn, 3);
                     tc_fence_after();
+                    // this warp's share of releasing dO_i is dP^T_i, which retired before dS_i could be computed: release it
+                    // now so that (with a single dO stage) the load of dO_{i+1} is not waiting behind this step's MMAs
+                    tc_commit(&bars->do_empty[sd]);
                     // dQ first: it gates the drain and with it the next dP^T; dK only has to finish before the dS tile
                     // is rewritten, which the in-order issue of this thread already guarantees
                     {
@@ -276,7 +278,9 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
                     tc_commit(&bars->dq_ready);
                     SNTL_TRACE_EV(true, 4, tn, 4);
                     // dK += dS^T Q with dS^T read from its shared-memory tile as a K-major A operand (rows = keys, the 64
-                    // contiguous elements run along the queries)
+                    // contiguous elements run along the queries).  It is issued before the next dP^T, so by the time the
+                    // compute warps see that dP^T and rewrite the dS tile this product has read it (one thread's MMAs run
+                    // in order).  Q_i is ready: ds_ready implies its load was seen.
                     {
                         uint64_t a = dDs_k, bq = sdesc_advance(dQ_mn0, sq * kTileBytes);
                         asm volatile("" : "+l"(a), "+l"(bq));
@@ -287,7 +291,6 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
                             mma_ss_c<true>(tm_dK, sdesc_advance(a, (ks >> 2) * kChunkBytes + (ks & 3) * 32), sdesc_advance(bq, ks * 2048), idesc_kv);
                     }
                     tc_commit(&bars->q_empty[sq]);    // this warp's share: dK_i
-                    tc_commit(&bars->do_empty[sd]);   // this warp's share: dP^T_i (issued one step earlier)
                     if (i + 1 < n_iter) {
                         const int nd = (i + 1) % kDoStages;
                         if (!(ok = mbar_wait(&bars->dq_drained, ph, abort_flag, kSiteDrained))) break;
@@ -386,13 +389,13 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
             const float4* lse4 = reinterpret_cast<const float4*>(sLse + sq * kT + col0);
             const bool diag = p.causal && (qt == kt);
             uint32_t pk[32];
+            const float2 sc2 = make_float2(p.scale_log2, p.scale_log2);
 #pragma unroll
             for (int c = 0; c < 16; ++c) {
-                const float4 l = lse4[c];
-                float p0 = ex2(fmaf(__uint_as_float(s[4 * c + 0]), p.scale_log2, -l.x));
-                float p1 = ex2(fmaf(__uint_as_float(s[4 * c + 1]), p.scale_log2, -l.y));
-                float p2 = ex2(fmaf(__uint_as_float(s[4 * c + 2]), p.scale_log2, -l.z));
-                float p3 = ex2(fmaf(__uint_as_float(s[4 * c + 3]), p.scale_log2, -l.w));
+                const float4 l = lse4[c];   // holds -LSE*log2(e): x = s*scale*log2(e) - LSE*log2(e) in one packed FMA per pair
+                const float2 x01 = ffma2(make_float2(__uint_as_float(s[4 * c + 0]), __uint_as_float(s[4 * c + 1])), sc2, make_float2(l.x, l.y));
+                const float2 x23 = ffma2(make_float2(__uint_as_float(s[4 * c + 2]), __uint_as_float(s[4 * c + 3])), sc2, make_float2(l.z, l.w));
+                float p0 = ex2(x01.x), p1 = ex2(x01.y), p2 = ex2(x23.x), p3 = ex2(x23.y);
                 if (diag) {   // key (row) > query (column) is masked
                     const int q = (int)col0 + 4 * c;
                     if (row > q + 0) p0 = 0.0f;
@@ -421,15 +424,13 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
             const float4* dl4 = reinterpret_cast<const float4*>(sDelta + sq * kT + col0);
 #pragma unroll
             for (int c = 0; c < 16; ++c) {
-                const float4 dl = dl4[c];
-                const float p0 = __uint_as_float(pk[2 * c] << 16), p1 = __uint_as_float(pk[2 * c] & 0xffff0000u);
-                const float p2 = __uint_as_float(pk[2 * c + 1] << 16), p3 = __uint_as_float(pk[2 * c + 1] & 0xffff0000u);
-                const float d0 = p0 * (__uint_as_float(s[4 * c + 0]) - dl.x);
-                const float d1 = p1 * (__uint_as_float(s[4 * c + 1]) - dl.y);
-                const float d2 = p2 * (__uint_as_float(s[4 * c + 2]) - dl.z);
-                const float d3 = p3 * (__uint_as_float(s[4 * c + 3]) - dl.w);
-                pk[2 * c] = pack_bf16(d0, d1);
-                pk[2 * c + 1] = pack_bf16(d2, d3);
+                const float4 dl = dl4[c];   // holds -delta
+                const float2 pa = make_float2(__uint_as_float(pk[2 * c] << 16), __uint_as_float(pk[2 * c] & 0xffff0000u));
+                const float2 pb = make_float2(__uint_as_float(pk[2 * c + 1] << 16), __uint_as_float(pk[2 * c + 1] & 0xffff0000u));
+                const float2 da = fmul2(pa, fadd2(make_float2(__uint_as_float(s[4 * c + 0]), __uint_as_float(s[4 * c + 1])), make_float2(dl.x, dl.y)));
+                const float2 db = fmul2(pb, fadd2(make_float2(__uint_as_float(s[4 * c + 2]), __uint_as_float(s[4 * c + 3])), make_float2(dl.z, dl.w)));
+                pk[2 * c] = pack_bf16(da.x, da.y);
+                pk[2 * c + 1] = pack_bf16(db.x, db.y);
             }
             // into shared memory, rows of 128 bytes with the 128-byte swizzle the MMA expects (both the dQ and the dK
             // product read this tile)
@@ -492,8 +493,9 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
     }
 }
 
-// delta = rowsum(dO o O), lse2 = LSE * log2(e) (+inf for padded rows and for rows without visible keys), and the
-// dQ accumulator zeroed.  One warp per (b, h, padded row).
+// -delta = -rowsum(dO o O), lse2 = -LSE * log2(e) (-inf for padded rows and for rows without visible keys, so that
+// they produce P = 0; both are stored negated so the main kernel can use them as FMA/ADD addends), and the dQ
+// accumulator zeroed.  One warp per (b, h, padded row).
 template <int D>
 __global__ void bwd_pre_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ dout,
                                const float* __restrict__ lse, float* __restrict__ lse2, float* __restrict__ delta,
@@ -508,7 +510,7 @@ __global__ void bwd_pre_kernel(const __nv_bfloat16* __restrict__ o, const __nv_b
     float4* z = reinterpret_cast<float4*>(dq_accum + r * D);
     for (int i = lane; i < D / 4; i += 32) z[i] = make_float4(0.f, 0.f, 0.f, 0.f);
     if (s >= Sq) {
-        if (lane == 0) { lse2[r] = INFINITY; delta[r] = 0.0f; }
+        if (lane == 0) { lse2[r] = -INFINITY; delta[r] = 0.0f; }
         return;
     }
     const size_t off = ((size_t)bh * Sq + s) * D;
@@ -523,8 +525,8 @@ __global__ void bwd_pre_kernel(const __nv_bfloat16* __restrict__ o, const __nv_b
     for (int m = 16; m > 0; m >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, m);
     if (lane == 0) {
         const float l = lse[(size_t)bh * Sq + s];
-        lse2[r] = (l == -INFINITY) ? INFINITY : l * 1.4426950408889634f;
-        delta[r] = acc;
+        lse2[r] = (l == -INFINITY) ? -INFINITY : -l * 1.4426950408889634f;
+        delta[r] = -acc;
     }
 }
 
