@@ -46,7 +46,7 @@ def load_peaks():
 class ClockSampler:
     """Samples SM clock and throttle reasons of one GPU through NVML while the timed region runs (read-only)."""
 
-    def __init__(self, index: int, period_s: float = 0.1):
+    def __init__(self, index: int, period_s: float = 0.005):
         self.index, self.period, self.samples, self.reasons, self.max_mhz = index, period_s, [], set(), None
         self._stop = threading.Event()
         self._thread = None

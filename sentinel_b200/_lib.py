@@ -6,7 +6,7 @@ import ctypes as C
 import os
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(HERE, "lib", "libsntl_attn.so")
+LIB_PATH = os.environ.get("SNTL_ATTN_LIB") or os.path.join(HERE, "lib", "libsntl_attn.so")   # env: another build of the same ABI
 
 OK, ERR_BAD_ARGUMENT, ERR_UNSUPPORTED, ERR_WORKSPACE, ERR_CUDA, ERR_NO_DEVICE, ERR_DEVICE_TIMEOUT = range(7)
 DTYPE_BF16, DTYPE_F32 = 0, 1
