@@ -29,6 +29,9 @@ sys.path.insert(0, ROOT)
 METRIC = "causal attention fwd+bwd TFLOP/s (causal-adjusted 7*B*Hq*S^2*D), aggregate over GPUs"
 UNIT = "TFLOP/s"
 FALLBACK_PEAKS = {"bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "hbm_gbs": 6650.0}
+# DRAM bytes (read + write) of one launch of the dominant kernel per batch element, from the ncu capture summarised in
+# profiles/attn_bwd_tc_kernel_gqa7b_d128.md (captured at batch 1; traffic grows in proportion to the batch)
+NCU_DRAM_BYTES_PER_BATCH = {"gqa7b_d128": 721.2e6 + 522.3e6}
 
 
 def load_peaks():
@@ -287,7 +290,7 @@ def main():
     roofline = {"bound": "tensor", "kernel": "attention backward (delta pass + dK/dV/dQ kernel + dQ convert, timed as one call)",
                 "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
                 "peak_source": f"{peaks['_source']} bf16_tflops_sustained (kernel timed inside a seconds-long loop)",
-                "traffic": None,
+                "traffic": (NCU_DRAM_BYTES_PER_BATCH[w.name] * w.batch if w.name in NCU_DRAM_BYTES_PER_BATCH and ring is None else None),
                 "fwd": {"achieved": flops_rank * 2.0 / 7.0 / (fwd_ms * 1e-3) / 1e12, "ms": fwd_ms},
                 "bwd_ms": bwd_ms,
                 "fwd_bwd_frac_of_burst_peak": flops_rank / (ms_per_step * 1e-3) / 1e12 / float(peaks.get("bf16_tflops", 1590.0))}
@@ -303,7 +306,7 @@ def main():
         line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
                 "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
                 "dtype": "bf16" if w.dtype == "bf16" else "f32", "data": "synthetic",
-                "config": {"workload": w.name, "B_per_gpu": w.batch, "global_batch": w.batch * world, "Hq": w.q_heads,
+                "config": {"workload": w.name, "B_per_gpu": w.batch, "global_batch": (w.batch if ring is not None else w.batch * world), "Hq": w.q_heads,
                            "Hkv": w.kv_heads, "S": w.seq, "D": w.head_dim, "causal": True,
                            "parallelism": (f"sequence split into {world} contiguous shards, zigzag-balanced ring of K/V chunks over NCCL"
                                            if ring is not None else f"batch x KV-group sharding over {world} GPU(s), no communication"),
