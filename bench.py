@@ -132,6 +132,20 @@ def cpu_reference_sample(workload, steps: int, warmup: int):
                       f"{len(times)} timed passes of {mean:.3f} s", "ms_per_step": mean * 1e3}
 
 
+def reference_cuda_sample(workload, q, k, v, do):
+    """The reference's own CUDA flash kernels (oracle/_ref, rebuilt for sm_100a) on the same tensors, where they can run."""
+    from oracle import cpu
+    if workload.head_dim > 64:
+        return {"unavailable": "the reference flash kernels stop at head_dim 64 (CudaFlashAttention.hpp:16)"}
+    if not cpu.ref_cuda_available():
+        return {"unavailable": "oracle/_ref/libsentinel_ref_cuda.so not built"}
+    qf, kf, vf, dof = (t.float().numpy() for t in (q, k, v, do))
+    _, _, _, _, _, ms = cpu.ref_cuda_flash(qf, kf, vf, dof, reps=5)
+    total = ms[0] + ms[1]
+    return {"value": workload.flops / (total * 1e-3) / 1e12, "unit": UNIT, "fwd_ms": ms[0], "bwd_ms": ms[1],
+            "note": "fp32 tensors, fp16 WMMA operands, K/V repeated to the query heads as at its call site (repeat not timed)"}
+
+
 def run_reference_arm(args, workload):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -318,6 +332,11 @@ def main():
                 "device_status": status}
         if cpu_base is not None:
             line["cpu_baseline"] = cpu_base
+        if world == 1 and ring is None and not args.no_cpu_baseline:
+            try:
+                line["reference_cuda"] = reference_cuda_sample(w, q, k, v, do)
+            except Exception as exc:
+                line["reference_cuda"] = {"unavailable": str(exc)}
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()

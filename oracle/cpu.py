@@ -187,3 +187,59 @@ def ref_core_fwd_bwd(q, k, v, dout=None, head_limit=0, want_outputs=True):
 
 def ref_threads() -> int:
     return ref_lib().ref_threads()
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# The reference's own CUDA flash kernels (GPU baseline / second parity subject), built into _ref/ by the Makefile
+# ---------------------------------------------------------------------------------------------------------------
+_REF_CUDA_SO = os.path.join(_HERE, "_ref", "libsentinel_ref_cuda.so")
+_ref_cuda = None
+
+
+def ref_cuda_available() -> bool:
+    return os.path.exists(_REF_CUDA_SO)
+
+
+def ref_cuda_flash(q, k, v, dout=None, reps=0):
+    """Runs the reference CUDA flash attention (its forwardMultiHead/backwardMultiHead) on [B,H,S,D] fp32 arrays.
+
+    Grouped-query inputs are expanded to the query head count first (the reference's call site does the same with
+    expandKvHeadsInto) and the expanded dK/dV are summed back per group.  head_dim <= 64 only (its maxHeadDimension).
+    Returns (O, LSE, dQ, dK, dV, (fwd_ms, bwd_ms))."""
+    global _ref_cuda
+    if _ref_cuda is None:
+        _ref_cuda = C.CDLL(_REF_CUDA_SO)
+    q, k, v = _f32(q), _f32(k), _f32(v)
+    B, Hq, S, D = q.shape
+    Hkv = k.shape[1]
+    g = Hq // Hkv
+    ke, ve = np.repeat(k, g, axis=1), np.repeat(v, g, axis=1)
+
+    def fm(x):   # [B,H,S,D] -> (H*D) x (B*S), sequences side by side
+        return np.ascontiguousarray(x.transpose(1, 3, 0, 2).reshape(x.shape[1] * D, B * S))
+
+    def unfm(m, H):
+        return np.ascontiguousarray(m.reshape(H, D, B, S).transpose(2, 0, 3, 1))
+
+    cols = B * S
+    out = np.empty((Hq * D, cols), np.float32)
+    lse = np.empty((Hq, cols), np.float32)
+    have_grad = dout is not None
+    dq = np.empty_like(out) if have_grad else None
+    dk = np.empty_like(out) if have_grad else None
+    dv = np.empty_like(out) if have_grad else None
+    ms = (C.c_float * 2)()
+    err = C.create_string_buffer(256)
+    rc = _ref_cuda.ref_cuda_flash_fwd_bwd(Hq, D, cols, S, B, _fp(fm(q)), _fp(fm(ke)), _fp(fm(ve)),
+                                          _fp(fm(_f32(dout))) if have_grad else None, _fp(out), _fp(lse), _fp(dq), _fp(dk),
+                                          _fp(dv), int(reps), ms, err, 256)
+    if rc != 0:
+        raise RuntimeError("reference CUDA flash attention threw: " + err.value.decode())
+    o = unfm(out, Hq)
+    lse_b = np.ascontiguousarray(lse.reshape(Hq, B, S).transpose(1, 0, 2))
+    if not have_grad:
+        return o, lse_b, None, None, None, (ms[0], ms[1])
+    dq_b = unfm(dq, Hq)
+    dk_b = unfm(dk, Hq).reshape(B, Hkv, g, S, D).sum(2)
+    dv_b = unfm(dv, Hq).reshape(B, Hkv, g, S, D).sum(2)
+    return o, lse_b, dq_b, dk_b, dv_b, (ms[0], ms[1])
