@@ -107,13 +107,8 @@ def attention_backward(q, k, v, o, lse, dout, *, causal=True, scale=None, flags=
 def attention_forward_backward_host(q, k, v, dout, *, causal=True, scale=None, flags=0, device="cuda"):
     """End-to-end call on HOST tensors (pinned memory recommended): uploads Q, K, V, dO, runs forward and
     backward on the device, downloads O, LSE, dQ, dK, dV.  This is the path the benchmark's ``e2e`` times."""
-    dev = torch.device(device)
-    dq_, dk_, dv_, do_ = (t.to(dev, non_blocking=True) for t in (q, k, v, dout))
-    o, lse = attention_forward(dq_, dk_, dv_, causal=causal, scale=scale, flags=flags)
-    gq, gk, gv = attention_backward(dq_, dk_, dv_, o, lse, do_, causal=causal, scale=scale, flags=flags)
-    outs = [t.to("cpu", non_blocking=True) for t in (o, lse, gq, gk, gv)]
-    torch.cuda.current_stream().synchronize()
-    return tuple(outs)
+    from .host_pipeline import forward_backward_host   # transfers overlapped with the kernels, chunked over the batch
+    return forward_backward_host(q, k, v, dout, causal=causal, scale=scale, flags=flags, device=device)
 
 
 def merge_partials(o_acc, lse_acc, o_part, lse_part):
