@@ -25,7 +25,7 @@
 //   * warp roles: 2 compute warpgroups (each owns 64 of the 128 query columns, one thread per key row),
 //     1 drain warpgroup, 2 MMA-issuing warps, 1 TMA-producer warp; registers are re-allocated per role
 //     (setmaxnreg).  Q (+LSE, delta) is double-buffered; dO is double-buffered for D=64 and single-buffered for
-//     D=128 (shared-memory budget).
+//     D=128 (shared-memory capacity).
 //
 // A pre-pass computes delta = rowsum(dO o O), LSE*log2e (padded rows get +inf so they produce P = 0) and
 // zeroes the dQ accumulator; a post-pass converts the accumulator to bf16 dQ (times scale).
@@ -75,7 +75,7 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
     constexpr int kTileBytes = kT * D * 2;
     constexpr int kChunkBytes = kT * 128;          // 128 rows x 128 B
     constexpr int kChunks = D / 64;
-    constexpr int kDoStages = (D == 128) ? 1 : 2;  // shared-memory budget: 227 KB
+    constexpr int kDoStages = (D == 128) ? 1 : 2;  // shared-memory capacity: 227 KB
     constexpr int kStageBytes = 32 * kT * 4;       // dQ staging: 32 columns x 128 rows fp32 = one bulk reduction
     constexpr int kDsBytes = kT * kT * 2;          // dS^T tile: [128 keys][128 queries] bf16 as two 64-query chunks
     // The layout uses every byte of the 227 KB a CTA may have (D = 128), so there is no room for an alignment
@@ -144,7 +144,7 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
     const uint32_t tm_S = tmem, tm_dP = tmem + 128u, tm_dV = tmem + 256u, tm_dK = tmem + 384u;
 
     // 512 threads start with 128 registers each; the issuing/producer warpgroup needs few, the others get the rest
-    // (each role re-allocates registers inside its own branch so that the compiler sees which budget applies where)
+    // (each role re-allocates registers inside its own branch so that the compiler sees which register count applies where)
 
 
     if (warp == 15) {
@@ -195,7 +195,7 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
             constexpr uint32_t idesc_dq = make_idesc(kT, D, true, true);      // dQ: both operands MN-major
             // C[128 x 128] = A[128 x D] * B[128 x D]^T, both K-major tiles; one descriptor per tile, advanced per k-step
             // by a 64-bit add (the empty asm keeps the compiler from hoisting every advanced descriptor out of the main
-            // loop, which would cost this warp more registers than its budget)
+            // loop, which would cost this warp more registers than it is allotted)
             auto issue_kmajor = [&](uint32_t d_tmem, uint64_t a, uint64_t b) {
                 asm volatile("" : "+l"(a), "+l"(b));
                 mma_ss_c<false>(d_tmem, a, b, idesc_st);

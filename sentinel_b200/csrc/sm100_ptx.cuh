@@ -74,7 +74,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity)
     return ok != 0;
 }
 
-constexpr uint64_t kWaitBudgetNs = 1000ull * 1000ull * 1000ull;  // 1 s
+constexpr uint64_t kWaitLimitNs = 1000ull * 1000ull * 1000ull;  // 1 s
 
 // Bounded wait for the phase with the given parity.  `abort_flag` is a CTA-shared word any waiter sets when
 // it gives up; all later waits of the CTA then return false at once.  Returns true when the phase completed.
@@ -88,7 +88,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
         if (mbar_try_wait(bar, parity)) return true;
         if ((++spins & 0x3ffu) == 0) {
             if (*abort_flag) return false;
-            if (*(volatile unsigned int*)&g_device_status != 0u || global_timer_ns() - t0 > kWaitBudgetNs) {
+            if (*(volatile unsigned int*)&g_device_status != 0u || global_timer_ns() - t0 > kWaitLimitNs) {
                 atomicCAS(&g_device_status, 0u, (site << 24) | (blockIdx.x & 0xffffffu));
                 *abort_flag = 1u;
                 return false;
