@@ -4,8 +4,9 @@ A caller that keeps its activations in host memory pays for 538 MB of PCIe traff
 several times the kernels' own time.  This module hides as much of it as the dependencies allow:
 
 * three streams: upload, compute, download (the two PCIe directions run concurrently);
-* the batch is cut into chunks of whole (batch element) units -- every chunk is a complete attention problem, so
-  nothing is exchanged between chunks -- and chunk c+1 uploads while chunk c computes and chunk c-1 downloads;
+* the problem is cut into chunks of whole (batch element, KV group) units -- every chunk is a complete attention
+  problem, contiguous in memory, so nothing is exchanged between chunks -- and chunk c+1 uploads while chunk c computes
+  and chunk c-1 downloads;
 * inside a chunk the forward starts as soon as Q, K, V are on the device (dO follows during the forward), O and LSE
   go back while the backward runs, and the gradients go back while the next chunk computes.
 
@@ -39,53 +40,67 @@ def _buffers(q, k, dev):
     return buf
 
 
+def _chunk_slices(B, Hq, Hkv, chunks):
+    """Cuts the B x Hkv independent (batch element, KV group) units into chunks that are contiguous in memory:
+    a chunk is a run of KV groups inside one batch element (with the query heads of those groups), or -- when there
+    are fewer chunks than batch elements -- a run of whole batch elements."""
+    g = Hq // Hkv
+    if chunks is None:
+        chunks = min(B * Hkv, 4)   # finer chunks leave the backward (one CTA per KV head and key tile) short of a full wave
+    chunks = max(1, min(chunks, B * Hkv))
+    if chunks <= B:
+        return [(slice(c * B // chunks, (c + 1) * B // chunks), slice(0, Hq), slice(0, Hkv)) for c in range(chunks)]
+    per_b = max(1, min(Hkv, -(-chunks // B)))
+    out = []
+    for b in range(B):
+        for c in range(per_b):
+            k0, k1 = c * Hkv // per_b, (c + 1) * Hkv // per_b
+            out.append((slice(b, b + 1), slice(k0 * g, k1 * g), slice(k0, k1)))
+    return out
+
+
 def forward_backward_host(q, k, v, dout, *, causal=True, scale=None, flags=0, device="cuda", chunks=None):
-    """Returns host tensors (O, LSE, dQ, dK, dV).  ``chunks`` = number of batch chunks (default: one per batch element,
-    at most 4)."""
+    """Returns host tensors (O, LSE, dQ, dK, dV).  ``chunks`` = number of pipeline chunks (default: up to 4, cut along
+    batch elements first and KV groups second; every chunk is a complete attention problem)."""
     dev = torch.device(device)
     if dev.index is None:
         dev = torch.device("cuda", torch.cuda.current_device())
-    B = q.shape[0]
-    n_chunks = max(1, min(B, 4) if chunks is None else min(chunks, B))
-    bounds = [(c * B // n_chunks, (c + 1) * B // n_chunks) for c in range(n_chunks)]
+    B, Hq, Hkv = q.shape[0], q.shape[1], k.shape[1]
     buf = _buffers(q, k, dev)
     comp = torch.cuda.current_stream(dev)
     up, down = buf["up"], buf["down"]
     up.wait_stream(comp)      # earlier users of the staging buffers are done
     down.wait_stream(comp)
-    done = []
-    for lo, hi in bounds:
-        sl = slice(lo, hi)
+    for sb, sq, sk in _chunk_slices(B, Hq, Hkv, chunks):
+        qs, ks = (sb, sq), (sb, sk)
         with torch.cuda.stream(up):
-            for name, src in (("q", q), ("k", k), ("v", v)):
-                buf[name][sl].copy_(src[sl], non_blocking=True)
+            buf["q"][qs].copy_(q[qs], non_blocking=True)
+            buf["k"][ks].copy_(k[ks], non_blocking=True)
+            buf["v"][ks].copy_(v[ks], non_blocking=True)
             ev_qkv = torch.cuda.Event()
             ev_qkv.record(up)
-            buf["do"][sl].copy_(dout[sl], non_blocking=True)
+            buf["do"][qs].copy_(dout[qs], non_blocking=True)
             ev_do = torch.cuda.Event()
             ev_do.record(up)
         comp.wait_event(ev_qkv)
-        fa.attention_forward(buf["q"][sl], buf["k"][sl], buf["v"][sl], causal=causal, scale=scale, flags=flags,
-                             out=buf["o"][sl], lse=buf["lse"][sl])
+        fa.attention_forward(buf["q"][qs], buf["k"][ks], buf["v"][ks], causal=causal, scale=scale, flags=flags,
+                             out=buf["o"][qs], lse=buf["lse"][qs])
         ev_fwd = torch.cuda.Event()
         ev_fwd.record(comp)
         with torch.cuda.stream(down):
             down.wait_event(ev_fwd)
-            buf["h_o"][sl].copy_(buf["o"][sl], non_blocking=True)
-            buf["h_lse"][sl].copy_(buf["lse"][sl], non_blocking=True)
+            buf["h_o"][qs].copy_(buf["o"][qs], non_blocking=True)
+            buf["h_lse"][qs].copy_(buf["lse"][qs], non_blocking=True)
         comp.wait_event(ev_do)
-        fa.attention_backward(buf["q"][sl], buf["k"][sl], buf["v"][sl], buf["o"][sl], buf["lse"][sl], buf["do"][sl], causal=causal,
-                              scale=scale, flags=flags, dq=buf["dq"][sl], dk=buf["dk"][sl], dv=buf["dv"][sl])
+        fa.attention_backward(buf["q"][qs], buf["k"][ks], buf["v"][ks], buf["o"][qs], buf["lse"][qs], buf["do"][qs],
+                              causal=causal, scale=scale, flags=flags, dq=buf["dq"][qs], dk=buf["dk"][ks], dv=buf["dv"][ks])
         ev_bwd = torch.cuda.Event()
         ev_bwd.record(comp)
         with torch.cuda.stream(down):
             down.wait_event(ev_bwd)
-            buf["h_dq"][sl].copy_(buf["dq"][sl], non_blocking=True)
-            buf["h_dk"][sl].copy_(buf["dk"][sl], non_blocking=True)
-            buf["h_dv"][sl].copy_(buf["dv"][sl], non_blocking=True)
-            ev = torch.cuda.Event()
-            ev.record(down)
-            done.append(ev)
+            buf["h_dq"][qs].copy_(buf["dq"][qs], non_blocking=True)
+            buf["h_dk"][ks].copy_(buf["dk"][ks], non_blocking=True)
+            buf["h_dv"][ks].copy_(buf["dv"][ks], non_blocking=True)
     comp.wait_stream(down)     # the timed region (events on the compute stream) ends after the last download
     comp.synchronize()
     return buf["h_o"], buf["h_lse"], buf["h_dq"], buf["h_dk"], buf["h_dv"]

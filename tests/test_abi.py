@@ -141,3 +141,26 @@ def test_missing_library_fails_loudly(monkeypatch, tmp_path):
     monkeypatch.setattr(_lib, "LIB_PATH", str(tmp_path / "nope.so"))
     with pytest.raises(_lib.LibraryMissing, match="no CPU or PyTorch fallback"):
         _lib.load()
+
+
+@pytest.mark.parametrize("B,Hq,Hkv,chunks", [(2, 28, 4, None), (2, 28, 4, 1), (2, 28, 4, 2), (2, 28, 4, 3), (3, 4, 2, 4),
+                                              (1, 32, 8, None), (8, 12, 12, None), (4, 4, 4, 100)])
+def test_host_pipeline_chunks_cover_every_unit_once(B, Hq, Hkv, chunks):
+    """The host-buffer call cuts the problem into (batch, KV group) chunks: every unit exactly once, query heads
+    matching their KV groups, each chunk contiguous in a [B,H,S,D] tensor."""
+    from sentinel_b200.host_pipeline import _chunk_slices
+    g = Hq // Hkv
+    seen_q, seen_k = set(), set()
+    for sb, sq, sk in _chunk_slices(B, Hq, Hkv, chunks):
+        bs, qs, ks = range(*sb.indices(B)), range(*sq.indices(Hq)), range(*sk.indices(Hkv))
+        assert len(bs) and len(qs) and len(ks)
+        assert qs.start == ks.start * g and qs.stop == ks.stop * g
+        assert len(bs) == 1 or (len(qs) == Hq and len(ks) == Hkv)      # contiguous: several batch elements only whole
+        for b in bs:
+            for h in qs:
+                assert (b, h) not in seen_q
+                seen_q.add((b, h))
+            for h in ks:
+                assert (b, h) not in seen_k
+                seen_k.add((b, h))
+    assert len(seen_q) == B * Hq and len(seen_k) == B * Hkv

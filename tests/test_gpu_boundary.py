@@ -20,7 +20,7 @@ def test_host_buffer_call_matches_device_calls(sb):
     qd, kd, vd, dod = (t.cuda() for t in (q, k, v, do))
     o, lse = sb.attention_forward(qd, kd, vd)
     dq, dk, dv = sb.attention_backward(qd, kd, vd, o, lse, dod)
-    for chunks in (None, 1, 2):
+    for chunks in (None, 1, 2, 6):      # KV-group chunks, whole problem, batch chunks, one chunk per unit
         from sentinel_b200.host_pipeline import forward_backward_host
         ho, hl, hdq, hdk, hdv = forward_backward_host(q, k, v, do, chunks=chunks)
         assert torch.equal(ho, o.cpu()) and torch.equal(hl, lse.cpu())
