@@ -82,6 +82,12 @@ typedef struct sntl_attn_desc {
     int32_t stride_columns;  /* SENTINEL layout: columns of the matrices (q.cols); ignored for BHSD */
     int32_t column_start;    /* SENTINEL layout: first column of the window; ignored for BHSD */
     int32_t flags;           /* SNTL_FLAG_* */
+    /* Sliding window with global tokens, the reference's CausalSelfAttention::allowsKey
+     * (CausalSelfAttention.cpp:95-100; its CUDA flash path refuses such layers, CudaCausalSelfAttention.cu:50):
+     * key j is visible to query i iff j <= i and (j < global_tokens or window_size <= 0 or j >= i - window_size + 1).
+     * Both need causal = 1; 0 / 0 is plain causal attention. */
+    int32_t window_size;     /* keys a query sees counting itself; <= 0: unlimited */
+    int32_t global_tokens;   /* the first global_tokens keys stay visible to every later query; >= 0 */
 } sntl_attn_desc;
 
 /* Library version (major*10000 + minor*100 + patch). */

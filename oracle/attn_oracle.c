@@ -47,7 +47,19 @@
 typedef struct {
     int batch, q_heads, kv_heads, seq_q, seq_kv, head_dim, causal;
     float scale;
+    int window;        /* sliding window (keys a query sees counting itself); <= 0: unlimited; needs causal */
+    int global_tokens; /* the first global_tokens keys stay visible to every later query */
 } oracle_shape;
+
+/* The window part of CausalSelfAttention::allowsKey (sentinel/NeuralNet/Layers/CausalSelfAttention.cpp:95-100):
+ * below the causal limit a key is visible iff it is a global token, or there is no window, or it lies inside
+ * [query - window + 1, query]. */
+static inline int window_allows(const oracle_shape* s, int query, int key)
+{
+    if (!s->causal || s->window <= 0) return 1;
+    if (key < s->global_tokens) return 1;
+    return key >= query - s->window + 1;
+}
 
 static inline int visible_keys(const oracle_shape* s, int query)
 {
@@ -58,11 +70,14 @@ static inline int visible_keys(const oracle_shape* s, int query)
     return (int)limit;
 }
 
-/* scores of one query row against keys [0, n): returns max; p[] receives raw scores */
-static double score_row(const float* q, const float* kbase, int n, int d, double scale, double* p)
+/* scores of query row `query` against keys [0, n): returns max; p[] receives raw scores, -inf for keys the window
+ * hides (they then get probability exactly 0 everywhere downstream) */
+static double score_row(const oracle_shape* s, int query, const float* q, const float* kbase, int n, int d, double scale,
+                        double* p)
 {
     double m = -INFINITY;
     for (int j = 0; j < n; ++j) {
+        if (!window_allows(s, query, j)) { p[j] = -INFINITY; continue; }
         const float* k = kbase + (size_t)j * d;
         double acc = 0.0;
         for (int t = 0; t < d; ++t) acc += (double)q[t] * (double)k[t];
@@ -103,7 +118,7 @@ int oracle_attn_fwd(const oracle_shape* s, const float* q, const float* k, const
                 lse[r] = -INFINITY;
                 continue;
             }
-            const double m = score_row(qrow, kb, n, D, (double)s->scale, p);
+            const double m = score_row(s, i, qrow, kb, n, D, (double)s->scale, p);
             double l = 0.0;
             for (int j = 0; j < n; ++j) { p[j] = exp(p[j] - m); l += p[j]; }
             for (int j = 0; j < n; ++j) {
@@ -161,7 +176,7 @@ int oracle_attn_bwd(const oracle_shape* s, const float* q, const float* k, const
                     for (int t = 0; t < D; ++t) dq_acc[t] = 0.0;
                     double dl = 0.0;
                     if (n > 0) {
-                        const double m = score_row(qrow, kb, n, D, (double)s->scale, p);
+                        const double m = score_row(s, i, qrow, kb, n, D, (double)s->scale, p);
                         double l = 0.0;
                         for (int j = 0; j < n; ++j) { p[j] = exp(p[j] - m); l += p[j]; }
                         for (int j = 0; j < n; ++j) {
@@ -228,7 +243,7 @@ int oracle_attn_rows(const oracle_shape* s, int b, int h, const float* q, const 
                 lse_rows[x] = -INFINITY;
                 continue;
             }
-            const double m = score_row(qrow, kb, n, D, (double)s->scale, p);
+            const double m = score_row(s, i, qrow, kb, n, D, (double)s->scale, p);
             double l = 0.0;
             for (int j = 0; j < n; ++j) { p[j] = exp(p[j] - m); l += p[j]; }
             for (int j = 0; j < n; ++j) {
@@ -300,7 +315,7 @@ int oracle_attn_cols(const oracle_shape* s, int b, int hk, const float* q, const
             const float* dorow = dout + r * D;
             const int n = visible_keys(s, i);
             if (n == 0) continue;
-            const double m = score_row(qrow, kb, n, D, (double)s->scale, p);
+            const double m = score_row(s, i, qrow, kb, n, D, (double)s->scale, p);
             double l = 0.0;
             for (int j = 0; j < n; ++j) { p[j] = exp(p[j] - m); l += p[j]; }
             double dl = 0.0;

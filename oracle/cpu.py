@@ -22,7 +22,8 @@ _REF_SO = os.path.join(_HERE, "_ref", "libsentinel_ref_attn.so")
 
 class _Shape(C.Structure):
     _fields_ = [("batch", C.c_int), ("q_heads", C.c_int), ("kv_heads", C.c_int), ("seq_q", C.c_int),
-                ("seq_kv", C.c_int), ("head_dim", C.c_int), ("causal", C.c_int), ("scale", C.c_float)]
+                ("seq_kv", C.c_int), ("head_dim", C.c_int), ("causal", C.c_int), ("scale", C.c_float),
+                ("window", C.c_int), ("global_tokens", C.c_int)]
 
 
 def build(force: bool = False) -> None:
@@ -72,18 +73,18 @@ def _f32(a):
     return np.ascontiguousarray(a, dtype=np.float32)
 
 
-def _shape(q, k, causal, scale):
+def _shape(q, k, causal, scale, window=0, global_tokens=0):
     B, Hq, Sq, D = q.shape
     _, Hkv, Skv, _ = k.shape
     if scale is None:
         scale = 1.0 / np.sqrt(D)
-    return _Shape(B, Hq, Hkv, Sq, Skv, D, int(bool(causal)), float(scale))
+    return _Shape(B, Hq, Hkv, Sq, Skv, D, int(bool(causal)), float(scale), int(window), int(global_tokens))
 
 
-def attn_fwd(q, k, v, causal=True, scale=None):
+def attn_fwd(q, k, v, causal=True, scale=None, window=0, global_tokens=0):
     """fp64 oracle forward -> (O [B,Hq,Sq,D], LSE [B,Hq,Sq]) as fp32 arrays."""
     q, k, v = _f32(q), _f32(k), _f32(v)
-    s = _shape(q, k, causal, scale)
+    s = _shape(q, k, causal, scale, window, global_tokens)
     o = np.empty_like(q)
     lse = np.empty(q.shape[:3], np.float32)
     rc = oracle_lib().oracle_attn_fwd(C.byref(s), _fp(q), _fp(k), _fp(v), _fp(o), _fp(lse))
@@ -91,10 +92,10 @@ def attn_fwd(q, k, v, causal=True, scale=None):
     return o, lse
 
 
-def attn_bwd(q, k, v, dout, causal=True, scale=None):
+def attn_bwd(q, k, v, dout, causal=True, scale=None, window=0, global_tokens=0):
     """fp64 oracle backward -> (dQ, dK, dV, delta)."""
     q, k, v, dout = _f32(q), _f32(k), _f32(v), _f32(dout)
-    s = _shape(q, k, causal, scale)
+    s = _shape(q, k, causal, scale, window, global_tokens)
     dq, dk, dv = np.empty_like(q), np.empty_like(k), np.empty_like(v)
     delta = np.empty(q.shape[:3], np.float32)
     rc = oracle_lib().oracle_attn_bwd(C.byref(s), _fp(q), _fp(k), _fp(v), _fp(dout), _fp(dq), _fp(dk), _fp(dv),
@@ -103,11 +104,11 @@ def attn_bwd(q, k, v, dout, causal=True, scale=None):
     return dq, dk, dv, delta
 
 
-def attn_rows(q, k, v, dout, b, h, rows, causal=True, scale=None):
+def attn_rows(q, k, v, dout, b, h, rows, causal=True, scale=None, window=0, global_tokens=0):
     """Sampled oracle: (O rows, LSE rows, dQ rows) for query indices ``rows`` of (b, h)."""
     q, k, v = _f32(q), _f32(k), _f32(v)
     dout = _f32(dout) if dout is not None else None
-    s = _shape(q, k, causal, scale)
+    s = _shape(q, k, causal, scale, window, global_tokens)
     rows = np.ascontiguousarray(rows, dtype=np.int32)
     D = q.shape[-1]
     o = np.empty((len(rows), D), np.float32)
@@ -119,10 +120,10 @@ def attn_rows(q, k, v, dout, b, h, rows, causal=True, scale=None):
     return o, lse, dq
 
 
-def attn_cols(q, k, v, dout, b, hk, cols, causal=True, scale=None):
+def attn_cols(q, k, v, dout, b, hk, cols, causal=True, scale=None, window=0, global_tokens=0):
     """Sampled oracle: (dK rows, dV rows) for key indices ``cols`` of (b, kv head hk)."""
     q, k, v, dout = _f32(q), _f32(k), _f32(v), _f32(dout)
-    s = _shape(q, k, causal, scale)
+    s = _shape(q, k, causal, scale, window, global_tokens)
     cols = np.ascontiguousarray(cols, dtype=np.int32)
     D = q.shape[-1]
     dk = np.empty((len(cols), D), np.float32)
@@ -146,10 +147,11 @@ def oracle_threads() -> int:
     return lib.oracle_threads()
 
 
-def ref_layer_fwd_bwd(q, k, v, dout=None):
+def ref_layer_fwd_bwd(q, k, v, dout=None, window=0, global_tokens=0):
     """The reference's public CausalSelfAttention layer on [Q;K;V] -> (O, LSE, dQ, dK, dV) (grads None without dout).
 
-    Causal, Sq == Skv, scale 1/sqrt(D): the only mode the reference layer has."""
+    Causal, Sq == Skv, scale 1/sqrt(D): the only mode the reference layer has; ``window`` / ``global_tokens`` are its
+    windowSize / globalTokenCount constructor arguments (0 = whole sequence)."""
     q, k, v = _f32(q), _f32(k), _f32(v)
     B, Hq, S, D = q.shape
     Hkv = k.shape[1]
@@ -159,8 +161,8 @@ def ref_layer_fwd_bwd(q, k, v, dout=None):
     if dout is not None:
         dout = _f32(dout)
         dq, dk, dv = np.empty_like(q), np.empty_like(k), np.empty_like(v)
-    rc = ref_lib().ref_layer_fwd_bwd(B, Hq, Hkv, S, D, _fp(q), _fp(k), _fp(v), _fp(dout), _fp(o), _fp(lse), _fp(dq),
-                                     _fp(dk), _fp(dv))
+    rc = ref_lib().ref_layer_fwd_bwd_windowed(B, Hq, Hkv, S, D, int(window), int(global_tokens), _fp(q), _fp(k), _fp(v),
+                                              _fp(dout), _fp(o), _fp(lse), _fp(dq), _fp(dk), _fp(dv))
     assert rc == 0, "reference layer threw"
     return o, lse, dq, dk, dv
 

@@ -96,8 +96,11 @@ int ref_threads()
 
 // Public-API route.  q,o,dout,dq: [B][Hq][S][D]; k,v,dk,dv: [B][Hkv][S][D]; lse: [B][Hq][S].
 // dout/dq/dk/dv may be null (forward only).  Returns 0, or 1 when the reference threw.
-int ref_layer_fwd_bwd(int B, int Hq, int Hkv, int S, int D, const float* q, const float* k, const float* v,
-                      const float* dout, float* o, float* lse, float* dq, float* dk, float* dv)
+// window <= 0: the whole sequence (plain causal).  With 0 < window < S the reference layer takes its sparse
+// branch (CausalSelfAttention.cpp:102-107, :128-148, :154-168, :296-331), the same mask computed pairwise.
+int ref_layer_fwd_bwd_windowed(int B, int Hq, int Hkv, int S, int D, int window, int global_tokens, const float* q,
+                               const float* k, const float* v, const float* dout, float* o, float* lse, float* dq,
+                               float* dk, float* dv)
 {
     try {
         const size_t qRows = (size_t)Hq * D, kvRows = (size_t)Hkv * D, inRows = qRows + 2 * kvRows;
@@ -107,7 +110,8 @@ int ref_layer_fwd_bwd(int B, int Hq, int Hkv, int S, int D, const float* q, cons
         RotaryEmbedding rope(D, S, RotaryEmbedding::DefaultBase);
         std::fill(rope.cosTable.begin(), rope.cosTable.end(), 1.0f);  // inputs arrive with RoPE already applied
         std::fill(rope.sinTable.begin(), rope.sinTable.end(), 0.0f);
-        CausalSelfAttention layer(wq, wk, wv, wo, rope, Hq, /*windowSize=*/S, /*globalTokenCount=*/0, Hkv);
+        CausalSelfAttention layer(wq, wk, wv, wo, rope, Hq, /*windowSize=*/window > 0 ? window : S,
+                                  /*globalTokenCount=*/global_tokens, Hkv);
 
         for (int b = 0; b < B; ++b) {
             Matrix input(inRows, (size_t)S, 0.0f);
@@ -133,6 +137,12 @@ int ref_layer_fwd_bwd(int B, int Hq, int Hkv, int S, int D, const float* q, cons
     } catch (...) {
         return 1;
     }
+}
+
+int ref_layer_fwd_bwd(int B, int Hq, int Hkv, int S, int D, const float* q, const float* k, const float* v,
+                      const float* dout, float* o, float* lse, float* dq, float* dk, float* dv)
+{
+    return ref_layer_fwd_bwd_windowed(B, Hq, Hkv, S, D, 0, 0, q, k, v, dout, o, lse, dq, dk, dv);
 }
 
 // Primitive route (timed baseline).  Same tensors as above; all outputs optional except none --

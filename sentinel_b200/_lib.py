@@ -25,7 +25,7 @@ class Desc(C.Structure):
     _fields_ = [("dtype", C.c_int32), ("layout", C.c_int32), ("batch", C.c_int32), ("q_heads", C.c_int32),
                 ("kv_heads", C.c_int32), ("seq_q", C.c_int32), ("seq_kv", C.c_int32), ("head_dim", C.c_int32),
                 ("scale", C.c_float), ("causal", C.c_int32), ("stride_columns", C.c_int32),
-                ("column_start", C.c_int32), ("flags", C.c_int32)]
+                ("column_start", C.c_int32), ("flags", C.c_int32), ("window_size", C.c_int32), ("global_tokens", C.c_int32)]
 
 
 class LibraryMissing(RuntimeError):
@@ -73,6 +73,9 @@ def load():
     lib.sntl_compat_forward_backward.argtypes = [fp, fp, fp, fp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_float, C.c_int,
                                                  C.c_int, C.c_int, C.c_int, C.c_int, fp, fp, fp, fp, fp, C.c_char_p, sz,
                                                  C.c_char_p, sz]
+    lib.sntl_compat_forward_backward_windowed.restype = C.c_int
+    lib.sntl_compat_forward_backward_windowed.argtypes = [fp, fp, fp, fp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_float] + \
+        [C.c_int] * 7 + [fp, fp, fp, fp, fp, C.c_char_p, sz, C.c_char_p, sz]
     lib.sntl_compat_validate.restype = C.c_int
     lib.sntl_compat_validate.argtypes = [C.c_int] * 8 + [C.c_char_p, sz]
     _lib = lib

@@ -29,6 +29,8 @@ int validate(const sntl_attn_desc* d)
     if (d->q_heads % d->kv_heads != 0) return SNTL_ERR_BAD_ARGUMENT;
     if (d->causal && d->seq_q != d->seq_kv) return SNTL_ERR_BAD_ARGUMENT;
     if (!(d->scale > 0.0f)) return SNTL_ERR_BAD_ARGUMENT;
+    if (d->global_tokens < 0) return SNTL_ERR_BAD_ARGUMENT;   // CausalSelfAttention.cpp:42
+    if ((d->window_size > 0 || d->global_tokens > 0) && !d->causal) return SNTL_ERR_BAD_ARGUMENT;
     if (d->head_dim > 256) return SNTL_ERR_UNSUPPORTED;
     if (d->batch > 65535 || d->q_heads > 65535) return SNTL_ERR_UNSUPPORTED;
     if (d->layout == SNTL_LAYOUT_SENTINEL) {
@@ -43,7 +45,10 @@ int validate(const sntl_attn_desc* d)
 
 AttnShape shape_of(const sntl_attn_desc* d)
 {
-    return AttnShape{d->batch, d->q_heads, d->kv_heads, d->seq_q, d->seq_kv, d->head_dim, d->scale, d->causal ? 1 : 0};
+    // a window that already covers the sequence is plain causal attention
+    const int window = (d->window_size > 0 && d->window_size < d->seq_kv) ? d->window_size : 0;
+    return AttnShape{d->batch, d->q_heads, d->kv_heads, d->seq_q, d->seq_kv, d->head_dim, d->scale, d->causal ? 1 : 0,
+                     window, window > 0 ? d->global_tokens : 0};
 }
 
 // tensor-core path is taken for bf16 tensors, or fp32 tensors when the caller allows bf16 operands

@@ -55,6 +55,7 @@ struct BwdParams {
     float* dq_accum;       // [B*Hq][n_qt][D/4][128][4]
     int B, Hq, Hkv, Sq, Skv, Sq_pad;
     int causal;
+    int window, global_tokens;   // sliding window and always-visible first keys (0, 0: plain causal)
     int n_qt, n_kt;
     float scale, scale_log2;
 };
@@ -67,7 +68,7 @@ struct BwdBarriers {
     uint32_t abort_flag;
 };
 
-template <int D>
+template <int D, bool kWin>
 __global__ void __launch_bounds__(kBwdThreads, 1)
 attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                    const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_do, const BwdParams p)
@@ -108,7 +109,10 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
     const int group = p.Hq / p.Hkv;
     const int k0 = kt * kT;
     const int qt_first = p.causal ? kt : 0;
-    const int per_head = p.n_qt - qt_first;             // query tiles per head this CTA visits
+    // with a sliding window the last query that sees this tile is (last key + window - 1), unless the tile holds
+    // global tokens, which every later query sees
+    const int qt_last = (kWin && k0 >= p.global_tokens) ? min(p.n_qt - 1, (k0 + kT - 1 + p.window - 1) / kT) : p.n_qt - 1;
+    const int per_head = qt_last - qt_first + 1;        // query tiles per head this CTA visits
     const int n_iter = per_head > 0 ? per_head * group : 0;
 
     if (warp == 13 && lane == 0) {
@@ -387,7 +391,8 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
             tmem_ld_wait();
             SNTL_TRACE_EV(tw, 1 + wg, tn, 2);
             const float4* lse4 = reinterpret_cast<const float4*>(sLse + sq * kT + col0);
-            const bool diag = p.causal && (qt == kt);
+            // tiles the mask cuts through: the diagonal one and, with a window, those reaching past (first key + window - 1)
+            const bool diag = (p.causal && qt == kt) || (kWin && qt * kT + kT - 1 > k0 + p.window - 1);
             uint32_t pk[32];
             const float2 sc2 = make_float2(p.scale_log2, p.scale_log2);
             // branch-free main body (the mask test lives in its own copy of the loop, taken only on the diagonal tile,
@@ -402,14 +407,20 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
                     pk[2 * c + 1] = pack_bf16(ex2(x23.x), ex2(x23.y));
                 }
             } else {
+                // this thread's key sees the queries from itself (causal) up to key + window - 1 (global keys: all)
+                const int key = k0 + row;
+                const int first_q = p.causal ? key - qt * kT : -1;
+                const int last_q = (kWin && key >= p.global_tokens) ? key + p.window - 1 - qt * kT : kT;
 #pragma unroll
                 for (int c = 0; c < 16; ++c) {
                     const float4 l = lse4[c];
                     const float2 x01 = ffma2(make_float2(__uint_as_float(s[4 * c + 0]), __uint_as_float(s[4 * c + 1])), sc2, make_float2(l.x, l.y));
                     const float2 x23 = ffma2(make_float2(__uint_as_float(s[4 * c + 2]), __uint_as_float(s[4 * c + 3])), sc2, make_float2(l.z, l.w));
-                    const int q = (int)col0 + 4 * c;   // key (row) > query (column) is masked
-                    const float p0 = row > q + 0 ? 0.0f : ex2(x01.x), p1 = row > q + 1 ? 0.0f : ex2(x01.y);
-                    const float p2 = row > q + 2 ? 0.0f : ex2(x23.x), p3 = row > q + 3 ? 0.0f : ex2(x23.y);
+                    const int q = (int)col0 + 4 * c;   // visible: first_q <= query (column) <= last_q
+                    const float p0 = (q + 0 < first_q || q + 0 > last_q) ? 0.0f : ex2(x01.x);
+                    const float p1 = (q + 1 < first_q || q + 1 > last_q) ? 0.0f : ex2(x01.y);
+                    const float p2 = (q + 2 < first_q || q + 2 > last_q) ? 0.0f : ex2(x23.x);
+                    const float p3 = (q + 3 < first_q || q + 3 > last_q) ? 0.0f : ex2(x23.y);
                     pk[2 * c] = pack_bf16(p0, p1);
                     pk[2 * c + 1] = pack_bf16(p2, p3);
                 }
@@ -573,7 +584,7 @@ __global__ void __launch_bounds__(256) bwd_post_kernel(const float* __restrict__
 
 inline size_t align256(size_t x) { return (x + 255) / 256 * 256; }
 
-template <int D>
+template <int D, bool kWin>
 cudaError_t launch_bwd(const TcArgs& a, cudaStream_t st)
 {
     const AttnShape& s = a.s;
@@ -600,6 +611,8 @@ cudaError_t launch_bwd(const TcArgs& a, cudaStream_t st)
     p.lse2 = lse2; p.delta = a.delta; p.dq_accum = a.dq_accum;
     p.B = s.B; p.Hq = s.Hq; p.Hkv = s.Hkv; p.Sq = s.Sq; p.Skv = s.Skv; p.Sq_pad = Sq_pad;
     p.causal = s.causal;
+    p.window = s.causal ? s.window : 0;
+    p.global_tokens = s.global_tokens;
     p.n_qt = n_qt; p.n_kt = n_kt;
     p.scale = s.scale;
     p.scale_log2 = s.scale * 1.4426950408889634f;
@@ -607,13 +620,13 @@ cudaError_t launch_bwd(const TcArgs& a, cudaStream_t st)
     const size_t smem = (size_t)(128 * D * 2) * (4 + kDoStages) + 128 * 128 * 2 + 2 * (32 * 128 * 4) + 4 * 128 * 4 + sizeof(BwdBarriers);
     static bool configured = false;
     if (!configured) {
-        if ((e = cudaFuncSetAttribute(attn_bwd_tc_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)) != cudaSuccess)
+        if ((e = cudaFuncSetAttribute(attn_bwd_tc_kernel<D, kWin>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)) != cudaSuccess)
             return e;
         configured = true;
     }
     const long long ctas = (long long)n_kt * s.B * s.Hkv;
     if (ctas > 0x7fffffffLL) return cudaErrorInvalidConfiguration;
-    attn_bwd_tc_kernel<D><<<(unsigned)ctas, kBwdThreads, smem, st>>>(tq, tk, tv, tdo, p);
+    attn_bwd_tc_kernel<D, kWin><<<(unsigned)ctas, kBwdThreads, smem, st>>>(tq, tk, tv, tdo, p);
     count_launch();
     if ((e = cudaGetLastError()) != cudaSuccess) return e;
     bwd_post_kernel<D><<<(unsigned)((long long)s.B * s.Hq * n_qt * 4), 256, 0, st>>>(a.dq_accum, a.dq, s.Sq, n_qt, s.scale);
@@ -638,7 +651,9 @@ size_t tc_backward_workspace_bytes(const AttnShape& s)
 
 cudaError_t tc_backward(const TcArgs& a, cudaStream_t st)
 {
-    return a.s.D == 64 ? launch_bwd<64>(a, st) : launch_bwd<128>(a, st);
+    const bool win = a.s.causal && a.s.window > 0;
+    if (a.s.D == 64) return win ? launch_bwd<64, true>(a, st) : launch_bwd<64, false>(a, st);
+    return win ? launch_bwd<128, true>(a, st) : launch_bwd<128, false>(a, st);
 }
 
 #ifdef SNTL_TRACE

@@ -48,6 +48,7 @@ struct FwdParams {
     float* lse;
     int B, Hq, Hkv, Sq, Skv;
     int causal;
+    int window, global_tokens;   // sliding window and always-visible first keys (0, 0: plain causal)
     int n_qblk;       // 256-row query blocks per (b, h)
     float scale_log2; // scale * log2(e)
 };
@@ -61,7 +62,8 @@ struct FwdBarriers {
     uint32_t abort_flag;
 };
 
-template <int D>
+// kWin: sliding-window instantiation (separate so that the plain causal kernel carries none of its bookkeeping)
+template <int D, bool kWin>
 __global__ void __launch_bounds__(kFwdThreads, 1)
 attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                    const __grid_constant__ CUtensorMap tmap_v, const FwdParams p)
@@ -88,13 +90,20 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
     const int bh_kv = b * p.Hkv + h / (p.Hq / p.Hkv);
     const int q0 = qblk * 2 * kM;
     const int n_ktiles_all = (p.Skv + kN - 1) / kN;
+    // Key tiles this CTA visits, in ascending order: the tiles holding global tokens, then the tiles from the window
+    // of the block's first query row up to the diagonal.  Without a window that is simply 0 .. diagonal.
+    const int g_tiles = kWin ? (p.global_tokens + kN - 1) / kN : 0;
+    const int w_first = kWin ? max(g_tiles, max(0, q0 - p.window + 1) / kN) : 0;
+    auto key_tile = [&](int j) { return j < g_tiles ? j : w_first + (j - g_tiles); };
     int n_t[2];
 #pragma unroll
     for (int t = 0; t < 2; ++t) {
         const int row0 = q0 + t * kM;
         if (row0 >= p.Sq) n_t[t] = 0;
-        else if (p.causal) n_t[t] = min(n_ktiles_all, row0 / kN + 1);
-        else n_t[t] = n_ktiles_all;
+        else if (p.causal) {
+            const int diag = min(n_ktiles_all - 1, row0 / kN);
+            n_t[t] = min(g_tiles, diag + 1) + max(0, diag - w_first + 1);
+        } else n_t[t] = n_ktiles_all;
     }
     const int n_max = max(n_t[0], n_t[1]);
 
@@ -146,11 +155,11 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
                 if (j >= 2 && !mbar_wait(&bars->k_empty[st], ((j >> 1) - 1) & 1, abort_flag, kSiteKEmpty)) break;
                 mbar_arrive_expect_tx(&bars->k_full[st], (uint32_t)kTileBytes);
                 for (int c = 0; c < kChunks; ++c)
-                    tma_load_3d(sK + st * kTileBytes + c * kChunkBytes, &tmap_k, &bars->k_full[st], c * 64, j * kN, bh_kv);
+                    tma_load_3d(sK + st * kTileBytes + c * kChunkBytes, &tmap_k, &bars->k_full[st], c * 64, key_tile(j) * kN, bh_kv);
                 if (j >= 2 && !mbar_wait(&bars->v_empty[st], ((j >> 1) - 1) & 1, abort_flag, kSiteVEmpty)) break;
                 mbar_arrive_expect_tx(&bars->v_full[st], (uint32_t)kTileBytes);
                 for (int c = 0; c < kChunks; ++c)
-                    tma_load_3d(sV + st * kTileBytes + c * kChunkBytes, &tmap_v, &bars->v_full[st], c * 64, j * kN, bh_kv);
+                    tma_load_3d(sV + st * kTileBytes + c * kChunkBytes, &tmap_v, &bars->v_full[st], c * 64, key_tile(j) * kN, bh_kv);
             }
         }
     } else if (warp == 8) {
@@ -249,11 +258,21 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
             tmem_ld_wait();
             SNTL_TRACE_EV(tw, 1 + t, tn, 2);
             // number of visible keys of this row inside this tile
-            int limit = (p.causal ? min(p.Skv, grow + 1) : p.Skv) - j * kN;
+            const int key0 = key_tile(j) * kN;
+            int limit = (p.causal ? min(p.Skv, grow + 1) : p.Skv) - key0;
             if (limit < kN) {
 #pragma unroll
                 for (int c = 0; c < kN; ++c)
                     if (c >= limit) s[c] = 0xff800000u;  // -inf
+            }
+            if (kWin) {
+                // keys below the row's window are hidden unless they are global tokens
+                const int lo = grow - p.window + 1 - key0, glim = p.global_tokens - key0;
+                if (lo > 0 && glim < min(lo, kN)) {
+#pragma unroll
+                    for (int c = 0; c < kN; ++c)
+                        if (c < lo && c >= glim) s[c] = 0xff800000u;
+                }
             }
             // row max with eight independent chains (a single 128-long dependent chain costs ~600 cycles)
             float mx8[8];
@@ -367,7 +386,7 @@ EncodeTiledFn encode_fn()
     return fn;
 }
 
-template <int D>
+template <int D, bool kWin>
 cudaError_t launch_fwd(const TcArgs& a, cudaStream_t st)
 {
     const AttnShape& s = a.s;
@@ -381,18 +400,20 @@ cudaError_t launch_fwd(const TcArgs& a, cudaStream_t st)
     p.lse = a.lse_out;
     p.B = s.B; p.Hq = s.Hq; p.Hkv = s.Hkv; p.Sq = s.Sq; p.Skv = s.Skv;
     p.causal = s.causal;
+    p.window = s.causal ? s.window : 0;
+    p.global_tokens = s.global_tokens;
     p.n_qblk = (s.Sq + 2 * kM - 1) / (2 * kM);
     p.scale_log2 = s.scale * 1.4426950408889634f;
     const size_t smem = 6 * (size_t)(128 * D * 2) + sizeof(FwdBarriers) + 1024;
     static bool configured = false;  // per instantiation
     if (!configured) {
-        if ((e = cudaFuncSetAttribute(attn_fwd_tc_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)) != cudaSuccess)
+        if ((e = cudaFuncSetAttribute(attn_fwd_tc_kernel<D, kWin>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)) != cudaSuccess)
             return e;
         configured = true;
     }
     const long long ctas = (long long)p.n_qblk * s.B * s.Hq;
     if (ctas > 0x7fffffffLL) return cudaErrorInvalidConfiguration;
-    attn_fwd_tc_kernel<D><<<(unsigned)ctas, kFwdThreads, smem, st>>>(tq, tk, tv, p);
+    attn_fwd_tc_kernel<D, kWin><<<(unsigned)ctas, kFwdThreads, smem, st>>>(tq, tk, tv, p);
     count_launch();
     return cudaGetLastError();
 }
@@ -421,7 +442,9 @@ bool tc_fwd_supported(const AttnShape& s)
 
 cudaError_t tc_forward(const TcArgs& a, cudaStream_t st)
 {
-    return a.s.D == 64 ? launch_fwd<64>(a, st) : launch_fwd<128>(a, st);
+    const bool win = a.s.causal && a.s.window > 0;
+    if (a.s.D == 64) return win ? launch_fwd<64, true>(a, st) : launch_fwd<64, false>(a, st);
+    return win ? launch_fwd<128, true>(a, st) : launch_fwd<128, false>(a, st);
 }
 
 #ifdef SNTL_TRACE

@@ -22,7 +22,16 @@ struct AttnShape {
     int B, Hq, Hkv, Sq, Skv, D;
     float scale;
     int causal;
+    int window;         // sliding window (keys a query sees counting itself); <= 0: unlimited.  Needs causal.
+    int global_tokens;  // the first global_tokens keys stay visible to every later query
 };
+
+// The window part of the reference's CausalSelfAttention::allowsKey (CausalSelfAttention.cpp:95-100); the causal part
+// (key <= query) is the caller's.
+__host__ __device__ __forceinline__ bool window_allows(const AttnShape& s, int query, int key)
+{
+    return s.window <= 0 || key < s.global_tokens || key >= query - s.window + 1;
+}
 
 // Exact-fp32 SIMT kernels (attn_simt.cu).  T = float or __nv_bfloat16 element type.
 struct SimtArgs {

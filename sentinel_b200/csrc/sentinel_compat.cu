@@ -80,9 +80,11 @@ bool device_available()
 }
 
 sntl_attn_desc make_desc(const CudaMatrix& query, int headCount, int kvHeads, int headDimension, float scale, bool causal,
-                         int columnStart, int columnCount, int packCount)
+                         int columnStart, int columnCount, int packCount, int windowSize, int globalTokenCount)
 {
     sntl_attn_desc d{};
+    d.window_size = windowSize;
+    d.global_tokens = globalTokenCount;
     d.dtype = SNTL_DTYPE_F32;
     d.layout = SNTL_LAYOUT_SENTINEL;
     d.batch = packCount;
@@ -146,7 +148,7 @@ const char* CudaFlashAttention::lastPath() { return sntl_attn_last_path(); }
 
 void CudaFlashAttention::forwardMultiHead(const CudaMatrix& query, const CudaMatrix& key, const CudaMatrix& value, CudaMatrix& out,
                                           CudaMatrix& logSumExp, int headCount, int headDimension, float scale, bool causal,
-                                          int columnStart, int columnCount, int packCount)
+                                          int columnStart, int columnCount, int packCount, int windowSize, int globalTokenCount)
 {
     const char* op = "CudaFlashAttention::forwardMultiHead";
     const int kvHeads = validate_shape(query, key, value, headCount, headDimension, op);
@@ -154,12 +156,16 @@ void CudaFlashAttention::forwardMultiHead(const CudaMatrix& query, const CudaMat
         throw std::invalid_argument(std::string(op) + " headDim exceeds maxHeadDimension");
     if (!device_available()) throw std::runtime_error(std::string(op) + " no CUDA device");
     if (packCount <= 0) packCount = 1;
+    if (globalTokenCount < 0) throw std::invalid_argument(std::string(op) + " globalTokenCount must be >= 0");
+    if ((windowSize > 0 || globalTokenCount > 0) && !causal)
+        throw std::invalid_argument(std::string(op) + " a sliding window needs the causal mask");
     resolve_window(query, columnStart, columnCount);
     if (columnStart + packCount * columnCount > (int)query.cols) throw std::invalid_argument(std::string(op) + " pack window exceeds columns");
 
     out.ensureSize(query.rows, query.cols);
     logSumExp.ensureSize((size_t)headCount, query.cols);
-    const sntl_attn_desc d = make_desc(query, headCount, kvHeads, headDimension, scale, causal, columnStart, columnCount, packCount);
+    const sntl_attn_desc d = make_desc(query, headCount, kvHeads, headDimension, scale, causal, columnStart, columnCount, packCount,
+                                       windowSize, globalTokenCount);
     const size_t ws = sntl_attn_fwd_workspace_bytes(&d);
     void* wsp = ws ? workspace(ws) : nullptr;
     status_or_throw(sntl_attn_fwd(&d, query.deviceData(), key.deviceData(), value.deviceData(), out.deviceData(),
@@ -177,7 +183,8 @@ void CudaFlashAttention::backwardMultiHead(const CudaMatrix& query, const CudaMa
                                            const CudaMatrix& out, const CudaMatrix& logSumExp, const CudaMatrix& outGradient,
                                            CudaMatrix& queryGradient, CudaMatrix& keyGradient, CudaMatrix& valueGradient,
                                            CudaMatrix& deltaWorkspace, int headCount, int headDimension, float scale, bool causal,
-                                           int columnStart, int columnCount, int packCount)
+                                           int columnStart, int columnCount, int packCount, int windowSize,
+                                           int globalTokenCount)
 {
     const char* op = "CudaFlashAttention::backwardMultiHead";
     const int kvHeads = validate_shape(query, key, value, headCount, headDimension, op);
@@ -188,6 +195,9 @@ void CudaFlashAttention::backwardMultiHead(const CudaMatrix& query, const CudaMa
         throw std::invalid_argument(std::string(op) + " logSumExp shape mismatch");
     if (!device_available()) throw std::runtime_error(std::string(op) + " no CUDA device");
     if (packCount <= 0) packCount = 1;
+    if (globalTokenCount < 0) throw std::invalid_argument(std::string(op) + " globalTokenCount must be >= 0");
+    if ((windowSize > 0 || globalTokenCount > 0) && !causal)
+        throw std::invalid_argument(std::string(op) + " a sliding window needs the causal mask");
     resolve_window(query, columnStart, columnCount);
     if (columnStart + packCount * columnCount > (int)query.cols) throw std::invalid_argument(std::string(op) + " pack window exceeds columns");
 
@@ -195,7 +205,8 @@ void CudaFlashAttention::backwardMultiHead(const CudaMatrix& query, const CudaMa
     keyGradient.ensureSize(key.rows, key.cols);
     valueGradient.ensureSize(value.rows, value.cols);
     deltaWorkspace.ensureSize((size_t)headCount, (size_t)packCount * (size_t)columnCount);
-    const sntl_attn_desc d = make_desc(query, headCount, kvHeads, headDimension, scale, causal, columnStart, columnCount, packCount);
+    const sntl_attn_desc d = make_desc(query, headCount, kvHeads, headDimension, scale, causal, columnStart, columnCount, packCount,
+                                       windowSize, globalTokenCount);
     const size_t ws = sntl_attn_bwd_workspace_bytes(&d);
     status_or_throw(sntl_attn_bwd(&d, query.deviceData(), key.deviceData(), value.deviceData(), out.deviceData(),
                                   logSumExp.deviceData(), outGradient.deviceData(), queryGradient.deviceData(),
@@ -231,10 +242,11 @@ void copy_err(char* err, size_t n, const char* what)
 
 extern "C" {
 
-int sntl_compat_forward_backward(const float* q, const float* k, const float* v, const float* dout, int headCount, int kvHeads,
-                                 int headDimension, int strideColumns, float scale, int causal, int columnStart, int columnCount,
-                                 int packCount, int allowReduced, float* out, float* lse, float* dq, float* dk, float* dv,
-                                 char* path, size_t path_len, char* err, size_t err_len)
+int sntl_compat_forward_backward_windowed(const float* q, const float* k, const float* v, const float* dout, int headCount,
+                                          int kvHeads, int headDimension, int strideColumns, float scale, int causal,
+                                          int columnStart, int columnCount, int packCount, int windowSize, int globalTokenCount,
+                                          int allowReduced, float* out, float* lse, float* dq, float* dk, float* dv, char* path,
+                                          size_t path_len, char* err, size_t err_len)
 {
     try {
         CudaFlashAttention::setAllowReducedPrecision(allowReduced != 0);
@@ -248,7 +260,7 @@ int sntl_compat_forward_backward(const float* q, const float* k, const float* v,
         mo.upload(fill.data(), qRows, (size_t)strideColumns);
         ml.upload(fill.data(), (size_t)headCount, (size_t)strideColumns);
         CudaFlashAttention::forwardMultiHead(mq, mk, mv, mo, ml, headCount, headDimension, scale, causal != 0, columnStart, columnCount,
-                                             packCount);
+                                             packCount, windowSize, globalTokenCount);
         copy_err(path, path_len, CudaFlashAttention::lastPath());
         mo.download(out);
         ml.download(lse);
@@ -258,7 +270,7 @@ int sntl_compat_forward_backward(const float* q, const float* k, const float* v,
             mdk.upload(fill.data(), kvRows, (size_t)strideColumns);
             mdv.upload(fill.data(), kvRows, (size_t)strideColumns);
             CudaFlashAttention::backwardMultiHead(mq, mk, mv, mo, ml, mg, mdq, mdk, mdv, mdelta, headCount, headDimension, scale,
-                                                  causal != 0, columnStart, columnCount, packCount);
+                                                  causal != 0, columnStart, columnCount, packCount, windowSize, globalTokenCount);
             mdq.download(dq);
             mdk.download(dk);
             mdv.download(dv);
@@ -271,6 +283,16 @@ int sntl_compat_forward_backward(const float* q, const float* k, const float* v,
         copy_err(err, err_len, e.what());
         return 2;
     }
+}
+
+int sntl_compat_forward_backward(const float* q, const float* k, const float* v, const float* dout, int headCount, int kvHeads,
+                                 int headDimension, int strideColumns, float scale, int causal, int columnStart, int columnCount,
+                                 int packCount, int allowReduced, float* out, float* lse, float* dq, float* dk, float* dv,
+                                 char* path, size_t path_len, char* err, size_t err_len)
+{
+    return sntl_compat_forward_backward_windowed(q, k, v, dout, headCount, kvHeads, headDimension, strideColumns, scale, causal,
+                                                 columnStart, columnCount, packCount, 0, 0, allowReduced, out, lse, dq, dk, dv, path,
+                                                 path_len, err, err_len);
 }
 
 // argument-check probe that needs no device work: runs the shape/window validation only

@@ -59,9 +59,13 @@ public:
     /// columns [columnStart, columnStart + packCount*columnCount) of strideColumns-wide matrices; every pack is an
     /// independent sequence.  key/value may carry fewer heads than query (rows = kvHeads*headDimension, kvHeads
     /// dividing headCount): grouped-query attention without repeating K/V.
+    /// windowSize / globalTokenCount (after the reference's arguments, default off) are the layer's sliding window and
+    /// global tokens (CausalSelfAttention::allowsKey, CausalSelfAttention.cpp:95-100), which the reference's flash path
+    /// refuses (CudaCausalSelfAttention.cu:50) and this one computes.
     static void forwardMultiHead(const CudaMatrix& query, const CudaMatrix& key, const CudaMatrix& value, CudaMatrix& out,
                                  CudaMatrix& logSumExp, int headCount, int headDimension, float scale, bool causal = true,
-                                 int columnStart = 0, int columnCount = 0, int packCount = 1);
+                                 int columnStart = 0, int columnCount = 0, int packCount = 1, int windowSize = 0,
+                                 int globalTokenCount = 0);
 
     static void backward(const CudaMatrix& query, const CudaMatrix& key, const CudaMatrix& value, const CudaMatrix& out,
                          const CudaMatrix& logSumExp, const CudaMatrix& outGradient, CudaMatrix& queryGradient,
@@ -73,7 +77,7 @@ public:
                                   const CudaMatrix& logSumExp, const CudaMatrix& outGradient, CudaMatrix& queryGradient,
                                   CudaMatrix& keyGradient, CudaMatrix& valueGradient, CudaMatrix& deltaWorkspace, int headCount,
                                   int headDimension, float scale, bool causal = true, int columnStart = 0, int columnCount = 0,
-                                  int packCount = 1);
+                                  int packCount = 1, int windowSize = 0, int globalTokenCount = 0);
 
     /// stream all launches go to (the reference reads CudaMatmul::activeStream(), CudaMatmul.cu:498-500)
     static void setActiveStream(cudaStream_t stream);

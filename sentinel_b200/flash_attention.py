@@ -53,7 +53,7 @@ def _require(t: torch.Tensor, name: str) -> None:
         raise ValueError(f"{name} must be contiguous")
 
 
-def _bhsd_desc(q, k, causal, scale, flags) -> _lib.Desc:
+def _bhsd_desc(q, k, causal, scale, flags, window=0, global_tokens=0) -> _lib.Desc:
     if q.dim() != 4 or k.dim() != 4:
         raise ValueError("expected [B, H, S, D] tensors")
     B, Hq, Sq, D = q.shape
@@ -63,17 +63,21 @@ def _bhsd_desc(q, k, causal, scale, flags) -> _lib.Desc:
     if scale is None:
         scale = D ** -0.5
     return _lib.Desc(_dtype_code(q), _lib.LAYOUT_BHSD, B, Hq, Hkv, Sq, Skv, D, float(scale), int(bool(causal)), 0, 0,
-                     int(flags))
+                     int(flags), int(window), int(global_tokens))
 
 
-def attention_forward(q, k, v, *, causal=True, scale=None, flags=0, out=None, lse=None):
-    """O, LSE = attention(Q, K, V).  q: [B,Hq,Sq,D]; k, v: [B,Hkv,Skv,D]; LSE: [B,Hq,Sq] fp32 (natural log)."""
+def attention_forward(q, k, v, *, causal=True, scale=None, flags=0, out=None, lse=None, window=0, global_tokens=0):
+    """O, LSE = attention(Q, K, V).  q: [B,Hq,Sq,D]; k, v: [B,Hkv,Skv,D]; LSE: [B,Hq,Sq] fp32 (natural log).
+
+    ``window`` / ``global_tokens``: the reference layer's sliding window and always-visible first keys
+    (CausalSelfAttention.cpp:95-100); key j is visible to query i iff j <= i and (j < global_tokens or window <= 0 or
+    j >= i - window + 1)."""
     lib = _lib.load()
     for t, n in ((q, "q"), (k, "k"), (v, "v")):
         _require(t, n)
     if k.shape != v.shape or k.dtype != q.dtype or v.dtype != q.dtype:
         raise ValueError("k and v must share shape; q, k, v must share dtype")
-    d = _bhsd_desc(q, k, causal, scale, flags)
+    d = _bhsd_desc(q, k, causal, scale, flags, window, global_tokens)
     o = torch.empty_like(q) if out is None else out
     lse = torch.empty(q.shape[:3], dtype=torch.float32, device=q.device) if lse is None else lse
     nbytes = lib.sntl_attn_fwd_workspace_bytes(C.byref(d))
@@ -84,14 +88,15 @@ def attention_forward(q, k, v, *, causal=True, scale=None, flags=0, out=None, ls
     return o, lse
 
 
-def attention_backward(q, k, v, o, lse, dout, *, causal=True, scale=None, flags=0, dq=None, dk=None, dv=None):
+def attention_backward(q, k, v, o, lse, dout, *, causal=True, scale=None, flags=0, dq=None, dk=None, dv=None, window=0,
+                       global_tokens=0):
     """dQ, dK, dV from dO (P recomputed from LSE).  Shapes as in attention_forward."""
     lib = _lib.load()
     for t, n in ((q, "q"), (k, "k"), (v, "v"), (o, "o"), (lse, "lse"), (dout, "dout")):
         _require(t, n)
     if o.shape != q.shape or dout.shape != q.shape or lse.shape != q.shape[:3] or lse.dtype != torch.float32:
         raise ValueError("o/dout must match q; lse must be fp32 [B,Hq,Sq]")
-    d = _bhsd_desc(q, k, causal, scale, flags)
+    d = _bhsd_desc(q, k, causal, scale, flags, window, global_tokens)
     dq = torch.empty_like(q) if dq is None else dq
     dk = torch.empty_like(k) if dk is None else dk
     dv = torch.empty_like(v) if dv is None else dv
@@ -167,7 +172,8 @@ class CudaFlashAttention:
     allow_reduced_precision = False
 
     @staticmethod
-    def _desc(query, key, headCount, headDimension, scale, causal, columnStart, columnCount, packCount):
+    def _desc(query, key, headCount, headDimension, scale, causal, columnStart, columnCount, packCount, windowSize=0,
+              globalTokenCount=0):
         op = "CudaFlashAttention"
         if query.numel() == 0 or key.numel() == 0:
             raise ValueError(f"{op} empty input")
@@ -191,15 +197,16 @@ class CudaFlashAttention:
         flags = _lib.FLAG_ALLOW_BF16_COMPUTE if CudaFlashAttention.allow_reduced_precision else 0
         return _lib.Desc(_lib.DTYPE_F32, _lib.LAYOUT_SENTINEL, packCount, headCount, key.shape[0] // headDimension,
                          columnCount, columnCount, headDimension, float(scale), int(bool(causal)), stride, columnStart,
-                         flags)
+                         flags, int(windowSize), int(globalTokenCount))
 
     @staticmethod
     def forwardMultiHead(query, key, value, out, logSumExp, headCount, headDimension, scale, causal=True, columnStart=0,
-                         columnCount=0, packCount=1):
+                         columnCount=0, packCount=1, windowSize=0, globalTokenCount=0):
         lib = _lib.load()
         if key.shape != value.shape:
             raise ValueError("CudaFlashAttention key/value rows mismatch")
-        d = CudaFlashAttention._desc(query, key, headCount, headDimension, scale, causal, columnStart, columnCount, packCount)
+        d = CudaFlashAttention._desc(query, key, headCount, headDimension, scale, causal, columnStart, columnCount, packCount,
+                                     windowSize, globalTokenCount)
         for t, n in ((query, "query"), (key, "key"), (value, "value")):
             _require(t, n)
         if out is None:
@@ -221,9 +228,10 @@ class CudaFlashAttention:
     @staticmethod
     def backwardMultiHead(query, key, value, out, logSumExp, outGradient, queryGradient, keyGradient, valueGradient,
                           deltaWorkspace, headCount, headDimension, scale, causal=True, columnStart=0, columnCount=0,
-                          packCount=1):
+                          packCount=1, windowSize=0, globalTokenCount=0):
         lib = _lib.load()
-        d = CudaFlashAttention._desc(query, key, headCount, headDimension, scale, causal, columnStart, columnCount, packCount)
+        d = CudaFlashAttention._desc(query, key, headCount, headDimension, scale, causal, columnStart, columnCount, packCount,
+                                     windowSize, globalTokenCount)
         if out.shape != query.shape:
             raise ValueError("CudaFlashAttention::backwardMultiHead out shape mismatch")
         if outGradient.shape != query.shape:

@@ -8,7 +8,7 @@ restatement and the CUDA kernels can be checked where the reference sources are 
 
 Run from the repository root, where the reference is mounted:   python tests/golden/make_golden.py
 Each case is stored as <name>.npz with inputs (q, k, v, dout) and reference outputs (o, lse, dq, dk, dv), fp32,
-token-major [B, H, S, D].
+token-major [B, H, S, D]; sliding-window cases also hold the layer's ``window`` and ``global_tokens``.
 """
 import os
 import sys
@@ -36,6 +36,18 @@ CASES = {
 }
 
 
+# sliding window + global tokens (the reference layer's windowSize / globalTokenCount): name: (spec as above, window, global)
+WINDOW_CASES = {
+    # shape and mask of the reference's runSparseMaskSmokeDemo(32, 2, 16, 32, 4, 2) (main.cpp:759)
+    "win4_g2_h2_s16_d16": ((1, 2, 2, 16, 16, 1.0, 111, False), 4, 2),
+    "win17_g0_h4_kv2_s96_d16": ((2, 4, 2, 96, 16, 1.0, 112, False), 17, 0),
+    "win64_g5_h4_s200_d32": ((1, 4, 4, 200, 32, 1.0, 113, False), 64, 5),
+    # tensor-core head sizes: windows that cut through tiles, global tokens, ragged lengths
+    "win100_g3_h4_kv1_s300_d64_bf16in": ((1, 4, 1, 300, 64, 0.5, 114, True), 100, 3),
+    "win130_g140_h2_kv1_s520_d128_bf16in": ((1, 2, 1, 520, 128, 0.5, 115, True), 130, 140),
+}
+
+
 def make_case(B, Hq, Hkv, S, D, std, seed, bf16_inputs):
     rng = np.random.default_rng(seed)
     q = (rng.standard_normal((B, Hq, S, D)) * std).astype(np.float32)
@@ -55,6 +67,13 @@ def main():
         o, lse, dq, dk, dv = cpu.ref_layer_fwd_bwd(q, k, v, dout)
         path = os.path.join(HERE, name + ".npz")
         np.savez_compressed(path, q=q, k=k, v=v, dout=dout, o=o, lse=lse, dq=dq, dk=dk, dv=dv)
+        print(f"{name}: wrote {os.path.getsize(path) / 1024:.0f} KiB")
+    for name, (spec, window, global_tokens) in WINDOW_CASES.items():
+        q, k, v, dout = make_case(*spec)
+        o, lse, dq, dk, dv = cpu.ref_layer_fwd_bwd(q, k, v, dout, window=window, global_tokens=global_tokens)
+        path = os.path.join(HERE, name + ".npz")
+        np.savez_compressed(path, q=q, k=k, v=v, dout=dout, o=o, lse=lse, dq=dq, dk=dk, dv=dv,
+                            window=np.int32(window), global_tokens=np.int32(global_tokens))
         print(f"{name}: wrote {os.path.getsize(path) / 1024:.0f} KiB")
 
 

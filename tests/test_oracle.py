@@ -4,7 +4,7 @@ smokes assert (GQA == MHA with repeated K/V, finite differences)."""
 import numpy as np
 import pytest
 
-from conftest import GOLDEN_CASES, load_golden, max_abs
+from conftest import GOLDEN_CASES, WINDOW_GOLDEN_CASES, load_golden, max_abs
 
 
 @pytest.mark.parametrize("name", GOLDEN_CASES)
@@ -18,6 +18,41 @@ def test_oracle_matches_reference_golden(oracle, name):
     assert max_abs(dq, g["dq"]) < 2e-5
     assert max_abs(dk, g["dk"]) < 2e-5
     assert max_abs(dv, g["dv"]) < 2e-5
+
+
+@pytest.mark.parametrize("name", WINDOW_GOLDEN_CASES)
+def test_oracle_sliding_window_matches_reference_golden(oracle, name):
+    """Sliding window + global tokens (CausalSelfAttention::allowsKey): the reference layer's frozen outputs."""
+    g = load_golden(name)
+    kw = dict(window=int(g["window"]), global_tokens=int(g["global_tokens"]))
+    o, lse = oracle.attn_fwd(g["q"], g["k"], g["v"], **kw)
+    dq, dk, dv, _ = oracle.attn_bwd(g["q"], g["k"], g["v"], g["dout"], **kw)
+    assert max_abs(o, g["o"]) < 5e-6
+    assert max_abs(lse, g["lse"]) < 5e-6
+    assert max_abs(dq, g["dq"]) < 2e-5
+    assert max_abs(dk, g["dk"]) < 2e-5
+    assert max_abs(dv, g["dv"]) < 2e-5
+    # the mask really bites: plain causal attention on the same inputs differs
+    o_plain, _ = oracle.attn_fwd(g["q"], g["k"], g["v"])
+    assert max_abs(o_plain, g["o"]) > 1e-3
+
+
+def test_oracle_window_mask_is_allows_key(oracle):
+    """With V = one-hot rows, O[i] is the probability vector of query i: it must be zero exactly where the
+    reference's allowsKey (CausalSelfAttention.cpp:95-100) says false, and a window >= S is plain causal."""
+    S, W, G = 24, 5, 3
+    rng = np.random.default_rng(3)
+    q = rng.standard_normal((1, 1, S, S), dtype=np.float32)
+    k = rng.standard_normal((1, 1, S, S), dtype=np.float32)
+    v = np.eye(S, dtype=np.float32)[None, None]
+    o, _ = oracle.attn_fwd(q, k, v, window=W, global_tokens=G)
+    for i in range(S):
+        for j in range(S):
+            allowed = j <= i and (j < G or j >= i - W + 1)
+            assert (o[0, 0, i, j] > 0) == allowed, (i, j)
+    o_wide, _ = oracle.attn_fwd(q, k, v, window=S, global_tokens=0)
+    o_plain, _ = oracle.attn_fwd(q, k, v)
+    assert np.array_equal(o_wide, o_plain)
 
 
 def test_reference_live_matches_golden_and_core_route(oracle):
