@@ -172,6 +172,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--batch", type=int, default=0, help="override the workload's per-GPU batch (profiling captures)")
     ap.add_argument("--skip-e2e", action="store_true", help="skip the host-buffer leg (profiling captures)")
+    ap.add_argument("--window", type=int, default=0, help="sliding window (keys per query); 0 = the workload's plain causal mask")
+    ap.add_argument("--global-tokens", type=int, default=0, help="always-visible first keys (with --window)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -221,17 +223,21 @@ def main():
 
     state = {}
 
+    mask = dict(window=args.window, global_tokens=args.global_tokens) if args.window > 0 else {}
+    if mask and ring is not None:
+        raise SystemExit("--window applies to the unsharded workloads")
+
     def fwd():
         if ring is not None:
             state["o"], state["lse"] = ring.forward(qd, kd, vd)
         else:
-            sb.attention_forward(qd, kd, vd, out=o, lse=lse)
+            sb.attention_forward(qd, kd, vd, out=o, lse=lse, **mask)
 
     def bwd():
         if ring is not None:
             ring.backward(qd, kd, vd, state["o"], state["lse"], dod)
         else:
-            sb.attention_backward(qd, kd, vd, o, lse, dod, dq=dq, dk=dk, dv=dv)
+            sb.attention_backward(qd, kd, vd, o, lse, dod, dq=dq, dk=dk, dv=dv, **mask)
 
     def step():
         fwd()
@@ -271,6 +277,13 @@ def main():
         bwd_ms = timed(bwd, args.steps) / args.steps
     ms_per_step = total_ms / args.steps
     flops_rank = w.flops / world if ring is not None else w.flops     # the ring workload's FLOPs are for the whole sequence
+    if mask:
+        # 7 GEMM-shaped products of 2*D flops per visible (query, key) pair; the plain causal figure is the same rule
+        # with S*S/2 pairs
+        import numpy as np
+        qi = np.arange(w.seq, dtype=np.int64)
+        pairs = np.minimum(qi + 1, args.window) + np.clip(np.minimum(args.global_tokens, qi - args.window + 1), 0, None)
+        flops_rank = 14.0 * w.head_dim * w.batch * w.q_heads * float(pairs.sum())
     value = flops_rank * world / (ms_per_step * 1e-3) / 1e12
 
     # end to end through the host-buffer call: H2D of Q,K,V,dO, forward+backward, D2H of O,LSE,dQ,dK,dV
@@ -282,7 +295,7 @@ def main():
             outs = [t.to("cpu", non_blocking=True) for t in (o_, lse_) + tuple(grads)]
             torch.cuda.current_stream().synchronize()
         else:
-            sb.attention_forward_backward_host(q, k, v, do, device=dev)
+            sb.attention_forward_backward_host(q, k, v, do, device=dev, **mask)
 
     if args.skip_e2e:
         e2e_ms = float("nan")
@@ -325,7 +338,9 @@ def main():
                            "parallelism": (f"sequence split into {world} contiguous shards, zigzag-balanced ring of K/V chunks over NCCL"
                                            if ring is not None else f"batch x KV-group sharding over {world} GPU(s), no communication"),
                            "l2": "per-step working set (Q,K,V,O,dO,dQ,dK,dV,dQ-accumulator) > 0.8 GB, larger than the 126 MB L2",
-                           "kernel_path": sb.last_path()},
+                           "kernel_path": sb.last_path(),
+                           **({"window": args.window, "global_tokens": args.global_tokens,
+                               "flop_rule": "14*D per visible (query, key) pair"} if mask else {})},
                 "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                         "ms_per_step": None if args.skip_e2e else e2e_ms},
                 "gpu_launches": int(launches), "clocks": clocks.summary(), "roofline": roofline,

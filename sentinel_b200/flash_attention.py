@@ -109,11 +109,13 @@ def attention_backward(q, k, v, o, lse, dout, *, causal=True, scale=None, flags=
     return dq, dk, dv
 
 
-def attention_forward_backward_host(q, k, v, dout, *, causal=True, scale=None, flags=0, device="cuda", chunks=None):
+def attention_forward_backward_host(q, k, v, dout, *, causal=True, scale=None, flags=0, device="cuda", chunks=None,
+                                    window=0, global_tokens=0):
     """End-to-end call on HOST tensors (pinned memory recommended): uploads Q, K, V, dO, runs forward and
     backward on the device, downloads O, LSE, dQ, dK, dV.  This is the path the benchmark's ``e2e`` times."""
     from .host_pipeline import forward_backward_host   # transfers overlapped with the kernels, chunked over (batch, KV group)
-    return forward_backward_host(q, k, v, dout, causal=causal, scale=scale, flags=flags, device=device, chunks=chunks)
+    return forward_backward_host(q, k, v, dout, causal=causal, scale=scale, flags=flags, device=device, chunks=chunks,
+                                 window=window, global_tokens=global_tokens)
 
 
 def merge_partials(o_acc, lse_acc, o_part, lse_part):

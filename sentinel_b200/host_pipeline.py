@@ -59,7 +59,8 @@ def _chunk_slices(B, Hq, Hkv, chunks):
     return out
 
 
-def forward_backward_host(q, k, v, dout, *, causal=True, scale=None, flags=0, device="cuda", chunks=None):
+def forward_backward_host(q, k, v, dout, *, causal=True, scale=None, flags=0, device="cuda", chunks=None, window=0,
+                          global_tokens=0):
     """Returns host tensors (O, LSE, dQ, dK, dV).  ``chunks`` = number of pipeline chunks (default: up to 4, cut along
     batch elements first and KV groups second; every chunk is a complete attention problem)."""
     dev = torch.device(device)
@@ -84,7 +85,7 @@ def forward_backward_host(q, k, v, dout, *, causal=True, scale=None, flags=0, de
             ev_do.record(up)
         comp.wait_event(ev_qkv)
         fa.attention_forward(buf["q"][qs], buf["k"][ks], buf["v"][ks], causal=causal, scale=scale, flags=flags,
-                             out=buf["o"][qs], lse=buf["lse"][qs])
+                             out=buf["o"][qs], lse=buf["lse"][qs], window=window, global_tokens=global_tokens)
         ev_fwd = torch.cuda.Event()
         ev_fwd.record(comp)
         with torch.cuda.stream(down):
@@ -93,7 +94,8 @@ def forward_backward_host(q, k, v, dout, *, causal=True, scale=None, flags=0, de
             buf["h_lse"][qs].copy_(buf["lse"][qs], non_blocking=True)
         comp.wait_event(ev_do)
         fa.attention_backward(buf["q"][qs], buf["k"][ks], buf["v"][ks], buf["o"][qs], buf["lse"][qs], buf["do"][qs],
-                              causal=causal, scale=scale, flags=flags, dq=buf["dq"][qs], dk=buf["dk"][ks], dv=buf["dv"][ks])
+                              causal=causal, scale=scale, flags=flags, dq=buf["dq"][qs], dk=buf["dk"][ks], dv=buf["dv"][ks],
+                              window=window, global_tokens=global_tokens)
         ev_bwd = torch.cuda.Event()
         ev_bwd.record(comp)
         with torch.cuda.stream(down):

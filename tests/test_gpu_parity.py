@@ -440,3 +440,37 @@ def test_sliding_window_through_reference_operator_classes(sb, name, reduced):
     rc = lib.sntl_compat_forward_backward_windowed(fp(q), fp(k), fp(v), None, Hq, Hkv, D, stride, D ** -0.5, 1, col0, S, B, W, -1,
                                                    0, fp(out), fp(lse), None, None, None, path, 64, err, 256)
     assert rc == 1 and b"globalTokenCount" in err.value
+
+
+def test_full_size_sliding_window_sampled_oracle(sb, oracle):
+    """The headline shape (batch cut to one element) with a 1024-key window and 64 global tokens: sampled oracle rows and
+    key columns, and the properties that do not depend on size."""
+    w = sb.WORKLOADS["gqa7b_d128"]
+    W, G = 1024, 64
+    q, k, v, do = _bf16_case(w, batch=1)
+    qd, kd, vd, dod = (t.cuda() for t in (q, k, v, do))
+    o, lse = sb.attention_forward(qd, kd, vd, window=W, global_tokens=G)
+    assert sb.last_path() == "tcgen05"
+    dq, dk, dv = sb.attention_backward(qd, kd, vd, o, lse, dod, window=W, global_tokens=G)
+    assert sb.poll_device_status() == 0
+    qf, kf, vf, dof = (t.to(torch.float32).numpy() for t in (q, k, v, do))
+    S = w.seq
+    rows = np.array([63, 64, 127, 1023, 1024, 1150, S // 2, S - 129, S - 1])
+    for h in (0, w.q_heads - 1):
+        wo, wl, wdq = oracle.attn_rows(qf, kf, vf, dof, 0, h, rows, window=W, global_tokens=G)
+        _check_bf16(_np(o[0, h, rows]), wo, "o rows")
+        assert max_abs(_np(lse[0, h, rows]), wl) <= 1e-3
+        _check_bf16(_np(dq[0, h, rows]), wdq, "dq rows")
+    cols = np.array([0, 63, 64, 127, 128, S // 2, S - 1025, S - 1])     # global keys, the first window-only key, late keys
+    hk = w.kv_heads - 1
+    wdk, wdv = oracle.attn_cols(qf, kf, vf, dof, 0, hk, cols, window=W, global_tokens=G)
+    _check_bf16(_np(dk[0, hk, cols]), wdk, "dk cols")
+    _check_bf16(_np(dv[0, hk, cols]), wdv, "dv cols")
+    # constant V => O is that constant; a window that covers the sequence is plain causal attention, bit for bit
+    o1, _ = sb.attention_forward(qd, kd, torch.ones_like(vd), window=W, global_tokens=G)
+    assert float((o1.float() - 1.0).abs().max()) <= 1e-2
+    o_wide, lse_wide = sb.attention_forward(qd, kd, vd, window=S, global_tokens=G)
+    o_plain, lse_plain = sb.attention_forward(qd, kd, vd)
+    assert torch.equal(o_wide, o_plain) and torch.equal(lse_wide, lse_plain)
+    # the first W rows see every earlier key, so they match plain causal attention exactly
+    assert torch.equal(o[:, :, :W], o_plain[:, :, :W])
