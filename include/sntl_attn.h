@@ -110,6 +110,21 @@ size_t sntl_attn_bwd_workspace_bytes(const sntl_attn_desc* desc);
 int sntl_attn_fwd(const sntl_attn_desc* desc, const void* q, const void* k, const void* v, void* o, float* lse,
                   void* workspace, size_t workspace_bytes, void* stream);
 
+/* New tokens against a KV cache, forward only: the reference's attendCachedQuery / decode
+ * (CudaCausalSelfAttention.cu:318-341, :557-571) and, with seq_q > 1, a prefill continued from a cache.
+ *   desc->seq_q   new tokens per head (1 for decode); desc->seq_kv  keys in use, the new tokens' own keys included
+ *   (append before calling, as the reference does); query i sits at position seq_kv - seq_q + i and sees keys
+ *   j <= that position, subject to window_size / global_tokens; desc->causal must be 1.
+ *   BHSD:     q, o [B][Hq][seq_q][D]; k_cache, v_cache [B][Hkv][cache_capacity][D]; lse [B][Hq][seq_q].
+ *   SENTINEL: q, o (Hq*D) x stride_columns with the new tokens at columns [column_start, column_start + seq_q);
+ *             k_cache, v_cache (Hkv*D) x cache_capacity, key j in column j (CudaKvCache); batch must be 1.
+ * bf16 BHSD tensors with head_dim 64 / 128 run on the tensor-core kernel: the query heads of one KV group are the
+ * rows of one tile (K/V are read once per group) and the keys are split over about one CTA per SM, merged by a
+ * second kernel.  Everything else runs on the exact kernel.  Scratch: sntl_attn_cached_fwd_workspace_bytes(). */
+size_t sntl_attn_cached_fwd_workspace_bytes(const sntl_attn_desc* desc, int32_t cache_capacity);
+int sntl_attn_cached_fwd(const sntl_attn_desc* desc, const void* q, const void* k_cache, const void* v_cache,
+                         int32_t cache_capacity, void* o, float* lse, void* workspace, size_t workspace_bytes, void* stream);
+
 /* dQ, dK, dV from dO with P recomputed as exp(scale*q.k - LSE) and delta = rowsum(dO o O).
  * dq: q_heads heads, overwritten.  dk, dv: kv_heads heads, overwritten with the sum over the query heads
  * of each group.  Asynchronous on `stream`. */

@@ -32,7 +32,10 @@
  *
  * Sequence lengths may differ between queries and keys (used by the ring
  * schedule's off-diagonal blocks, which are non-causal).  With causal != 0 a
- * key j is visible to query i iff j <= i + (Skv - Sq).
+ * key j is visible to query i iff j <= i + (Skv - Sq): query i sits at
+ * position i + (Skv - Sq), the case of new tokens attending a KV cache
+ * (sentinel/NeuralNet/Cuda/CudaCausalSelfAttention.cu:318-341); the window is
+ * measured from that position too.
  */
 #include <math.h>
 #include <stddef.h>
@@ -77,7 +80,7 @@ static double score_row(const oracle_shape* s, int query, const float* q, const 
 {
     double m = -INFINITY;
     for (int j = 0; j < n; ++j) {
-        if (!window_allows(s, query, j)) { p[j] = -INFINITY; continue; }
+        if (!window_allows(s, query + (s->causal ? s->seq_kv - s->seq_q : 0), j)) { p[j] = -INFINITY; continue; }
         const float* k = kbase + (size_t)j * d;
         double acc = 0.0;
         for (int t = 0; t < d; ++t) acc += (double)q[t] * (double)k[t];

@@ -6,10 +6,12 @@ Python host side: it binds that ABI with ctypes and mirrors the reference's oper
 (``CudaFlashAttention``).  PyTorch is used for device memory, streams and process groups only.
 """
 from . import _lib
-from .flash_attention import (CudaFlashAttention, accumulate, attention_backward, attention_forward, attention_forward_backward_host,
+from .flash_attention import (CudaFlashAttention, accumulate, attention_backward, attention_cached_forward, attention_forward,
+                              attention_forward_backward_host,
                               last_path, launch_count, merge_partials, poll_device_status)
 from .workloads import WORKLOADS, Workload, make_inputs
 
-__all__ = ["CudaFlashAttention", "attention_forward", "attention_backward", "attention_forward_backward_host",
+__all__ = ["CudaFlashAttention", "attention_forward", "attention_backward", "attention_cached_forward",
+           "attention_forward_backward_host",
            "merge_partials", "accumulate", "last_path", "launch_count", "poll_device_status", "WORKLOADS", "Workload", "make_inputs",
            "_lib"]

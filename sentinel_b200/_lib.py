@@ -16,7 +16,8 @@ FLAG_ALLOW_BF16_COMPUTE, FLAG_FORCE_SIMT = 1, 2
 # every symbol include/sntl_attn.h declares
 EXPORTS = ["sntl_attn_version", "sntl_status_string", "sntl_attn_fwd_workspace_bytes", "sntl_attn_bwd_workspace_bytes",
            "sntl_attn_fwd", "sntl_attn_bwd", "sntl_attn_merge", "sntl_attn_last_path", "sntl_attn_launch_count",
-           "sntl_attn_poll_device_status", "sntl_attn_bwd_static_scratch", "sntl_attn_static_scratch_capacity", "sntl_attn_accumulate"]
+           "sntl_attn_poll_device_status", "sntl_attn_bwd_static_scratch", "sntl_attn_static_scratch_capacity", "sntl_attn_accumulate",
+           "sntl_attn_cached_fwd", "sntl_attn_cached_fwd_workspace_bytes"]
 ERR_SCRATCH_LIMIT = 7
 
 
@@ -54,6 +55,10 @@ def load():
     lib.sntl_attn_bwd_workspace_bytes.argtypes = [dp]
     lib.sntl_attn_fwd.restype = C.c_int
     lib.sntl_attn_fwd.argtypes = [dp, vp, vp, vp, vp, vp, vp, sz, vp]
+    lib.sntl_attn_cached_fwd_workspace_bytes.restype = sz
+    lib.sntl_attn_cached_fwd_workspace_bytes.argtypes = [dp, C.c_int32]
+    lib.sntl_attn_cached_fwd.restype = C.c_int
+    lib.sntl_attn_cached_fwd.argtypes = [dp, vp, vp, vp, C.c_int32, vp, vp, vp, sz, vp]
     lib.sntl_attn_bwd.restype = C.c_int
     lib.sntl_attn_bwd.argtypes = [dp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, sz, vp]
     lib.sntl_attn_bwd_static_scratch.restype = C.c_int

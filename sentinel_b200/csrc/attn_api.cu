@@ -221,6 +221,82 @@ int sntl_attn_fwd(const sntl_attn_desc* d, const void* q, const void* k, const v
     return SNTL_OK;
 }
 
+namespace sntl {
+namespace {
+
+// seq_q new tokens per head against seq_kv cached keys (the new tokens' own keys included, at the end)
+int validate_cached(const sntl_attn_desc* d, int32_t capacity)
+{
+    if (!d) return SNTL_ERR_BAD_ARGUMENT;
+    if (d->dtype != SNTL_DTYPE_BF16 && d->dtype != SNTL_DTYPE_F32) return SNTL_ERR_BAD_ARGUMENT;
+    if (d->layout != SNTL_LAYOUT_BHSD && d->layout != SNTL_LAYOUT_SENTINEL) return SNTL_ERR_BAD_ARGUMENT;
+    if (d->batch <= 0 || d->q_heads <= 0 || d->kv_heads <= 0 || d->seq_q <= 0 || d->seq_kv <= 0 || d->head_dim <= 0)
+        return SNTL_ERR_BAD_ARGUMENT;
+    if (d->q_heads % d->kv_heads != 0) return SNTL_ERR_BAD_ARGUMENT;
+    if (!d->causal) return SNTL_ERR_BAD_ARGUMENT;                 // a cached query never sees later keys
+    if (d->seq_q > d->seq_kv) return SNTL_ERR_BAD_ARGUMENT;       // the new tokens are appended before the call
+    if (capacity < d->seq_kv) return SNTL_ERR_BAD_ARGUMENT;       // CudaCausalSelfAttention.cu:566 (cache full)
+    if (!(d->scale > 0.0f)) return SNTL_ERR_BAD_ARGUMENT;
+    if (d->global_tokens < 0) return SNTL_ERR_BAD_ARGUMENT;
+    if (d->head_dim > 256 || d->head_dim % 2 != 0) return SNTL_ERR_UNSUPPORTED;
+    if (d->batch > 65535 || d->q_heads > 65535) return SNTL_ERR_UNSUPPORTED;
+    if (d->layout == SNTL_LAYOUT_SENTINEL) {
+        if (d->dtype != SNTL_DTYPE_F32) return SNTL_ERR_UNSUPPORTED;
+        if (d->batch != 1) return SNTL_ERR_UNSUPPORTED;           // the reference's cache holds one sequence
+        if (d->column_start < 0 || d->stride_columns <= 0) return SNTL_ERR_BAD_ARGUMENT;
+        if ((long long)d->column_start + d->seq_q > (long long)d->stride_columns) return SNTL_ERR_BAD_ARGUMENT;
+    }
+    return SNTL_OK;
+}
+
+bool cached_wants_tc(const sntl_attn_desc* d)
+{
+    if (d->flags & SNTL_FLAG_FORCE_SIMT) return false;
+    if (d->dtype != SNTL_DTYPE_BF16 || d->layout != SNTL_LAYOUT_BHSD) return false;
+    return tc_cache_supported(shape_of(d));
+}
+
+}  // namespace
+}  // namespace sntl
+
+size_t sntl_attn_cached_fwd_workspace_bytes(const sntl_attn_desc* d, int32_t cache_capacity)
+{
+    if (validate_cached(d, cache_capacity) != SNTL_OK || !cached_wants_tc(d)) return 0;
+    return tc_cache_workspace_bytes(shape_of(d));
+}
+
+int sntl_attn_cached_fwd(const sntl_attn_desc* d, const void* q, const void* k_cache, const void* v_cache,
+                         int32_t cache_capacity, void* o, float* lse, void* workspace, size_t workspace_bytes, void* stream)
+{
+    int rc = validate_cached(d, cache_capacity);
+    if (rc != SNTL_OK) return rc;
+    if (!q || !k_cache || !v_cache || !o || !lse) return SNTL_ERR_BAD_ARGUMENT;
+    if (!device_ok()) return SNTL_ERR_NO_DEVICE;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (cached_wants_tc(d)) {
+        const size_t need = tc_cache_workspace_bytes(shape_of(d));
+        if (need && (!workspace || workspace_bytes < need)) return SNTL_ERR_WORKSPACE;
+        TcArgs t{};
+        t.s = shape_of(d);
+        t.q = (const __nv_bfloat16*)q; t.k = (const __nv_bfloat16*)k_cache; t.v = (const __nv_bfloat16*)v_cache;
+        t.o_out = (__nv_bfloat16*)o; t.lse_out = lse;
+        g_last_path = "tcgen05_cache";
+        return cuda_status(tc_cache_forward(t, cache_capacity, workspace, st));
+    }
+    // exact kernels: the same forward kernel, keys addressed with the cache's row pitch
+    SimtArgs a{};
+    a.s = shape_of(d);
+    a.is_bf16 = d->dtype == SNTL_DTYPE_BF16;
+    const size_t off = d->layout == SNTL_LAYOUT_SENTINEL ? (size_t)d->column_start * sizeof(float) : 0;
+    a.q = (const char*)q + off; a.k = k_cache; a.v = v_cache;
+    a.o_out = (char*)o + off; a.lse_out = (float*)((char*)lse + off);
+    views(d, a.vq, a.vkv, a.vlse);
+    const long long D = d->head_dim, C = cache_capacity;
+    a.vkv = d->layout == SNTL_LAYOUT_BHSD ? View4{(long long)d->kv_heads * C * D, C * D, D, 1} : View4{0, D * C, 1, C};
+    g_last_path = a.is_bf16 ? "simt_bf16" : "simt_f32";
+    return cuda_status(simt_forward(a, st));
+}
+
 int sntl_attn_bwd(const sntl_attn_desc* d, const void* q, const void* k, const void* v, const void* o,
                   const float* lse, const void* dout, void* dq, void* dk, void* dv, void* workspace,
                   size_t workspace_bytes, void* stream)

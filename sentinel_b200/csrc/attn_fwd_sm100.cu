@@ -25,6 +25,7 @@
 #include "common.cuh"
 #include "sm100_ptx.cuh"
 
+#include <algorithm>
 #include <mutex>
 
 namespace sntl {
@@ -49,6 +50,10 @@ struct FwdParams {
     int B, Hq, Hkv, Sq, Skv;
     int causal;
     int window, global_tokens;   // sliding window and always-visible first keys (0, 0: plain causal)
+    // KV-cache mode: the rows of one slab are the (query head of the group, new token) pairs of one KV head, row r
+    // sits at position Skv - new_tokens + r % new_tokens, and the key tiles are dealt to n_splits CTAs whose partial
+    // (O, LSE) land in o / lse as [split][slab][row]
+    int new_tokens, n_splits, tiles_per_split;
     int n_qblk;       // 256-row query blocks per (b, h)
     float scale_log2; // scale * log2(e)
 };
@@ -62,8 +67,12 @@ struct FwdBarriers {
     uint32_t abort_flag;
 };
 
-// kWin: sliding-window instantiation (separate so that the plain causal kernel carries none of its bookkeeping)
-template <int D, bool kWin>
+// kMode: kPlain = causal / full attention of a whole sequence; kWindow adds the sliding window (separate so that the
+// plain kernel carries none of its bookkeeping); kCache = new tokens against a KV cache, grouped-query heads packed into
+// the rows of one tile, keys split over CTAs.
+enum FwdMode : int { kPlain = 0, kWindow = 1, kCache = 2 };
+
+template <int D, int kMode>
 __global__ void __launch_bounds__(kFwdThreads, 1)
 attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                    const __grid_constant__ CUtensorMap tmap_v, const FwdParams p)
@@ -82,25 +91,44 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
     // ---- work decode: heaviest query blocks first; the heads of one KV group are adjacent ----
-    const int bh_count = p.B * p.Hq;
-    const int qblk_rank = blockIdx.x / bh_count;
+    constexpr bool kWin = kMode != kPlain;
+    const int bh_count = kMode == kCache ? p.B * p.Hkv : p.B * p.Hq;
+    int qblk_rank = blockIdx.x / bh_count;
     const int bh = blockIdx.x - qblk_rank * bh_count;
-    const int qblk = p.causal ? (p.n_qblk - 1 - qblk_rank) : qblk_rank;
-    const int b = bh / p.Hq, h = bh - b * p.Hq;
-    const int bh_kv = b * p.Hkv + h / (p.Hq / p.Hkv);
+    int split = 0;
+    if (kMode == kCache) {
+        split = qblk_rank / p.n_qblk;
+        qblk_rank -= split * p.n_qblk;
+    }
+    const int qblk = (p.causal && kMode != kCache) ? (p.n_qblk - 1 - qblk_rank) : qblk_rank;
+    int bh_kv = bh;
+    if (kMode != kCache) {
+        const int b = bh / p.Hq, h = bh - b * p.Hq;
+        bh_kv = b * p.Hkv + h / (p.Hq / p.Hkv);
+    }
     const int q0 = qblk * 2 * kM;
     const int n_ktiles_all = (p.Skv + kN - 1) / kN;
+    // position of a row in its sequence (what the causal and window masks compare keys with)
+    auto row_pos = [&](int r) { return kMode == kCache ? p.Skv - p.new_tokens + r % p.new_tokens : r; };
     // Key tiles this CTA visits, in ascending order: the tiles holding global tokens, then the tiles from the window
     // of the block's first query row up to the diagonal.  Without a window that is simply 0 .. diagonal.
-    const int g_tiles = kWin ? (p.global_tokens + kN - 1) / kN : 0;
-    const int w_first = kWin ? max(g_tiles, max(0, q0 - p.window + 1) / kN) : 0;
-    auto key_tile = [&](int j) { return j < g_tiles ? j : w_first + (j - g_tiles); };
+    // In cache mode every row of the slab sees keys up to (almost) the end of the cache; the list is cut into
+    // tiles_per_split pieces and this CTA takes piece `split`.
+    const int first_pos = kMode == kCache ? p.Skv - p.new_tokens : q0;   // lowest position among the CTA's rows
+    const bool windowed = kWin && p.window > 0;
+    const int g_tiles = windowed ? (p.global_tokens + kN - 1) / kN : 0;
+    const int w_first = windowed ? max(g_tiles, max(0, first_pos - p.window + 1) / kN) : 0;
+    const int list0 = kMode == kCache ? split * p.tiles_per_split : 0;
+    auto key_tile = [&](int j) { j += list0; return j < g_tiles ? j : w_first + (j - g_tiles); };
     int n_t[2];
 #pragma unroll
     for (int t = 0; t < 2; ++t) {
         const int row0 = q0 + t * kM;
         if (row0 >= p.Sq) n_t[t] = 0;
-        else if (p.causal) {
+        else if (kMode == kCache) {
+            const int n_list = min(g_tiles, n_ktiles_all) + max(0, n_ktiles_all - w_first);
+            n_t[t] = max(0, min(p.tiles_per_split, n_list - list0));
+        } else if (p.causal) {
             const int diag = min(n_ktiles_all - 1, row0 / kN);
             n_t[t] = min(g_tiles, diag + 1) + max(0, diag - w_first + 1);
         } else n_t[t] = n_ktiles_all;
@@ -259,15 +287,16 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
             SNTL_TRACE_EV(tw, 1 + t, tn, 2);
             // number of visible keys of this row inside this tile
             const int key0 = key_tile(j) * kN;
-            int limit = (p.causal ? min(p.Skv, grow + 1) : p.Skv) - key0;
+            const int qpos = row_pos(grow);
+            int limit = (p.causal ? min(p.Skv, qpos + 1) : p.Skv) - key0;
             if (limit < kN) {
 #pragma unroll
                 for (int c = 0; c < kN; ++c)
                     if (c >= limit) s[c] = 0xff800000u;  // -inf
             }
-            if (kWin) {
+            if (kWin && (kMode != kCache || p.window > 0)) {
                 // keys below the row's window are hidden unless they are global tokens
-                const int lo = grow - p.window + 1 - key0, glim = p.global_tokens - key0;
+                const int lo = qpos - p.window + 1 - key0, glim = p.global_tokens - key0;
                 if (lo > 0 && glim < min(lo, kN)) {
 #pragma unroll
                     for (int c = 0; c < kN; ++c)
@@ -332,7 +361,8 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
             tc_fence_after();
             const float inv = l > 0.0f ? 1.0f / l : 0.0f;
             const bool store = grow < p.Sq;
-            __nv_bfloat16* orow = p.o + ((size_t)bh * p.Sq + (size_t)(store ? grow : 0)) * D;
+            const size_t out_row = ((size_t)split * bh_count + bh) * p.Sq + (size_t)(store ? grow : 0);   // split = 0 outside cache mode
+            __nv_bfloat16* orow = p.o + out_row * D;
 #pragma unroll
             for (int c = 0; c < D / 32; ++c) {
                 uint32_t o[32];
@@ -351,7 +381,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
                 }
             }
             if (store)
-                p.lse[(size_t)bh * p.Sq + grow] = l > 0.0f ? (m_ref + log2f(l)) * 0.6931471805599453f : -INFINITY;
+                p.lse[out_row] = l > 0.0f ? (m_ref + log2f(l)) * 0.6931471805599453f : -INFINITY;
         }
     }
 
@@ -386,7 +416,7 @@ EncodeTiledFn encode_fn()
     return fn;
 }
 
-template <int D, bool kWin>
+template <int D, int kMode>
 cudaError_t launch_fwd(const TcArgs& a, cudaStream_t st)
 {
     const AttnShape& s = a.s;
@@ -407,26 +437,157 @@ cudaError_t launch_fwd(const TcArgs& a, cudaStream_t st)
     const size_t smem = 6 * (size_t)(128 * D * 2) + sizeof(FwdBarriers) + 1024;
     static bool configured = false;  // per instantiation
     if (!configured) {
-        if ((e = cudaFuncSetAttribute(attn_fwd_tc_kernel<D, kWin>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)) != cudaSuccess)
+        if ((e = cudaFuncSetAttribute(attn_fwd_tc_kernel<D, kMode>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)) != cudaSuccess)
             return e;
         configured = true;
     }
     const long long ctas = (long long)p.n_qblk * s.B * s.Hq;
     if (ctas > 0x7fffffffLL) return cudaErrorInvalidConfiguration;
-    attn_fwd_tc_kernel<D, kWin><<<(unsigned)ctas, kFwdThreads, smem, st>>>(tq, tk, tv, p);
+    attn_fwd_tc_kernel<D, kMode><<<(unsigned)ctas, kFwdThreads, smem, st>>>(tq, tk, tv, p);
     count_launch();
     return cudaGetLastError();
 }
 
+// ---- KV-cache mode ----------------------------------------------------------------------------------------------
+// Combines the per-split partial results: LSE = log sum_s exp(lse_s), O = sum_s exp(lse_s - LSE) * O_s.  One warp per
+// row; a split that saw no visible key for the row carries LSE = -inf and weighs nothing.
+template <int D>
+__global__ void __launch_bounds__(256) cache_merge_kernel(const __nv_bfloat16* __restrict__ o_part, const float* __restrict__ lse_part,
+                                                          int n_splits, long long rows, __nv_bfloat16* __restrict__ o,
+                                                          float* __restrict__ lse)
+{
+    const long long r = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (r >= rows) return;
+    float m = -INFINITY;
+    for (int sp = lane; sp < n_splits; sp += 32) m = fmaxf(m, lse_part[(size_t)sp * rows + r]);
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, off));
+    float sum = 0.0f;
+    if (m > -INFINITY)
+        for (int sp = lane; sp < n_splits; sp += 32) sum += __expf(lse_part[(size_t)sp * rows + r] - m);
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
+    const float total = m > -INFINITY ? m + __logf(sum) : -INFINITY;
+    constexpr int kPer = D / 32;   // consecutive elements per lane
+    float acc[kPer];
+#pragma unroll
+    for (int i = 0; i < kPer; ++i) acc[i] = 0.0f;
+    for (int sp = 0; sp < n_splits; ++sp) {
+        const float l = lse_part[(size_t)sp * rows + r];
+        if (!(l > -INFINITY)) continue;
+        const float w = __expf(l - total);
+        const __nv_bfloat16* src = o_part + ((size_t)sp * rows + r) * D + lane * kPer;
+#pragma unroll
+        for (int i = 0; i < kPer; ++i) acc[i] = fmaf(w, __bfloat162float(src[i]), acc[i]);
+    }
+    __nv_bfloat16* dst = o + (size_t)r * D + lane * kPer;
+#pragma unroll
+    for (int i = 0; i < kPer; ++i) dst[i] = __float2bfloat16(acc[i]);
+    if (lane == 0) lse[r] = total;
+}
+
+template <int D>
+cudaError_t launch_cache(const TcArgs& a, int capacity, void* workspace, cudaStream_t st)
+{
+    const AttnShape& s = a.s;
+    const CachePlan plan = tc_cache_plan(s);
+    const int group = s.Hq / s.Hkv, rows_per_slab = group * s.Sq, slabs = s.B * s.Hkv;
+    const long long rows = (long long)slabs * rows_per_slab;
+    CUtensorMap tq, tk, tv;
+    cudaError_t e;
+    // Q [B][Hq][new][D] read as [B*Hkv][group*new][D]: the query heads of a group are consecutive heads
+    if ((e = encode_tmap_bf16_3d(&tq, a.q, D, rows_per_slab, slabs, 128)) != cudaSuccess) return e;
+    if ((e = encode_tmap_bf16_3d(&tk, a.k, D, s.Skv, slabs, 128, capacity)) != cudaSuccess) return e;
+    if ((e = encode_tmap_bf16_3d(&tv, a.v, D, s.Skv, slabs, 128, capacity)) != cudaSuccess) return e;
+    __nv_bfloat16* o_part = a.o_out;
+    float* lse_part = a.lse_out;
+    if (plan.n_splits > 1) {
+        lse_part = reinterpret_cast<float*>(workspace);
+        o_part = reinterpret_cast<__nv_bfloat16*>(reinterpret_cast<uint8_t*>(workspace) +
+                                                  (((size_t)plan.n_splits * rows * sizeof(float) + 255) / 256) * 256);
+    }
+    FwdParams p{};
+    p.o = o_part;
+    p.lse = lse_part;
+    p.B = s.B; p.Hq = s.Hq; p.Hkv = s.Hkv; p.Sq = rows_per_slab; p.Skv = s.Skv;
+    p.causal = 1;
+    p.window = s.window;
+    p.global_tokens = s.global_tokens;
+    p.new_tokens = s.Sq;
+    p.n_splits = plan.n_splits;
+    p.tiles_per_split = plan.tiles_per_split;
+    p.n_qblk = (rows_per_slab + 2 * kM - 1) / (2 * kM);
+    p.scale_log2 = s.scale * 1.4426950408889634f;
+    const size_t smem = 6 * (size_t)(128 * D * 2) + sizeof(FwdBarriers) + 1024;
+    static bool configured = false;
+    if (!configured) {
+        if ((e = cudaFuncSetAttribute(attn_fwd_tc_kernel<D, kCache>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)) != cudaSuccess)
+            return e;
+        configured = true;
+    }
+    const long long ctas = (long long)plan.n_splits * p.n_qblk * slabs;
+    if (ctas > 0x7fffffffLL) return cudaErrorInvalidConfiguration;
+    attn_fwd_tc_kernel<D, kCache><<<(unsigned)ctas, kFwdThreads, smem, st>>>(tq, tk, tv, p);
+    count_launch();
+    if ((e = cudaGetLastError()) != cudaSuccess) return e;
+    if (plan.n_splits > 1) {
+        cache_merge_kernel<D><<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(o_part, lse_part, plan.n_splits, rows, a.o_out, a.lse_out);
+        count_launch();
+        e = cudaGetLastError();
+    }
+    return e;
+}
+
 }  // namespace
 
-cudaError_t encode_tmap_bf16_3d(CUtensorMap* out, const void* base, int D, int rows, int slabs, int box_rows)
+// Key tiles the cache-mode kernel visits (global-token tiles, then the window of the oldest new token up to the end of
+// the cache) and how they are dealt to CTAs: about one CTA per SM in total.
+CachePlan tc_cache_plan(const AttnShape& s)
 {
+    const int n_tiles = (s.Skv + kN - 1) / kN;
+    int n_list = n_tiles;
+    if (s.window > 0) {
+        const int g_tiles = (s.global_tokens + kN - 1) / kN;
+        const int first_pos = s.Skv - s.Sq;
+        const int w_first = std::max(g_tiles, std::max(0, first_pos - s.window + 1) / kN);
+        n_list = std::min(g_tiles, n_tiles) + std::max(0, n_tiles - w_first);
+    }
+    const int group = s.Hq / s.Hkv;
+    const long long base = (long long)s.B * s.Hkv * ((group * s.Sq + 2 * kM - 1) / (2 * kM));
+    int want = (int)std::max(1LL, std::min<long long>(n_list, 148 / std::max(1LL, base)));
+    CachePlan plan;
+    plan.tiles_per_split = (n_list + want - 1) / want;
+    plan.n_splits = (n_list + plan.tiles_per_split - 1) / plan.tiles_per_split;
+    return plan;
+}
+
+size_t tc_cache_workspace_bytes(const AttnShape& s)
+{
+    const CachePlan plan = tc_cache_plan(s);
+    if (plan.n_splits <= 1) return 0;
+    const size_t rows = (size_t)s.B * s.Hq * s.Sq;
+    return (((size_t)plan.n_splits * rows * sizeof(float) + 255) / 256) * 256 + (size_t)plan.n_splits * rows * s.D * 2;
+}
+
+bool tc_cache_supported(const AttnShape& s)
+{
+    return (s.D == 64 || s.D == 128) && s.causal && s.Sq <= s.Skv;
+}
+
+cudaError_t tc_cache_forward(const TcArgs& a, int capacity, void* workspace, cudaStream_t st)
+{
+    return a.s.D == 64 ? launch_cache<64>(a, capacity, workspace, st) : launch_cache<128>(a, capacity, workspace, st);
+}
+
+cudaError_t encode_tmap_bf16_3d(CUtensorMap* out, const void* base, int D, int rows, int slabs, int box_rows, int slab_rows)
+{
+    if (slab_rows <= 0) slab_rows = rows;   // rows of storage per slab (a KV cache holds more rows than are in use)
     EncodeTiledFn fn = encode_fn();
     if (!fn) return cudaErrorNotSupported;
     if (((uintptr_t)base & 15u) != 0) return cudaErrorMisalignedAddress;
     cuuint64_t dims[3] = {(cuuint64_t)D, (cuuint64_t)rows, (cuuint64_t)slabs};
-    cuuint64_t strides[2] = {(cuuint64_t)D * 2, (cuuint64_t)rows * D * 2};
+    cuuint64_t strides[2] = {(cuuint64_t)D * 2, (cuuint64_t)slab_rows * D * 2};
     cuuint32_t box[3] = {64u, (cuuint32_t)box_rows, 1u};
     cuuint32_t estr[3] = {1u, 1u, 1u};
     CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
@@ -443,8 +604,8 @@ bool tc_fwd_supported(const AttnShape& s)
 cudaError_t tc_forward(const TcArgs& a, cudaStream_t st)
 {
     const bool win = a.s.causal && a.s.window > 0;
-    if (a.s.D == 64) return win ? launch_fwd<64, true>(a, st) : launch_fwd<64, false>(a, st);
-    return win ? launch_fwd<128, true>(a, st) : launch_fwd<128, false>(a, st);
+    if (a.s.D == 64) return win ? launch_fwd<64, kWindow>(a, st) : launch_fwd<64, kPlain>(a, st);
+    return win ? launch_fwd<128, kWindow>(a, st) : launch_fwd<128, kPlain>(a, st);
 }
 
 #ifdef SNTL_TRACE

@@ -93,6 +93,7 @@ __global__ void __launch_bounds__(kWarps * 32) simt_fwd_kernel(SimtArgs a)
         sq[e] = (row0 + r) < s.Sq ? ldf(qb + (long long)(row0 + r) * a.vq.ss + d * a.vq.sd) : 0.0f;
     }
     const int last_row = min(row0 + kWarps, s.Sq) - 1;
+    const int shift = s.causal ? s.Skv - s.Sq : 0;      // query row r sits at position r + shift (new tokens after a KV cache)
     const int n_block = visible_keys(s, last_row);      // keys any row of the block can see
     const int n_mine = live ? visible_keys(s, row) : 0;
 
@@ -102,7 +103,7 @@ __global__ void __launch_bounds__(kWarps * 32) simt_fwd_kernel(SimtArgs a)
 
     for (int k0 = 0; k0 < n_block; k0 += kTile) {
         // tiles between the global tokens and the window of the block's first row are visible to no row of the block
-        if (s.window > 0 && k0 >= s.global_tokens && k0 + kTile - 1 < row0 - s.window + 1) continue;
+        if (s.window > 0 && k0 >= s.global_tokens && k0 + kTile - 1 < row0 + shift - s.window + 1) continue;
         __syncthreads();
         stage_tile(sk, ld, kb, a.vkv.ss, a.vkv.sd, k0, s.Skv, D);
         stage_tile(sv, ld, vb, a.vkv.ss, a.vkv.sd, k0, s.Skv, D);
@@ -112,7 +113,7 @@ __global__ void __launch_bounds__(kWarps * 32) simt_fwd_kernel(SimtArgs a)
         const float* qr = sq + warp * D;
         const float* kr = sk + lane * ld;
         for (int d = 0; d < D; ++d) sc = fmaf(qr[d], kr[d], sc);
-        sc = (k0 + lane < n_mine && window_allows(s, row, k0 + lane)) ? sc * s.scale : -INFINITY;
+        sc = (k0 + lane < n_mine && window_allows(s, row + shift, k0 + lane)) ? sc * s.scale : -INFINITY;
         const float m_new = fmaxf(m, warp_max(sc));
         if (m_new == -INFINITY) continue;                 // nothing visible yet (tile below this row's window)
         const float p = expf(sc - m_new);
@@ -184,6 +185,7 @@ __global__ void __launch_bounds__(kWarps * 32) simt_dq_kernel(SimtArgs a)
         sg[e] = ok ? ldf((const T*)a.dout + off) : 0.0f;
     }
     const int last_row = min(row0 + kWarps, s.Sq) - 1;
+    const int shift = s.causal ? s.Skv - s.Sq : 0;
     const int n_block = visible_keys(s, last_row);
     const int n_mine = live ? visible_keys(s, row) : 0;
     float lse = 0.0f, delta = 0.0f;
@@ -197,7 +199,7 @@ __global__ void __launch_bounds__(kWarps * 32) simt_dq_kernel(SimtArgs a)
 
     for (int k0 = 0; k0 < n_block; k0 += kTile) {
         // tiles between the global tokens and the window of the block's first row are visible to no row of the block
-        if (s.window > 0 && k0 >= s.global_tokens && k0 + kTile - 1 < row0 - s.window + 1) continue;
+        if (s.window > 0 && k0 >= s.global_tokens && k0 + kTile - 1 < row0 + shift - s.window + 1) continue;
         __syncthreads();
         stage_tile(sk, ld, kb, a.vkv.ss, a.vkv.sd, k0, s.Skv, D);
         stage_tile(sv, ld, vb, a.vkv.ss, a.vkv.sd, k0, s.Skv, D);
@@ -212,7 +214,7 @@ __global__ void __launch_bounds__(kWarps * 32) simt_dq_kernel(SimtArgs a)
             sc = fmaf(qr[d], kr[d], sc);
             dp = fmaf(gr[d], vr[d], dp);
         }
-        const bool vis = (k0 + lane < n_mine) && window_allows(s, row, k0 + lane) && lse > -INFINITY;
+        const bool vis = (k0 + lane < n_mine) && window_allows(s, row + shift, k0 + lane) && lse > -INFINITY;
         const float p = vis ? expf(sc * s.scale - lse) : 0.0f;
         const float ds = p * (dp - delta) * s.scale;
         for (int j = 0; j < kTile; ++j) {
@@ -270,7 +272,7 @@ __global__ void __launch_bounds__(kWarps * 32) simt_dkv_kernel(SimtArgs a)
         const long long qoff = b * a.vq.sb + h * a.vq.sh;
         for (int q0 = (q_first_block / kTile) * kTile; q0 < s.Sq; q0 += kTile) {
             // past the window of the block's last key (and no key of the block is global): no later query sees the block
-            if (s.window > 0 && key0 >= s.global_tokens && q0 > key0 + kWarps - 1 + s.window - 1) break;
+            if (s.window > 0 && key0 >= s.global_tokens && q0 + shift > key0 + kWarps - 1 + s.window - 1) break;
             __syncthreads();
             stage_tile(sq, ld, (const T*)a.q + qoff, a.vq.ss, a.vq.sd, q0, s.Sq, D);
             stage_tile(sg, ld, (const T*)a.dout + qoff, a.vq.ss, a.vq.sd, q0, s.Sq, D);
@@ -292,7 +294,7 @@ __global__ void __launch_bounds__(kWarps * 32) simt_dkv_kernel(SimtArgs a)
             }
             const int qi = q0 + lane;
             const float lse = sl[lane];
-            const bool vis = qi < s.Sq && qi >= q_first_mine && window_allows(s, qi, key) && lse > -INFINITY;
+            const bool vis = qi < s.Sq && qi >= q_first_mine && window_allows(s, qi + shift, key) && lse > -INFINITY;
             const float p = vis ? expf(sc * s.scale - lse) : 0.0f;
             const float ds = p * (dp - sd[lane]) * s.scale;
             for (int i = 0; i < kTile; ++i) {

@@ -60,6 +60,14 @@ struct TcArgs {
 bool tc_fwd_supported(const AttnShape& s);
 bool tc_bwd_supported(const AttnShape& s);
 cudaError_t tc_forward(const TcArgs& a, cudaStream_t st);
+// New tokens against a KV cache (forward only): s.Sq new tokens per head at positions Skv-Sq .. Skv-1, K/V slabs
+// `capacity` rows apart.  The keys are dealt to n_splits CTAs per (KV head, query block); with more than one split the
+// partial results go through `workspace` (tc_cache_workspace_bytes) and a merge kernel.
+struct CachePlan { int n_splits, tiles_per_split; };
+CachePlan tc_cache_plan(const AttnShape& s);
+size_t tc_cache_workspace_bytes(const AttnShape& s);
+bool tc_cache_supported(const AttnShape& s);
+cudaError_t tc_cache_forward(const TcArgs& a, int capacity, void* workspace, cudaStream_t st);
 cudaError_t tc_backward(const TcArgs& a, cudaStream_t st);
 size_t tc_backward_workspace_bytes(const AttnShape& s);
 

@@ -328,6 +328,6 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi)
 
 // Host side: encode a 3-D tiled tensor map over a bf16 [slabs][rows][D] tensor with a {64, box_rows, 1} box and
 // 128-byte swizzle.  The driver entry point is looked up at run time, so the library does not link libcuda.
-cudaError_t encode_tmap_bf16_3d(CUtensorMap* out, const void* base, int D, int rows, int slabs, int box_rows);
+cudaError_t encode_tmap_bf16_3d(CUtensorMap* out, const void* base, int D, int rows, int slabs, int box_rows, int slab_rows = 0);
 
 }  // namespace sntl

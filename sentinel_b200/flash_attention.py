@@ -88,6 +88,36 @@ def attention_forward(q, k, v, *, causal=True, scale=None, flags=0, out=None, ls
     return o, lse
 
 
+def attention_cached_forward(q, k_cache, v_cache, cache_length, *, scale=None, flags=0, out=None, lse=None, window=0,
+                             global_tokens=0):
+    """New tokens against a KV cache (the reference's attendCachedQuery / decode, CudaCausalSelfAttention.cu:318-341).
+
+    q: [B,Hq,T,D], the T newest tokens; k_cache, v_cache: [B,Hkv,capacity,D] with the first ``cache_length`` rows in use,
+    the new tokens' keys already appended at the end.  Query i sits at position cache_length - T + i.  Returns
+    (O [B,Hq,T,D], LSE [B,Hq,T])."""
+    lib = _lib.load()
+    for t, n in ((q, "q"), (k_cache, "k_cache"), (v_cache, "v_cache")):
+        _require(t, n)
+    if k_cache.shape != v_cache.shape or k_cache.dtype != q.dtype or v_cache.dtype != q.dtype:
+        raise ValueError("k_cache and v_cache must share shape; q and the caches must share dtype")
+    if q.dim() != 4 or k_cache.dim() != 4 or k_cache.shape[0] != q.shape[0] or k_cache.shape[3] != q.shape[3]:
+        raise ValueError("expected q [B,Hq,T,D] and caches [B,Hkv,capacity,D]")
+    B, Hq, T, D = q.shape
+    Hkv, capacity = k_cache.shape[1], k_cache.shape[2]
+    if scale is None:
+        scale = D ** -0.5
+    d = _lib.Desc(_dtype_code(q), _lib.LAYOUT_BHSD, B, Hq, Hkv, T, int(cache_length), D, float(scale), 1, 0, 0, int(flags),
+                  int(window), int(global_tokens))
+    o = torch.empty_like(q) if out is None else out
+    lse = torch.empty(q.shape[:3], dtype=torch.float32, device=q.device) if lse is None else lse
+    nbytes = lib.sntl_attn_cached_fwd_workspace_bytes(C.byref(d), capacity)
+    ws = _workspace(nbytes, q.device)
+    rc = lib.sntl_attn_cached_fwd(C.byref(d), q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), capacity, o.data_ptr(),
+                                  lse.data_ptr(), ws.data_ptr() if ws is not None else None, nbytes, _stream_ptr())
+    _lib.check(rc, "sntl_attn_cached_fwd")
+    return o, lse
+
+
 def attention_backward(q, k, v, o, lse, dout, *, causal=True, scale=None, flags=0, dq=None, dk=None, dv=None, window=0,
                        global_tokens=0):
     """dQ, dK, dV from dO (P recomputed from LSE).  Shapes as in attention_forward."""

@@ -55,6 +55,19 @@ def test_oracle_window_mask_is_allows_key(oracle):
     assert np.array_equal(o_wide, o_plain)
 
 
+@pytest.mark.parametrize("name", ["mha_h4_s48_d16", "win64_g5_h4_s200_d32", "win100_g3_h4_kv1_s300_d64_bf16in"])
+def test_oracle_cached_queries_equal_reference_full_sequence_rows(oracle, name):
+    """New tokens against a KV cache (Sq < Skv, query i at position Skv - Sq + i, window measured from there) are the
+    last rows of full causal attention: the reference CPU layer's frozen outputs pin the offset rule."""
+    g = load_golden(name)
+    kw = dict(window=int(g["window"]), global_tokens=int(g["global_tokens"])) if "window" in g else {}
+    S = g["q"].shape[2]
+    for T in (1, 5):
+        o, lse = oracle.attn_fwd(g["q"][:, :, S - T:], g["k"], g["v"], **kw)
+        assert max_abs(o, g["o"][:, :, S - T:]) < 5e-6
+        assert max_abs(lse, g["lse"][:, :, S - T:]) < 5e-6
+
+
 def test_reference_live_matches_golden_and_core_route(oracle):
     """Where the reference CPU path is built: it reproduces its own fixtures bit for bit, and the primitive
     route used for timing is bit-identical to the public layer route."""
