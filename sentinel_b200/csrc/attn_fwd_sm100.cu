@@ -106,7 +106,10 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
         const int b = bh / p.Hq, h = bh - b * p.Hq;
         bh_kv = b * p.Hkv + h / (p.Hq / p.Hkv);
     }
-    const int q0 = qblk * 2 * kM;
+    // plain / window: the CTA owns two consecutive 128-row tiles.  Cache mode: it owns ONE 128-row tile and its two
+    // softmax warpgroups take alternate key tiles of the CTA's piece (two independent streams, each with its own K/V
+    // stage, S and O columns and running max / sum), so one stream's softmax overlaps the other's MMAs.
+    const int q0 = kMode == kCache ? qblk * kM : qblk * 2 * kM;
     const int n_ktiles_all = (p.Skv + kN - 1) / kN;
     // position of a row in its sequence (what the causal and window masks compare keys with)
     auto row_pos = [&](int r) { return kMode == kCache ? p.Skv - p.new_tokens + r % p.new_tokens : r; };
@@ -119,21 +122,23 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
     const int g_tiles = windowed ? (p.global_tokens + kN - 1) / kN : 0;
     const int w_first = windowed ? max(g_tiles, max(0, first_pos - p.window + 1) / kN) : 0;
     const int list0 = kMode == kCache ? split * p.tiles_per_split : 0;
-    auto key_tile = [&](int j) { j += list0; return j < g_tiles ? j : w_first + (j - g_tiles); };
+    auto key_tile = [&](int j) { j += list0; return j < g_tiles ? j : w_first + (j - g_tiles); };   // j-th load of the CTA
     int n_t[2];
 #pragma unroll
     for (int t = 0; t < 2; ++t) {
-        const int row0 = q0 + t * kM;
+        const int row0 = kMode == kCache ? q0 : q0 + t * kM;
         if (row0 >= p.Sq) n_t[t] = 0;
         else if (kMode == kCache) {
             const int n_list = min(g_tiles, n_ktiles_all) + max(0, n_ktiles_all - w_first);
-            n_t[t] = max(0, min(p.tiles_per_split, n_list - list0));
+            const int mine = max(0, min(p.tiles_per_split, n_list - list0));
+            n_t[t] = (mine + 1 - t) / 2;       // stream t takes loads t, t + 2, ...
         } else if (p.causal) {
             const int diag = min(n_ktiles_all - 1, row0 / kN);
             n_t[t] = min(g_tiles, diag + 1) + max(0, diag - w_first + 1);
         } else n_t[t] = n_ktiles_all;
     }
     const int n_max = max(n_t[0], n_t[1]);
+    const int n_loads = kMode == kCache ? n_t[0] + n_t[1] : n_max;   // K/V tiles the producer brings in
 
     // ---- setup ----
     if (warp == 9 && lane == 0) {
@@ -172,13 +177,18 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
         setmaxnreg_dec<72>();
         // =========================== TMA producer ===========================
         if (lane == 0) {
-            int n_valid = (n_t[0] > 0) + (n_t[1] > 0);
-            mbar_arrive_expect_tx(&bars->q_full, (uint32_t)(n_valid * kTileBytes));
-            for (int t = 0; t < 2; ++t)
-                if (n_t[t] > 0)
-                    for (int c = 0; c < kChunks; ++c)
-                        tma_load_3d(sQ + t * kTileBytes + c * kChunkBytes, &tmap_q, &bars->q_full, c * 64, q0 + t * kM, bh);
-            for (int j = 0; j < n_max; ++j) {
+            if (kMode == kCache) {      // one query tile, shared by both streams
+                if (n_loads > 0) mbar_arrive_expect_tx(&bars->q_full, (uint32_t)kTileBytes);
+                for (int c = 0; c < kChunks && n_loads > 0; ++c) tma_load_3d(sQ + c * kChunkBytes, &tmap_q, &bars->q_full, c * 64, q0, bh);
+            } else {
+                int n_valid = (n_t[0] > 0) + (n_t[1] > 0);
+                mbar_arrive_expect_tx(&bars->q_full, (uint32_t)(n_valid * kTileBytes));
+                for (int t = 0; t < 2; ++t)
+                    if (n_t[t] > 0)
+                        for (int c = 0; c < kChunks; ++c)
+                            tma_load_3d(sQ + t * kTileBytes + c * kChunkBytes, &tmap_q, &bars->q_full, c * 64, q0 + t * kM, bh);
+            }
+            for (int j = 0; j < n_loads; ++j) {
                 const int st = j & 1;
                 if (j >= 2 && !mbar_wait(&bars->k_empty[st], ((j >> 1) - 1) & 1, abort_flag, kSiteKEmpty)) break;
                 mbar_arrive_expect_tx(&bars->k_full[st], (uint32_t)kTileBytes);
@@ -202,7 +212,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
             const uint64_t dk0 = make_sdesc(smem_u32(sK), 16, 1024), dk1 = sdesc_advance(dk0, kTileBytes);
             const uint64_t dv0 = make_sdesc(smem_u32(sV), kChunkBytes, 1024), dv1 = sdesc_advance(dv0, kTileBytes);
             auto issue_s = [&](int t, int st) {
-                uint64_t a = t ? dq1 : dq0, b = st ? dk1 : dk0;
+                uint64_t a = (t && kMode != kCache) ? dq1 : dq0, b = st ? dk1 : dk0;
                 asm volatile("" : "+l"(a), "+l"(b));   // keeps the advanced descriptors from being hoisted into registers
                 const uint32_t d = tmem_S[t];
                 mma_ss_c<false>(d, a, b, idesc_s);
@@ -223,6 +233,34 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
                 for (int ks = 1; ks < kN / 16; ++ks) mma_ts_c<true>(d, a + (uint32_t)(ks * 8), sdesc_advance(b, ks * 2048), idesc_pv);
                 tc_commit(&bars->o_ready[t]);
             };
+            if constexpr (kMode == kCache) {
+                // two independent streams: stream t owns K/V stage t, S_t and O_t; its jj-th key tile is load 2*jj + t
+                bool ok = n_max > 0 && mbar_wait(&bars->q_full, 0, abort_flag, kSiteQ);
+                for (int t = 0; t < 2 && ok; ++t) {
+                    if (n_t[t] == 0) continue;
+                    if (!(ok = mbar_wait(&bars->k_full[t], 0, abort_flag, kSiteKFull))) break;
+                    tc_fence_after();
+                    issue_s(t, t);
+                    tc_commit(&bars->k_empty[t]);
+                }
+                for (int jj = 0; ok && jj < n_max; ++jj) {
+                    const uint32_t ph = (uint32_t)(jj & 1), nph = ph ^ 1u;
+                    for (int t = 0; t < 2 && ok; ++t) {
+                        if (jj >= n_t[t]) continue;
+                        if (!(ok = mbar_wait(&bars->v_full[t], ph, abort_flag, kSiteVFull))) break;
+                        if (!(ok = mbar_wait(&bars->p_ready[t], ph, abort_flag, kSitePReady))) break;
+                        tc_fence_after();
+                        issue_pv(t, t, jj > 0);
+                        tc_commit(&bars->v_empty[t]);
+                        if (jj + 1 < n_t[t]) {
+                            if (!(ok = mbar_wait(&bars->k_full[t], nph, abort_flag, kSiteKFull))) break;
+                            tc_fence_after();
+                            issue_s(t, t);
+                            tc_commit(&bars->k_empty[t]);
+                        }
+                    }
+                }
+            } else {
             bool ok = n_max > 0 && mbar_wait(&bars->q_full, 0, abort_flag, kSiteQ) &&
                       mbar_wait(&bars->k_full[0], 0, abort_flag, kSiteKFull);
             if (ok) {
@@ -259,6 +297,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
                 if (j + 1 < n_max) tc_commit(&bars->k_empty[nst]);
                 tc_commit(&bars->v_empty[st]);
             }
+            }
             // every MMA issued above must have retired before shared memory / TMEM are given up
             tc_commit(&bars->final_bar);
             mbar_wait(&bars->final_bar, 0, abort_flag, kSiteFinal);
@@ -269,7 +308,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
         const int t = warp >> 2;                       // tile 0 or 1
         const int row = (warp & 3) * 32 + lane;        // row inside the tile == TMEM lane
         const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;
-        const int grow = q0 + t * kM + row;            // global query index
+        const int grow = kMode == kCache ? q0 + row : q0 + t * kM + row;   // query row inside the (batch, head) slab
         const int n_mine = n_t[t];
         SNTL_TRACE_DECL(tn);
         const bool tw = (warp & 3) == 0 && lane == 0;
@@ -286,7 +325,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
             tmem_ld_wait();
             SNTL_TRACE_EV(tw, 1 + t, tn, 2);
             // number of visible keys of this row inside this tile
-            const int key0 = key_tile(j) * kN;
+            const int key0 = key_tile(kMode == kCache ? 2 * j + t : j) * kN;
             const int qpos = row_pos(grow);
             int limit = (p.causal ? min(p.Skv, qpos + 1) : p.Skv) - key0;
             if (limit < kN) {
@@ -361,7 +400,9 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
             tc_fence_after();
             const float inv = l > 0.0f ? 1.0f / l : 0.0f;
             const bool store = grow < p.Sq;
-            const size_t out_row = ((size_t)split * bh_count + bh) * p.Sq + (size_t)(store ? grow : 0);   // split = 0 outside cache mode
+            // cache mode: each stream of each split writes its own partial result, [2 * split + t][slab][row]
+            const size_t part = kMode == kCache ? (size_t)(2 * split + t) : 0;
+            const size_t out_row = (part * bh_count + bh) * p.Sq + (size_t)(store ? grow : 0);
             __nv_bfloat16* orow = p.o + out_row * D;
 #pragma unroll
             for (int c = 0; c < D / 32; ++c) {
@@ -382,6 +423,9 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
             }
             if (store)
                 p.lse[out_row] = l > 0.0f ? (m_ref + log2f(l)) * 0.6931471805599453f : -INFINITY;
+        } else if (kMode == kCache && ok && n_mine == 0 && grow < p.Sq) {
+            // a stream that got no key tile (a piece of one tile): its partial result weighs nothing in the merge
+            p.lse[((size_t)(2 * split + t) * bh_count + bh) * p.Sq + grow] = -INFINITY;
         }
     }
 
@@ -500,13 +544,10 @@ cudaError_t launch_cache(const TcArgs& a, int capacity, void* workspace, cudaStr
     if ((e = encode_tmap_bf16_3d(&tq, a.q, D, rows_per_slab, slabs, 128)) != cudaSuccess) return e;
     if ((e = encode_tmap_bf16_3d(&tk, a.k, D, s.Skv, slabs, 128, capacity)) != cudaSuccess) return e;
     if ((e = encode_tmap_bf16_3d(&tv, a.v, D, s.Skv, slabs, 128, capacity)) != cudaSuccess) return e;
-    __nv_bfloat16* o_part = a.o_out;
-    float* lse_part = a.lse_out;
-    if (plan.n_splits > 1) {
-        lse_part = reinterpret_cast<float*>(workspace);
-        o_part = reinterpret_cast<__nv_bfloat16*>(reinterpret_cast<uint8_t*>(workspace) +
-                                                  (((size_t)plan.n_splits * rows * sizeof(float) + 255) / 256) * 256);
-    }
+    const int n_parts = 2 * plan.n_splits;   // two key streams per CTA
+    float* lse_part = reinterpret_cast<float*>(workspace);
+    __nv_bfloat16* o_part = reinterpret_cast<__nv_bfloat16*>(reinterpret_cast<uint8_t*>(workspace) +
+                                                             (((size_t)n_parts * rows * sizeof(float) + 255) / 256) * 256);
     FwdParams p{};
     p.o = o_part;
     p.lse = lse_part;
@@ -517,7 +558,7 @@ cudaError_t launch_cache(const TcArgs& a, int capacity, void* workspace, cudaStr
     p.new_tokens = s.Sq;
     p.n_splits = plan.n_splits;
     p.tiles_per_split = plan.tiles_per_split;
-    p.n_qblk = (rows_per_slab + 2 * kM - 1) / (2 * kM);
+    p.n_qblk = (rows_per_slab + kM - 1) / kM;
     p.scale_log2 = s.scale * 1.4426950408889634f;
     const size_t smem = 6 * (size_t)(128 * D * 2) + sizeof(FwdBarriers) + 1024;
     static bool configured = false;
@@ -531,12 +572,9 @@ cudaError_t launch_cache(const TcArgs& a, int capacity, void* workspace, cudaStr
     attn_fwd_tc_kernel<D, kCache><<<(unsigned)ctas, kFwdThreads, smem, st>>>(tq, tk, tv, p);
     count_launch();
     if ((e = cudaGetLastError()) != cudaSuccess) return e;
-    if (plan.n_splits > 1) {
-        cache_merge_kernel<D><<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(o_part, lse_part, plan.n_splits, rows, a.o_out, a.lse_out);
-        count_launch();
-        e = cudaGetLastError();
-    }
-    return e;
+    cache_merge_kernel<D><<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(o_part, lse_part, n_parts, rows, a.o_out, a.lse_out);
+    count_launch();
+    return cudaGetLastError();
 }
 
 }  // namespace
@@ -554,8 +592,9 @@ CachePlan tc_cache_plan(const AttnShape& s)
         n_list = std::min(g_tiles, n_tiles) + std::max(0, n_tiles - w_first);
     }
     const int group = s.Hq / s.Hkv;
-    const long long base = (long long)s.B * s.Hkv * ((group * s.Sq + 2 * kM - 1) / (2 * kM));
-    int want = (int)std::max(1LL, std::min<long long>(n_list, 148 / std::max(1LL, base)));
+    const long long base = (long long)s.B * s.Hkv * ((group * s.Sq + kM - 1) / kM);
+    // pieces of at least two tiles (one per stream of a CTA), about one CTA per SM in total
+    int want = (int)std::max(1LL, std::min<long long>((n_list + 1) / 2, 148 / std::max(1LL, base)));
     CachePlan plan;
     plan.tiles_per_split = (n_list + want - 1) / want;
     plan.n_splits = (n_list + plan.tiles_per_split - 1) / plan.tiles_per_split;
@@ -564,10 +603,9 @@ CachePlan tc_cache_plan(const AttnShape& s)
 
 size_t tc_cache_workspace_bytes(const AttnShape& s)
 {
-    const CachePlan plan = tc_cache_plan(s);
-    if (plan.n_splits <= 1) return 0;
+    const size_t n_parts = 2 * (size_t)tc_cache_plan(s).n_splits;
     const size_t rows = (size_t)s.B * s.Hq * s.Sq;
-    return (((size_t)plan.n_splits * rows * sizeof(float) + 255) / 256) * 256 + (size_t)plan.n_splits * rows * s.D * 2;
+    return ((n_parts * rows * sizeof(float) + 255) / 256) * 256 + n_parts * rows * s.D * 2;
 }
 
 bool tc_cache_supported(const AttnShape& s)

@@ -61,8 +61,8 @@ bool tc_fwd_supported(const AttnShape& s);
 bool tc_bwd_supported(const AttnShape& s);
 cudaError_t tc_forward(const TcArgs& a, cudaStream_t st);
 // New tokens against a KV cache (forward only): s.Sq new tokens per head at positions Skv-Sq .. Skv-1, K/V slabs
-// `capacity` rows apart.  The keys are dealt to n_splits CTAs per (KV head, query block); with more than one split the
-// partial results go through `workspace` (tc_cache_workspace_bytes) and a merge kernel.
+// `capacity` rows apart.  The keys are dealt to n_splits CTAs per (KV head, 128-row query block), each running two key
+// streams; the 2 * n_splits partial results go through `workspace` (tc_cache_workspace_bytes) and a merge kernel.
 struct CachePlan { int n_splits, tiles_per_split; };
 CachePlan tc_cache_plan(const AttnShape& s);
 size_t tc_cache_workspace_bytes(const AttnShape& s);
