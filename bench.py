@@ -32,6 +32,9 @@ FALLBACK_PEAKS = {"bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "hbm_g
 # DRAM bytes (read + write) of one launch of the dominant kernel per batch element, from the ncu capture summarised in
 # profiles/attn_bwd_tc_kernel_gqa7b_d128.md (captured at batch 1; traffic grows in proportion to the batch)
 NCU_DRAM_BYTES_PER_BATCH = {"gqa7b_d128": 721.2e6 + 522.3e6}
+# the same for the cache-mode forward kernel, one new token, no window (profiles/attn_fwd_tc_kernel_cache_mode_gqa7b_d128.md,
+# captured at batch 16)
+NCU_CACHED_DRAM_BYTES_PER_BATCH = {"gqa7b_d128": (268640768 + 5306880) / 16.0}
 
 
 def load_peaks():
@@ -162,6 +165,64 @@ def run_reference_arm(args, workload):
     print(json.dumps(line), flush=True)
 
 
+def run_cached_forward(args, w):
+    """Auxiliary mode (--cached-tokens T): T new tokens per sequence against a KV cache of the workload's length, the
+    reference's decode step (CudaCausalSelfAttention.cu:318-341).  HBM-bound: the algorithmic bytes of one call are the
+    K and V rows in use (read once per KV head) plus Q, O and LSE; prints its own JSON line."""
+    import torch
+    import sentinel_b200 as sb
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a B200 GPU: there is no CPU fallback for the product path")
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    sb._lib.load()
+    T, L = args.cached_tokens, w.seq
+    B = w.batch
+    g = torch.Generator(device="cpu").manual_seed(20261125 + w.index)
+    mk = lambda h, s_, std: (torch.randn(B, h, s_, w.head_dim, generator=g) * std).to(torch.bfloat16).to(dev)
+    q, kc, vc = mk(w.q_heads, T, w.qk_std), mk(w.kv_heads, L, w.qk_std), mk(w.kv_heads, L, w.v_std)
+    o = torch.empty_like(q)
+    lse = torch.empty(q.shape[:3], dtype=torch.float32, device=dev)
+    mask = dict(window=args.window, global_tokens=args.global_tokens) if args.window > 0 else {}
+
+    def step():
+        sb.attention_cached_forward(q, kc, vc, L, out=o, lse=lse, **mask)
+
+    for _ in range(args.warmup):
+        step()
+    launches0 = sb.launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(0) as clocks:
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(args.steps):
+            step()
+        e1.record()
+        torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / args.steps
+    launches = sb.launch_count() - launches0
+    keys = L if args.window <= 0 else min(L, args.window + T - 1 + args.global_tokens)
+    kv_bytes = 2.0 * B * w.kv_heads * keys * w.head_dim * 2
+    io_bytes = kv_bytes + 2.0 * q.numel() * 2 + 4.0 * lse.numel()
+    peaks = load_peaks()
+    peak = float(peaks.get("hbm_gbs", FALLBACK_PEAKS["hbm_gbs"]))
+    achieved = io_bytes / (ms * 1e-3) / 1e9
+    line = {"metric": "attention_cached_fwd_hbm_gbs", "value": achieved, "unit": "GB/s", "n_gpus": 1, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": w.name + "_cached", "B": B, "Hq": w.q_heads, "Hkv": w.kv_heads, "cache_length": L,
+                       "new_tokens": T, "D": w.head_dim, "l2": f"K/V in use {kv_bytes / 1e6:.0f} MB per call",
+                       "kernel_path": sb.last_path(), **mask},
+            "tokens_per_s": B * T / (ms * 1e-3),
+            "roofline": {"bound": "hbm", "kernel": "cache-mode forward kernel + split merge (timed as one call)", "achieved": achieved,
+                         "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_source": f"{peaks['_source']} hbm_gbs",
+                         "traffic": (NCU_CACHED_DRAM_BYTES_PER_BATCH[w.name] * B
+                                     if w.name in NCU_CACHED_DRAM_BYTES_PER_BATCH and T == 1 and not mask else None),
+                         "algorithmic_bytes": io_bytes},
+            "gpu_launches": int(launches), "clocks": clocks.summary(), "device_status": sb.poll_device_status()}
+    print(json.dumps(line), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -172,6 +233,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--batch", type=int, default=0, help="override the workload's per-GPU batch (profiling captures)")
     ap.add_argument("--skip-e2e", action="store_true", help="skip the host-buffer leg (profiling captures)")
+    ap.add_argument("--cached-tokens", type=int, default=0,
+                    help="auxiliary mode: this many new tokens per sequence against a KV cache of the workload's length")
     ap.add_argument("--window", type=int, default=0, help="sliding window (keys per query); 0 = the workload's plain causal mask")
     ap.add_argument("--global-tokens", type=int, default=0, help="always-visible first keys (with --window)")
     args = ap.parse_args()
@@ -184,6 +247,9 @@ def main():
         w = dataclasses.replace(w, batch=args.batch)
     if args.impl == "reference":
         run_reference_arm(args, w)
+        return
+    if args.cached_tokens > 0:
+        run_cached_forward(args, w)
         return
 
     import torch
