@@ -146,6 +146,25 @@ int sntl_attn_bwd_static_scratch(const sntl_attn_desc* desc, const void* q, cons
 /* Size in bytes of the built-in scratch used by sntl_attn_bwd_static_scratch.  No counterpart in the reference. */
 size_t sntl_attn_static_scratch_capacity(void);
 
+/* Boundary conversions fused with the rotary embedding: one read and one write per element where the reference
+ * makes separate passes (rotaryRotateInPlace / rotaryRotateInverseInPlace over fp32 matrices, CudaOps.cu:362-399, called
+ * at CudaCausalSelfAttention.cu:206-207, :508-509) before its flash kernel converts operands on every load.
+ *   pack:   src fp32 feature-major (heads*head_dim) x stride_columns, tokens of pack b at columns
+ *           column_start + b*seq + s  ->  dst bf16 [batch][heads][seq][head_dim], rotated by the angle tables.
+ *   unpack: the reverse relayout to fp32; inverse != 0 applies the inverse rotation (the gradients dQ, dK),
+ *           inverse == 0 the forward one.
+ * cos_table / sin_table: [table_positions][head_dim/2] fp32, entry [position][i] for the pair (2i, 2i+1)
+ * (RotaryEmbedding.cpp:19-27); both null = no rotation (V, O, dV).  Token s of every pack sits at position
+ * position_offset + s (packs restart at 0: CudaOps.cu:366).  Products and sums are rounded separately, as the
+ * reference's host code computes them, so the result is the bf16 rounding of exactly that fp32 value.
+ * Asynchronous on `stream`. */
+int sntl_attn_pack_heads(const float* src, void* dst, int32_t batch, int32_t heads, int32_t seq, int32_t head_dim,
+                         int32_t stride_columns, int32_t column_start, const float* cos_table, const float* sin_table,
+                         int32_t position_offset, int32_t table_positions, void* stream);
+int sntl_attn_unpack_heads(const void* src, float* dst, int32_t batch, int32_t heads, int32_t seq, int32_t head_dim,
+                           int32_t stride_columns, int32_t column_start, const float* cos_table, const float* sin_table,
+                           int32_t position_offset, int32_t table_positions, int32_t inverse, void* stream);
+
 /* Log-sum-exp merge of two partial attention results over disjoint key sets (the ring schedule's
  * combine step): o_acc,lse_acc <- merge((o_acc,lse_acc),(o_part,lse_part)).  BHSD layout, `rows` =
  * B*Hq*Sq rows of head_dim elements; the accumulator and the partial may have different element types

@@ -377,3 +377,45 @@ int oracle_threads(void)
     return 1;
 #endif
 }
+
+/*
+ * Rotary position embedding, restated from sentinel/NeuralNet/Layers/RotaryEmbedding.cpp: the angle tables (:19-27,
+ * fp32 pow / cos / sin) and the in-place rotation of a feature-major (heads*head_dim) x cols matrix (:38-59; inverse
+ * :61-81).  Column c sits at position (segment > 0 ? c % segment : position_offset + c), the rule of the reference's
+ * device kernel (sentinel/NeuralNet/Cuda/CudaOps.cu:366).  fp32 arithmetic with separately rounded products and sums,
+ * as the reference's host code computes: integer-exact parity is expected of anything compared with it.
+ */
+void oracle_rope_tables(int head_dim, int positions, float base, float* cos_t, float* sin_t)
+{
+    const int pairs = head_dim / 2;
+    for (int pos = 0; pos < positions; ++pos)
+        for (int i = 0; i < pairs; ++i) {
+            const float exponent = -2.0f * (float)i / (float)head_dim;
+            const float angle = (float)pos * powf(base, exponent);
+            cos_t[(size_t)pos * pairs + i] = cosf(angle);
+            sin_t[(size_t)pos * pairs + i] = sinf(angle);
+        }
+}
+
+void oracle_rope_rotate(float* tensor, int heads, int head_dim, int cols, const float* cos_t, const float* sin_t,
+                        int position_offset, int segment, int inverse)
+{
+    const int pairs = head_dim / 2;
+    for (int h = 0; h < heads; ++h)
+        for (int c = 0; c < cols; ++c) {
+            const int pos = segment > 0 ? c % segment : position_offset + c;
+            for (int i = 0; i < pairs; ++i) {
+                float* even = tensor + ((size_t)h * head_dim + 2 * i) * cols + c;
+                float* odd = even + cols;
+                const float cs = cos_t[(size_t)pos * pairs + i], sn = sin_t[(size_t)pos * pairs + i];
+                const float e = *even, o = *odd;
+                if (!inverse) {
+                    *even = e * cs - o * sn;
+                    *odd = e * sn + o * cs;
+                } else {
+                    *even = e * cs + o * sn;
+                    *odd = -e * sn + o * cs;
+                }
+            }
+        }
+}

@@ -141,6 +141,47 @@ def round_bf16(x):
     return y
 
 
+def rope_tables(head_dim, positions, base=10000.0):
+    """cos/sin tables [positions][head_dim/2] as RotaryEmbedding.cpp:19-27 builds them (fp32 pow/cos/sin)."""
+    cos_t = np.empty((positions, head_dim // 2), np.float32)
+    sin_t = np.empty_like(cos_t)
+    oracle_lib().oracle_rope_tables(int(head_dim), int(positions), C.c_float(base), _fp(cos_t), _fp(sin_t))
+    return cos_t, sin_t
+
+
+def rope_rotate(matrix, heads, head_dim, cos_t, sin_t, position_offset=0, segment=0, inverse=False):
+    """Rotates a feature-major (heads*head_dim) x cols fp32 matrix; returns a new array."""
+    m = _f32(matrix).copy()
+    assert m.shape[0] == heads * head_dim
+    oracle_lib().oracle_rope_rotate(_fp(m), int(heads), int(head_dim), int(m.shape[1]), _fp(_f32(cos_t)), _fp(_f32(sin_t)),
+                                    int(position_offset), int(segment), int(bool(inverse)))
+    return m
+
+
+def ref_rope(matrix, heads, head_dim, positions, base=10000.0, inverse=False):
+    """The reference's RotaryEmbedding::rotateInPlace / rotateInverseInPlace -> (rotated matrix, cos table, sin table)."""
+    m = _f32(matrix).copy()
+    cos_t = np.empty((positions, head_dim // 2), np.float32)
+    sin_t = np.empty_like(cos_t)
+    rc = ref_lib().ref_rope(int(head_dim), int(positions), C.c_float(base), int(heads), int(m.shape[1]), _fp(m),
+                            int(bool(inverse)), _fp(cos_t), _fp(sin_t))
+    assert rc == 0, "reference RotaryEmbedding threw"
+    return m, cos_t, sin_t
+
+
+def ref_layer_fwd_bwd_rope(q, k, v, dout, rope_base=10000.0, window=0, global_tokens=0):
+    """The reference layer with its own rotary embedding active: q, k are un-rotated; returns (O, dQ, dK, dV) with the
+    gradients taken with respect to the un-rotated inputs."""
+    q, k, v, dout = _f32(q), _f32(k), _f32(v), _f32(dout)
+    B, Hq, S, D = q.shape
+    Hkv = k.shape[1]
+    o, dq, dk, dv = np.empty_like(q), np.empty_like(q), np.empty_like(k), np.empty_like(v)
+    rc = ref_lib().ref_layer_fwd_bwd_rope(B, Hq, Hkv, S, D, C.c_float(rope_base), int(window), int(global_tokens), _fp(q),
+                                          _fp(k), _fp(v), _fp(dout), _fp(o), _fp(dq), _fp(dk), _fp(dv))
+    assert rc == 0, "reference layer threw"
+    return o, dq, dk, dv
+
+
 def oracle_threads() -> int:
     lib = oracle_lib()
     lib.oracle_threads.restype = C.c_int

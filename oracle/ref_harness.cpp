@@ -145,6 +145,65 @@ int ref_layer_fwd_bwd(int B, int Hq, int Hkv, int S, int D, const float* q, cons
     return ref_layer_fwd_bwd_windowed(B, Hq, Hkv, S, D, 0, 0, q, k, v, dout, o, lse, dq, dk, dv);
 }
 
+// The reference's RotaryEmbedding on a feature-major (heads*D) x cols matrix, in place (forward or inverse rotation),
+// and its angle tables ([positions][D/2]; pass null to skip).  Returns 0, or 1 when the reference threw.
+int ref_rope(int D, int positions, float base, int heads, int cols, float* tensor, int inverse, float* cos_out, float* sin_out)
+{
+    try {
+        RotaryEmbedding rope(D, positions, base);
+        if (cos_out) std::memcpy(cos_out, rope.cosTable.data(), rope.cosTable.size() * sizeof(float));
+        if (sin_out) std::memcpy(sin_out, rope.sinTable.data(), rope.sinTable.size() * sizeof(float));
+        if (tensor) {
+            Matrix m((size_t)heads * D, (size_t)cols, 0.0f);
+            std::memcpy(m.data.data(), tensor, m.data.size() * sizeof(float));
+            if (inverse) rope.rotateInverseInPlace(m, heads);
+            else rope.rotateInPlace(m, heads);
+            std::memcpy(tensor, m.data.data(), m.data.size() * sizeof(float));
+        }
+        return 0;
+    } catch (...) {
+        return 1;
+    }
+}
+
+// The public layer route with the layer's own rotary embedding left in place (rope_base > 0): inputs are the
+// un-rotated Q and K, the layer rotates them (CausalSelfAttention.cpp:232-236) and its backward applies the inverse
+// rotation to dQ and dK (:355-356), so dq / dk come back with respect to the un-rotated inputs.
+int ref_layer_fwd_bwd_rope(int B, int Hq, int Hkv, int S, int D, float rope_base, int window, int global_tokens, const float* q,
+                           const float* k, const float* v, const float* dout, float* o, float* dq, float* dk, float* dv)
+{
+    try {
+        const size_t qRows = (size_t)Hq * D, kvRows = (size_t)Hkv * D, inRows = qRows + 2 * kvRows;
+        Matrix wq(qRows, inRows, 0.0f), wk(kvRows, inRows, 0.0f), wv(kvRows, inRows, 0.0f), wo(qRows, qRows, 0.0f);
+        for (size_t r = 0; r < qRows; ++r) { wq.at(r, r) = 1.0f; wo.at(r, r) = 1.0f; }
+        for (size_t r = 0; r < kvRows; ++r) { wk.at(r, qRows + r) = 1.0f; wv.at(r, qRows + kvRows + r) = 1.0f; }
+        RotaryEmbedding rope(D, S, rope_base);
+        CausalSelfAttention layer(wq, wk, wv, wo, rope, Hq, window > 0 ? window : S, global_tokens, Hkv);
+        for (int b = 0; b < B; ++b) {
+            Matrix input(inRows, (size_t)S, 0.0f);
+            gather_rows(q + (size_t)b * Hq * S * D, Hq, S, D, input, 0);
+            gather_rows(k + (size_t)b * Hkv * S * D, Hkv, S, D, input, qRows);
+            gather_rows(v + (size_t)b * Hkv * S * D, Hkv, S, D, input, qRows + kvRows);
+            CausalSelfAttentionCache cache;
+            Matrix out = layer.forward(input, cache);
+            scatter_rows(out, 0, Hq, S, D, o + (size_t)b * Hq * S * D);
+            if (dout && dq && dk && dv) {
+                Matrix grad(qRows, (size_t)S, 0.0f);
+                gather_rows(dout + (size_t)b * Hq * S * D, Hq, S, D, grad, 0);
+                Matrix gwq, gwk, gwv, gwo;
+                Matrix inGrad = layer.backward(grad, cache, gwq, gwk, gwv, gwo);
+                // with selector weights the input gradient is [dQ; dK; dV] with respect to the un-rotated inputs
+                scatter_rows(inGrad, 0, Hq, S, D, dq + (size_t)b * Hq * S * D);
+                scatter_rows(inGrad, qRows, Hkv, S, D, dk + (size_t)b * Hkv * S * D);
+                scatter_rows(inGrad, qRows + kvRows, Hkv, S, D, dv + (size_t)b * Hkv * S * D);
+            }
+        }
+        return 0;
+    } catch (...) {
+        return 1;
+    }
+}
+
 // Primitive route (timed baseline).  Same tensors as above; all outputs optional except none --
 // pass null to skip a store.  seconds[0] = forward time, seconds[1] = backward time (attention core only,
 // layout gathers excluded).  head_limit > 0 restricts the run to the first head_limit query heads of

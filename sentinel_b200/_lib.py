@@ -17,7 +17,7 @@ FLAG_ALLOW_BF16_COMPUTE, FLAG_FORCE_SIMT = 1, 2
 EXPORTS = ["sntl_attn_version", "sntl_status_string", "sntl_attn_fwd_workspace_bytes", "sntl_attn_bwd_workspace_bytes",
            "sntl_attn_fwd", "sntl_attn_bwd", "sntl_attn_merge", "sntl_attn_last_path", "sntl_attn_launch_count",
            "sntl_attn_poll_device_status", "sntl_attn_bwd_static_scratch", "sntl_attn_static_scratch_capacity", "sntl_attn_accumulate",
-           "sntl_attn_cached_fwd", "sntl_attn_cached_fwd_workspace_bytes"]
+           "sntl_attn_cached_fwd", "sntl_attn_cached_fwd_workspace_bytes", "sntl_attn_pack_heads", "sntl_attn_unpack_heads"]
 ERR_SCRATCH_LIMIT = 7
 
 
@@ -66,6 +66,10 @@ def load():
     lib.sntl_attn_static_scratch_capacity.restype = sz
     lib.sntl_attn_accumulate.restype = C.c_int
     lib.sntl_attn_accumulate.argtypes = [C.c_int32, C.c_int64, vp, vp, vp]
+    lib.sntl_attn_pack_heads.restype = C.c_int
+    lib.sntl_attn_pack_heads.argtypes = [vp, vp] + [C.c_int32] * 6 + [vp, vp, C.c_int32, C.c_int32, vp]
+    lib.sntl_attn_unpack_heads.restype = C.c_int
+    lib.sntl_attn_unpack_heads.argtypes = [vp, vp] + [C.c_int32] * 6 + [vp, vp, C.c_int32, C.c_int32, C.c_int32, vp]
     lib.sntl_attn_merge.restype = C.c_int
     lib.sntl_attn_merge.argtypes = [C.c_int32, C.c_int32, C.c_int64, C.c_int32, vp, vp, vp, vp, vp]
     lib.sntl_attn_last_path.restype = C.c_char_p

@@ -388,6 +388,49 @@ int sntl_attn_accumulate(int32_t part_dtype, int64_t count, float* acc, const vo
     return cuda_status(accumulate_f32(part_dtype, acc, part, (size_t)count, (cudaStream_t)stream));
 }
 
+namespace sntl {
+namespace {
+int validate_pack(const void* a, const void* b, int32_t batch, int32_t heads, int32_t seq, int32_t head_dim, int32_t stride_columns,
+                  int32_t column_start, const float* cos_table, const float* sin_table, int32_t position_offset,
+                  int32_t table_positions)
+{
+    if (!a || !b) return SNTL_ERR_BAD_ARGUMENT;
+    if (batch <= 0 || heads <= 0 || seq <= 0 || head_dim <= 0 || head_dim % 2 != 0) return SNTL_ERR_BAD_ARGUMENT;   // RotaryEmbedding.cpp:11
+    if (column_start < 0 || stride_columns <= 0) return SNTL_ERR_BAD_ARGUMENT;
+    if ((long long)column_start + (long long)batch * seq > (long long)stride_columns) return SNTL_ERR_BAD_ARGUMENT;
+    if ((cos_table == nullptr) != (sin_table == nullptr)) return SNTL_ERR_BAD_ARGUMENT;
+    // RotaryEmbedding.cpp:42: a sequence longer than the table is an argument error
+    if (cos_table && (position_offset < 0 || (long long)position_offset + seq > (long long)table_positions)) return SNTL_ERR_BAD_ARGUMENT;
+    if (batch > 65535 || heads > 65535 || (long long)batch * heads > 65535) return SNTL_ERR_UNSUPPORTED;
+    return SNTL_OK;
+}
+}  // namespace
+}  // namespace sntl
+
+int sntl_attn_pack_heads(const float* src, void* dst, int32_t batch, int32_t heads, int32_t seq, int32_t head_dim,
+                         int32_t stride_columns, int32_t column_start, const float* cos_table, const float* sin_table,
+                         int32_t position_offset, int32_t table_positions, void* stream)
+{
+    const int rc = validate_pack(src, dst, batch, heads, seq, head_dim, stride_columns, column_start, cos_table, sin_table,
+                                 position_offset, table_positions);
+    if (rc != SNTL_OK) return rc;
+    if (!device_ok()) return SNTL_ERR_NO_DEVICE;
+    return cuda_status(rope_pack_bf16(src, (__nv_bfloat16*)dst, batch, heads, seq, head_dim, stride_columns, column_start, cos_table,
+                                      sin_table, position_offset, (cudaStream_t)stream));
+}
+
+int sntl_attn_unpack_heads(const void* src, float* dst, int32_t batch, int32_t heads, int32_t seq, int32_t head_dim,
+                           int32_t stride_columns, int32_t column_start, const float* cos_table, const float* sin_table,
+                           int32_t position_offset, int32_t table_positions, int32_t inverse, void* stream)
+{
+    const int rc = validate_pack(src, dst, batch, heads, seq, head_dim, stride_columns, column_start, cos_table, sin_table,
+                                 position_offset, table_positions);
+    if (rc != SNTL_OK) return rc;
+    if (!device_ok()) return SNTL_ERR_NO_DEVICE;
+    return cuda_status(rope_unpack_f32((const __nv_bfloat16*)src, dst, batch, heads, seq, head_dim, stride_columns, column_start,
+                                       cos_table, sin_table, position_offset, inverse != 0, (cudaStream_t)stream));
+}
+
 int sntl_attn_poll_device_status(void* stream, uint32_t* detail)
 {
     uint32_t word = 0, word_bwd = 0;

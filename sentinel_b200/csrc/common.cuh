@@ -72,6 +72,12 @@ cudaError_t tc_backward(const TcArgs& a, cudaStream_t st);
 size_t tc_backward_workspace_bytes(const AttnShape& s);
 
 // Layout / dtype staging (layout_convert.cu): SENTINEL fp32 feature-major <-> bf16 BHSD.
+// The same relayouts with the rotary embedding applied on the way (cos_t == nullptr: plain relayout).
+cudaError_t rope_pack_bf16(const float* src, __nv_bfloat16* dst, int B, int H, int S, int D, int stride_columns,
+                           int column_start, const float* cos_t, const float* sin_t, int position_offset, cudaStream_t st);
+cudaError_t rope_unpack_f32(const __nv_bfloat16* src, float* dst, int B, int H, int S, int D, int stride_columns,
+                            int column_start, const float* cos_t, const float* sin_t, int position_offset, bool inverse,
+                            cudaStream_t st);
 cudaError_t sentinel_to_bhsd_bf16(const float* src, __nv_bfloat16* dst, int B, int H, int S, int D, int stride_columns,
                                   int column_start, cudaStream_t st);
 cudaError_t bhsd_bf16_to_sentinel(const __nv_bfloat16* src, float* dst, int B, int H, int S, int D, int stride_columns,

@@ -45,6 +45,72 @@ __global__ void bhsd_to_sentinel_kernel(const __nv_bfloat16* __restrict__ src, f
     }
 }
 
+// Rotary position embedding fused into the two transposes above: what the reference does as separate passes
+// (rotaryRotateInPlace / rotaryRotateInverseInPlace over the fp32 matrices, sentinel/NeuralNet/Cuda/CudaOps.cu:362-399,
+// then the flash kernel's per-load conversion) becomes part of the one read + one write of the relayout.
+// Pairs are interleaved, (2i, 2i+1), angle table entry [position][i] (RotaryEmbedding.cpp:19-27, :38-59); the two members
+// of a pair are neighbouring d, i.e. neighbouring lanes of the token-major side, so the partner comes from a shuffle.
+// Products and sums are rounded separately (no FMA contraction), which is what the reference's host code computes.
+template <bool kInverse>
+__device__ __forceinline__ float rotate_lane(float mine, int d, float c, float sn)
+{
+    const float other = __shfl_xor_sync(0xffffffffu, mine, 1);
+    const float even = (d & 1) ? other : mine, odd = (d & 1) ? mine : other;
+    if (!kInverse)   // even' = e*cos - o*sin ; odd' = e*sin + o*cos
+        return (d & 1) ? __fadd_rn(__fmul_rn(even, sn), __fmul_rn(odd, c)) : __fsub_rn(__fmul_rn(even, c), __fmul_rn(odd, sn));
+    // inverse (transpose of the rotation): even' = e*cos + o*sin ; odd' = -e*sin + o*cos
+    return (d & 1) ? __fadd_rn(__fmul_rn(-even, sn), __fmul_rn(odd, c)) : __fadd_rn(__fmul_rn(even, c), __fmul_rn(odd, sn));
+}
+
+__global__ void rope_pack_kernel(const float* __restrict__ src, __nv_bfloat16* __restrict__ dst, int H, int S, int D,
+                                 int stride_columns, int column_start, const float* __restrict__ cos_t,
+                                 const float* __restrict__ sin_t, int position_offset)
+{
+    __shared__ float tile[32][33];
+    const int bh = blockIdx.z, b = bh / H, h = bh % H;
+    const int s0 = blockIdx.x * 32, d0 = blockIdx.y * 32;
+    const int tx = threadIdx.x, ty = threadIdx.y;  // 32 x 8
+    for (int r = ty; r < 32; r += 8) {
+        const int d = d0 + r, s = s0 + tx;
+        tile[r][tx] = (d < D && s < S) ? src[(long long)(h * D + d) * stride_columns + column_start + (long long)b * S + s] : 0.0f;
+    }
+    __syncthreads();
+    const int pairs = D >> 1;
+    for (int r = ty; r < 32; r += 8) {
+        const int s = s0 + r, d = d0 + tx;       // D is even and d0 a multiple of 32: a pair never straddles tiles
+        const bool live = s < S && d < D;
+        const long long ti = (long long)(position_offset + s) * pairs + (d >> 1);
+        const float c = live ? cos_t[ti] : 1.0f, sn = live ? sin_t[ti] : 0.0f;
+        const float v = rotate_lane<false>(tile[tx][r], d, c, sn);
+        if (live) dst[((long long)bh * S + s) * D + d] = __float2bfloat16_rn(v);
+    }
+}
+
+template <bool kInverse>
+__global__ void rope_unpack_kernel(const __nv_bfloat16* __restrict__ src, float* __restrict__ dst, int H, int S, int D,
+                                   int stride_columns, int column_start, const float* __restrict__ cos_t,
+                                   const float* __restrict__ sin_t, int position_offset)
+{
+    __shared__ float tile[32][33];
+    const int bh = blockIdx.z, b = bh / H, h = bh % H;
+    const int s0 = blockIdx.x * 32, d0 = blockIdx.y * 32;
+    const int tx = threadIdx.x, ty = threadIdx.y;
+    const int pairs = D >> 1;
+    for (int r = ty; r < 32; r += 8) {
+        const int s = s0 + r, d = d0 + tx;
+        const bool live = s < S && d < D;
+        const float x = live ? __bfloat162float(src[((long long)bh * S + s) * D + d]) : 0.0f;
+        const long long ti = (long long)(position_offset + s) * pairs + (d >> 1);
+        const float c = live ? cos_t[ti] : 1.0f, sn = live ? sin_t[ti] : 0.0f;
+        tile[r][tx] = rotate_lane<kInverse>(x, d, c, sn);
+    }
+    __syncthreads();
+    for (int r = ty; r < 32; r += 8) {
+        const int d = d0 + r, s = s0 + tx;
+        if (d < D && s < S) dst[(long long)(h * D + d) * stride_columns + column_start + (long long)b * S + s] = tile[tx][r];
+    }
+}
+
 __global__ void f32_to_bf16_kernel(const float* __restrict__ src, __nv_bfloat16* __restrict__ dst, size_t n)
 {
     for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
@@ -127,6 +193,30 @@ cudaError_t bhsd_bf16_to_sentinel(const __nv_bfloat16* src, float* dst, int B, i
 {
     dim3 grid((S + 31) / 32, (D + 31) / 32, B * H), block(32, 8);
     bhsd_to_sentinel_kernel<<<grid, block, 0, st>>>(src, dst, H, S, D, stride_columns, column_start);
+    count_launch();
+    return cudaGetLastError();
+}
+
+cudaError_t rope_pack_bf16(const float* src, __nv_bfloat16* dst, int B, int H, int S, int D, int stride_columns,
+                           int column_start, const float* cos_t, const float* sin_t, int position_offset, cudaStream_t st)
+{
+    if (!cos_t) return sentinel_to_bhsd_bf16(src, dst, B, H, S, D, stride_columns, column_start, st);
+    dim3 grid((S + 31) / 32, (D + 31) / 32, B * H), block(32, 8);
+    rope_pack_kernel<<<grid, block, 0, st>>>(src, dst, H, S, D, stride_columns, column_start, cos_t, sin_t, position_offset);
+    count_launch();
+    return cudaGetLastError();
+}
+
+cudaError_t rope_unpack_f32(const __nv_bfloat16* src, float* dst, int B, int H, int S, int D, int stride_columns,
+                            int column_start, const float* cos_t, const float* sin_t, int position_offset, bool inverse,
+                            cudaStream_t st)
+{
+    if (!cos_t) return bhsd_bf16_to_sentinel(src, dst, B, H, S, D, stride_columns, column_start, st);
+    dim3 grid((S + 31) / 32, (D + 31) / 32, B * H), block(32, 8);
+    if (inverse)
+        rope_unpack_kernel<true><<<grid, block, 0, st>>>(src, dst, H, S, D, stride_columns, column_start, cos_t, sin_t, position_offset);
+    else
+        rope_unpack_kernel<false><<<grid, block, 0, st>>>(src, dst, H, S, D, stride_columns, column_start, cos_t, sin_t, position_offset);
     count_launch();
     return cudaGetLastError();
 }

@@ -118,6 +118,55 @@ def attention_cached_forward(q, k_cache, v_cache, cache_length, *, scale=None, f
     return o, lse
 
 
+def _tables(cos_table, sin_table, head_dim, device):
+    if (cos_table is None) != (sin_table is None):
+        raise ValueError("cos_table and sin_table come together")
+    if cos_table is None:
+        return None, None, 0
+    for t, n in ((cos_table, "cos_table"), (sin_table, "sin_table")):
+        _require(t, n)
+        if t.dtype != torch.float32 or t.dim() != 2 or t.shape[1] != head_dim // 2:
+            raise ValueError(f"{n} must be fp32 [positions, head_dim/2]")
+    if cos_table.shape != sin_table.shape:
+        raise ValueError("cos_table and sin_table must share shape")
+    return cos_table.data_ptr(), sin_table.data_ptr(), cos_table.shape[0]
+
+
+def pack_heads(matrix, batch, heads, seq, head_dim, *, column_start=0, cos_table=None, sin_table=None, position_offset=0,
+               out=None):
+    """fp32 feature-major ``(heads*head_dim) x stride`` matrix -> bf16 ``[batch, heads, seq, head_dim]``, rotated by the
+    angle tables on the way (``None``: no rotation).  One kernel in place of the reference's rotaryRotateInPlace
+    (CudaOps.cu:362-381) plus a relayout and a cast."""
+    lib = _lib.load()
+    _require(matrix, "matrix")
+    if matrix.dtype != torch.float32 or matrix.dim() != 2 or matrix.shape[0] != heads * head_dim:
+        raise ValueError("matrix must be fp32 (heads*head_dim) x stride")
+    cp, sp, positions = _tables(cos_table, sin_table, head_dim, matrix.device)
+    dst = torch.empty(batch, heads, seq, head_dim, dtype=torch.bfloat16, device=matrix.device) if out is None else out
+    rc = lib.sntl_attn_pack_heads(matrix.data_ptr(), dst.data_ptr(), batch, heads, seq, head_dim, matrix.shape[1], column_start,
+                                  cp, sp, position_offset, positions, _stream_ptr())
+    _lib.check(rc, "sntl_attn_pack_heads")
+    return dst
+
+
+def unpack_heads(tensor, matrix, *, column_start=0, cos_table=None, sin_table=None, position_offset=0, inverse=False):
+    """bf16 ``[batch, heads, seq, head_dim]`` -> columns of an fp32 feature-major matrix (written in place), with the
+    forward or (``inverse=True``, for dQ and dK) inverse rotation on the way."""
+    lib = _lib.load()
+    _require(tensor, "tensor")
+    _require(matrix, "matrix")
+    if tensor.dtype != torch.bfloat16 or tensor.dim() != 4:
+        raise ValueError("tensor must be bf16 [batch, heads, seq, head_dim]")
+    batch, heads, seq, head_dim = tensor.shape
+    if matrix.dtype != torch.float32 or matrix.dim() != 2 or matrix.shape[0] != heads * head_dim:
+        raise ValueError("matrix must be fp32 (heads*head_dim) x stride")
+    cp, sp, positions = _tables(cos_table, sin_table, head_dim, tensor.device)
+    rc = lib.sntl_attn_unpack_heads(tensor.data_ptr(), matrix.data_ptr(), batch, heads, seq, head_dim, matrix.shape[1],
+                                    column_start, cp, sp, position_offset, positions, int(bool(inverse)), _stream_ptr())
+    _lib.check(rc, "sntl_attn_unpack_heads")
+    return matrix
+
+
 def attention_backward(q, k, v, o, lse, dout, *, causal=True, scale=None, flags=0, dq=None, dk=None, dv=None, window=0,
                        global_tokens=0):
     """dQ, dK, dV from dO (P recomputed from LSE).  Shapes as in attention_forward."""

@@ -24,6 +24,8 @@ GOLDEN_CASES = ["toy_f32_b4_h4_s64_d16", "gqa_h8_kv2_s16_d8", "mha_h4_s48_d16", 
                 "gqa_h4_kv2_s136_d128_bf16in"]
 WINDOW_GOLDEN_CASES = ["win4_g2_h2_s16_d16", "win17_g0_h4_kv2_s96_d16", "win64_g5_h4_s200_d32",
                        "win100_g3_h4_kv1_s300_d64_bf16in", "win130_g140_h2_kv1_s520_d128_bf16in"]
+ROPE_GOLDEN_CASES = ["rope_h3_d16_c40_base1e4", "rope_h2_d128_c70_base1e6"]
+ROPE_LAYER_GOLDEN = "ropelayer_h4_kv2_s160_d64_bf16in"
 
 
 def max_abs(a, b):

@@ -48,6 +48,17 @@ WINDOW_CASES = {
 }
 
 
+# rotary embedding: (heads, head_dim, cols, table positions, base, seed): the reference's RotaryEmbedding on a feature-major matrix
+ROPE_CASES = {
+    "rope_h3_d16_c40_base1e4": (3, 16, 40, 64, 1.0e4, 121),
+    "rope_h2_d128_c70_base1e6": (2, 128, 70, 96, 1.0e6, 122),
+}
+# the reference layer with its rotary embedding active (un-rotated inputs in, gradients w.r.t. them out): (spec, base)
+ROPE_LAYER_CASES = {
+    "ropelayer_h4_kv2_s160_d64_bf16in": ((1, 4, 2, 160, 64, 0.5, 131, True), 1.0e4),
+}
+
+
 def make_case(B, Hq, Hkv, S, D, std, seed, bf16_inputs):
     rng = np.random.default_rng(seed)
     q = (rng.standard_normal((B, Hq, S, D)) * std).astype(np.float32)
@@ -74,6 +85,20 @@ def main():
         path = os.path.join(HERE, name + ".npz")
         np.savez_compressed(path, q=q, k=k, v=v, dout=dout, o=o, lse=lse, dq=dq, dk=dk, dv=dv,
                             window=np.int32(window), global_tokens=np.int32(global_tokens))
+        print(f"{name}: wrote {os.path.getsize(path) / 1024:.0f} KiB")
+    for name, (H, D, cols, positions, base, seed) in ROPE_CASES.items():
+        m = np.random.default_rng(seed).standard_normal((H * D, cols)).astype(np.float32)
+        rotated, cos_t, sin_t = cpu.ref_rope(m, H, D, positions, base)
+        unrotated, _, _ = cpu.ref_rope(m, H, D, positions, base, inverse=True)
+        path = os.path.join(HERE, name + ".npz")
+        np.savez_compressed(path, matrix=m, cos=cos_t, sin=sin_t, rotated=rotated, inverse_rotated=unrotated,
+                            heads=np.int32(H), head_dim=np.int32(D), base=np.float32(base))
+        print(f"{name}: wrote {os.path.getsize(path) / 1024:.0f} KiB")
+    for name, (spec, base) in ROPE_LAYER_CASES.items():
+        q, k, v, dout = make_case(*spec)
+        o, dq, dk, dv = cpu.ref_layer_fwd_bwd_rope(q, k, v, dout, base)
+        path = os.path.join(HERE, name + ".npz")
+        np.savez_compressed(path, q=q, k=k, v=v, dout=dout, o=o, dq=dq, dk=dk, dv=dv, base=np.float32(base))
         print(f"{name}: wrote {os.path.getsize(path) / 1024:.0f} KiB")
 
 

@@ -4,7 +4,7 @@ smokes assert (GQA == MHA with repeated K/V, finite differences)."""
 import numpy as np
 import pytest
 
-from conftest import GOLDEN_CASES, WINDOW_GOLDEN_CASES, load_golden, max_abs
+from conftest import GOLDEN_CASES, ROPE_GOLDEN_CASES, ROPE_LAYER_GOLDEN, WINDOW_GOLDEN_CASES, load_golden, max_abs
 
 
 @pytest.mark.parametrize("name", GOLDEN_CASES)
@@ -66,6 +66,42 @@ def test_oracle_cached_queries_equal_reference_full_sequence_rows(oracle, name):
         o, lse = oracle.attn_fwd(g["q"][:, :, S - T:], g["k"], g["v"], **kw)
         assert max_abs(o, g["o"][:, :, S - T:]) < 5e-6
         assert max_abs(lse, g["lse"][:, :, S - T:]) < 5e-6
+
+
+@pytest.mark.parametrize("name", ROPE_GOLDEN_CASES)
+def test_oracle_rotary_embedding_matches_reference_bit_for_bit(oracle, name):
+    """Angle tables and both rotations against the frozen outputs of the reference's RotaryEmbedding: exact equality."""
+    g = load_golden(name)
+    H, D = int(g["heads"]), int(g["head_dim"])
+    cos_t, sin_t = oracle.rope_tables(D, g["cos"].shape[0], float(g["base"]))
+    assert np.array_equal(cos_t, g["cos"]) and np.array_equal(sin_t, g["sin"])
+    assert np.array_equal(oracle.rope_rotate(g["matrix"], H, D, cos_t, sin_t), g["rotated"])
+    assert np.array_equal(oracle.rope_rotate(g["matrix"], H, D, cos_t, sin_t, inverse=True), g["inverse_rotated"])
+    # packs restart positions; an offset continues a sequence
+    cols = g["matrix"].shape[1]
+    seg = oracle.rope_rotate(g["matrix"], H, D, cos_t, sin_t, segment=cols // 2)
+    assert np.array_equal(seg[:, :cols // 2], g["rotated"][:, :cols // 2])
+    assert np.array_equal(seg[:, cols // 2:2 * (cols // 2)],
+                          oracle.rope_rotate(np.ascontiguousarray(g["matrix"][:, cols // 2:2 * (cols // 2)]), H, D, cos_t, sin_t))
+    off = oracle.rope_rotate(np.ascontiguousarray(g["matrix"][:, 5:]), H, D, cos_t, sin_t, position_offset=5)
+    assert np.array_equal(off, g["rotated"][:, 5:])
+
+
+def test_oracle_composed_with_rotation_matches_reference_layer_with_rope(oracle):
+    """rotate -> attention -> inverse-rotate the gradients, restated piecewise, against the reference layer run with its
+    rotary embedding active (frozen outputs)."""
+    g = load_golden(ROPE_LAYER_GOLDEN)
+    B, Hq, S, D = g["q"].shape
+    Hkv = g["k"].shape[1]
+    cos_t, sin_t = oracle.rope_tables(D, S, float(g["base"]))
+    fm = lambda x: np.ascontiguousarray(x[0].transpose(0, 2, 1).reshape(-1, S))
+    un = lambda m, H: np.ascontiguousarray(m.reshape(H, D, S).transpose(0, 2, 1))[None]
+    qr, kr = un(oracle.rope_rotate(fm(g["q"]), Hq, D, cos_t, sin_t), Hq), un(oracle.rope_rotate(fm(g["k"]), Hkv, D, cos_t, sin_t), Hkv)
+    o, _ = oracle.attn_fwd(qr, kr, g["v"])
+    dq, dk, dv, _ = oracle.attn_bwd(qr, kr, g["v"], g["dout"])
+    dq = un(oracle.rope_rotate(fm(dq), Hq, D, cos_t, sin_t, inverse=True), Hq)
+    dk = un(oracle.rope_rotate(fm(dk), Hkv, D, cos_t, sin_t, inverse=True), Hkv)
+    assert max_abs(o, g["o"]) < 5e-6 and max_abs(dq, g["dq"]) < 2e-5 and max_abs(dk, g["dk"]) < 2e-5 and max_abs(dv, g["dv"]) < 2e-5
 
 
 def test_reference_live_matches_golden_and_core_route(oracle):
