@@ -111,6 +111,88 @@ __global__ void rope_unpack_kernel(const __nv_bfloat16* __restrict__ src, float*
     }
 }
 
+// Head sizes that are multiples of 64 (the tensor-core kernels' sizes) take 64-token x 64-feature tiles: every global
+// access is a full 128-byte line per warp (32 tokens of one feature on the fp32 side, the 64 features of one token as
+// bf16 pairs on the other), each thread keeps 16 loads in flight, and a rotation pair lives in one thread.
+// kRot: 0 no rotation, 1 forward, 2 inverse.
+template <int kRot>
+__device__ __forceinline__ void rotate_pair(float& even, float& odd, float c, float sn)
+{
+    if (kRot == 0) return;
+    const float e = even, o = odd;
+    if (kRot == 1) {
+        even = __fsub_rn(__fmul_rn(e, c), __fmul_rn(o, sn));
+        odd = __fadd_rn(__fmul_rn(e, sn), __fmul_rn(o, c));
+    } else {
+        even = __fadd_rn(__fmul_rn(e, c), __fmul_rn(o, sn));
+        odd = __fadd_rn(__fmul_rn(-e, sn), __fmul_rn(o, c));
+    }
+}
+
+template <int kRot>
+__global__ void __launch_bounds__(256) pack64_kernel(const float* __restrict__ src, __nv_bfloat16* __restrict__ dst, int H, int S, int D,
+                                                     int stride_columns, int column_start, const float* __restrict__ cos_t,
+                                                     const float* __restrict__ sin_t, int position_offset)
+{
+    __shared__ float tile[64][65];   // [token][feature]
+    const int bh = blockIdx.z, b = bh / H, h = bh % H;
+    const int s0 = blockIdx.x * 64, d0 = blockIdx.y * 64;
+    const float* base = src + (long long)(h * D + d0) * stride_columns + column_start + (long long)b * S + s0;
+#pragma unroll
+    for (int r = 0; r < 16; ++r) {
+        const int idx = r * 256 + threadIdx.x, d = idx >> 6, sl = idx & 63;
+        tile[sl][d] = (s0 + sl < S) ? base[(long long)d * stride_columns + sl] : 0.0f;
+    }
+    __syncthreads();
+    const int pairs = D >> 1;
+#pragma unroll
+    for (int r = 0; r < 8; ++r) {
+        const int idx = r * 256 + threadIdx.x, sl = idx >> 5, pr = idx & 31;
+        const int s = s0 + sl;
+        if (s >= S) continue;
+        float even = tile[sl][2 * pr], odd = tile[sl][2 * pr + 1];
+        if (kRot != 0) {
+            const long long ti = (long long)(position_offset + s) * pairs + (d0 >> 1) + pr;
+            rotate_pair<kRot>(even, odd, cos_t[ti], sin_t[ti]);
+        }
+        reinterpret_cast<__nv_bfloat162*>(dst + ((long long)bh * S + s) * D + d0)[pr] = __floats2bfloat162_rn(even, odd);
+    }
+}
+
+template <int kRot>
+__global__ void __launch_bounds__(256) unpack64_kernel(const __nv_bfloat16* __restrict__ src, float* __restrict__ dst, int H, int S, int D,
+                                                       int stride_columns, int column_start, const float* __restrict__ cos_t,
+                                                       const float* __restrict__ sin_t, int position_offset)
+{
+    __shared__ float tile[64][65];
+    const int bh = blockIdx.z, b = bh / H, h = bh % H;
+    const int s0 = blockIdx.x * 64, d0 = blockIdx.y * 64;
+    const int pairs = D >> 1;
+#pragma unroll
+    for (int r = 0; r < 8; ++r) {
+        const int idx = r * 256 + threadIdx.x, sl = idx >> 5, pr = idx & 31;
+        const int s = s0 + sl;
+        float even = 0.0f, odd = 0.0f;
+        if (s < S) {
+            const float2 x = __bfloat1622float2(reinterpret_cast<const __nv_bfloat162*>(src + ((long long)bh * S + s) * D + d0)[pr]);
+            even = x.x; odd = x.y;
+            if (kRot != 0) {
+                const long long ti = (long long)(position_offset + s) * pairs + (d0 >> 1) + pr;
+                rotate_pair<kRot>(even, odd, cos_t[ti], sin_t[ti]);
+            }
+        }
+        tile[sl][2 * pr] = even;
+        tile[sl][2 * pr + 1] = odd;
+    }
+    __syncthreads();
+    float* base = dst + (long long)(h * D + d0) * stride_columns + column_start + (long long)b * S + s0;
+#pragma unroll
+    for (int r = 0; r < 16; ++r) {
+        const int idx = r * 256 + threadIdx.x, d = idx >> 6, sl = idx & 63;
+        if (s0 + sl < S) base[(long long)d * stride_columns + sl] = tile[sl][d];
+    }
+}
+
 __global__ void f32_to_bf16_kernel(const float* __restrict__ src, __nv_bfloat16* __restrict__ dst, size_t n)
 {
     for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
@@ -182,6 +264,7 @@ inline int blocks_for(size_t n, int threads)
 cudaError_t sentinel_to_bhsd_bf16(const float* src, __nv_bfloat16* dst, int B, int H, int S, int D, int stride_columns,
                                   int column_start, cudaStream_t st)
 {
+    if (D % 64 == 0 && (long long)B * H <= 65535) return rope_pack_bf16(src, dst, B, H, S, D, stride_columns, column_start, nullptr, nullptr, 0, st);
     dim3 grid((S + 31) / 32, (D + 31) / 32, B * H), block(32, 8);
     sentinel_to_bhsd_kernel<<<grid, block, 0, st>>>(src, dst, H, S, D, stride_columns, column_start);
     count_launch();
@@ -191,6 +274,8 @@ cudaError_t sentinel_to_bhsd_bf16(const float* src, __nv_bfloat16* dst, int B, i
 cudaError_t bhsd_bf16_to_sentinel(const __nv_bfloat16* src, float* dst, int B, int H, int S, int D, int stride_columns,
                                   int column_start, cudaStream_t st)
 {
+    if (D % 64 == 0 && (long long)B * H <= 65535)
+        return rope_unpack_f32(src, dst, B, H, S, D, stride_columns, column_start, nullptr, nullptr, 0, false, st);
     dim3 grid((S + 31) / 32, (D + 31) / 32, B * H), block(32, 8);
     bhsd_to_sentinel_kernel<<<grid, block, 0, st>>>(src, dst, H, S, D, stride_columns, column_start);
     count_launch();
@@ -200,6 +285,13 @@ cudaError_t bhsd_bf16_to_sentinel(const __nv_bfloat16* src, float* dst, int B, i
 cudaError_t rope_pack_bf16(const float* src, __nv_bfloat16* dst, int B, int H, int S, int D, int stride_columns,
                            int column_start, const float* cos_t, const float* sin_t, int position_offset, cudaStream_t st)
 {
+    if (D % 64 == 0) {
+        dim3 grid((S + 63) / 64, D / 64, B * H);
+        if (cos_t) pack64_kernel<1><<<grid, 256, 0, st>>>(src, dst, H, S, D, stride_columns, column_start, cos_t, sin_t, position_offset);
+        else pack64_kernel<0><<<grid, 256, 0, st>>>(src, dst, H, S, D, stride_columns, column_start, nullptr, nullptr, 0);
+        count_launch();
+        return cudaGetLastError();
+    }
     if (!cos_t) return sentinel_to_bhsd_bf16(src, dst, B, H, S, D, stride_columns, column_start, st);
     dim3 grid((S + 31) / 32, (D + 31) / 32, B * H), block(32, 8);
     rope_pack_kernel<<<grid, block, 0, st>>>(src, dst, H, S, D, stride_columns, column_start, cos_t, sin_t, position_offset);
@@ -211,6 +303,14 @@ cudaError_t rope_unpack_f32(const __nv_bfloat16* src, float* dst, int B, int H, 
                             int column_start, const float* cos_t, const float* sin_t, int position_offset, bool inverse,
                             cudaStream_t st)
 {
+    if (D % 64 == 0) {
+        dim3 grid((S + 63) / 64, D / 64, B * H);
+        if (!cos_t) unpack64_kernel<0><<<grid, 256, 0, st>>>(src, dst, H, S, D, stride_columns, column_start, nullptr, nullptr, 0);
+        else if (inverse) unpack64_kernel<2><<<grid, 256, 0, st>>>(src, dst, H, S, D, stride_columns, column_start, cos_t, sin_t, position_offset);
+        else unpack64_kernel<1><<<grid, 256, 0, st>>>(src, dst, H, S, D, stride_columns, column_start, cos_t, sin_t, position_offset);
+        count_launch();
+        return cudaGetLastError();
+    }
     if (!cos_t) return bhsd_bf16_to_sentinel(src, dst, B, H, S, D, stride_columns, column_start, st);
     dim3 grid((S + 31) / 32, (D + 31) / 32, B * H), block(32, 8);
     if (inverse)
