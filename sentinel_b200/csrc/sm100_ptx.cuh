@@ -317,6 +317,13 @@ __device__ __forceinline__ float ex2(float x)
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
+// three-input maximum in one instruction (NaN operands are ignored, like fmaxf)
+__device__ __forceinline__ float fmax3(float a, float b, float c)
+{
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi)
 {
     uint32_t r;

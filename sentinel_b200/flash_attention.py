@@ -27,10 +27,11 @@ def _stream_ptr() -> int:
 
 
 def _workspace(nbytes: int, device) -> torch.Tensor | None:
-    """Grow-only scratch per device (the reference grows its buffers the same way, CudaMatmul.cu:119-136)."""
+    """Grow-only scratch per (device, stream) (the reference grows its buffers the same way, CudaMatmul.cu:119-136).
+    Calls on different streams may overlap on the GPU, so each stream gets scratch of its own."""
     if nbytes == 0:
         return None
-    key = (device.type, device.index)
+    key = (device.type, device.index, torch.cuda.current_stream(device).cuda_stream)
     buf = _ws_cache.get(key)
     if buf is None or buf.numel() < nbytes:
         buf = torch.empty(nbytes, dtype=torch.uint8, device=device)

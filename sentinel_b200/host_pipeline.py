@@ -3,10 +3,12 @@
 A caller that keeps its activations in host memory pays for 538 MB of PCIe traffic per step of the headline workload,
 several times the kernels' own time.  This module hides as much of it as the dependencies allow:
 
-* three streams: upload, compute, download (the two PCIe directions run concurrently);
+* an upload stream, a download stream (the two PCIe directions run concurrently) and two compute streams;
 * the problem is cut into chunks of whole (batch element, KV group) units -- every chunk is a complete attention
   problem, contiguous in memory, so nothing is exchanged between chunks -- and chunk c+1 uploads while chunk c computes
   and chunk c-1 downloads;
+* chunks alternate between the two compute streams: a chunk's backward ends with a few long-running CTAs (the first
+  key tiles visit every query tile), and the next chunk's kernels fill the SMs those leave idle;
 * inside a chunk the forward starts as soon as Q, K, V are on the device (dO follows during the forward), O and LSE
   go back while the backward runs, and the gradients go back while the next chunk computes.
 
@@ -34,6 +36,7 @@ def _buffers(q, k, dev):
             "h_dk": torch.empty(k.shape, dtype=k.dtype).pin_memory(), "h_dv": torch.empty(k.shape, dtype=k.dtype).pin_memory(),
             "h_lse": torch.empty(q.shape[:3], dtype=torch.float32).pin_memory(),
             "up": torch.cuda.Stream(device=dev), "down": torch.cuda.Stream(device=dev),
+            "compute": [torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)],
         }
         _cache.clear()          # one shape at a time: the staging buffers are as large as the problem
         _cache[key] = buf
@@ -68,12 +71,13 @@ def forward_backward_host(q, k, v, dout, *, causal=True, scale=None, flags=0, de
         dev = torch.device("cuda", torch.cuda.current_device())
     B, Hq, Hkv = q.shape[0], q.shape[1], k.shape[1]
     buf = _buffers(q, k, dev)
-    comp = torch.cuda.current_stream(dev)
-    up, down = buf["up"], buf["down"]
-    up.wait_stream(comp)      # earlier users of the staging buffers are done
-    down.wait_stream(comp)
-    for sb, sq, sk in _chunk_slices(B, Hq, Hkv, chunks):
+    caller = torch.cuda.current_stream(dev)
+    up, down, lanes = buf["up"], buf["down"], buf["compute"]
+    for st in (up, down, *lanes):
+        st.wait_stream(caller)      # earlier users of the staging buffers are done
+    for c, (sb, sq, sk) in enumerate(_chunk_slices(B, Hq, Hkv, chunks)):
         qs, ks = (sb, sq), (sb, sk)
+        comp = lanes[c % len(lanes)]
         with torch.cuda.stream(up):
             buf["q"][qs].copy_(q[qs], non_blocking=True)
             buf["k"][ks].copy_(k[ks], non_blocking=True)
@@ -83,26 +87,29 @@ def forward_backward_host(q, k, v, dout, *, causal=True, scale=None, flags=0, de
             buf["do"][qs].copy_(dout[qs], non_blocking=True)
             ev_do = torch.cuda.Event()
             ev_do.record(up)
-        comp.wait_event(ev_qkv)
-        fa.attention_forward(buf["q"][qs], buf["k"][ks], buf["v"][ks], causal=causal, scale=scale, flags=flags,
-                             out=buf["o"][qs], lse=buf["lse"][qs], window=window, global_tokens=global_tokens)
-        ev_fwd = torch.cuda.Event()
-        ev_fwd.record(comp)
+        with torch.cuda.stream(comp):
+            comp.wait_event(ev_qkv)
+            fa.attention_forward(buf["q"][qs], buf["k"][ks], buf["v"][ks], causal=causal, scale=scale, flags=flags,
+                                 out=buf["o"][qs], lse=buf["lse"][qs], window=window, global_tokens=global_tokens)
+            ev_fwd = torch.cuda.Event()
+            ev_fwd.record(comp)
         with torch.cuda.stream(down):
             down.wait_event(ev_fwd)
             buf["h_o"][qs].copy_(buf["o"][qs], non_blocking=True)
             buf["h_lse"][qs].copy_(buf["lse"][qs], non_blocking=True)
-        comp.wait_event(ev_do)
-        fa.attention_backward(buf["q"][qs], buf["k"][ks], buf["v"][ks], buf["o"][qs], buf["lse"][qs], buf["do"][qs],
-                              causal=causal, scale=scale, flags=flags, dq=buf["dq"][qs], dk=buf["dk"][ks], dv=buf["dv"][ks],
-                              window=window, global_tokens=global_tokens)
-        ev_bwd = torch.cuda.Event()
-        ev_bwd.record(comp)
+        with torch.cuda.stream(comp):
+            comp.wait_event(ev_do)
+            fa.attention_backward(buf["q"][qs], buf["k"][ks], buf["v"][ks], buf["o"][qs], buf["lse"][qs], buf["do"][qs],
+                                  causal=causal, scale=scale, flags=flags, dq=buf["dq"][qs], dk=buf["dk"][ks],
+                                  dv=buf["dv"][ks], window=window, global_tokens=global_tokens)
+            ev_bwd = torch.cuda.Event()
+            ev_bwd.record(comp)
         with torch.cuda.stream(down):
             down.wait_event(ev_bwd)
             buf["h_dq"][qs].copy_(buf["dq"][qs], non_blocking=True)
             buf["h_dk"][ks].copy_(buf["dk"][ks], non_blocking=True)
             buf["h_dv"][ks].copy_(buf["dv"][ks], non_blocking=True)
-    comp.wait_stream(down)     # the timed region (events on the compute stream) ends after the last download
-    comp.synchronize()
+    for st in (up, down, *lanes):
+        caller.wait_stream(st)     # a timed region (events on the caller's stream) ends after the last download
+    caller.synchronize()
     return buf["h_o"], buf["h_lse"], buf["h_dq"], buf["h_dk"], buf["h_dv"]
