@@ -29,6 +29,12 @@
 //
 // A pre-pass computes delta = rowsum(dO o O), LSE*log2e (padded rows get +inf so they produce P = 0) and
 // zeroes the dQ accumulator; a post-pass converts the accumulator to bf16 dQ (times scale).
+//
+// Long key tiles.  The CTA of key tile 0 visits every query tile of every head of its group; when the grid is small
+// (few batch elements x KV heads, as in the chunks of the host-buffer pipeline) or a sliding window leaves only the
+// global-token tiles long, that one CTA outlasts the average SM's whole load and bounds the kernel.  Such tiles are
+// cut by query head: one CTA per (key tile, KV head, query head of the group), each leaving its dK/dV as an fp32
+// partial in scratch, and a small kernel adds the partials in head order (deterministic) and writes bf16.
 // TMEM map (512 columns): S^T/P^T [0,128)  dP^T/dS^T/dQ [128,256)  dV [256,256+D)  dK [384,384+D).
 #include "common.cuh"
 #include "sm100_ptx.cuh"
@@ -57,8 +63,36 @@ struct BwdParams {
     int causal;
     int window, global_tokens;   // sliding window and always-visible first keys (0, 0: plain causal)
     int n_qt, n_kt;
+    int split_tiles;       // the first split_tiles key tiles are cut into one CTA per query head of the group
+    float* dkv_part;       // [split tile][slab][head of group][dV, dK][128][D] fp32
     float scale, scale_log2;
 };
+
+constexpr int kSmCount = 148;
+
+// Query tiles per head that key tile kt visits (the kernel's own rule)
+__host__ __device__ inline int bwd_tiles_per_head(int kt, int n_qt, int causal, int window, int global_tokens)
+{
+    const int qt_first = causal ? kt : 0;
+    const int k0 = kt * kT;
+    const int qt_last = (window > 0 && k0 >= global_tokens) ? min(n_qt - 1, (k0 + kT - 1 + window - 1) / kT) : n_qt - 1;
+    return max(0, qt_last - qt_first + 1);
+}
+
+// How many leading key tiles to cut by query head: those whose CTA would run longer than the average load of an SM.
+inline int bwd_split_tiles(const AttnShape& s)
+{
+    const int group = s.Hq / s.Hkv;
+    if (group <= 1) return 0;
+    const int n_qt = (s.Sq + kT - 1) / kT, n_kt = (s.Skv + kT - 1) / kT;
+    const int window = s.causal ? s.window : 0;
+    double total = 0.0;
+    for (int kt = 0; kt < n_kt; ++kt) total += bwd_tiles_per_head(kt, n_qt, s.causal, window, s.global_tokens);
+    const double avg = total * group * s.B * s.Hkv / kSmCount;
+    int n = 0;
+    while (n < n_kt && (double)bwd_tiles_per_head(n, n_qt, s.causal, window, s.global_tokens) * group > avg) ++n;
+    return n;
+}
 
 struct BwdBarriers {
     uint64_t kv_full;
@@ -68,7 +102,9 @@ struct BwdBarriers {
     uint32_t abort_flag;
 };
 
-template <int D, bool kWin>
+// kSplit: the grid may hold key tiles cut by query head (a separate instantiation, so that the plain kernel carries none
+// of that bookkeeping)
+template <int D, bool kWin, bool kSplit>
 __global__ void __launch_bounds__(kBwdThreads, 1)
 attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                    const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_do, const BwdParams p)
@@ -103,17 +139,30 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
 
     // ---- work decode: key tile 0 sees every query tile, so low key tiles go first ----
     const int slabs = p.B * p.Hkv;
-    const int kt = blockIdx.x / slabs;
-    const int slab = blockIdx.x - kt * slabs;           // b * Hkv + hk
-    const int b = slab / p.Hkv, hk = slab - b * p.Hkv;
     const int group = p.Hq / p.Hkv;
+    // the first split_tiles key tiles come as one CTA per (tile, head of the group, slab), the rest as one per (tile, slab)
+    const int n_split_ctas = kSplit ? p.split_tiles * group * slabs : 0;
+    int kt, slab, g0 = 0, n_heads = group;
+    const bool split = kSplit && (int)blockIdx.x < n_split_ctas;
+    if (split) {
+        kt = blockIdx.x / (group * slabs);
+        const int rem = blockIdx.x - kt * group * slabs;
+        g0 = rem / slabs;
+        slab = rem - g0 * slabs;
+        n_heads = 1;
+    } else {
+        const int idx = blockIdx.x - n_split_ctas;
+        kt = p.split_tiles + idx / slabs;
+        slab = idx - (idx / slabs) * slabs;             // b * Hkv + hk
+    }
+    const int b = slab / p.Hkv, hk = slab - b * p.Hkv;
     const int k0 = kt * kT;
     const int qt_first = p.causal ? kt : 0;
     // with a sliding window the last query that sees this tile is (last key + window - 1), unless the tile holds
     // global tokens, which every later query sees
     const int qt_last = (kWin && k0 >= p.global_tokens) ? min(p.n_qt - 1, (k0 + kT - 1 + p.window - 1) / kT) : p.n_qt - 1;
     const int per_head = qt_last - qt_first + 1;        // query tiles per head this CTA visits
-    const int n_iter = per_head > 0 ? per_head * group : 0;
+    const int n_iter = per_head > 0 ? per_head * n_heads : 0;
 
     if (warp == 13 && lane == 0) {
         prefetch_tensormap(&tmap_q);
@@ -165,7 +214,7 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
             }
             for (int i = 0; i < n_iter; ++i) {
                 const int g = i / per_head, qt = qt_first + (i - g * per_head);
-                const int bh = b * p.Hq + hk * group + g;
+                const int bh = b * p.Hq + hk * group + g0 + g;
                 const int sq = i & 1;
                 if (i >= 2 && !mbar_wait(&bars->q_empty[sq], (uint32_t)(((i >> 1) - 1) & 1), abort_flag, kSiteQEmpty)) break;
                 mbar_arrive_expect_tx(&bars->q_full[sq], (uint32_t)(kTileBytes + 2 * kT * 4));
@@ -323,7 +372,7 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
         bool ok = true;
         for (int i = 0; i < n_iter; ++i) {
             const int g = i / per_head, qt = qt_first + (i - g * per_head);
-            const int bh = b * p.Hq + hk * group + g;
+            const int bh = b * p.Hq + hk * group + g0 + g;
             float* tile = p.dq_accum + ((size_t)bh * p.n_qt + qt) * (size_t)(kT * D);
             ok = __all_sync(0xffffffffu, mbar_wait(&bars->dq_ready, (uint32_t)(i & 1), abort_flag, kSiteDQ));
             SNTL_TRACE_EV(tw, 3, tn, 1);
@@ -466,7 +515,26 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
         }
         // ---- epilogue: dV (warpgroup 0) and dK (warpgroup 1) ----
         ok = __all_sync(0xffffffffu, ok && n_iter > 0 && mbar_wait(&bars->final_bar, 0, abort_flag, kSiteFinal));
-        if (ok) {
+        if (split) {
+            // this CTA's share of dV (warpgroup 0) / dK (warpgroup 1) as an fp32 partial; zeros if it saw no query
+            float* dst = p.dkv_part + ((((size_t)kt * slabs + slab) * group + g0) * 2 + wg) * (size_t)(kT * D) + (size_t)row * D;
+            const uint32_t src = (wg == 0 ? tm_dV : tm_dK) + lane_off;
+            if (ok) tc_fence_after();
+#pragma unroll
+            for (int c = 0; c < D / 32; ++c) {
+                uint32_t r[32];
+                if (ok) {
+                    tmem_ld32(src + (uint32_t)(c * 32), r);
+                    tmem_ld_wait();
+                } else {
+#pragma unroll
+                    for (int v = 0; v < 32; ++v) r[v] = 0u;
+                }
+#pragma unroll
+                for (int v = 0; v < 8; ++v)
+                    *reinterpret_cast<uint4*>(dst + c * 32 + v * 4) = make_uint4(r[4 * v], r[4 * v + 1], r[4 * v + 2], r[4 * v + 3]);
+            }
+        } else if (ok) {
             tc_fence_after();
             const int key = k0 + row;
             const bool store = key < p.Skv;
@@ -584,7 +652,42 @@ __global__ void __launch_bounds__(256) bwd_post_kernel(const float* __restrict__
 
 inline size_t align256(size_t x) { return (x + 255) / 256 * 256; }
 
-template <int D, bool kWin>
+// dV / dK of the key tiles that were cut by query head: the partials of a tile are added in head order and written as
+// bf16 (dK times the softmax scale).  One thread per 8 consecutive features of one key row.
+template <int D>
+__global__ void __launch_bounds__(256) bwd_dkv_reduce_kernel(const float* __restrict__ part, __nv_bfloat16* __restrict__ dk,
+                                                             __nv_bfloat16* __restrict__ dv, int slabs, int group, int Skv,
+                                                             float scale, long long n_units)
+{
+    const long long u = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (u >= n_units) return;
+    constexpr int kPerRow = D / 8;
+    const int d8 = (int)(u % kPerRow) * 8;
+    long long r = u / kPerRow;
+    const int row = (int)(r % kT); r /= kT;
+    const int which = (int)(r & 1); r >>= 1;              // 0: dV, 1: dK
+    const int slab = (int)(r % slabs);
+    const int kt = (int)(r / slabs);
+    const int key = kt * kT + row;
+    if (key >= Skv) return;
+    const float* src = part + (((size_t)kt * slabs + slab) * group * 2 + which) * (size_t)(kT * D) + (size_t)row * D + d8;
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int g = 0; g < group; ++g) {
+        const float4 a = *reinterpret_cast<const float4*>(src + (size_t)g * 2 * kT * D);
+        const float4 c = *reinterpret_cast<const float4*>(src + (size_t)g * 2 * kT * D + 4);
+        acc[0] += a.x; acc[1] += a.y; acc[2] += a.z; acc[3] += a.w;
+        acc[4] += c.x; acc[5] += c.y; acc[6] += c.z; acc[7] += c.w;
+    }
+    const float mul = which ? scale : 1.0f;
+    uint4 w;
+    w.x = pack_bf16(acc[0] * mul, acc[1] * mul);
+    w.y = pack_bf16(acc[2] * mul, acc[3] * mul);
+    w.z = pack_bf16(acc[4] * mul, acc[5] * mul);
+    w.w = pack_bf16(acc[6] * mul, acc[7] * mul);
+    *reinterpret_cast<uint4*>((which ? dk : dv) + ((size_t)slab * Skv + key) * D + d8) = w;
+}
+
+template <int D, bool kWin, bool kSplit>
 cudaError_t launch_bwd(const TcArgs& a, cudaStream_t st)
 {
     const AttnShape& s = a.s;
@@ -614,21 +717,31 @@ cudaError_t launch_bwd(const TcArgs& a, cudaStream_t st)
     p.window = s.causal ? s.window : 0;
     p.global_tokens = s.global_tokens;
     p.n_qt = n_qt; p.n_kt = n_kt;
+    p.split_tiles = kSplit ? bwd_split_tiles(s) : 0;
+    p.dkv_part = reinterpret_cast<float*>(reinterpret_cast<char*>(a.dq_accum) + align256(4 * (size_t)rows_padded * D));
     p.scale = s.scale;
     p.scale_log2 = s.scale * 1.4426950408889634f;
     constexpr int kDoStages = (D == 128) ? 1 : 2;
     const size_t smem = (size_t)(128 * D * 2) * (4 + kDoStages) + 128 * 128 * 2 + 2 * (32 * 128 * 4) + 4 * 128 * 4 + sizeof(BwdBarriers);
     static bool configured = false;
     if (!configured) {
-        if ((e = cudaFuncSetAttribute(attn_bwd_tc_kernel<D, kWin>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)) != cudaSuccess)
+        if ((e = cudaFuncSetAttribute(attn_bwd_tc_kernel<D, kWin, kSplit>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)) != cudaSuccess)
             return e;
         configured = true;
     }
-    const long long ctas = (long long)n_kt * s.B * s.Hkv;
+    const int group = s.Hq / s.Hkv, slabs = s.B * s.Hkv;
+    const long long ctas = (long long)p.split_tiles * group * slabs + (long long)(n_kt - p.split_tiles) * slabs;
     if (ctas > 0x7fffffffLL) return cudaErrorInvalidConfiguration;
-    attn_bwd_tc_kernel<D, kWin><<<(unsigned)ctas, kBwdThreads, smem, st>>>(tq, tk, tv, tdo, p);
+    attn_bwd_tc_kernel<D, kWin, kSplit><<<(unsigned)ctas, kBwdThreads, smem, st>>>(tq, tk, tv, tdo, p);
     count_launch();
     if ((e = cudaGetLastError()) != cudaSuccess) return e;
+    if (p.split_tiles > 0) {
+        const long long n_units = (long long)p.split_tiles * slabs * 2 * kT * (D / 8);
+        bwd_dkv_reduce_kernel<D><<<(unsigned)((n_units + 255) / 256), 256, 0, st>>>(p.dkv_part, a.dk, a.dv, slabs, group, s.Skv,
+                                                                                   s.scale, n_units);
+        count_launch();
+        if ((e = cudaGetLastError()) != cudaSuccess) return e;
+    }
     bwd_post_kernel<D><<<(unsigned)((long long)s.B * s.Hq * n_qt * 4), 256, 0, st>>>(a.dq_accum, a.dq, s.Sq, n_qt, s.scale);
     count_launch();
     return cudaGetLastError();
@@ -641,19 +754,25 @@ bool tc_bwd_supported(const AttnShape& s)
     return (s.D == 64 || s.D == 128) && (!s.causal || s.Sq == s.Skv);
 }
 
-// [delta: B*Hq*Sq_pad fp32][lse2: same], 256-byte aligned, then the fp32 dQ accumulator B*Hq*Sq_pad*D
+// [delta: B*Hq*Sq_pad fp32][lse2: same], 256-byte aligned, then the fp32 dQ accumulator B*Hq*Sq_pad*D, then the fp32
+// dK/dV partials of the key tiles that are cut by query head (none for most shapes)
 size_t tc_backward_workspace_bytes(const AttnShape& s)
 {
     const size_t sq_pad = ((size_t)s.Sq + kT - 1) / kT * kT;
     const size_t rows = (size_t)s.B * s.Hq * sq_pad;
-    return align256(2 * 4 * rows) + align256(4 * rows * (size_t)s.D);
+    const size_t part = (size_t)bwd_split_tiles(s) * s.B * s.Hq * 2 * kT * (size_t)s.D * 4;   // slabs * group = B * Hq
+    return align256(2 * 4 * rows) + align256(4 * rows * (size_t)s.D) + align256(part);
 }
 
 cudaError_t tc_backward(const TcArgs& a, cudaStream_t st)
 {
     const bool win = a.s.causal && a.s.window > 0;
-    if (a.s.D == 64) return win ? launch_bwd<64, true>(a, st) : launch_bwd<64, false>(a, st);
-    return win ? launch_bwd<128, true>(a, st) : launch_bwd<128, false>(a, st);
+    if (bwd_split_tiles(a.s) > 0) {
+        if (a.s.D == 64) return win ? launch_bwd<64, true, true>(a, st) : launch_bwd<64, false, true>(a, st);
+        return win ? launch_bwd<128, true, true>(a, st) : launch_bwd<128, false, true>(a, st);
+    }
+    if (a.s.D == 64) return win ? launch_bwd<64, true, false>(a, st) : launch_bwd<64, false, false>(a, st);
+    return win ? launch_bwd<128, true, false>(a, st) : launch_bwd<128, false, false>(a, st);
 }
 
 #ifdef SNTL_TRACE

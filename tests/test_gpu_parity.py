@@ -257,7 +257,8 @@ def test_staged_fp32_sentinel_layout_on_tensor_cores(sb, oracle):
 
 def test_forward_is_deterministic_and_recompute_stable(sb):
     """Activation checkpointing re-runs the forward inside backward (CudaTransformerBlock.cu:277-284): two runs
-    must agree bit for bit, and so must two backward runs of dK/dV (each is owned by one CTA)."""
+    must agree bit for bit, and so must two backward runs of dK/dV (each key tile is owned by one CTA, or by one CTA
+    per query head whose partials are added in a fixed order)."""
     w = sb.WORKLOADS["gqa7b_d128"]
     q, k, v, do = (t.cuda() for t in _bf16_case(w, batch=1, q_heads=4, kv_heads=1, seq=512))
     o1, l1 = sb.attention_forward(q, k, v)
@@ -266,6 +267,38 @@ def test_forward_is_deterministic_and_recompute_stable(sb):
     _, dk1, dv1 = sb.attention_backward(q, k, v, o1, l1, do)
     _, dk2, dv2 = sb.attention_backward(q, k, v, o1, l1, do)
     assert torch.equal(dk1, dk2) and torch.equal(dv1, dv2)
+
+
+def test_backward_long_key_tiles_cut_by_query_head(sb, oracle):
+    """On a small grid the backward cuts the key tiles whose CTA would outlast an SM's average load into one CTA per
+    query head of the group and adds their fp32 dK/dV partials in head order.  B4 / Hq28 / Hkv4 / S768 mixes cut tiles
+    (the first four) with uncut ones (the last two): dK/dV of both kinds against fp64-oracle columns and against the
+    exact kernels on a whole slice, dQ rows against the oracle, and two runs bit-identical."""
+    w = sb.WORKLOADS["gqa7b_d128"]
+    q, k, v, do = _bf16_case(w, batch=4, q_heads=28, kv_heads=4, seq=768)
+    qd, kd, vd, dod = (t.cuda() for t in (q, k, v, do))
+    o, lse = sb.attention_forward(qd, kd, vd)
+    dq, dk, dv = sb.attention_backward(qd, kd, vd, o, lse, dod)
+    assert sb.last_path() == "tcgen05" and sb.poll_device_status() == 0
+    dq2, dk2, dv2 = sb.attention_backward(qd, kd, vd, o, lse, dod)
+    assert torch.equal(dk, dk2) and torch.equal(dv, dv2)
+    qf, kf, vf, dof = (t.to(torch.float32).numpy() for t in (q, k, v, do))
+    cols = np.array([0, 100, 383, 511, 512, 767])       # key tiles 0, 0, 2, 3 (cut) and 4, 5 (uncut)
+    for (b, hk) in ((0, 0), (3, 3)):
+        wdk, wdv = oracle.attn_cols(qf, kf, vf, dof, b, hk, cols)
+        _check_bf16(_np(dk[b, hk, cols]), wdk, "dk cols")
+        _check_bf16(_np(dv[b, hk, cols]), wdv, "dv cols")
+    rows = np.array([127, 128, 400, 767])
+    _, _, wdq = oracle.attn_rows(qf, kf, vf, dof, 2, 13, rows)
+    _check_bf16(_np(dq[2, 13, rows]), wdq, "dq rows")
+    b, hk = 1, 2
+    hs = slice(hk * 7, (hk + 1) * 7)
+    q1, k1, v1, do1 = qd[b:b + 1, hs].float(), kd[b:b + 1, hk:hk + 1].float(), vd[b:b + 1, hk:hk + 1].float(), dod[b:b + 1, hs].float()
+    o1, l1 = sb.attention_forward(q1, k1, v1)
+    assert sb.last_path() == "simt_f32"
+    dq1, dk1, dv1 = sb.attention_backward(q1, k1, v1, o1, l1, do1)
+    for got, want, what in ((dq[b:b + 1, hs], dq1, "dQ"), (dk[b:b + 1, hk:hk + 1], dk1, "dK"), (dv[b:b + 1, hk:hk + 1], dv1, "dV")):
+        _check_bf16(_np(got), _np(want), what + " slice vs exact kernels")
 
 
 @pytest.mark.parametrize("wname", ["gpt2_small", "llama1b_gqa", "gqa7b_d128"])
