@@ -240,8 +240,67 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
         //   warp 14 ("dS side"):  dK_i += dS^T Q_i ,  dQ_i = dS K ,  dP^T_{i+1} = V dO_{i+1}^T
         // Every TMEM region with a write-after-read hazard is touched by one of the two only (S^T/P^T by warp 12,
         // dP^T/dS^T/dQ by warp 14), so the in-order execution of one thread's MMAs still covers those hazards.  The Q
-        // and dO stages are read by both and are released when both have committed (barrier count 2).
-        if (lane == 0 && n_iter > 0) {
+        // and dO stages are read by both and are released when both have committed (barrier count 2).  Each commits its
+        // share of a dO stage right after its own product that reads it: with one dO stage (head_dim 128) the next dO tile
+        // can only be loaded once both have, and dP^T_{i+1} waits for that load.
+        if (warp == 12 && n_iter > 0) {
+            // P side: all 32 lanes walk the loop (warp-uniform control flow lets descriptors and addresses live in uniform
+            // registers) and one elected lane issues each tcgen05 instruction.  dV_i and S^T_{i+1} head the chain the compute
+            // warps wait on, and this form issues 8 MMAs in ~720 cycles against ~1100 for a single-lane loop.
+            SNTL_TRACE_DECL(tn);
+            const bool tl = lane == 0;
+            (void)tl;
+            constexpr uint32_t idesc_st = make_idesc(kT, kT, false, false);
+            constexpr uint32_t idesc_kv = make_idesc(kT, D, false, true);
+            auto wait = [&](uint64_t* bar, uint32_t parity, uint32_t site) {
+                return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag, site));
+            };
+            auto issue_kmajor = [&](uint32_t d_tmem, uint64_t a, uint64_t b) {
+                mma_ss_e<false>(d_tmem, a, b, idesc_st);
+#pragma unroll
+                for (int ks = 1; ks < D / 16; ++ks) {
+                    const uint32_t off = (uint32_t)((ks >> 2) * kChunkBytes + (ks & 3) * 32);
+                    mma_ss_e<true>(d_tmem, sdesc_advance(a, off), sdesc_advance(b, off), idesc_st);
+                }
+            };
+            auto issue_from_tmem = [&](uint32_t d_tmem, uint32_t a_tmem, uint64_t b, bool accumulate) {
+                if (accumulate) mma_ts_e<true>(d_tmem, a_tmem, b, idesc_kv);
+                else mma_ts_e<false>(d_tmem, a_tmem, b, idesc_kv);
+#pragma unroll
+                for (int ks = 1; ks < kT / 16; ++ks)
+                    mma_ts_e<true>(d_tmem, a_tmem + (uint32_t)((ks >> 2) * 64 + (ks & 3) * 8), sdesc_advance(b, ks * 2048), idesc_kv);
+            };
+            bool ok = wait(&bars->kv_full, 0, kSiteKV);
+            const uint64_t dK_k = make_sdesc(smem_u32(sK), 16, 1024);
+            const uint64_t dQ_k0 = make_sdesc(smem_u32(sQ), 16, 1024), dDo_mn0 = make_sdesc(smem_u32(sDo), kChunkBytes, 1024);
+            ok = ok && wait(&bars->q_full[0], 0, kSiteQFull);
+            if (ok) {
+                tc_fence_after();
+                issue_kmajor(tm_S, dK_k, dQ_k0);
+                tc_commit_e(&bars->s_ready);
+            }
+            for (int i = 0; ok && i < n_iter; ++i) {
+                const int sq = i & 1, sd = i % kDoStages;
+                if (!(ok = wait(&bars->p_ready, (uint32_t)(i & 1), kSiteP))) break;
+                if (!(ok = wait(&bars->do_full[sd], (uint32_t)((i / kDoStages) & 1), kSiteDoFull))) break;
+                SNTL_TRACE_EV(tl, 0, tn, 1);
+                tc_fence_after();
+                issue_from_tmem(tm_dV, tm_S, sdesc_advance(dDo_mn0, sd * kTileBytes), i > 0);
+                tc_commit_e(&bars->do_empty[sd]);
+                tc_commit_e(&bars->q_empty[sq]);
+                SNTL_TRACE_EV(tl, 0, tn, 2);
+                if (i + 1 < n_iter) {
+                    const int nq = (i + 1) & 1;
+                    if (!(ok = wait(&bars->q_full[nq], (uint32_t)(((i + 1) >> 1) & 1), kSiteQFull))) break;
+                    tc_fence_after();
+                    issue_kmajor(tm_S, dK_k, sdesc_advance(dQ_k0, nq * kTileBytes));
+                    tc_commit_e(&bars->s_ready);
+                    SNTL_TRACE_EV(tl, 0, tn, 9);
+                }
+            }
+            tc_commit_e(&bars->final_bar);
+            wait(&bars->final_bar, 0, kSiteFinal);
+        } else if (warp == 14 && lane == 0 && n_iter > 0) {
             SNTL_TRACE_DECL(tn);
             constexpr uint32_t idesc_st = make_idesc(kT, kT, false, false);   // S^T, dP^T
             constexpr uint32_t idesc_kv = make_idesc(kT, D, false, true);     // dV, dK: A in TMEM, B MN-major
@@ -258,47 +317,8 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
                     mma_ss_c<true>(d_tmem, sdesc_advance(a, off), sdesc_advance(b, off), idesc_st);
                 }
             };
-            // C[128 keys x D] (+)= A^T[128 keys x 128 q] (packed bf16 in TMEM) * B[128 q x D] (MN-major tile)
-            auto issue_from_tmem = [&](uint32_t d_tmem, uint32_t a_tmem, uint64_t b, bool accumulate) {
-                asm volatile("" : "+l"(b));
-                if (accumulate) mma_ts_c<true>(d_tmem, a_tmem, b, idesc_kv);
-                else mma_ts_c<false>(d_tmem, a_tmem, b, idesc_kv);
-#pragma unroll
-                for (int ks = 1; ks < kT / 16; ++ks)
-                    mma_ts_c<true>(d_tmem, a_tmem + (uint32_t)((ks >> 2) * 64 + (ks & 3) * 8), sdesc_advance(b, ks * 2048), idesc_kv);
-            };
             bool ok = mbar_wait(&bars->kv_full, 0, abort_flag, kSiteKV);
-            if (warp == 12) {
-                const uint64_t dK_k = make_sdesc(smem_u32(sK), 16, 1024);
-                const uint64_t dQ_k0 = make_sdesc(smem_u32(sQ), 16, 1024), dDo_mn0 = make_sdesc(smem_u32(sDo), kChunkBytes, 1024);
-                ok = ok && mbar_wait(&bars->q_full[0], 0, abort_flag, kSiteQFull);
-                if (ok) {
-                    tc_fence_after();
-                    issue_kmajor(tm_S, dK_k, dQ_k0);
-                    tc_commit(&bars->s_ready);
-                }
-                for (int i = 0; ok && i < n_iter; ++i) {
-                    const int sq = i & 1, sd = i % kDoStages;
-                    if (!(ok = mbar_wait(&bars->p_ready, (uint32_t)(i & 1), abort_flag, kSiteP))) break;
-                    // dO_i has normally been consumed by the other issuer's dP^T_i already, but nothing orders the two
-                    // issuers, so this one checks the stage itself
-                    if (!(ok = mbar_wait(&bars->do_full[sd], (uint32_t)((i / kDoStages) & 1), abort_flag, kSiteDoFull))) break;
-                    SNTL_TRACE_EV(true, 0, tn, 1);
-                    tc_fence_after();
-                    issue_from_tmem(tm_dV, tm_S, sdesc_advance(dDo_mn0, sd * kTileBytes), i > 0);
-                    tc_commit(&bars->do_empty[sd]);   // this warp's share: dV_i
-                    tc_commit(&bars->q_empty[sq]);    // this warp's share: S^T_i (issued one step earlier)
-                    SNTL_TRACE_EV(true, 0, tn, 2);
-                    if (i + 1 < n_iter) {
-                        const int nq = (i + 1) & 1;
-                        if (!(ok = mbar_wait(&bars->q_full[nq], (uint32_t)(((i + 1) >> 1) & 1), abort_flag, kSiteQFull))) break;
-                        tc_fence_after();
-                        issue_kmajor(tm_S, dK_k, sdesc_advance(dQ_k0, nq * kTileBytes));
-                        tc_commit(&bars->s_ready);
-                        SNTL_TRACE_EV(true, 0, tn, 9);
-                    }
-                }
-            } else {
+            {
                 const uint64_t dV_k = make_sdesc(smem_u32(sV), 16, 1024), dDo_k0 = make_sdesc(smem_u32(sDo), 16, 1024);
                 const uint64_t dK_mn = make_sdesc(smem_u32(sK), kChunkBytes, 1024), dDs_mn = make_sdesc(smem_u32(sDs), kChunkBytes, 1024);
                 const uint64_t dDs_k = make_sdesc(smem_u32(sDs), 16, 1024);
@@ -308,16 +328,14 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
                     tc_fence_after();
                     issue_kmajor(tm_dP, dV_k, dDo_k0);
                     tc_commit(&bars->dp_ready);
+                    tc_commit(&bars->do_empty[0]);   // this warp's share of releasing dO_0: dP^T_0
                 }
                 for (int i = 0; ok && i < n_iter; ++i) {
                     const uint32_t ph = (uint32_t)(i & 1);
-                    const int sq = i & 1, sd = i % kDoStages;
+                    const int sq = i & 1;
                     if (!(ok = mbar_wait(&bars->ds_ready, ph, abort_flag, kSiteDS))) break;
                     SNTL_TRACE_EV(true, 4, tn, 3);
                     tc_fence_after();
-                    // this warp's share of releasing dO_i is dP^T_i, which retired before dS_i could be computed: release it
-                    // now so that (with a single dO stage) the load of dO_{i+1} is not waiting behind this step's MMAs
-                    tc_commit(&bars->do_empty[sd]);
                     // dQ first: it gates the drain and with it the next dP^T; dK only has to finish before the dS tile
                     // is rewritten, which the in-order issue of this thread already guarantees
                     {
@@ -352,6 +370,9 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
                         tc_fence_after();
                         issue_kmajor(tm_dP, dV_k, sdesc_advance(dDo_k0, nd * kTileBytes));
                         tc_commit(&bars->dp_ready);
+                        // this warp's share of releasing dO_{i+1}, committed at once: with a single dO stage the load of the
+                        // next tile starts as soon as this product and dV_{i+1} have read the stage
+                        tc_commit(&bars->do_empty[nd]);
                         SNTL_TRACE_EV(true, 4, tn, 6);
                     }
                 }

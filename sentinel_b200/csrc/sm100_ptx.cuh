@@ -280,6 +280,34 @@ __device__ __forceinline__ void mma_ts_c(uint32_t d_tmem, uint32_t a_tmem, uint6
                      : "memory");
 }
 
+// One lane of a fully active warp (always the same one): lets an MMA-issuing warp run its loop with all 32 lanes --
+// warp-uniform control flow, so descriptors and addresses can live in uniform registers -- with only the tcgen05
+// instruction itself behind the election.
+__device__ __forceinline__ bool elect_one()
+{
+    uint32_t pred = 0;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "elect.sync _|p, 0xffffffff;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(pred));
+    return pred != 0;
+}
+template <bool kAccumulate>
+__device__ __forceinline__ void mma_ss_e(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc)
+{
+    if (elect_one()) mma_ss_c<kAccumulate>(d_tmem, a_desc, b_desc, idesc);
+}
+template <bool kAccumulate>
+__device__ __forceinline__ void mma_ts_e(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc)
+{
+    if (elect_one()) mma_ts_c<kAccumulate>(d_tmem, a_tmem, b_desc, idesc);
+}
+__device__ __forceinline__ void tc_commit_e(uint64_t* bar)
+{
+    if (elect_one()) tc_commit(bar);
+}
+
 // ---------------------------------------------------------------------------------------------------
 // TMEM <-> registers.  32x32b shape: thread `lane` of warp w touches TMEM lane 32*(w%4)+lane and 32 (or 16)
 // consecutive 32-bit columns starting at the column in taddr.  taddr = (lane << 16) | column.
