@@ -383,7 +383,8 @@ def main():
     roofline = {"bound": "tensor", "kernel": "attention backward (delta pass + dK/dV/dQ kernel + dQ convert, timed as one call)",
                 "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
                 "peak_source": f"{peaks['_source']} bf16_tflops_sustained (kernel timed inside a seconds-long loop)",
-                "traffic": (NCU_DRAM_BYTES_PER_BATCH[w.name] * w.batch if w.name in NCU_DRAM_BYTES_PER_BATCH and ring is None else None),
+                "traffic": (NCU_DRAM_BYTES_PER_BATCH[w.name] * w.batch
+                            if w.name in NCU_DRAM_BYTES_PER_BATCH and ring is None and not mask else None),
                 "fwd": {"achieved": flops_rank * 2.0 / 7.0 / (fwd_ms * 1e-3) / 1e12, "ms": fwd_ms},
                 "bwd_ms": bwd_ms,
                 "fwd_bwd_frac_of_burst_peak": flops_rank / (ms_per_step * 1e-3) / 1e12 / float(peaks.get("bf16_tflops", 1590.0))}
