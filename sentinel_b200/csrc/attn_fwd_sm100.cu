@@ -484,12 +484,8 @@ cudaError_t launch_fwd(const TcArgs& a, cudaStream_t st)
     p.n_qblk = (s.Sq + 2 * kM - 1) / (2 * kM);
     p.scale_log2 = s.scale * 1.4426950408889634f;
     const size_t smem = 6 * (size_t)(128 * D * 2) + sizeof(FwdBarriers) + 1024;
-    static bool configured = false;  // per instantiation
-    if (!configured) {
-        if ((e = cudaFuncSetAttribute(attn_fwd_tc_kernel<D, kMode>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)) != cudaSuccess)
-            return e;
-        configured = true;
-    }
+    static unsigned long long configured = 0;   // per instantiation, one bit per device
+    if ((e = ensure_dynamic_smem(attn_fwd_tc_kernel<D, kMode>, smem, configured)) != cudaSuccess) return e;
     const long long ctas = (long long)p.n_qblk * s.B * s.Hq;
     if (ctas > 0x7fffffffLL) return cudaErrorInvalidConfiguration;
     attn_fwd_tc_kernel<D, kMode><<<(unsigned)ctas, kFwdThreads, smem, st>>>(tq, tk, tv, p);
@@ -566,12 +562,8 @@ cudaError_t launch_cache(const TcArgs& a, int capacity, void* workspace, cudaStr
     p.n_qblk = (rows_per_slab + kM - 1) / kM;
     p.scale_log2 = s.scale * 1.4426950408889634f;
     const size_t smem = 6 * (size_t)(128 * D * 2) + sizeof(FwdBarriers) + 1024;
-    static bool configured = false;
-    if (!configured) {
-        if ((e = cudaFuncSetAttribute(attn_fwd_tc_kernel<D, kCache>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)) != cudaSuccess)
-            return e;
-        configured = true;
-    }
+    static unsigned long long configured = 0;   // one bit per device
+    if ((e = ensure_dynamic_smem(attn_fwd_tc_kernel<D, kCache>, smem, configured)) != cudaSuccess) return e;
     const long long ctas = (long long)plan.n_splits * p.n_qblk * slabs;
     if (ctas > 0x7fffffffLL) return cudaErrorInvalidConfiguration;
     attn_fwd_tc_kernel<D, kCache><<<(unsigned)ctas, kFwdThreads, smem, st>>>(tq, tk, tv, p);

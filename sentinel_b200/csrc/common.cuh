@@ -33,6 +33,23 @@ __host__ __device__ __forceinline__ bool window_allows(const AttnShape& s, int q
     return s.window <= 0 || key < s.global_tokens || key >= query - s.window + 1;
 }
 
+// Opt-in to more than 48 KB of dynamic shared memory for `kernel`, once per device: cudaFuncSetAttribute applies to the
+// current device only, so a process that drives several GPUs needs it on each.  `done_mask` is the caller's static
+// bookkeeping word (one bit per device ordinal below 64; higher ordinals simply set the attribute on every call).
+// The first call on a device has to come before any stream capture, like the reference's own lazy configuration
+// (CudaFlashAttention.cu:49-66).
+template <typename Kernel>
+inline cudaError_t ensure_dynamic_smem(Kernel kernel, size_t bytes, unsigned long long& done_mask)
+{
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev >= 0 && dev < 64 && ((done_mask >> dev) & 1ull)) return cudaSuccess;
+    if ((e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes)) != cudaSuccess) return e;
+    if (dev >= 0 && dev < 64) done_mask |= 1ull << dev;
+    return cudaSuccess;
+}
+
 // Exact-fp32 SIMT kernels (attn_simt.cu).  T = float or __nv_bfloat16 element type.
 struct SimtArgs {
     AttnShape s;
