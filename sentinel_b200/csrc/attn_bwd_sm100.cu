@@ -623,11 +623,13 @@ __global__ void bwd_pre_kernel(const __nv_bfloat16* __restrict__ o, const __nv_b
     }
     const size_t off = ((size_t)bh * Sq + s) * D;
     float acc = 0.0f;
-    for (int d = lane * 2; d < D; d += 64) {
-        const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(o + off + d);
-        const __nv_bfloat162 g = *reinterpret_cast<const __nv_bfloat162*>(dout + off + d);
-        acc = fmaf(__bfloat162float(a.x), __bfloat162float(g.x), acc);
-        acc = fmaf(__bfloat162float(a.y), __bfloat162float(g.y), acc);
+    for (int d = lane * 4; d < D; d += 128) {      // 8 bytes per lane: a row of head_dim 128 is one load per tensor
+        const uint2 a = *reinterpret_cast<const uint2*>(o + off + d);
+        const uint2 g = *reinterpret_cast<const uint2*>(dout + off + d);
+        acc = fmaf(__uint_as_float(a.x << 16), __uint_as_float(g.x << 16), acc);
+        acc = fmaf(__uint_as_float(a.x & 0xffff0000u), __uint_as_float(g.x & 0xffff0000u), acc);
+        acc = fmaf(__uint_as_float(a.y << 16), __uint_as_float(g.y << 16), acc);
+        acc = fmaf(__uint_as_float(a.y & 0xffff0000u), __uint_as_float(g.y & 0xffff0000u), acc);
     }
 #pragma unroll
     for (int m = 16; m > 0; m >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, m);
