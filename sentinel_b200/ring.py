@@ -96,9 +96,12 @@ class _StackCache:
 
 
 class RingAttention:
-    def __init__(self, backend, group=None):
+    def __init__(self, backend, group=None, batch_pairs=True):
+        """``batch_pairs``: send the two unmasked block pairs of a step to the backend as one call, stacked along the
+        batch axis (False: one call per pair)."""
         self.backend = backend
         self.group = group
+        self.batch_pairs = batch_pairs
         self.rank = dist.get_rank(group)
         self.world = dist.get_world_size(group)
 
@@ -169,7 +172,7 @@ class RingAttention:
                 works = self._rotate_start(kv, nxt_kv)
             pairs = visible_pairs(q_ids, kv_ids)
             full = [(qi, ki) for qi, ki, causal in pairs if not causal]
-            if len(full) == 2:
+            if len(full) == 2 and self.batch_pairs:
                 # two unmasked pairs go as ONE call with the pairs stacked along the batch axis: twice the CTAs per
                 # launch fill the last wave of the grid better (the backward of one 8192 x 8192 block is 3.46 waves
                 # of CTAs on 148 SMs, two blocks are 6.9) and the per-call passes are paid once
@@ -211,7 +214,7 @@ class RingAttention:
                 works = self._rotate_start(kv, nxt_kv)
             pairs = visible_pairs(q_ids, kv_ids)
             full = [(qi, ki) for qi, ki, causal in pairs if not causal]
-            if len(full) == 2:      # as in the forward: the two unmasked pairs as one call, stacked along the batch axis
+            if len(full) == 2 and self.batch_pairs:      # as in the forward: the two unmasked pairs as one call, stacked along the batch axis
                 (qa, ka), (qb, kb) = full
                 sel = (qa, qb)
                 dq_p, dk_p, dv_p = be.bwd(q_stack(qz, sel), torch.cat([kv[ka], kv[kb]], 0), torch.cat([kv[2 + ka], kv[2 + kb]], 0),
