@@ -81,27 +81,10 @@ class GpuBackend:
         return torch.full(shape, float("-inf"), dtype=torch.float32, device=like.device)
 
 
-class _StackCache:
-    """Two query-side chunks stacked along the batch axis, built once per selection (the query side does not travel)."""
-
-    def __init__(self):
-        self._made = {}
-
-    def __call__(self, chunks, sel):
-        t = self._made.get(sel)
-        if t is None:
-            t = torch.cat([chunks[sel[0]], chunks[sel[1]]], 0)
-            self._made[sel] = t
-        return t
-
-
 class RingAttention:
-    def __init__(self, backend, group=None, batch_pairs=True):
-        """``batch_pairs``: send the two unmasked block pairs of a step to the backend as one call, stacked along the
-        batch axis (False: one call per pair)."""
+    def __init__(self, backend, group=None):
         self.backend = backend
         self.group = group
-        self.batch_pairs = batch_pairs
         self.rank = dist.get_rank(group)
         self.world = dist.get_world_size(group)
 
@@ -162,7 +145,6 @@ class RingAttention:
         o_acc = [be.zeros_f32(t) for t in qz]
         lse_acc = [be.neg_inf(t.shape[:3], t) for t in qz]
         kv = list(kz) + list(vz)
-        q_stack = _StackCache()
         for step in range(W):
             src = (r - step) % W
             kv_ids = zigzag_chunks(src, W)
@@ -170,19 +152,7 @@ class RingAttention:
             if step + 1 < W:
                 nxt_kv = [torch.empty_like(t) for t in kv]
                 works = self._rotate_start(kv, nxt_kv)
-            pairs = visible_pairs(q_ids, kv_ids)
-            full = [(qi, ki) for qi, ki, causal in pairs if not causal]
-            if len(full) == 2 and self.batch_pairs:
-                # two unmasked pairs go as ONE call with the pairs stacked along the batch axis: twice the CTAs per
-                # launch fill the last wave of the grid better (the backward of one 8192 x 8192 block is 3.46 waves
-                # of CTAs on 148 SMs, two blocks are 6.9) and the per-call passes are paid once
-                (qa, ka), (qb, kb) = full
-                o_p, lse_p = be.fwd(q_stack(qz, (qa, qb)), torch.cat([kv[ka], kv[kb]], 0), torch.cat([kv[2 + ka], kv[2 + kb]], 0), False)
-                nb = qz[0].shape[0]
-                be.merge(o_acc[qa], lse_acc[qa], o_p[:nb], lse_p[:nb])
-                be.merge(o_acc[qb], lse_acc[qb], o_p[nb:], lse_p[nb:])
-                pairs = [p for p in pairs if p[2]]
-            for qi, ki, causal in pairs:
+            for qi, ki, causal in visible_pairs(q_ids, kv_ids):
                 o_p, lse_p = be.fwd(qz[qi], kv[ki], kv[2 + ki], causal)
                 be.merge(o_acc[qi], lse_acc[qi], o_p, lse_p)
             if step + 1 < W:
@@ -204,7 +174,6 @@ class RingAttention:
         dq_acc = [be.zeros_f32(t) for t in qz]
         kv = list(kz) + list(vz)
         dkv = [be.zeros_f32(t) for t in kv]          # travels with its key/value chunk
-        q_stack, o_stack, lse_stack, do_stack = _StackCache(), _StackCache(), _StackCache(), _StackCache()
         for step in range(W):
             src = (r - step) % W
             kv_ids = zigzag_chunks(src, W)
@@ -212,21 +181,7 @@ class RingAttention:
             if step + 1 < W:                          # K/V of the next step can move while this step computes
                 nxt_kv = [torch.empty_like(t) for t in kv]
                 works = self._rotate_start(kv, nxt_kv)
-            pairs = visible_pairs(q_ids, kv_ids)
-            full = [(qi, ki) for qi, ki, causal in pairs if not causal]
-            if len(full) == 2 and self.batch_pairs:      # as in the forward: the two unmasked pairs as one call, stacked along the batch axis
-                (qa, ka), (qb, kb) = full
-                sel = (qa, qb)
-                dq_p, dk_p, dv_p = be.bwd(q_stack(qz, sel), torch.cat([kv[ka], kv[kb]], 0), torch.cat([kv[2 + ka], kv[2 + kb]], 0),
-                                          o_stack(oz, sel), lse_stack(lsez, sel), do_stack(doz, sel), False)
-                nb = qz[0].shape[0]
-                for half, (qi, ki) in enumerate(full):
-                    rows = slice(half * nb, (half + 1) * nb)
-                    be.accumulate(dq_acc[qi], dq_p[rows])
-                    be.accumulate(dkv[ki], dk_p[rows])
-                    be.accumulate(dkv[2 + ki], dv_p[rows])
-                pairs = [p for p in pairs if p[2]]
-            for qi, ki, causal in pairs:
+            for qi, ki, causal in visible_pairs(q_ids, kv_ids):
                 dq_p, dk_p, dv_p = be.bwd(qz[qi], kv[ki], kv[2 + ki], oz[qi], lsez[qi], doz[qi], causal)
                 be.accumulate(dq_acc[qi], dq_p)
                 be.accumulate(dkv[ki], dk_p)

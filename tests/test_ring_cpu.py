@@ -26,13 +26,13 @@ class OracleBackend:
         self.calls = []
 
     def fwd(self, q, k, v, causal):
-        self.calls.append(("fwd", causal, q.shape[0]))
+        self.calls.append(("fwd", causal))
         o, lse = self.cpu.attn_fwd(q.numpy(), k.numpy(), v.numpy(), causal=causal)
         return torch.from_numpy(o), torch.from_numpy(lse)
 
     def bwd(self, q, k, v, o, lse, do, causal):
         # global probabilities from the FINAL lse, exactly what the kernels do: P = exp(scale*qk - lse)
-        self.calls.append(("bwd", causal, q.shape[0]))
+        self.calls.append(("bwd", causal))
         qn, kn, vn, don = (t.double() for t in (q, k, v, do))
         B, Hq, Sq, D = qn.shape
         g = Hq // kn.shape[1]
@@ -89,12 +89,9 @@ def _ring_worker(rank, world, port, shape, out_dir):
         n_fwd = len(be.calls)
         dq, dk, dv = ring.backward(q[:, :, sl].contiguous(), k[:, :, sl].contiguous(), v[:, :, sl].contiguous(), o, lse,
                                    do[:, :, sl].contiguous())
-        # balance: every rank runs the same number of block pairs: 2 per step, 3 at step 0 (two of them diagonal halves);
-        # the two unmasked pairs of a later step travel as one call, stacked along the batch axis
-        pairs = lambda calls: sum(c[2] // B for c in calls)
-        assert pairs(be.calls[:n_fwd]) == 2 * world + 1 and n_fwd == world + 2, (n_fwd, be.calls[:n_fwd])
-        assert pairs(be.calls[n_fwd:]) == 2 * world + 1 and len(be.calls) - n_fwd == world + 2
-        assert all(c[2] == (B if c[1] else 2 * B) for c in be.calls[3:n_fwd])
+        # balance: every rank runs the same number of block pairs: 2 per step, 3 at step 0 (two of them diagonal halves)
+        assert n_fwd == 2 * world + 1, n_fwd
+        assert len(be.calls) - n_fwd == 2 * world + 1
         np.savez(os.path.join(out_dir, f"rank{rank}.npz"), o=o.numpy(), lse=lse.numpy(), dq=dq.numpy(), dk=dk.numpy(), dv=dv.numpy())
         # zigzag deal and its inverse are exact permutations
         x = torch.arange(B * Hq * (S // world) * D, dtype=torch.float32).reshape(B, Hq, S // world, D) + 1e6 * rank
