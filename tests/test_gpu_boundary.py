@@ -60,3 +60,28 @@ def test_c_abi_calls_are_graph_capturable(sb):
         assert torch.equal(got, ref)
     assert float((dq.float() - want_dq.float()).abs().max()) <= 1e-3 * float(want_dq.float().abs().max())
     assert sb.poll_device_status() == 0
+
+
+def test_calls_on_two_streams_keep_their_scratch_apart(sb):
+    """Backward calls that overlap on the GPU (two streams, as in the host-buffer pipeline's two compute streams) must
+    not share scratch: each stream's results equal those of the same call run alone."""
+    w = sb.WORKLOADS["gqa7b_d128"]
+    cases = []
+    for seed in (0, 1):
+        q, k, v, do = (t.cuda() for t in sb.make_inputs(w, batch=1, q_heads=7, kv_heads=1, seq=1024, seed_offset=seed))
+        o, lse = sb.attention_forward(q, k, v)
+        dq, dk, dv = sb.attention_backward(q, k, v, o, lse, do)
+        cases.append((q, k, v, do, o, lse, dq.clone(), dk.clone(), dv.clone()))
+    torch.cuda.synchronize()
+    streams = [torch.cuda.Stream(), torch.cuda.Stream()]
+    for _ in range(5):
+        outs = []
+        for st, (q, k, v, do, o, lse, *_ref) in zip(streams, cases):
+            st.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(st):
+                outs.append(sb.attention_backward(q, k, v, o, lse, do))
+        torch.cuda.synchronize()
+        for (dq, dk, dv), case in zip(outs, cases):
+            assert torch.equal(dk, case[7]) and torch.equal(dv, case[8])
+            assert float((dq.float() - case[6].float()).abs().max()) <= 1e-3 * float(case[6].float().abs().max())
+    assert sb.poll_device_status() == 0
