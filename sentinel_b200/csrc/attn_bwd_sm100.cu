@@ -113,7 +113,12 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
     constexpr int kChunkBytes = kT * 128;          // 128 rows x 128 B
     constexpr int kChunks = D / 64;
     constexpr int kDoStages = (D == 128) ? 1 : 2;  // shared-memory capacity: 227 KB
-    constexpr int kStageBytes = 32 * kT * 4;       // dQ staging: 32 columns x 128 rows fp32 = one bulk reduction
+    // columns of a dQ tile per bulk reduction: 8 KB pieces (four in flight) at head_dim 128, where the tile loads of Q and
+    // dO queue behind the reductions in the TMA engine and shorter pieces let them through sooner (-3 % kernel time);
+    // 16 KB pieces at head_dim 64 (there the finer split costs 1 %, and 4 KB pieces cost 10-20 % at either size)
+    constexpr int kStageCols = (D == 128) ? 16 : 32;
+    constexpr int kStageBytes = kStageCols * kT * 4;   // dQ staging: kStageCols columns x 128 rows fp32 = one bulk reduction
+    constexpr int kStages = 2 * 32 * kT * 4 / kStageBytes;   // 32 KB of staging in all
     constexpr int kDsBytes = kT * kT * 2;          // dS^T tile: [128 keys][128 queries] bf16 as two 64-query chunks
     // The layout uses every byte of the 227 KB a CTA may have (D = 128), so there is no room for an alignment
     // pad: the kernel has no static shared memory, which puts the dynamic window at the 1024-byte aligned start
@@ -125,8 +130,8 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
     uint8_t* sQ = sV + kTileBytes;                 // [2]
     uint8_t* sDo = sQ + 2 * kTileBytes;            // [kDoStages]
     uint8_t* sDs = sDo + kDoStages * kTileBytes;
-    uint8_t* sStage = sDs + kDsBytes;              // [2][kStageBytes]
-    float* sLse = (float*)(sStage + 2 * kStageBytes);   // [2][128]
+    uint8_t* sStage = sDs + kDsBytes;              // [kStages][kStageBytes]
+    float* sLse = (float*)(sStage + kStages * kStageBytes);   // [2][128]
     float* sDelta = sLse + 2 * kT;                 // [2][128]
     BwdBarriers* bars = (BwdBarriers*)(sDelta + 2 * kT);
     volatile uint32_t* abort_flag = &bars->abort_flag;
@@ -403,10 +408,10 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
             // once; pushing 64 KB (D = 128) through the reduction path (~30 bytes/clock per SM) is the slow part and
             // overlaps the next step.  The data leave through the TMA engine, not the load/store unit: reductions
             // issued as instructions queue up in the unit that also carries the compute warps' shared-memory and
-            // TMEM traffic and stall them.  32 columns at a time: registers -> staging buffer -> one asynchronous
-            // bulk add-reduction of 16 KB (contiguous in the accumulator thanks to its [d/4][row][4] order).  Two
-            // staging buffers alternate; the elected thread makes sure a buffer's previous reduction has finished
-            // reading it before it is overwritten.
+            // TMEM traffic and stall them.  kStageCols columns at a time: registers -> staging buffer -> one asynchronous
+            // bulk add-reduction (contiguous in the accumulator thanks to its [d/4][row][4] order).  The staging buffers
+            // (32 KB in all) rotate; the elected thread makes sure a buffer's previous reduction has finished reading it
+            // before it is overwritten.
             uint32_t r[D];
 #pragma unroll
             for (int c = 0; c < D / 32; ++c) tmem_ld32(tm_dP + lane_off + (uint32_t)(c * 32), r + c * 32);
@@ -415,18 +420,18 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
             mbar_arrive(&bars->dq_drained);
             SNTL_TRACE_EV(tw, 3, tn, 2);
 #pragma unroll
-            for (int c = 0; c < D / 32; ++c) {
-                uint8_t* stage = sStage + (c & 1) * kStageBytes;
-                if (elected) bulk_wait_read<1>();
+            for (int c = 0; c < D / kStageCols; ++c) {
+                uint8_t* stage = sStage + (c % kStages) * kStageBytes;
+                if (elected) bulk_wait_read<kStages - 1>();
                 named_barrier_sync(1, 128);
 #pragma unroll
-                for (int v = 0; v < 8; ++v)
+                for (int v = 0; v < kStageCols / 4; ++v)
                     *reinterpret_cast<uint4*>(stage + ((size_t)v * kT + row) * 16) =
-                        make_uint4(r[c * 32 + 4 * v], r[c * 32 + 4 * v + 1], r[c * 32 + 4 * v + 2], r[c * 32 + 4 * v + 3]);
+                        make_uint4(r[c * kStageCols + 4 * v], r[c * kStageCols + 4 * v + 1], r[c * kStageCols + 4 * v + 2], r[c * kStageCols + 4 * v + 3]);
                 fence_proxy_async_smem();
                 named_barrier_sync(1, 128);
                 if (elected) {
-                    bulk_reduce_add_f32(tile + (size_t)c * 32 * kT, stage, (uint32_t)kStageBytes);
+                    bulk_reduce_add_f32(tile + (size_t)c * kStageCols * kT, stage, (uint32_t)kStageBytes);
                     bulk_commit();
                 }
             }
