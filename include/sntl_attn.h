@@ -16,7 +16,8 @@
  *                      (call site sentinel/NeuralNet/Cuda/CudaCausalSelfAttention.cu:421-438)
  *   sntl_attn_bwd_workspace_bytes / sntl_attn_fwd_workspace_bytes
  *                   <- the callee-side ensureSize of deltaWorkspace, CudaFlashAttention.cu:1638
- *   shape checks    <- validateMultiHeadShape / resolveColumnWindow, CudaFlashAttention.cu:1458-1471, :1533-1539
+ *   shape checks    <- validateMultiHeadShape / resolveColumnWindow,
+ *                      sentinel/NeuralNet/Cuda/CudaFlashAttention.cu:1458-1471, :1533-1539
  *
  * Differences from the reference that a binding must know:
  *   - grouped-query attention is native: K/V carry kv_heads heads (the reference needs them repeated to
@@ -83,7 +84,8 @@ typedef struct sntl_attn_desc {
     int32_t column_start;    /* SENTINEL layout: first column of the window; ignored for BHSD */
     int32_t flags;           /* SNTL_FLAG_* */
     /* Sliding window with global tokens, the reference's CausalSelfAttention::allowsKey
-     * (CausalSelfAttention.cpp:95-100; its CUDA flash path refuses such layers, CudaCausalSelfAttention.cu:50):
+     * (sentinel/NeuralNet/Layers/CausalSelfAttention.cpp:95-100; its CUDA flash path refuses such layers,
+     * sentinel/NeuralNet/Cuda/CudaCausalSelfAttention.cu:50):
      * key j is visible to query i iff j <= i and (j < global_tokens or window_size <= 0 or j >= i - window_size + 1).
      * Both need causal = 1; 0 / 0 is plain causal attention. */
     int32_t window_size;     /* keys a query sees counting itself; <= 0: unlimited */
@@ -111,7 +113,7 @@ int sntl_attn_fwd(const sntl_attn_desc* desc, const void* q, const void* k, cons
                   void* workspace, size_t workspace_bytes, void* stream);
 
 /* New tokens against a KV cache, forward only: the reference's attendCachedQuery / decode
- * (CudaCausalSelfAttention.cu:318-341, :557-571) and, with seq_q > 1, a prefill continued from a cache.
+ * (sentinel/NeuralNet/Cuda/CudaCausalSelfAttention.cu:318-341, :557-571) and, with seq_q > 1, a prefill continued from a cache.
  *   desc->seq_q   new tokens per head (1 for decode); desc->seq_kv  keys in use, the new tokens' own keys included
  *   (append before calling, as the reference does); query i sits at position seq_kv - seq_q + i and sees keys
  *   j <= that position, subject to window_size / global_tokens; desc->causal must be 1.
@@ -147,14 +149,15 @@ int sntl_attn_bwd_static_scratch(const sntl_attn_desc* desc, const void* q, cons
 size_t sntl_attn_static_scratch_capacity(void);
 
 /* Boundary conversions fused with the rotary embedding: one read and one write per element where the reference
- * makes separate passes (rotaryRotateInPlace / rotaryRotateInverseInPlace over fp32 matrices, CudaOps.cu:362-399, called
+ * makes separate passes (rotaryRotateInPlace / rotaryRotateInverseInPlace over fp32 matrices,
+ * sentinel/NeuralNet/Cuda/CudaOps.cu:362-399, called
  * at CudaCausalSelfAttention.cu:206-207, :508-509) before its flash kernel converts operands on every load.
  *   pack:   src fp32 feature-major (heads*head_dim) x stride_columns, tokens of pack b at columns
  *           column_start + b*seq + s  ->  dst bf16 [batch][heads][seq][head_dim], rotated by the angle tables.
  *   unpack: the reverse relayout to fp32; inverse != 0 applies the inverse rotation (the gradients dQ, dK),
  *           inverse == 0 the forward one.
  * cos_table / sin_table: [table_positions][head_dim/2] fp32, entry [position][i] for the pair (2i, 2i+1)
- * (RotaryEmbedding.cpp:19-27); both null = no rotation (V, O, dV).  Token s of every pack sits at position
+ * (sentinel/NeuralNet/Layers/RotaryEmbedding.cpp:19-27); both null = no rotation (V, O, dV).  Token s of every pack sits at position
  * position_offset + s (packs restart at 0: CudaOps.cu:366).  Products and sums are rounded separately, as the
  * reference's host code computes them, so the result is the bf16 rounding of exactly that fp32 value.
  * Asynchronous on `stream`. */
@@ -190,6 +193,24 @@ uint64_t sntl_attn_launch_count(void);
  * waits runs out.  Synchronises `stream`.  Returns SNTL_OK or SNTL_ERR_DEVICE_TIMEOUT; *detail (optional)
  * receives the raw word (which wait, which CTA). */
 int sntl_attn_poll_device_status(void* stream, uint32_t* detail);
+
+/* The same poll with the two words kept apart: the forward kernels (and the self-test below) report in one, the
+ * backward kernels in the other.  Either pointer may be null.  No counterpart in the reference. */
+int sntl_attn_poll_device_status_words(void* stream, uint32_t* forward_word, uint32_t* backward_word);
+
+/* What a timeout means for the caller.  Every device-side wait of the tensor-core kernels is bounded (about one
+ * second).  A wait that runs out records its site in the status word, the kernel unwinds and returns normally (no
+ * trap; the context stays usable), and the tensors that call was writing hold garbage.  sntl_attn_fwd / _bwd have
+ * long returned SNTL_OK by then: they are asynchronous.  The status word stays set until it is polled, and for one
+ * wait limit after a give-up other waits on that GPU give up early too, so calls launched in that interval may be
+ * cut short as well.  A caller therefore polls at the points where it synchronises anyway (end of a training step,
+ * before reading results back) and discards the step on SNTL_ERR_DEVICE_TIMEOUT. */
+
+/* Self-test of that path, for test suites: launches one warp whose only wait can never complete, limited to
+ * limit_us microseconds (1..100000).  The wait runs out, the kernel returns, and the next poll reports
+ * SNTL_ERR_DEVICE_TIMEOUT with site code 0x7e in the top byte of the forward word.  Nothing hangs or faults.
+ * Asynchronous on `stream`.  No counterpart in the reference. */
+int sntl_attn_selftest_wait_timeout(uint32_t limit_us, void* stream);
 
 #ifdef __cplusplus
 }

@@ -26,12 +26,19 @@ class _Shape(C.Structure):
                 ("window", C.c_int), ("global_tokens", C.c_int)]
 
 
-def build(force: bool = False) -> None:
-    """Compile the checkers (make); the reference build is skipped when its sources are absent."""
-    if force or not os.path.exists(_ORACLE_SO) or \
+def build(force: bool = False, everything: bool = False) -> None:
+    """Compile the checkers (make); the reference builds are skipped when its sources are absent.
+
+    ``everything`` also runs the targets that depend on the product library (the drop-in smokes), whatever the age
+    of the fp64 checker."""
+    if force or everything or not os.path.exists(_ORACLE_SO) or \
             os.path.getmtime(_ORACLE_SO) < os.path.getmtime(os.path.join(_HERE, "attn_oracle.c")):
         subprocess.run(["make", "-C", _HERE, "-B"] if force else ["make", "-C", _HERE], check=True,
                        stdout=subprocess.DEVNULL)
+
+
+DROPIN_SMOKE = os.path.join(_HERE, "_ref", "dropin_smoke")
+DROPIN_SMOKE_D128 = os.path.join(_HERE, "_ref", "dropin_smoke_d128")
 
 
 _oracle = None

@@ -8,10 +8,11 @@ Python host side: it binds that ABI with ctypes and mirrors the reference's oper
 from . import _lib
 from .flash_attention import (CudaFlashAttention, accumulate, attention_backward, attention_cached_forward, attention_forward,
                               attention_forward_backward_host,
-                              last_path, launch_count, merge_partials, pack_heads, poll_device_status, unpack_heads)
+                              last_path, launch_count, merge_partials, pack_heads, poll_device_status,
+                              raise_if_device_wait_timed_out, unpack_heads)
 from .workloads import WORKLOADS, Workload, make_inputs
 
 __all__ = ["CudaFlashAttention", "attention_forward", "attention_backward", "attention_cached_forward",
            "attention_forward_backward_host",
-           "merge_partials", "accumulate", "pack_heads", "unpack_heads", "last_path", "launch_count", "poll_device_status", "WORKLOADS", "Workload", "make_inputs",
+           "merge_partials", "accumulate", "pack_heads", "unpack_heads", "last_path", "launch_count", "poll_device_status", "raise_if_device_wait_timed_out", "WORKLOADS", "Workload", "make_inputs",
            "_lib"]

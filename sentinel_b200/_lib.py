@@ -17,7 +17,8 @@ FLAG_ALLOW_BF16_COMPUTE, FLAG_FORCE_SIMT = 1, 2
 EXPORTS = ["sntl_attn_version", "sntl_status_string", "sntl_attn_fwd_workspace_bytes", "sntl_attn_bwd_workspace_bytes",
            "sntl_attn_fwd", "sntl_attn_bwd", "sntl_attn_merge", "sntl_attn_last_path", "sntl_attn_launch_count",
            "sntl_attn_poll_device_status", "sntl_attn_bwd_static_scratch", "sntl_attn_static_scratch_capacity", "sntl_attn_accumulate",
-           "sntl_attn_cached_fwd", "sntl_attn_cached_fwd_workspace_bytes", "sntl_attn_pack_heads", "sntl_attn_unpack_heads"]
+           "sntl_attn_cached_fwd", "sntl_attn_cached_fwd_workspace_bytes", "sntl_attn_pack_heads", "sntl_attn_unpack_heads",
+           "sntl_attn_poll_device_status_words", "sntl_attn_selftest_wait_timeout"]
 ERR_SCRATCH_LIMIT = 7
 
 
@@ -76,6 +77,10 @@ def load():
     lib.sntl_attn_launch_count.restype = C.c_uint64
     lib.sntl_attn_poll_device_status.restype = C.c_int
     lib.sntl_attn_poll_device_status.argtypes = [vp, C.POINTER(C.c_uint32)]
+    lib.sntl_attn_poll_device_status_words.restype = C.c_int
+    lib.sntl_attn_poll_device_status_words.argtypes = [vp, C.POINTER(C.c_uint32), C.POINTER(C.c_uint32)]
+    lib.sntl_attn_selftest_wait_timeout.restype = C.c_int
+    lib.sntl_attn_selftest_wait_timeout.argtypes = [C.c_uint32, vp]
     # test hooks of the C++ operator class (sentinel_compat.cu)
     fp = C.POINTER(C.c_float)
     lib.sntl_compat_forward_backward.restype = C.c_int

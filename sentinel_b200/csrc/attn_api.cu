@@ -431,14 +431,29 @@ int sntl_attn_unpack_heads(const void* src, float* dst, int32_t batch, int32_t h
                                        cos_table, sin_table, position_offset, inverse != 0, (cudaStream_t)stream));
 }
 
-int sntl_attn_poll_device_status(void* stream, uint32_t* detail)
+int sntl_attn_poll_device_status_words(void* stream, uint32_t* forward_word, uint32_t* backward_word)
 {
     uint32_t word = 0, word_bwd = 0;
     if (read_and_clear_fwd_status((cudaStream_t)stream, &word) != cudaSuccess) return SNTL_ERR_CUDA;
     if (read_and_clear_bwd_status((cudaStream_t)stream, &word_bwd) != cudaSuccess) return SNTL_ERR_CUDA;
-    if (word == 0) word = word_bwd;
-    if (detail) *detail = word;
-    return word == 0 ? SNTL_OK : SNTL_ERR_DEVICE_TIMEOUT;
+    if (forward_word) *forward_word = word;
+    if (backward_word) *backward_word = word_bwd;
+    return (word | word_bwd) == 0 ? SNTL_OK : SNTL_ERR_DEVICE_TIMEOUT;
+}
+
+int sntl_attn_poll_device_status(void* stream, uint32_t* detail)
+{
+    uint32_t word = 0, word_bwd = 0;
+    const int rc = sntl_attn_poll_device_status_words(stream, &word, &word_bwd);
+    if (detail) *detail = word ? word : word_bwd;
+    return rc;
+}
+
+int sntl_attn_selftest_wait_timeout(uint32_t limit_us, void* stream)
+{
+    if (limit_us == 0 || limit_us > 100000u) return SNTL_ERR_BAD_ARGUMENT;   // 0.1 s at most: this is a test hook
+    if (!device_ok()) return SNTL_ERR_NO_DEVICE;
+    return cuda_status(launch_wait_selftest((unsigned long long)limit_us * 1000ull, nullptr, (cudaStream_t)stream));
 }
 
 }  // extern "C"

@@ -751,7 +751,7 @@ cudaError_t launch_bwd(const TcArgs& a, cudaStream_t st)
     p.scale_log2 = s.scale * 1.4426950408889634f;
     constexpr int kDoStages = (D == 128) ? 1 : 2;
     const size_t smem = (size_t)(128 * D * 2) * (4 + kDoStages) + 128 * 128 * 2 + 2 * (32 * 128 * 4) + 4 * 128 * 4 + sizeof(BwdBarriers);
-    static unsigned long long configured = 0;   // per instantiation, one bit per device
+    static std::atomic<unsigned long long> configured{0};   // per instantiation, one bit per device
     if ((e = ensure_dynamic_smem(attn_bwd_tc_kernel<D, kWin, kSplit>, smem, configured)) != cudaSuccess) return e;
     const int group = s.Hq / s.Hkv, slabs = s.B * s.Hkv;
     const long long ctas = (long long)p.split_tiles * group * slabs + (long long)(n_kt - p.split_tiles) * slabs;

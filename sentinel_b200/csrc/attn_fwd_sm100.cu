@@ -484,7 +484,7 @@ cudaError_t launch_fwd(const TcArgs& a, cudaStream_t st)
     p.n_qblk = (s.Sq + 2 * kM - 1) / (2 * kM);
     p.scale_log2 = s.scale * 1.4426950408889634f;
     const size_t smem = 6 * (size_t)(128 * D * 2) + sizeof(FwdBarriers) + 1024;
-    static unsigned long long configured = 0;   // per instantiation, one bit per device
+    static std::atomic<unsigned long long> configured{0};   // per instantiation, one bit per device
     if ((e = ensure_dynamic_smem(attn_fwd_tc_kernel<D, kMode>, smem, configured)) != cudaSuccess) return e;
     const long long ctas = (long long)p.n_qblk * s.B * s.Hq;
     if (ctas > 0x7fffffffLL) return cudaErrorInvalidConfiguration;
@@ -562,7 +562,7 @@ cudaError_t launch_cache(const TcArgs& a, int capacity, void* workspace, cudaStr
     p.n_qblk = (rows_per_slab + kM - 1) / kM;
     p.scale_log2 = s.scale * 1.4426950408889634f;
     const size_t smem = 6 * (size_t)(128 * D * 2) + sizeof(FwdBarriers) + 1024;
-    static unsigned long long configured = 0;   // one bit per device
+    static std::atomic<unsigned long long> configured{0};   // one bit per device
     if ((e = ensure_dynamic_smem(attn_fwd_tc_kernel<D, kCache>, smem, configured)) != cudaSuccess) return e;
     const long long ctas = (long long)plan.n_splits * p.n_qblk * slabs;
     if (ctas > 0x7fffffffLL) return cudaErrorInvalidConfiguration;
@@ -654,6 +654,31 @@ extern "C" int sntl_debug_trace_fwd(unsigned long long* out, int n_words, int se
     return cudaMemcpyToSymbol(ptx::g_trace_cta, &c, sizeof(c)) == cudaSuccess ? 0 : 3;
 }
 #endif
+
+// Self-test of the bounded wait: one warp waits on a barrier that by construction never receives its arrival, with a
+// limit of `limit_ns` instead of the kernels' one second.  The wait runs out, records kSiteSelfTest in the status word
+// exactly as a stuck production wait would, and the kernel returns normally (no trap, the context stays usable).
+constexpr uint32_t kSiteSelfTest = 0x7e;
+__global__ void wait_selftest_kernel(unsigned long long limit_ns, unsigned int* gave_up)
+{
+    __shared__ uint64_t bar;
+    __shared__ uint32_t abort_word;
+    if (threadIdx.x == 0) {
+        ptx::mbar_init(&bar, 1);
+        abort_word = 0;
+        ptx::fence_mbar_init();
+    }
+    __syncthreads();
+    const bool done = ptx::mbar_wait_for(&bar, 0, &abort_word, kSiteSelfTest, limit_ns);
+    if (threadIdx.x == 0 && gave_up) *gave_up = done ? 0u : 1u;
+}
+
+cudaError_t launch_wait_selftest(unsigned long long limit_ns, unsigned int* gave_up, cudaStream_t st)
+{
+    wait_selftest_kernel<<<1, 32, 0, st>>>(limit_ns, gave_up);
+    count_launch();
+    return cudaGetLastError();
+}
 
 cudaError_t read_and_clear_fwd_status(cudaStream_t st, uint32_t* word)
 {

@@ -5,6 +5,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <atomic>
+
 #include "sntl_attn.h"
 
 namespace sntl {
@@ -39,14 +41,14 @@ __host__ __device__ __forceinline__ bool window_allows(const AttnShape& s, int q
 // The first call on a device has to come before any stream capture, like the reference's own lazy configuration
 // (CudaFlashAttention.cu:49-66).
 template <typename Kernel>
-inline cudaError_t ensure_dynamic_smem(Kernel kernel, size_t bytes, unsigned long long& done_mask)
+inline cudaError_t ensure_dynamic_smem(Kernel kernel, size_t bytes, std::atomic<unsigned long long>& done_mask)
 {
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return e;
-    if (dev >= 0 && dev < 64 && ((done_mask >> dev) & 1ull)) return cudaSuccess;
+    if (dev >= 0 && dev < 64 && ((done_mask.load(std::memory_order_acquire) >> dev) & 1ull)) return cudaSuccess;
     if ((e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes)) != cudaSuccess) return e;
-    if (dev >= 0 && dev < 64) done_mask |= 1ull << dev;
+    if (dev >= 0 && dev < 64) done_mask.fetch_or(1ull << dev, std::memory_order_release);
     return cudaSuccess;
 }
 
@@ -111,6 +113,10 @@ cudaError_t merge_partials(int acc_dtype, int part_dtype, long long rows, int D,
 
 // Launch accounting (attn_api.cu).
 void count_launch(int n = 1);
+
+// A one-warp kernel whose only wait can never complete, limited to limit_ns (attn_fwd_sm100.cu): exercises the
+// give-up path of the bounded waits without hanging or faulting anything.  *gave_up (device memory, optional) <- 1.
+cudaError_t launch_wait_selftest(unsigned long long limit_ns, unsigned int* gave_up, cudaStream_t st);
 
 // Device status words written by bounded waits (one per tensor-core translation unit).
 cudaError_t read_and_clear_fwd_status(cudaStream_t st, uint32_t* word);

@@ -7,8 +7,13 @@
 // missing device or a failed launch.
 #include "sentinel_compat.hpp"
 
+#include <cstdio>
+#include <cstdlib>
+#include <map>
+#include <mutex>
 #include <stdexcept>
 #include <string>
+#include <utility>
 
 #include "sntl_attn.h"
 
@@ -16,10 +21,24 @@ namespace sentinel_b200 {
 
 namespace {
 
+#ifdef SNTL_COMPAT_USE_SENTINEL_TYPES
+// inside a Sentinel build: the reference's own matrix type and its process-global launch stream
+using Matrix_t = ::CudaMatrix;
+inline const float* dev(const Matrix_t& m) { return m.buffer.deviceData; }
+inline float* dev(Matrix_t& m) { return m.buffer.deviceData; }
+inline cudaStream_t launch_stream() { return CudaMatmul::activeStream(); }
+bool g_allow_reduced = [] {
+    const char* e = std::getenv("SNTL_ATTN_REDUCED_PRECISION");
+    return e && e[0] == '1';
+}();
+#else
+using Matrix_t = CudaMatrix;
 cudaStream_t g_stream = nullptr;
+inline const float* dev(const Matrix_t& m) { return m.deviceData(); }
+inline float* dev(Matrix_t& m) { return m.deviceData(); }
+inline cudaStream_t launch_stream() { return g_stream; }
 bool g_allow_reduced = false;
-void* g_workspace = nullptr;   // grow-only, like the reference's CudaDeviceBuffer::ensureCapacity (CudaMatmul.cu:119-136)
-size_t g_workspace_bytes = 0;
+#endif
 
 void cuda_or_throw(cudaError_t e, const char* what)
 {
@@ -34,22 +53,52 @@ void status_or_throw(int status, const char* op)
     throw std::runtime_error(msg);
 }
 
-void* workspace(size_t bytes)
-{
-    if (bytes > g_workspace_bytes) {
-        if (g_workspace) cuda_or_throw(cudaFree(g_workspace), "CudaFlashAttention workspace free");
-        g_workspace = nullptr;
-        g_workspace_bytes = 0;
-        cuda_or_throw(cudaMalloc(&g_workspace, bytes), "CudaFlashAttention workspace alloc");
-        g_workspace_bytes = bytes;
+// Scratch for the C ABI calls: one grow-only buffer per (device ordinal, stream), like the reference's
+// CudaDeviceBuffer::ensureCapacity (CudaMatmul.cu:119-136).  Calls on different devices or streams never share a
+// buffer, so they neither race on it nor hand one GPU another GPU's memory; the map itself is guarded by a mutex.
+// A buffer is only ever replaced by a larger one when its own (device, stream) asks for more, which -- as with
+// every grow-only buffer of the reference -- must not happen while earlier work of that stream still uses it or
+// inside a stream capture: sizes are stable after the first step, which the trainer runs eagerly
+// (CudaLanguageModel.cu:761-793).  The map is never destroyed: at process exit the context is already gone.
+struct Scratch {
+#ifdef SNTL_COMPAT_USE_SENTINEL_TYPES
+    CudaDeviceBuffer buffer;   // the reference's buffer type: its free() keeps CudaAmp's half caches coherent (CudaMatmul.cu:169)
+    void* grow(size_t bytes)
+    {
+        this->buffer.ensureCapacity(bytes);
+        return this->buffer.deviceData;
     }
-    return g_workspace;
+#else
+    void* data = nullptr;
+    size_t capacity = 0;
+    void* grow(size_t bytes)
+    {
+        if (bytes > this->capacity) {
+            if (this->data) cuda_or_throw(cudaFree(this->data), "CudaFlashAttention workspace free");
+            this->data = nullptr;
+            this->capacity = 0;
+            cuda_or_throw(cudaMalloc(&this->data, bytes), "CudaFlashAttention workspace alloc");
+            this->capacity = bytes;
+        }
+        return this->data;
+    }
+#endif
+};
+
+void* workspace(size_t bytes, cudaStream_t stream)
+{
+    static std::mutex* guard = new std::mutex;
+    static auto* buffers = new std::map<std::pair<int, cudaStream_t>, Scratch>;
+    int device = 0;
+    cuda_or_throw(cudaGetDevice(&device), "CudaFlashAttention workspace device");
+    std::lock_guard<std::mutex> lock(*guard);
+    return (*buffers)[std::make_pair(device, stream)].grow(bytes);
 }
 
-bool empty(const CudaMatrix& m) { return m.rows == 0 || m.cols == 0; }
+bool empty(const Matrix_t& m) { return m.rows == 0 || m.cols == 0; }
 
 // returns kv head count
-int validate_shape(const CudaMatrix& query, const CudaMatrix& key, const CudaMatrix& value, int headCount, int headDimension,
+int validate_shape(const Matrix_t& query, const Matrix_t& key, const Matrix_t& value, int headCount, int headDimension,
                    const char* op)
 {
     if (empty(query) || empty(key) || empty(value)) throw std::invalid_argument(std::string(op) + " empty input");
@@ -65,7 +114,7 @@ int validate_shape(const CudaMatrix& query, const CudaMatrix& key, const CudaMat
     return kvHeads;
 }
 
-void resolve_window(const CudaMatrix& query, int& columnStart, int& columnCount)
+void resolve_window(const Matrix_t& query, int& columnStart, int& columnCount)
 {
     const int strideColumns = (int)query.cols;
     if (columnCount <= 0) columnCount = strideColumns - columnStart;
@@ -79,7 +128,7 @@ bool device_available()
     return cudaGetDeviceCount(&n) == cudaSuccess && n > 0;
 }
 
-sntl_attn_desc make_desc(const CudaMatrix& query, int headCount, int kvHeads, int headDimension, float scale, bool causal,
+sntl_attn_desc make_desc(const Matrix_t& query, int headCount, int kvHeads, int headDimension, float scale, bool causal,
                          int columnStart, int columnCount, int packCount, int windowSize, int globalTokenCount)
 {
     sntl_attn_desc d{};
@@ -101,9 +150,141 @@ sntl_attn_desc make_desc(const CudaMatrix& query, int headCount, int kvHeads, in
     return d;
 }
 
+void forward_impl(const Matrix_t& query, const Matrix_t& key, const Matrix_t& value, Matrix_t& out, Matrix_t& logSumExp,
+                  int headCount, int headDimension, float scale, bool causal, int columnStart, int columnCount, int packCount,
+                  int windowSize, int globalTokenCount)
+{
+    const char* op = "CudaFlashAttention::forwardMultiHead";
+    const int kvHeads = validate_shape(query, key, value, headCount, headDimension, op);
+    if (headDimension > 256)  // tensor-core kernels stop at maxHeadDimension; the exact-fp32 kernels at 256
+        throw std::invalid_argument(std::string(op) + " headDim exceeds maxHeadDimension");
+    if (!device_available()) throw std::runtime_error(std::string(op) + " no CUDA device");
+    if (packCount <= 0) packCount = 1;
+    if (globalTokenCount < 0) throw std::invalid_argument(std::string(op) + " globalTokenCount must be >= 0");
+    if ((windowSize > 0 || globalTokenCount > 0) && !causal)
+        throw std::invalid_argument(std::string(op) + " a sliding window needs the causal mask");
+    resolve_window(query, columnStart, columnCount);
+    if (columnStart + packCount * columnCount > (int)query.cols) throw std::invalid_argument(std::string(op) + " pack window exceeds columns");
+
+    out.ensureSize(query.rows, query.cols);
+    logSumExp.ensureSize((size_t)headCount, query.cols);
+    const sntl_attn_desc d = make_desc(query, headCount, kvHeads, headDimension, scale, causal, columnStart, columnCount, packCount,
+                                       windowSize, globalTokenCount);
+    const cudaStream_t stream = launch_stream();
+    const size_t ws = sntl_attn_fwd_workspace_bytes(&d);
+    void* wsp = ws ? workspace(ws, stream) : nullptr;
+    status_or_throw(sntl_attn_fwd(&d, dev(query), dev(key), dev(value), dev(out), dev(logSumExp), wsp, ws, stream), op);
+}
+
+void backward_impl(const Matrix_t& query, const Matrix_t& key, const Matrix_t& value, const Matrix_t& out, const Matrix_t& logSumExp,
+                   const Matrix_t& outGradient, Matrix_t& queryGradient, Matrix_t& keyGradient, Matrix_t& valueGradient,
+                   Matrix_t& deltaWorkspace, int headCount, int headDimension, float scale, bool causal, int columnStart,
+                   int columnCount, int packCount, int windowSize, int globalTokenCount)
+{
+    const char* op = "CudaFlashAttention::backwardMultiHead";
+    const int kvHeads = validate_shape(query, key, value, headCount, headDimension, op);
+    if (out.rows != query.rows || out.cols != query.cols) throw std::invalid_argument(std::string(op) + " out shape mismatch");
+    if (outGradient.rows != query.rows || outGradient.cols != query.cols)
+        throw std::invalid_argument(std::string(op) + " outGradient shape mismatch");
+    if (logSumExp.rows != (size_t)headCount || logSumExp.cols != query.cols)
+        throw std::invalid_argument(std::string(op) + " logSumExp shape mismatch");
+    if (!device_available()) throw std::runtime_error(std::string(op) + " no CUDA device");
+    if (packCount <= 0) packCount = 1;
+    if (globalTokenCount < 0) throw std::invalid_argument(std::string(op) + " globalTokenCount must be >= 0");
+    if ((windowSize > 0 || globalTokenCount > 0) && !causal)
+        throw std::invalid_argument(std::string(op) + " a sliding window needs the causal mask");
+    resolve_window(query, columnStart, columnCount);
+    if (columnStart + packCount * columnCount > (int)query.cols) throw std::invalid_argument(std::string(op) + " pack window exceeds columns");
+
+    queryGradient.ensureSize(query.rows, query.cols);
+    keyGradient.ensureSize(key.rows, key.cols);
+    valueGradient.ensureSize(value.rows, value.cols);
+    deltaWorkspace.ensureSize((size_t)headCount, (size_t)packCount * (size_t)columnCount);
+    const sntl_attn_desc d = make_desc(query, headCount, kvHeads, headDimension, scale, causal, columnStart, columnCount, packCount,
+                                       windowSize, globalTokenCount);
+    const cudaStream_t stream = launch_stream();
+    const size_t ws = sntl_attn_bwd_workspace_bytes(&d);
+    status_or_throw(sntl_attn_bwd(&d, dev(query), dev(key), dev(value), dev(out), dev(logSumExp), dev(outGradient), dev(queryGradient),
+                                  dev(keyGradient), dev(valueGradient), workspace(ws, stream), ws, stream),
+                    op);
+}
+
+void throw_if_device_wait_timed_out(cudaStream_t stream)
+{
+    uint32_t fwd = 0, bwd = 0;
+    const int rc = sntl_attn_poll_device_status_words(stream, &fwd, &bwd);
+    if (rc == SNTL_OK) return;
+    char words[64];
+    snprintf(words, sizeof(words), " (forward 0x%08x, backward 0x%08x)", fwd, bwd);
+    throw std::runtime_error(std::string("CudaFlashAttention ") + sntl_status_string(rc) + words);
+}
+
 }  // namespace
 
-#ifndef SNTL_COMPAT_USE_SENTINEL_TYPES
+#ifdef SNTL_COMPAT_USE_SENTINEL_TYPES
+
+void setAllowReducedPrecision(bool allow) { g_allow_reduced = allow; }
+const char* lastPath() { return sntl_attn_last_path(); }
+void throwIfDeviceWaitTimedOut() { throw_if_device_wait_timed_out(launch_stream()); }
+
+void forwardMultiHeadWindowed(const CudaMatrix& query, const CudaMatrix& key, const CudaMatrix& value, CudaMatrix& out,
+                              CudaMatrix& logSumExp, int headCount, int headDimension, float scale, bool causal, int columnStart,
+                              int columnCount, int packCount, int windowSize, int globalTokenCount)
+{
+    forward_impl(query, key, value, out, logSumExp, headCount, headDimension, scale, causal, columnStart, columnCount, packCount,
+                 windowSize, globalTokenCount);
+}
+
+void backwardMultiHeadWindowed(const CudaMatrix& query, const CudaMatrix& key, const CudaMatrix& value, const CudaMatrix& out,
+                               const CudaMatrix& logSumExp, const CudaMatrix& outGradient, CudaMatrix& queryGradient,
+                               CudaMatrix& keyGradient, CudaMatrix& valueGradient, CudaMatrix& deltaWorkspace, int headCount,
+                               int headDimension, float scale, bool causal, int columnStart, int columnCount, int packCount,
+                               int windowSize, int globalTokenCount)
+{
+    backward_impl(query, key, value, out, logSumExp, outGradient, queryGradient, keyGradient, valueGradient, deltaWorkspace, headCount,
+                  headDimension, scale, causal, columnStart, columnCount, packCount, windowSize, globalTokenCount);
+}
+
+}  // namespace sentinel_b200
+
+// ---- the reference's class, as declared by its own header (sentinel/NeuralNet/Cuda/CudaFlashAttention.hpp:12-41) ----
+
+void CudaFlashAttention::forwardMultiHead(const CudaMatrix& query, const CudaMatrix& key, const CudaMatrix& value, CudaMatrix& out,
+                                          CudaMatrix& logSumExp, int headCount, int headDimension, float scale, bool causal,
+                                          int columnStart, int columnCount, int packCount)
+{
+    sentinel_b200::forwardMultiHeadWindowed(query, key, value, out, logSumExp, headCount, headDimension, scale, causal, columnStart,
+                                            columnCount, packCount, 0, 0);
+}
+
+void CudaFlashAttention::forward(const CudaMatrix& query, const CudaMatrix& key, const CudaMatrix& value, CudaMatrix& out,
+                                 CudaMatrix& logSumExp, float scale, bool causal)
+{
+    CudaFlashAttention::forwardMultiHead(query, key, value, out, logSumExp, 1, (int)query.rows, scale, causal, 0, (int)query.cols);
+}
+
+void CudaFlashAttention::backwardMultiHead(const CudaMatrix& query, const CudaMatrix& key, const CudaMatrix& value,
+                                           const CudaMatrix& out, const CudaMatrix& logSumExp, const CudaMatrix& outGradient,
+                                           CudaMatrix& queryGradient, CudaMatrix& keyGradient, CudaMatrix& valueGradient,
+                                           CudaMatrix& deltaWorkspace, int headCount, int headDimension, float scale, bool causal,
+                                           int columnStart, int columnCount, int packCount)
+{
+    sentinel_b200::backwardMultiHeadWindowed(query, key, value, out, logSumExp, outGradient, queryGradient, keyGradient, valueGradient,
+                                             deltaWorkspace, headCount, headDimension, scale, causal, columnStart, columnCount,
+                                             packCount, 0, 0);
+}
+
+void CudaFlashAttention::backward(const CudaMatrix& query, const CudaMatrix& key, const CudaMatrix& value, const CudaMatrix& out,
+                                  const CudaMatrix& logSumExp, const CudaMatrix& outGradient, CudaMatrix& queryGradient,
+                                  CudaMatrix& keyGradient, CudaMatrix& valueGradient, float scale, bool causal)
+{
+    CudaMatrix deltaWorkspace;
+    CudaFlashAttention::backwardMultiHead(query, key, value, out, logSumExp, outGradient, queryGradient, keyGradient, valueGradient,
+                                          deltaWorkspace, 1, (int)query.rows, scale, causal, 0, (int)query.cols);
+}
+
+#else  // stand-alone build: own matrix type, class in namespace sentinel_b200, test hooks
+
 CudaMatrix::CudaMatrix(size_t rowCount, size_t columnCount) { this->ensureSize(rowCount, columnCount); }
 
 CudaMatrix::~CudaMatrix()
@@ -138,8 +319,8 @@ void CudaMatrix::download(float* host) const
     cuda_or_throw(cudaMemcpyAsync(host, this->data, this->rows * this->cols * sizeof(float), cudaMemcpyDeviceToHost, g_stream),
                   "CudaMatrix download");
     cuda_or_throw(cudaStreamSynchronize(g_stream), "CudaMatrix download sync");
+    throw_if_device_wait_timed_out(g_stream);   // this is a synchronisation point: a timed-out wait surfaces here
 }
-#endif
 
 void CudaFlashAttention::setActiveStream(cudaStream_t stream) { g_stream = stream; }
 cudaStream_t CudaFlashAttention::activeStream() { return g_stream; }
@@ -150,27 +331,8 @@ void CudaFlashAttention::forwardMultiHead(const CudaMatrix& query, const CudaMat
                                           CudaMatrix& logSumExp, int headCount, int headDimension, float scale, bool causal,
                                           int columnStart, int columnCount, int packCount, int windowSize, int globalTokenCount)
 {
-    const char* op = "CudaFlashAttention::forwardMultiHead";
-    const int kvHeads = validate_shape(query, key, value, headCount, headDimension, op);
-    if (headDimension > 256)  // tensor-core kernels stop at maxHeadDimension; the exact-fp32 kernels at 256
-        throw std::invalid_argument(std::string(op) + " headDim exceeds maxHeadDimension");
-    if (!device_available()) throw std::runtime_error(std::string(op) + " no CUDA device");
-    if (packCount <= 0) packCount = 1;
-    if (globalTokenCount < 0) throw std::invalid_argument(std::string(op) + " globalTokenCount must be >= 0");
-    if ((windowSize > 0 || globalTokenCount > 0) && !causal)
-        throw std::invalid_argument(std::string(op) + " a sliding window needs the causal mask");
-    resolve_window(query, columnStart, columnCount);
-    if (columnStart + packCount * columnCount > (int)query.cols) throw std::invalid_argument(std::string(op) + " pack window exceeds columns");
-
-    out.ensureSize(query.rows, query.cols);
-    logSumExp.ensureSize((size_t)headCount, query.cols);
-    const sntl_attn_desc d = make_desc(query, headCount, kvHeads, headDimension, scale, causal, columnStart, columnCount, packCount,
-                                       windowSize, globalTokenCount);
-    const size_t ws = sntl_attn_fwd_workspace_bytes(&d);
-    void* wsp = ws ? workspace(ws) : nullptr;
-    status_or_throw(sntl_attn_fwd(&d, query.deviceData(), key.deviceData(), value.deviceData(), out.deviceData(),
-                                  logSumExp.deviceData(), wsp, ws, g_stream),
-                    op);
+    forward_impl(query, key, value, out, logSumExp, headCount, headDimension, scale, causal, columnStart, columnCount, packCount,
+                 windowSize, globalTokenCount);
 }
 
 void CudaFlashAttention::forward(const CudaMatrix& query, const CudaMatrix& key, const CudaMatrix& value, CudaMatrix& out,
@@ -186,32 +348,8 @@ void CudaFlashAttention::backwardMultiHead(const CudaMatrix& query, const CudaMa
                                            int columnStart, int columnCount, int packCount, int windowSize,
                                            int globalTokenCount)
 {
-    const char* op = "CudaFlashAttention::backwardMultiHead";
-    const int kvHeads = validate_shape(query, key, value, headCount, headDimension, op);
-    if (out.rows != query.rows || out.cols != query.cols) throw std::invalid_argument(std::string(op) + " out shape mismatch");
-    if (outGradient.rows != query.rows || outGradient.cols != query.cols)
-        throw std::invalid_argument(std::string(op) + " outGradient shape mismatch");
-    if (logSumExp.rows != (size_t)headCount || logSumExp.cols != query.cols)
-        throw std::invalid_argument(std::string(op) + " logSumExp shape mismatch");
-    if (!device_available()) throw std::runtime_error(std::string(op) + " no CUDA device");
-    if (packCount <= 0) packCount = 1;
-    if (globalTokenCount < 0) throw std::invalid_argument(std::string(op) + " globalTokenCount must be >= 0");
-    if ((windowSize > 0 || globalTokenCount > 0) && !causal)
-        throw std::invalid_argument(std::string(op) + " a sliding window needs the causal mask");
-    resolve_window(query, columnStart, columnCount);
-    if (columnStart + packCount * columnCount > (int)query.cols) throw std::invalid_argument(std::string(op) + " pack window exceeds columns");
-
-    queryGradient.ensureSize(query.rows, query.cols);
-    keyGradient.ensureSize(key.rows, key.cols);
-    valueGradient.ensureSize(value.rows, value.cols);
-    deltaWorkspace.ensureSize((size_t)headCount, (size_t)packCount * (size_t)columnCount);
-    const sntl_attn_desc d = make_desc(query, headCount, kvHeads, headDimension, scale, causal, columnStart, columnCount, packCount,
-                                       windowSize, globalTokenCount);
-    const size_t ws = sntl_attn_bwd_workspace_bytes(&d);
-    status_or_throw(sntl_attn_bwd(&d, query.deviceData(), key.deviceData(), value.deviceData(), out.deviceData(),
-                                  logSumExp.deviceData(), outGradient.deviceData(), queryGradient.deviceData(),
-                                  keyGradient.deviceData(), valueGradient.deviceData(), workspace(ws), ws, g_stream),
-                    op);
+    backward_impl(query, key, value, out, logSumExp, outGradient, queryGradient, keyGradient, valueGradient, deltaWorkspace, headCount,
+                  headDimension, scale, causal, columnStart, columnCount, packCount, windowSize, globalTokenCount);
 }
 
 void CudaFlashAttention::backward(const CudaMatrix& query, const CudaMatrix& key, const CudaMatrix& value, const CudaMatrix& out,
@@ -319,3 +457,5 @@ int sntl_compat_validate(int qRows, int kvRows, int cols, int headCount, int hea
 }
 
 }  // extern "C"
+
+#endif  // stand-alone build

@@ -1,15 +1,21 @@
 // Host-side mirror of the reference's flash-attention operator interface, implemented on the C ABI.
 //
-// A Sentinel build links this translation unit in place of its own
-// sentinel/NeuralNet/Cuda/CudaFlashAttention.cu: the class name, the four static methods, their argument
-// order, defaults and meaning, and the exception types are those of
-// sentinel/NeuralNet/Cuda/CudaFlashAttention.hpp:10-41, so CudaCausalSelfAttention.cu:237-249 and :421-438
-// compile and behave unchanged and LanguageModel::enableCuda() / setCudaPreferFlashAttention keep working.
+// Two ways to build the accompanying sentinel_compat.cu:
 //
-// Standing alone (as built here) the class needs a device matrix type; `CudaMatrix` below is a minimal
-// stand-in with the members the operator touches (rows, cols, device pointer, grow-only ensureSize, upload /
-// download), shaped after sentinel/NeuralNet/Cuda/CudaMatmul.hpp:100-171.  Inside a Sentinel build the real
-// CudaMatrix is used instead (define SNTL_COMPAT_USE_SENTINEL_TYPES and include CudaMatmul.hpp first).
+//  * Inside a Sentinel build (-DSNTL_COMPAT_USE_SENTINEL_TYPES, include path = the reference's `sentinel/` folder):
+//    the translation unit includes the reference's OWN header sentinel/NeuralNet/Cuda/CudaFlashAttention.hpp and
+//    defines the four static methods that header declares (class `CudaFlashAttention` in the global namespace,
+//    CudaFlashAttention.hpp:12-41) on the reference's own CudaMatrix (device pointer = buffer.deviceData,
+//    CudaMatmul.hpp:10-13, :100-104) and launch stream (CudaMatmul::activeStream(), CudaMatmul.hpp:221).  It is
+//    linked IN PLACE OF sentinel/NeuralNet/Cuda/CudaFlashAttention.cu; no other file of the reference changes, so
+//    CudaCausalSelfAttention.cu:237-249 and :421-438 compile and behave unchanged and LanguageModel::enableCuda() /
+//    setCudaPreferFlashAttention keep working.  The extras of this library that the reference's header has no slot
+//    for are the free functions of namespace sentinel_b200 declared below.
+//
+//  * Standing alone (as built into libsntl_attn.so): the class lives in namespace sentinel_b200 and works on a
+//    minimal stand-in `CudaMatrix` with the members the operator touches (rows, cols, device pointer, grow-only
+//    ensureSize, upload / download), shaped after sentinel/NeuralNet/Cuda/CudaMatmul.hpp:100-171.  This is what the
+//    unit tests drive through the extern "C" hooks at the end of sentinel_compat.cu.
 #pragma once
 
 #include <cstddef>
@@ -17,9 +23,42 @@
 
 #include <cuda_runtime.h>
 
+#ifdef SNTL_COMPAT_USE_SENTINEL_TYPES
+
+#include "NeuralNet/Cuda/CudaFlashAttention.hpp"
+
 namespace sentinel_b200 {
 
-#ifndef SNTL_COMPAT_USE_SENTINEL_TYPES
+/// fp32 matrices are computed exactly in fp32 unless this is set; then head dimensions 64/128 run on the tensor
+/// cores with bf16 operands (the reference's own flash kernel rounds operands to fp16, CudaFlashAttention.cu:209-214).
+/// The environment variable SNTL_ATTN_REDUCED_PRECISION=1 sets the initial value.
+void setAllowReducedPrecision(bool allow);
+
+/// "tcgen05_staged", "simt_f32" ...: which kernel family the last call on this thread used
+const char* lastPath();
+
+/// Synchronises the active stream and throws std::runtime_error if a bounded device-side wait ran out since the
+/// last poll (see sntl_attn_poll_device_status); call it where the training step synchronises anyway.
+void throwIfDeviceWaitTimedOut();
+
+/// The same operators with the layer's sliding window and global tokens (CausalSelfAttention::allowsKey,
+/// sentinel/NeuralNet/Layers/CausalSelfAttention.cpp:95-100), which the reference's flash path refuses
+/// (CudaCausalSelfAttention.cu:50), and with grouped-query K/V (rows = kvHeads*headDimension).
+void forwardMultiHeadWindowed(const CudaMatrix& query, const CudaMatrix& key, const CudaMatrix& value, CudaMatrix& out,
+                              CudaMatrix& logSumExp, int headCount, int headDimension, float scale, bool causal, int columnStart,
+                              int columnCount, int packCount, int windowSize, int globalTokenCount);
+void backwardMultiHeadWindowed(const CudaMatrix& query, const CudaMatrix& key, const CudaMatrix& value, const CudaMatrix& out,
+                               const CudaMatrix& logSumExp, const CudaMatrix& outGradient, CudaMatrix& queryGradient,
+                               CudaMatrix& keyGradient, CudaMatrix& valueGradient, CudaMatrix& deltaWorkspace, int headCount,
+                               int headDimension, float scale, bool causal, int columnStart, int columnCount, int packCount,
+                               int windowSize, int globalTokenCount);
+
+}  // namespace sentinel_b200
+
+#else  // stand-alone build
+
+namespace sentinel_b200 {
+
 /// row-major fp32 device matrix, data[row * cols + col]; storage grows but never shrinks
 class CudaMatrix {
 public:
@@ -35,6 +74,7 @@ public:
     /// reshape; reallocates only when the element count exceeds the capacity (never inside a stream capture)
     void ensureSize(size_t rowCount, size_t columnCount);
     void upload(const float* host, size_t rowCount, size_t columnCount);
+    /// copies to the host, then throws std::runtime_error if a device-side wait ran out since the last check
     void download(float* host) const;
     float* deviceData() { return this->data; }
     const float* deviceData() const { return this->data; }
@@ -43,7 +83,6 @@ private:
     float* data = nullptr;
     size_t capacity = 0;
 };
-#endif
 
 /// tiled causal attention with online softmax on sm_100a; forward stores per-query log-sum-exp for backward.
 /// multi-head tensors are (headCount * headDim) x strideColumns, logSumExp is headCount x strideColumns
@@ -72,7 +111,8 @@ public:
                          CudaMatrix& keyGradient, CudaMatrix& valueGradient, float scale, bool causal = true);
 
     /// deltaWorkspace is kept for signature compatibility and sized like the reference does
-    /// (headCount x packCount*columnCount); the library's own scratch is a grow-only internal buffer.
+    /// (headCount x packCount*columnCount); the library's own scratch is a grow-only internal buffer per
+    /// (device, stream).
     static void backwardMultiHead(const CudaMatrix& query, const CudaMatrix& key, const CudaMatrix& value, const CudaMatrix& out,
                                   const CudaMatrix& logSumExp, const CudaMatrix& outGradient, CudaMatrix& queryGradient,
                                   CudaMatrix& keyGradient, CudaMatrix& valueGradient, CudaMatrix& deltaWorkspace, int headCount,
@@ -92,3 +132,5 @@ public:
 };
 
 }  // namespace sentinel_b200
+
+#endif

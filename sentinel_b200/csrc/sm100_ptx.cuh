@@ -1,7 +1,7 @@
 // Thin inline-PTX wrappers for the Blackwell (sm_100a) primitives the attention kernels use:
 // mbarrier, TMA tensor loads, tcgen05 MMA / TMEM load-store / alloc, and the UMMA descriptors.
-// Every wait is bounded: it gives up after ~1 s of wall time (or as soon as another wait in the grid has
-// given up), records where in a device status word, and returns false so the caller can unwind.
+// Every wait is bounded: it gives up after ~1 s of wall time (or at once when another wait on this GPU gave
+// up less than a second ago), records where in a device status word, and returns false so the caller can unwind.
 #pragma once
 
 #include <cuda.h>
@@ -13,9 +13,15 @@ namespace sntl {
 namespace ptx {
 
 // ---------------------------------------------------------------------------------------------------
-// device status word: 0 = fine; otherwise (site << 24) | (blockIdx.x & 0xffffff) of the first wait that gave up
+// device status word: 0 = fine; otherwise (site << 24) | (blockIdx.x & 0xffffff) of the first wait that gave up.
+// It is a sticky REPORT: only the host clears it (sntl_attn_poll_device_status).  It never makes a kernel give up.
+// What lets the remaining CTAs of a stuck grid leave without each spending its own full limit is g_abort_until_ns:
+// a give-up writes (now + its wait limit) there; a wait that has spun for a while and finds that time still in the
+// future gives up too (and renews it, so the later waves of the same grid follow).  One limit after the last
+// give-up the word is stale and launches behave normally again, whether or not the host has polled.
 // ---------------------------------------------------------------------------------------------------
-static __device__ unsigned int g_device_status;  // one copy per translation unit; each exposes its own reader
+static __device__ unsigned int g_device_status;          // one copy per translation unit; each exposes its own reader
+static __device__ unsigned long long g_abort_until_ns;   // 0 = no wait has ever given up
 
 // Optional phase tracing (compile with -DSNTL_TRACE): one chosen CTA records (SM clock << 8 | event) per role, so
 // the length of each pipeline phase and each hand-off can be read back.  Compiles to nothing otherwise.
@@ -78,7 +84,8 @@ constexpr uint64_t kWaitLimitNs = 1000ull * 1000ull * 1000ull;  // 1 s
 
 // Bounded wait for the phase with the given parity.  `abort_flag` is a CTA-shared word any waiter sets when
 // it gives up; all later waits of the CTA then return false at once.  Returns true when the phase completed.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag, uint32_t site)
+__device__ __forceinline__ bool mbar_wait_for(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag, uint32_t site,
+                                              uint64_t limit_ns)
 {
     if (mbar_try_wait(bar, parity)) return true;
     if (*abort_flag) return false;
@@ -88,13 +95,19 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
         if (mbar_try_wait(bar, parity)) return true;
         if ((++spins & 0x3ffu) == 0) {
             if (*abort_flag) return false;
-            if (*(volatile unsigned int*)&g_device_status != 0u || global_timer_ns() - t0 > kWaitLimitNs) {
+            const uint64_t now = global_timer_ns();
+            if (now < *(volatile unsigned long long*)&g_abort_until_ns || now - t0 > limit_ns) {
                 atomicCAS(&g_device_status, 0u, (site << 24) | (blockIdx.x & 0xffffffu));
+                *(volatile unsigned long long*)&g_abort_until_ns = now + limit_ns;
                 *abort_flag = 1u;
                 return false;
             }
         }
     }
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag, uint32_t site)
+{
+    return mbar_wait_for(bar, parity, abort_flag, site, kWaitLimitNs);
 }
 
 // ---------------------------------------------------------------------------------------------------

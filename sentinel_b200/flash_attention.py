@@ -190,12 +190,13 @@ def attention_backward(q, k, v, o, lse, dout, *, causal=True, scale=None, flags=
 
 
 def attention_forward_backward_host(q, k, v, dout, *, causal=True, scale=None, flags=0, device="cuda", chunks=None,
-                                    window=0, global_tokens=0):
+                                    window=0, global_tokens=0, out=None):
     """End-to-end call on HOST tensors (pinned memory recommended): uploads Q, K, V, dO, runs forward and
-    backward on the device, downloads O, LSE, dQ, dK, dV.  This is the path the benchmark's ``e2e`` times."""
+    backward on the device, downloads O, LSE, dQ, dK, dV.  This is the path the benchmark's ``e2e`` times.
+    The returned tensors are reused by the next call unless ``out`` = (O, LSE, dQ, dK, dV) supplies the caller's own."""
     from .host_pipeline import forward_backward_host   # transfers overlapped with the kernels, chunked over (batch, KV group)
     return forward_backward_host(q, k, v, dout, causal=causal, scale=scale, flags=flags, device=device, chunks=chunks,
-                                 window=window, global_tokens=global_tokens)
+                                 window=window, global_tokens=global_tokens, out=out)
 
 
 def merge_partials(o_acc, lse_acc, o_part, lse_part):
@@ -238,6 +239,18 @@ def poll_device_status() -> int:
     if rc not in (_lib.OK, _lib.ERR_DEVICE_TIMEOUT):
         _lib.check(rc, "sntl_attn_poll_device_status")
     return int(word.value)
+
+
+def raise_if_device_wait_timed_out() -> None:
+    """Synchronises the current stream and raises ``_lib.SntlError`` (a RuntimeError) when a bounded device-side wait
+    ran out since the last poll: the results of the calls made since then are not to be trusted.  The asynchronous
+    entry points cannot report this themselves; the host-buffer call and the ring schedule call this at the point
+    where they synchronise anyway."""
+    fwd, bwd = C.c_uint32(0), C.c_uint32(0)
+    rc = _lib.load().sntl_attn_poll_device_status_words(_stream_ptr(), C.byref(fwd), C.byref(bwd))
+    if rc == _lib.ERR_DEVICE_TIMEOUT:
+        raise _lib.SntlError(rc, f"device status (forward 0x{fwd.value:08x}, backward 0x{bwd.value:08x})")
+    _lib.check(rc, "sntl_attn_poll_device_status_words")
 
 
 class CudaFlashAttention:

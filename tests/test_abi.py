@@ -164,3 +164,17 @@ def test_host_pipeline_chunks_cover_every_unit_once(B, Hq, Hkv, chunks):
                 assert (b, h) not in seen_k
                 seen_k.add((b, h))
     assert len(seen_q) == B * Hq and len(seen_k) == B * Hkv
+
+
+def test_dropin_smoke_binaries_resolve_their_libraries():
+    """The reference's attention layer linked with this library's compat translation unit in place of the reference's
+    CudaFlashAttention.cu (oracle/Makefile, target dropin): both executables load, i.e. every symbol the reference's
+    call sites need is defined by that translation unit and libsntl_attn.so.  Without a GPU they stop at "no CUDA device"."""
+    import subprocess
+    from oracle import cpu
+    for exe, want in ((cpu.DROPIN_SMOKE, "64"), (cpu.DROPIN_SMOKE_D128, "128")):
+        if not os.path.exists(exe):
+            pytest.skip("drop-in smokes not built (reference sources absent at build time)")
+        r = subprocess.run([exe, "gqa"], capture_output=True, text=True, timeout=120)
+        assert f"maxHeadDimension={want}" in r.stdout, (r.stdout, r.stderr)
+        assert r.returncode in (0, 4), (r.returncode, r.stdout, r.stderr)

@@ -85,3 +85,35 @@ def test_calls_on_two_streams_keep_their_scratch_apart(sb):
             assert torch.equal(dk, case[7]) and torch.equal(dv, case[8])
             assert float((dq.float() - case[6].float()).abs().max()) <= 1e-3 * float(case[6].float().abs().max())
     assert sb.poll_device_status() == 0
+
+
+def test_bounded_wait_runs_out_reports_and_leaves_the_context_usable(sb):
+    """Failure detection without a fault: a one-warp kernel waits, with a 2 ms limit, on a barrier that by construction
+    never receives its arrival.  The wait runs out exactly as a stuck production wait would after its one second: the
+    kernel returns normally, the poll reports SNTL_ERR_DEVICE_TIMEOUT with the self-test's site code, the report is
+    cleared by that poll, and the next real call (made after the short give-up window has passed) is clean and exact."""
+    import ctypes as C
+    import time
+    from sentinel_b200 import _lib
+    lib = _lib.load()
+    assert sb.poll_device_status() == 0
+    stream = torch.cuda.current_stream().cuda_stream
+    assert lib.sntl_attn_selftest_wait_timeout(2000, stream) == _lib.OK
+    fwd, bwd = C.c_uint32(0), C.c_uint32(0)
+    rc = lib.sntl_attn_poll_device_status_words(stream, C.byref(fwd), C.byref(bwd))
+    assert rc == _lib.ERR_DEVICE_TIMEOUT
+    assert fwd.value >> 24 == 0x7e and bwd.value == 0
+    assert lib.sntl_attn_poll_device_status_words(stream, C.byref(fwd), C.byref(bwd)) == _lib.OK   # cleared by the poll
+    with pytest.raises(RuntimeError):      # the python mirror raises at its synchronisation point
+        assert lib.sntl_attn_selftest_wait_timeout(1000, stream) == _lib.OK
+        sb.raise_if_device_wait_timed_out()
+    time.sleep(0.05)                       # well past the 1-2 ms during which other waits would give up early
+    w = sb.WORKLOADS["gqa7b_d128"]
+    q, k, v, do = (t.cuda() for t in sb.make_inputs(w, batch=1, q_heads=4, kv_heads=2, seq=512))
+    o1, lse1 = sb.attention_forward(q, k, v)
+    dq1, dk1, dv1 = sb.attention_backward(q, k, v, o1, lse1, do)
+    assert sb.poll_device_status() == 0
+    o2, lse2 = sb.attention_forward(q, k, v)
+    assert torch.equal(o1, o2) and torch.equal(lse1, lse2)
+    assert lib.sntl_attn_selftest_wait_timeout(0, stream) == _lib.ERR_BAD_ARGUMENT
+    assert lib.sntl_attn_selftest_wait_timeout(200000, stream) == _lib.ERR_BAD_ARGUMENT
