@@ -100,15 +100,44 @@ class ClockSampler:
         return {"sm_mhz": s[len(s) // 2], "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": len(s)}
 
 
-def cpu_reference_sample(workload, steps: int, warmup: int):
-    """Times the reference's own CPU attention (attention core only) on ONE query head of ONE sequence at a reduced
-    length; the causal FLOP formula is applied to the sample so the unit matches the GPU metric."""
+CPU_SAMPLE_MAX_SEQ = 8192     # one head at S = 8192 keeps two S x S fp32 matrices (2 x 268 MB): the largest length sampled
+CPU_SAMPLE_PASSES = 3         # about 4 s per pass at S = 8192 on 16-32 cores
+
+
+def _host_cores() -> int:
+    try:
+        import psutil
+        n = psutil.cpu_count(logical=False)
+        if n:
+            return int(n)
+    except Exception:
+        pass
+    return os.cpu_count() or 1
+
+
+def _set_openmp_threads(n: int) -> None:
+    """torch.distributed.run exports OMP_NUM_THREADS=1 to its children; the CPU baseline is meant to use every core,
+    so the thread count is set explicitly in the OpenMP runtime the checker libraries link."""
+    import ctypes
+    os.environ["OMP_NUM_THREADS"] = str(n)
+    try:
+        ctypes.CDLL("libgomp.so.1", mode=ctypes.RTLD_GLOBAL).omp_set_num_threads(int(n))
+    except OSError:
+        pass
+
+
+def cpu_reference_sample(workload):
+    """Times the reference's own CPU attention (attention core only) on ONE query head of ONE sequence of the
+    workload's own length (capped at 8192: the reference keeps whole S x S score matrices); the causal FLOP formula
+    is applied to the sample so the unit matches the GPU metric.  One warm-up pass, then CPU_SAMPLE_PASSES timed
+    passes, on all physical cores.  The product arm's `cpu_baseline` and `--impl reference` both call this."""
     import numpy as np
     from oracle import cpu
+    _set_openmp_threads(_host_cores())
     if not cpu.ref_available():
         cpu.build()
     kind = "reference" if cpu.ref_available() else "port"
-    S = min(workload.seq, 2048)
+    S = min(workload.seq, CPU_SAMPLE_MAX_SEQ)
     D = workload.head_dim
     rng = np.random.default_rng(20261125)
     q = (rng.standard_normal((1, 1, S, D)) * workload.qk_std).astype(np.float32)
@@ -117,7 +146,7 @@ def cpu_reference_sample(workload, steps: int, warmup: int):
     do = (rng.standard_normal((1, 1, S, D)) * workload.do_std).astype(np.float32)
     flops = 7.0 * S * S * D
     times = []
-    for i in range(warmup + steps):
+    for i in range(1 + CPU_SAMPLE_PASSES):
         t0 = time.perf_counter()
         if kind == "reference":
             _, _, _, _, secs = cpu.ref_core_fwd_bwd(q, k, v, do, want_outputs=False)
@@ -126,13 +155,15 @@ def cpu_reference_sample(workload, steps: int, warmup: int):
             cpu.attn_fwd(q, k, v)
             cpu.attn_bwd(q, k, v, do)
             dt = time.perf_counter() - t0
-        if i >= warmup:
+        if i >= 1:
             times.append(dt)
     mean = sum(times) / len(times)
     cores = cpu.ref_threads() if kind == "reference" else cpu.oracle_threads()
+    note = "" if S == workload.seq else f" (the workload's S = {workload.seq} does not fit the reference's dense S x S matrices)"
     return {"value": flops / mean / 1e12, "unit": UNIT, "cores": cores, "kind": kind,
-            "sample": f"1 sequence x 1 query head, S={S}, D={D}, fp32, attention core only (dense S^2 work), "
-                      f"{len(times)} timed passes of {mean:.3f} s", "ms_per_step": mean * 1e3}
+            "sample": f"1 sequence x 1 query head of the workload, S={S}{note}, D={D}, fp32, attention core only (dense S^2 work), "
+                      f"1 warm-up + {len(times)} timed passes of {mean:.3f} s (passes capped at {CPU_SAMPLE_PASSES} whatever --steps says)",
+            "ms_per_step": mean * 1e3}
 
 
 def reference_cuda_sample(workload, q, k, v, do):
@@ -153,7 +184,7 @@ def run_reference_arm(args, workload):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    res = cpu_reference_sample(workload, max(1, args.steps), max(1, min(args.warmup, 2)))
+    res = cpu_reference_sample(workload)
     line = {"impl": "reference", "metric": METRIC, "value": res["value"], "unit": UNIT, "n_gpus": args.gpus,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": res["ms_per_step"], "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
@@ -223,6 +254,219 @@ def run_cached_forward(args, w):
     print(json.dumps(line), flush=True)
 
 
+def _make_timed(torch, dist, dev, world, local):
+    def barrier():
+        if world > 1:
+            dist.barrier(device_ids=[local])
+        torch.cuda.synchronize()
+
+    def timed(fn, n):
+        """n calls of fn between CUDA events on the current stream; returns max-over-ranks milliseconds."""
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        e1.synchronize()
+        barrier()
+        ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item())
+
+    return barrier, timed
+
+
+def copy_bound(torch, dist, dev, world, host_in, host_out_like, timed):
+    """The plain transfer time of one e2e step: pinned H2D of Q, K, V, dO and D2H of O, LSE, dQ, dK, dV, one
+    cudaMemcpyAsync per tensor, both directions at once on two streams, no kernels.  With N ranks all of them copy
+    at the same time (they share the host's memory and PCIe root ports), so this is the ceiling the e2e figure of the
+    same N can reach."""
+    dev_in = [torch.empty(t.shape, dtype=t.dtype, device=dev) for t in host_in]
+    dev_out = [torch.empty(t.shape, dtype=t.dtype, device=dev) for t in host_out_like]
+    host_out = [torch.empty(t.shape, dtype=t.dtype).pin_memory() for t in host_out_like]
+    up, down = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
+
+    def step():
+        cur = torch.cuda.current_stream(dev)
+        up.wait_stream(cur)
+        down.wait_stream(cur)
+        with torch.cuda.stream(up):
+            for h, d in zip(host_in, dev_in):
+                d.copy_(h, non_blocking=True)
+        with torch.cuda.stream(down):
+            for d, h in zip(dev_out, host_out):
+                h.copy_(d, non_blocking=True)
+        cur.wait_stream(up)
+        cur.wait_stream(down)
+
+    step()
+    return timed(step, 5) / 5
+
+
+def run_other_workload(torch, sb, name, dev, peaks, steps=20):
+    """fwd+bwd of another configuration on this GPU (device-resident), so that its figure is in the record too."""
+    from sentinel_b200.workloads import WORKLOADS, make_inputs
+    w = WORKLOADS[name]
+    q, k, v, do = (t.to(dev) for t in make_inputs(w))
+    o = torch.empty_like(q)
+    lse = torch.empty(q.shape[:3], dtype=torch.float32, device=dev)
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+
+    def fwd():
+        sb.attention_forward(q, k, v, out=o, lse=lse)
+
+    def bwd():
+        sb.attention_backward(q, k, v, o, lse, do, dq=dq, dk=dk, dv=dv)
+
+    def ms_of(fn):
+        for _ in range(5):
+            fn()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        e1.synchronize()
+        return e0.elapsed_time(e1) / steps
+
+    t_step = ms_of(lambda: (fwd(), bwd()))
+    t_fwd, t_bwd = ms_of(fwd), ms_of(bwd)
+    tf = w.flops / (t_step * 1e-3) / 1e12
+    return {"workload": name, "B": w.batch, "Hq": w.q_heads, "Hkv": w.kv_heads, "S": w.seq, "D": w.head_dim, "value": tf,
+            "unit": UNIT, "ms_per_step": t_step, "fwd_ms": t_fwd, "bwd_ms": t_bwd,
+            "frac_of_burst_peak": tf / float(peaks.get("bf16_tflops", FALLBACK_PEAKS["bf16_tflops"])),
+            "kernel_path": sb.last_path()}
+
+
+def run_strong_scaling(torch, dist, sb, w, dev, rank, world, timed, steps, weak_ms_per_step):
+    """The workload's OWN global batch cut over the ranks at (batch element, KV group) granularity, no communication:
+    with 8 ranks every GPU gets one KV group (7 query heads) of the 7B-class configuration."""
+    from sentinel_b200.workloads import make_inputs, shard_units
+    units = shard_units(w.batch, w.kv_heads, rank, world)
+    if not units or any(b != units[0][0] for b, _ in units):
+        return {"unavailable": "a rank's units span more than one batch element"}
+    g = w.q_heads // w.kv_heads
+    b, hk0, hk1 = units[0][0], units[0][1], units[-1][1] + 1
+    q, k, v, do = make_inputs(w)          # every rank draws the same global tensors and keeps its slice
+    qs, dos = (t[b:b + 1, hk0 * g:hk1 * g].contiguous().to(dev) for t in (q, do))
+    ks, vs = (t[b:b + 1, hk0:hk1].contiguous().to(dev) for t in (k, v))
+    del q, k, v, do
+    o = torch.empty_like(qs)
+    lse = torch.empty(qs.shape[:3], dtype=torch.float32, device=dev)
+    dq, dk, dv = torch.empty_like(qs), torch.empty_like(ks), torch.empty_like(vs)
+
+    def step():
+        sb.attention_forward(qs, ks, vs, out=o, lse=lse)
+        sb.attention_backward(qs, ks, vs, o, lse, dos, dq=dq, dk=dk, dv=dv)
+
+    for _ in range(3):
+        step()
+    ms = timed(step, steps) / steps
+    value = w.flops / (ms * 1e-3) / 1e12
+    return {"value": value, "unit": UNIT, "ms_per_step": ms, "scaling": "strong",
+            "config": {"global_batch": w.batch, "units_total": w.batch * w.kv_heads, "units_per_gpu": len(units),
+                       "query_heads_per_gpu": len(units) * g},
+            "efficiency_vs_one_gpu": weak_ms_per_step / (world * ms),
+            "one_gpu_ms_per_step": weak_ms_per_step}
+
+
+def ring_oracle_check(torch, w_local, rank, world, o, lse, dq, dk, dv):
+    """Sampled fp64 oracle of the FULL sequence against this rank's shard of the ring's results: a few query rows of
+    one head (O, LSE, dQ) and, on the last rank, a few of the latest key columns of one KV head (dK, dV; early key
+    columns need every later query, S^2 work the CPU cannot do at this length)."""
+    import numpy as np
+    from oracle import cpu
+    from sentinel_b200.workloads import make_inputs
+    _set_openmp_threads(_host_cores())
+    S_local = w_local.seq
+    h, hk = 5 % w_local.q_heads, 1 % w_local.kv_heads
+    g = w_local.q_heads // w_local.kv_heads
+    hq0 = hk * g
+    qs, ks, vs, dos = [], [], [], []
+    for r in range(world):                 # the full-sequence tensors of the heads sampled, shard by shard as the ranks drew them
+        q, k, v, do = make_inputs(w_local, seed_offset=r)
+        hs = sorted({h, *range(hq0, hq0 + g)})
+        qs.append(q[:, hs].float().numpy()); dos.append(do[:, hs].float().numpy())
+        ks.append(k[:, [h // g, hk]].float().numpy()); vs.append(v[:, [h // g, hk]].float().numpy())
+    hs = sorted({h, *range(hq0, hq0 + g)})
+    qf, dof, kf, vf = (np.concatenate(x, axis=2) for x in (qs, dos, ks, vs))
+    base = rank * S_local
+    out = {}
+    # rows: head h against its KV head (index 0 of the kept pair)
+    rows = np.array(sorted({0, 1, S_local // 2 - 1, S_local // 2, S_local - 129, S_local - 1}), dtype=np.int32) + base
+    hi = hs.index(h)
+    wo, wl, wdq = cpu.attn_rows(qf[:, hi:hi + 1], kf[:, 0:1], vf[:, 0:1], dof[:, hi:hi + 1], 0, 0, rows)
+    loc = rows - base
+    got_o, got_dq = o[0, h, loc].float().cpu().numpy(), dq[0, h, loc].float().cpu().numpy()
+    got_l = lse[0, h, loc].float().cpu().numpy()
+
+    def errs(got, want):
+        return {"max_abs": float(np.abs(got - want).max()), "rel_l2": float(np.linalg.norm(got - want) / max(np.linalg.norm(want), 1e-30))}
+
+    out["o"], out["dq"] = errs(got_o, wo), errs(got_dq, wdq)
+    out["lse_max_abs"] = float(np.abs(got_l - wl).max())
+    out["rows"] = [int(x) for x in rows]
+    if rank == world - 1:
+        S = S_local * world
+        cols = np.array([S - 385, S - 130, S - 1], dtype=np.int32)
+        gi = [hs.index(x) for x in range(hq0, hq0 + g)]
+        wdk, wdv = cpu.attn_cols(qf[:, gi], kf[:, 1:2], vf[:, 1:2], dof[:, gi], 0, 0, cols)
+        locc = cols - base
+        out["dk"] = errs(dk[0, hk, locc].float().cpu().numpy(), wdk)
+        out["dv"] = errs(dv[0, hk, locc].float().cpu().numpy(), wdv)
+        out["cols"] = [int(x) for x in cols]
+    vals = [out[n] for n in ("o", "dq", "dk", "dv") if n in out]
+    out["within_tolerance"] = bool(all(e["max_abs"] <= 2e-2 and e["rel_l2"] <= 5e-3 for e in vals) and out["lse_max_abs"] <= 2e-2)
+    return out
+
+
+def run_ring(torch, dist, sb, dev, rank, world, timed, steps, per_gpu_value):
+    """The long-context workload: 16384 tokens per rank (131072 at 8 ranks), K/V chunks travelling round the ring."""
+    import dataclasses
+    from sentinel_b200.ring import GpuBackend, RingAttention
+    from sentinel_b200.workloads import WORKLOADS, make_inputs
+    w = WORKLOADS["longctx_ring"]
+    shard = w.seq // w.seq_shards
+    w_local = dataclasses.replace(w, seq=shard, seq_shards=1)
+    q, k, v, do = (t.to(dev) for t in make_inputs(w_local, seed_offset=rank))
+    ring = RingAttention(GpuBackend())
+    res = {}
+
+    def fwd():
+        res["o"], res["lse"] = ring.forward(q, k, v, keep_state=True)
+
+    def bwd():
+        res["g"] = ring.backward(q, k, v, res["o"], res["lse"], do, use_saved_state=True)
+
+    for _ in range(2):
+        fwd(); bwd()
+    total = timed(lambda: (fwd(), bwd()), steps) / steps
+    fwd_ms = timed(fwd, steps) / steps
+    bwd_ms = total - fwd_ms                # the backward consumes the state its forward kept, so it is not timed alone
+    # one profiled step: where the time of a step goes on the compute stream
+    prof = RingAttention(GpuBackend(), profile=True)
+    o_, l_ = prof.forward(q, k, v, keep_state=True)
+    prof.backward(q, k, v, o_, l_, do, use_saved_state=True)
+    S = shard * world
+    flops = 7.0 * w.batch * w.q_heads * float(S) ** 2 * w.head_dim
+    value = flops / (total * 1e-3) / 1e12
+    check = ring_oracle_check(torch, w_local, rank, world, res["o"], res["lse"], *res["g"]) if rank in (0, world - 1) else None
+    gathered = [None] * world
+    dist.all_gather_object(gathered, check)
+    kv_bytes = 2 * 2 * w.batch * w.kv_heads * (shard // 2) * w.head_dim * 2          # K and V, two chunks, bf16
+    acc_bytes = 2 * 2 * w.batch * w.kv_heads * (shard // 2) * w.head_dim * 4         # dK and dV accumulators, fp32
+    return {"workload": "longctx_ring", "S": S, "tokens_per_gpu": shard, "value": value, "unit": UNIT, "ms_per_step": total,
+            "fwd_ms": fwd_ms, "bwd_ms": bwd_ms, "efficiency_vs_n_times_one_gpu": value / (world * per_gpu_value),
+            "bytes_sent_per_gpu_per_step": {"forward": (world - 1) * kv_bytes, "backward": (world - 1) * kv_bytes + world * acc_bytes,
+                                            "redistribution": "one of the two half-shards of Q,K,V,O,dO,LSE each way, once"},
+            "compute_stream_breakdown_ms": prof.timings,
+            "oracle": {"first_rank": gathered[0], "last_rank": gathered[world - 1],
+                       "bound": "max abs <= 2e-2 and relative L2 <= 5e-3 against the fp64 oracle over the full sequence"}}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -233,6 +477,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--batch", type=int, default=0, help="override the workload's per-GPU batch (profiling captures)")
     ap.add_argument("--skip-e2e", action="store_true", help="skip the host-buffer leg (profiling captures)")
+    ap.add_argument("--lean", action="store_true",
+                    help="headline timing only: no sustained loop, other workloads, strong-scaling or ring legs (profiling captures)")
     ap.add_argument("--cached-tokens", type=int, default=0,
                     help="auxiliary mode: this many new tokens per sequence against a KV cache of the workload's length")
     ap.add_argument("--window", type=int, default=0, help="sliding window (keys per query); 0 = the workload's plain causal mask")
@@ -266,6 +512,7 @@ def main():
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     sb._lib.load()
+    barrier, timed = _make_timed(torch, dist, dev, world, local)
 
     ring = None
     if w.seq_shards > 1:
@@ -295,39 +542,19 @@ def main():
 
     def fwd():
         if ring is not None:
-            state["o"], state["lse"] = ring.forward(qd, kd, vd)
+            state["o"], state["lse"] = ring.forward(qd, kd, vd, keep_state=True)
         else:
             sb.attention_forward(qd, kd, vd, out=o, lse=lse, **mask)
 
     def bwd():
         if ring is not None:
-            ring.backward(qd, kd, vd, state["o"], state["lse"], dod)
+            ring.backward(qd, kd, vd, state["o"], state["lse"], dod, use_saved_state=True)
         else:
             sb.attention_backward(qd, kd, vd, o, lse, dod, dq=dq, dk=dk, dv=dv, **mask)
 
     def step():
         fwd()
         bwd()
-
-    def barrier():
-        if world > 1:
-            dist.barrier(device_ids=[local])
-        torch.cuda.synchronize()
-
-    def timed(fn, n):
-        """n calls of fn between CUDA events on the current stream; returns max-over-ranks milliseconds."""
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        barrier()
-        e0.record()
-        for _ in range(n):
-            fn()
-        e1.record()
-        e1.synchronize()
-        barrier()
-        ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
-        if world > 1:
-            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-        return float(ms.item())
 
     for _ in range(args.warmup):
         step()
@@ -339,8 +566,12 @@ def main():
     with ClockSampler(local) as clocks:
         total_ms = timed(step, args.steps)
         launches = sb.launch_count() - launches0
-        fwd_ms = timed(fwd, args.steps) / args.steps
-        bwd_ms = timed(bwd, args.steps) / args.steps
+        if ring is not None:
+            fwd_ms = timed(fwd, args.steps) / args.steps
+            bwd_ms = total_ms / args.steps - fwd_ms       # the ring backward consumes the state its forward kept
+        else:
+            fwd_ms = timed(fwd, args.steps) / args.steps
+            bwd_ms = timed(bwd, args.steps) / args.steps
     ms_per_step = total_ms / args.steps
     flops_rank = w.flops / world if ring is not None else w.flops     # the ring workload's FLOPs are for the whole sequence
     if mask:
@@ -351,18 +582,36 @@ def main():
         pairs = np.minimum(qi + 1, args.window) + np.clip(np.minimum(args.global_tokens, qi - args.window + 1), 0, None)
         flops_rank = 14.0 * w.head_dim * w.batch * w.q_heads * float(pairs.sum())
     value = flops_rank * world / (ms_per_step * 1e-3) / 1e12
+    peaks = load_peaks()
+    burst = float(peaks.get("bf16_tflops", FALLBACK_PEAKS["bf16_tflops"]))
+    sustained_peak = float(peaks.get("bf16_tflops_sustained", FALLBACK_PEAKS["bf16_tflops_sustained"]))
+    clock_summary = clocks.summary()
+
+    # the same loop for at least two seconds: what the 1000 W cap leaves of the burst figure
+    sustained = None
+    if not args.lean and ring is None:
+        n_sus = max(args.steps, int(2200.0 / ms_per_step) + 1)
+        with ClockSampler(local) as sus_clocks:
+            sus_ms = timed(step, n_sus) / n_sus
+        sc = sus_clocks.summary()
+        sus_tf = flops_rank / (sus_ms * 1e-3) / 1e12
+        sustained = {"value": sus_tf * world, "unit": UNIT, "per_gpu": sus_tf, "steps": n_sus, "seconds": sus_ms * n_sus * 1e-3,
+                     "ms_per_step": sus_ms, "sm_mhz_median": sc["sm_mhz"], "reasons": sc["reasons"],
+                     "mcycles_per_step": (sus_ms * 1e-3 * sc["sm_mhz"]) if sc["sm_mhz"] else None,
+                     "frac_of_sustained_peak": sus_tf / sustained_peak, "frac_of_burst_peak": sus_tf / burst}
 
     # end to end through the host-buffer call: H2D of Q,K,V,dO, forward+backward, D2H of O,LSE,dQ,dK,dV
     def e2e_step():
         if ring is not None:
             sh = [t.to(dev, non_blocking=True) for t in (q, k, v, do)]
-            o_, lse_ = ring.forward(sh[0], sh[1], sh[2])
-            grads = ring.backward(sh[0], sh[1], sh[2], o_, lse_, sh[3])
+            o_, lse_ = ring.forward(sh[0], sh[1], sh[2], keep_state=True)
+            grads = ring.backward(sh[0], sh[1], sh[2], o_, lse_, sh[3], use_saved_state=True)
             outs = [t.to("cpu", non_blocking=True) for t in (o_, lse_) + tuple(grads)]
             torch.cuda.current_stream().synchronize()
         else:
             sb.attention_forward_backward_host(q, k, v, do, device=dev, **mask)
 
+    copy_ms = None
     if args.skip_e2e:
         e2e_ms = float("nan")
     else:
@@ -370,30 +619,47 @@ def main():
             e2e_step()
         e2e_steps = max(3, min(args.steps, 10))
         e2e_ms = timed(e2e_step, e2e_steps) / e2e_steps
+        if not args.lean:
+            copy_ms = copy_bound(torch, dist, dev, world, [q, k, v, do], [q, lse.cpu(), q, k, v], timed)
     esz = q.element_size()
     h2d = esz * (2 * q.numel() + 2 * k.numel())
     d2h = esz * (2 * q.numel() + 2 * k.numel()) + 4 * lse.numel()
     e2e_value = None if args.skip_e2e else flops_rank * world / (e2e_ms * 1e-3) / 1e12
     status = sb.poll_device_status()
 
-    peaks = load_peaks()
-    peak = float(peaks.get("bf16_tflops_sustained", FALLBACK_PEAKS["bf16_tflops_sustained"]))
+    # roofline of the dominant call.  The denominator follows the length of the timed region: a kernel timed in a
+    # burst (< 1 s) is read against the burst cuBLAS figure, one timed inside a seconds-long loop against the sustained one
+    region_s = total_ms * 1e-3
+    use_burst = region_s < 1.0
+    peak = burst if use_burst else sustained_peak
     bwd_flops = flops_rank * 5.0 / 7.0
     achieved = bwd_flops / (bwd_ms * 1e-3) / 1e12
     roofline = {"bound": "tensor", "kernel": "attention backward (delta pass + dK/dV/dQ kernel + dQ convert, timed as one call)",
                 "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
-                "peak_source": f"{peaks['_source']} bf16_tflops_sustained (kernel timed inside a seconds-long loop)",
+                "peak_source": f"{peaks['_source']} {'bf16_tflops (burst)' if use_burst else 'bf16_tflops_sustained'}: the timed region of "
+                               f"{args.steps} steps lasted {region_s:.3f} s at a median {clock_summary['sm_mhz']} MHz",
+                "frac_of_burst_peak": achieved / burst, "frac_of_sustained_peak": achieved / sustained_peak,
                 "traffic": (NCU_DRAM_BYTES_PER_BATCH[w.name] * w.batch
                             if w.name in NCU_DRAM_BYTES_PER_BATCH and ring is None and not mask else None),
-                "fwd": {"achieved": flops_rank * 2.0 / 7.0 / (fwd_ms * 1e-3) / 1e12, "ms": fwd_ms},
+                "fwd": {"achieved": flops_rank * 2.0 / 7.0 / (fwd_ms * 1e-3) / 1e12, "ms": fwd_ms,
+                        "frac_of_burst_peak": flops_rank * 2.0 / 7.0 / (fwd_ms * 1e-3) / 1e12 / burst},
                 "bwd_ms": bwd_ms,
-                "fwd_bwd_frac_of_burst_peak": flops_rank / (ms_per_step * 1e-3) / 1e12 / float(peaks.get("bf16_tflops", 1590.0))}
+                "fwd_bwd_frac_of_burst_peak": flops_rank / (ms_per_step * 1e-3) / 1e12 / burst}
+
+    extras = {}
+    plain_headline = ring is None and not mask and args.batch == 0 and not args.lean
+    if plain_headline and world == 1:
+        extras["other_workloads"] = [run_other_workload(torch, sb, n, dev, peaks) for n in ("llama1b_gqa", "gpt2_small")]
+    if plain_headline and world > 1:
+        extras["strong"] = run_strong_scaling(torch, dist, sb, w, dev, rank, world, timed, args.steps, ms_per_step)
+        extras["ring"] = run_ring(torch, dist, sb, dev, rank, world, timed, max(3, min(args.steps, 5)), value / world)
+    status = status or sb.poll_device_status()
 
     if rank == 0:
         cpu_base = None
-        if world == 1 and not args.no_cpu_baseline:
+        if not args.no_cpu_baseline and world == 1:
             try:
-                r = cpu_reference_sample(w, 3, 1)
+                r = cpu_reference_sample(w)
                 cpu_base = {kk: r[kk] for kk in ("value", "unit", "cores", "kind", "sample")}
             except Exception as exc:  # the checker is optional for the bench line, never for the product path
                 cpu_base = {"value": None, "unit": UNIT, "cores": 0, "kind": "port", "sample": f"unavailable: {exc}"}
@@ -405,13 +671,19 @@ def main():
                            "parallelism": (f"sequence split into {world} contiguous shards, zigzag-balanced ring of K/V chunks over NCCL"
                                            if ring is not None else f"batch x KV-group sharding over {world} GPU(s), no communication"),
                            "l2": "per-step working set (Q,K,V,O,dO,dQ,dK,dV,dQ-accumulator) > 0.8 GB, larger than the 126 MB L2",
-                           "kernel_path": sb.last_path(),
+                           "kernel_path": "tcgen05" if w.dtype == "bf16" else "simt_f32",
                            **({"window": args.window, "global_tokens": args.global_tokens,
                                "flop_rule": "14*D per visible (query, key) pair"} if mask else {})},
                 "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                        "ms_per_step": None if args.skip_e2e else e2e_ms},
-                "gpu_launches": int(launches), "clocks": clocks.summary(), "roofline": roofline,
+                        "ms_per_step": None if args.skip_e2e else e2e_ms,
+                        "copy_bound_ms": copy_ms,
+                        "frac_of_copy_bound": (copy_ms / e2e_ms) if (copy_ms and not args.skip_e2e) else None,
+                        "copy_bound": "the same bytes as plain pinned copies, both directions at once, all ranks at once, no kernels"},
+                "gpu_launches": int(launches), "clocks": clock_summary, "roofline": roofline,
                 "device_status": status}
+        if sustained is not None:
+            line["sustained"] = sustained
+        line.update(extras)
         if cpu_base is not None:
             line["cpu_baseline"] = cpu_base
         if world == 1 and ring is None and not args.no_cpu_baseline:

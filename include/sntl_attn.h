@@ -134,6 +134,29 @@ int sntl_attn_bwd(const sntl_attn_desc* desc, const void* q, const void* k, cons
                   const float* lse, const void* dout, void* dq, void* dk, void* dv, void* workspace,
                   size_t workspace_bytes, void* stream);
 
+/* Backward in pieces, for schedules in which one block of queries meets several blocks of keys in turn (the
+ * sequence-sharded ring): what sntl_attn_bwd does in one call, split at its three launches so that the parts that
+ * depend only on the query block run once per block instead of once per pair.
+ *   sntl_attn_bwd_begin   delta = rowsum(dO o O) and the rescaled LSE of the query block; its fp32 dQ accumulator
+ *                         (inside `workspace`) zeroed.  desc: the query block (seq_kv / causal are not used).
+ *   sntl_attn_bwd_block   one (query block, key block) pair with the query block's FINAL lse / delta: adds the
+ *                         pair's dQ into the accumulator, and adds dK * scale and dV into the caller's fp32
+ *                         dk_acc, dv_acc [B][kv_heads][seq_kv][D] (read-modify-write by one owner per element: no
+ *                         atomics, deterministic given the call order).  desc: seq_q as in begin; seq_kv = the key
+ *                         block; causal = 1 only for the diagonal pair (seq_q == seq_kv, same positions).
+ *   sntl_attn_bwd_end     dq (bf16) = scale * accumulator.
+ * `workspace` (sntl_attn_bwd_pieces_workspace_bytes, a function of batch, q_heads, seq_q, head_dim only) carries
+ * delta, LSE and the accumulator from begin to end and belongs to that one query block meanwhile.  bf16 BHSD
+ * tensors with head_dim 64 / 128 only (SNTL_ERR_UNSUPPORTED otherwise), no sliding window.  Asynchronous on
+ * `stream`.  No counterpart in the reference (it has no sequence-parallel path; its backward is one call,
+ * sentinel/NeuralNet/Cuda/CudaFlashAttention.cu:1615-1700). */
+size_t sntl_attn_bwd_pieces_workspace_bytes(const sntl_attn_desc* desc);
+int sntl_attn_bwd_begin(const sntl_attn_desc* desc, const void* o, const float* lse, const void* dout, void* workspace,
+                        size_t workspace_bytes, void* stream);
+int sntl_attn_bwd_block(const sntl_attn_desc* desc, const void* q, const void* k, const void* v, const void* dout,
+                        float* dk_acc, float* dv_acc, void* workspace, size_t workspace_bytes, void* stream);
+int sntl_attn_bwd_end(const sntl_attn_desc* desc, void* dq, void* workspace, size_t workspace_bytes, void* stream);
+
 /* The same backward for callers that cannot allocate device memory and so cannot bring a workspace (a plugin
  * running inside another component's stream capture, a host that bans cudaMalloc in its hot loop, a binding with
  * no allocator to lend).  The scratch is a fixed array inside the library image, sntl_attn_static_scratch_capacity()

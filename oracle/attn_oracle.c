@@ -293,6 +293,8 @@ int oracle_attn_cols(const oracle_shape* s, int b, int hk, const float* q, const
     const float* kb = k + ((size_t)b * s->kv_heads + hk) * (size_t)s->seq_kv * D;
     const float* vb = v + ((size_t)b * s->kv_heads + hk) * (size_t)s->seq_kv * D;
     const long n_q = (long)group * s->seq_q;
+    int min_col = s->seq_kv;
+    for (int c = 0; c < n_cols; ++c) if (cols[c] < min_col) min_col = cols[c];
     int threads = 1;
 #if defined(_OPENMP)
     threads = omp_get_max_threads();
@@ -317,7 +319,10 @@ int oracle_attn_cols(const oracle_shape* s, int b, int hk, const float* q, const
             const float* qrow = q + r * D;
             const float* dorow = dout + r * D;
             const int n = visible_keys(s, i);
-            if (n == 0) continue;
+            if (n == 0 || n <= min_col) continue;      /* this query sees none of the sampled keys */
+            int any = 0;                               /* a query whose dO row is all zero adds nothing to dK, dV */
+            for (int t = 0; t < D && !any; ++t) any = dorow[t] != 0.0f;
+            if (!any) continue;
             const double m = score_row(s, i, qrow, kb, n, D, (double)s->scale, p);
             double l = 0.0;
             for (int j = 0; j < n; ++j) { p[j] = exp(p[j] - m); l += p[j]; }

@@ -39,6 +39,7 @@ def build(force: bool = False, everything: bool = False) -> None:
 
 DROPIN_SMOKE = os.path.join(_HERE, "_ref", "dropin_smoke")
 DROPIN_SMOKE_D128 = os.path.join(_HERE, "_ref", "dropin_smoke_d128")
+DROPIN_SMOKE_REFERENCE = os.path.join(_HERE, "_ref", "dropin_smoke_reference")
 
 
 _oracle = None

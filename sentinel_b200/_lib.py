@@ -18,7 +18,8 @@ EXPORTS = ["sntl_attn_version", "sntl_status_string", "sntl_attn_fwd_workspace_b
            "sntl_attn_fwd", "sntl_attn_bwd", "sntl_attn_merge", "sntl_attn_last_path", "sntl_attn_launch_count",
            "sntl_attn_poll_device_status", "sntl_attn_bwd_static_scratch", "sntl_attn_static_scratch_capacity", "sntl_attn_accumulate",
            "sntl_attn_cached_fwd", "sntl_attn_cached_fwd_workspace_bytes", "sntl_attn_pack_heads", "sntl_attn_unpack_heads",
-           "sntl_attn_poll_device_status_words", "sntl_attn_selftest_wait_timeout"]
+           "sntl_attn_poll_device_status_words", "sntl_attn_selftest_wait_timeout",
+           "sntl_attn_bwd_pieces_workspace_bytes", "sntl_attn_bwd_begin", "sntl_attn_bwd_block", "sntl_attn_bwd_end"]
 ERR_SCRATCH_LIMIT = 7
 
 
@@ -77,6 +78,14 @@ def load():
     lib.sntl_attn_launch_count.restype = C.c_uint64
     lib.sntl_attn_poll_device_status.restype = C.c_int
     lib.sntl_attn_poll_device_status.argtypes = [vp, C.POINTER(C.c_uint32)]
+    lib.sntl_attn_bwd_pieces_workspace_bytes.restype = sz
+    lib.sntl_attn_bwd_pieces_workspace_bytes.argtypes = [dp]
+    lib.sntl_attn_bwd_begin.restype = C.c_int
+    lib.sntl_attn_bwd_begin.argtypes = [dp, vp, vp, vp, vp, sz, vp]
+    lib.sntl_attn_bwd_block.restype = C.c_int
+    lib.sntl_attn_bwd_block.argtypes = [dp, vp, vp, vp, vp, vp, vp, vp, sz, vp]
+    lib.sntl_attn_bwd_end.restype = C.c_int
+    lib.sntl_attn_bwd_end.argtypes = [dp, vp, vp, sz, vp]
     lib.sntl_attn_poll_device_status_words.restype = C.c_int
     lib.sntl_attn_poll_device_status_words.argtypes = [vp, C.POINTER(C.c_uint32), C.POINTER(C.c_uint32)]
     lib.sntl_attn_selftest_wait_timeout.restype = C.c_int

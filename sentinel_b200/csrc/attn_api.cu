@@ -371,6 +371,89 @@ int sntl_attn_bwd(const sntl_attn_desc* d, const void* q, const void* k, const v
     return SNTL_OK;
 }
 
+// ---- backward in pieces ----
+namespace sntl {
+namespace {
+int validate_pieces(const sntl_attn_desc* d)
+{
+    const int rc = validate(d);
+    if (rc != SNTL_OK) return rc;
+    if (d->dtype != SNTL_DTYPE_BF16 || d->layout != SNTL_LAYOUT_BHSD) return SNTL_ERR_UNSUPPORTED;
+    if (d->window_size > 0 || d->global_tokens > 0) return SNTL_ERR_UNSUPPORTED;
+    if (d->flags & SNTL_FLAG_FORCE_SIMT) return SNTL_ERR_UNSUPPORTED;
+    if (!tc_bwd_supported(shape_of(d))) return SNTL_ERR_UNSUPPORTED;
+    return SNTL_OK;
+}
+size_t pieces_workspace_bytes(const sntl_attn_desc* d)
+{
+    const size_t sq_pad = ((size_t)d->seq_q + 127) / 128 * 128;
+    const size_t rows = (size_t)d->batch * d->q_heads * sq_pad;
+    return align_up(2 * 4 * rows) + align_up(4 * rows * (size_t)d->head_dim);
+}
+void pieces_args(const sntl_attn_desc* d, void* workspace, TcArgs& t)
+{
+    t.s = shape_of(d);
+    const size_t sq_pad = ((size_t)d->seq_q + 127) / 128 * 128;
+    t.delta = (float*)workspace;
+    t.dq_accum = (float*)((char*)workspace + align_up(2 * 4 * (size_t)d->batch * d->q_heads * sq_pad));
+}
+}  // namespace
+}  // namespace sntl
+
+size_t sntl_attn_bwd_pieces_workspace_bytes(const sntl_attn_desc* d)
+{
+    return validate_pieces(d) == SNTL_OK ? pieces_workspace_bytes(d) : 0;
+}
+
+int sntl_attn_bwd_begin(const sntl_attn_desc* d, const void* o, const float* lse, const void* dout, void* workspace,
+                        size_t workspace_bytes, void* stream)
+{
+    const int rc = validate_pieces(d);
+    if (rc != SNTL_OK) return rc;
+    if (!o || !lse || !dout) return SNTL_ERR_BAD_ARGUMENT;
+    if (!workspace || workspace_bytes < pieces_workspace_bytes(d)) return SNTL_ERR_WORKSPACE;
+    if (!device_ok()) return SNTL_ERR_NO_DEVICE;
+    TcArgs t{};
+    pieces_args(d, workspace, t);
+    t.o = (const __nv_bfloat16*)o; t.dout = (const __nv_bfloat16*)dout; t.lse = lse;
+    t.phases = kBwdPre;
+    g_last_path = "tcgen05";
+    return cuda_status(tc_backward(t, (cudaStream_t)stream));
+}
+
+int sntl_attn_bwd_block(const sntl_attn_desc* d, const void* q, const void* k, const void* v, const void* dout, float* dk_acc,
+                        float* dv_acc, void* workspace, size_t workspace_bytes, void* stream)
+{
+    const int rc = validate_pieces(d);
+    if (rc != SNTL_OK) return rc;
+    if (!q || !k || !v || !dout || !dk_acc || !dv_acc) return SNTL_ERR_BAD_ARGUMENT;
+    if (!workspace || workspace_bytes < pieces_workspace_bytes(d)) return SNTL_ERR_WORKSPACE;
+    if (!device_ok()) return SNTL_ERR_NO_DEVICE;
+    TcArgs t{};
+    pieces_args(d, workspace, t);
+    t.q = (const __nv_bfloat16*)q; t.k = (const __nv_bfloat16*)k; t.v = (const __nv_bfloat16*)v;
+    t.dout = (const __nv_bfloat16*)dout;
+    t.dk_acc = dk_acc; t.dv_acc = dv_acc;
+    t.phases = kBwdMain;
+    g_last_path = "tcgen05";
+    return cuda_status(tc_backward(t, (cudaStream_t)stream));
+}
+
+int sntl_attn_bwd_end(const sntl_attn_desc* d, void* dq, void* workspace, size_t workspace_bytes, void* stream)
+{
+    const int rc = validate_pieces(d);
+    if (rc != SNTL_OK) return rc;
+    if (!dq) return SNTL_ERR_BAD_ARGUMENT;
+    if (!workspace || workspace_bytes < pieces_workspace_bytes(d)) return SNTL_ERR_WORKSPACE;
+    if (!device_ok()) return SNTL_ERR_NO_DEVICE;
+    TcArgs t{};
+    pieces_args(d, workspace, t);
+    t.dq = (__nv_bfloat16*)dq;
+    t.phases = kBwdPost;
+    g_last_path = "tcgen05";
+    return cuda_status(tc_backward(t, (cudaStream_t)stream));
+}
+
 int sntl_attn_merge(int32_t acc_dtype, int32_t part_dtype, int64_t rows, int32_t head_dim, void* o_acc, float* lse_acc,
                     const void* o_part, const float* lse_part, void* stream)
 {

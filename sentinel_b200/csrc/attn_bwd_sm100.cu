@@ -65,6 +65,7 @@ struct BwdParams {
     int n_qt, n_kt;
     int split_tiles;       // the first split_tiles key tiles are cut into one CTA per query head of the group
     float* dkv_part;       // [split tile][slab][head of group][dV, dK][128][D] fp32
+    float *dk_acc, *dv_acc;   // non-null: dK*scale / dV are ADDED into these fp32 [B*Hkv][Skv][D] tensors (no bf16 store)
     float scale, scale_log2;
 };
 
@@ -560,6 +561,31 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
                 for (int v = 0; v < 8; ++v)
                     *reinterpret_cast<uint4*>(dst + c * 32 + v * 4) = make_uint4(r[4 * v], r[4 * v + 1], r[4 * v + 2], r[4 * v + 3]);
             }
+        } else if (ok && p.dk_acc != nullptr) {
+            // accumulate form: this CTA is the only writer of its 128 key rows in this launch
+            tc_fence_after();
+            const int key = k0 + row;
+            const bool store = key < p.Skv;
+            const float mul = wg == 0 ? 1.0f : p.scale;
+            float* dst = (wg == 0 ? p.dv_acc : p.dk_acc) + ((size_t)slab * p.Skv + (size_t)(store ? key : 0)) * D;
+            const uint32_t src = (wg == 0 ? tm_dV : tm_dK) + lane_off;
+#pragma unroll
+            for (int c = 0; c < D / 32; ++c) {
+                uint32_t r[32];
+                tmem_ld32(src + (uint32_t)(c * 32), r);
+                tmem_ld_wait();
+                if (store) {
+#pragma unroll
+                    for (int v = 0; v < 8; ++v) {
+                        float4 a = *reinterpret_cast<const float4*>(dst + c * 32 + v * 4);
+                        a.x = fmaf(__uint_as_float(r[4 * v + 0]), mul, a.x);
+                        a.y = fmaf(__uint_as_float(r[4 * v + 1]), mul, a.y);
+                        a.z = fmaf(__uint_as_float(r[4 * v + 2]), mul, a.z);
+                        a.w = fmaf(__uint_as_float(r[4 * v + 3]), mul, a.w);
+                        *reinterpret_cast<float4*>(dst + c * 32 + v * 4) = a;
+                    }
+                }
+            }
         } else if (ok) {
             tc_fence_after();
             const int key = k0 + row;
@@ -584,7 +610,7 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
                     }
                 }
             }
-        } else if (n_iter == 0) {
+        } else if (n_iter == 0 && p.dk_acc == nullptr) {
             // a key tile no query can see (cannot happen for causal with Sq == Skv; kept for safety): zero grads
             const int key = k0 + row;
             if (key < p.Skv) {
@@ -724,7 +750,8 @@ cudaError_t launch_bwd(const TcArgs& a, cudaStream_t st)
     const long long rows_padded = (long long)s.B * s.Hq * Sq_pad;
     float* lse2 = a.delta + rows_padded;   // workspace: [delta | lse2] then the accumulator (see tc_backward_workspace_bytes)
     cudaError_t e;
-    {
+    const int phases = a.phases ? a.phases : (kBwdPre | kBwdMain | kBwdPost);
+    if (phases & kBwdPre) {
         const int warps = 8;
         const long long blocks = (rows_padded + warps - 1) / warps;
         bwd_pre_kernel<D><<<(unsigned)blocks, warps * 32, 0, st>>>(a.o, a.dout, a.lse, lse2, a.delta, a.dq_accum, s.Sq, Sq_pad,
@@ -732,6 +759,7 @@ cudaError_t launch_bwd(const TcArgs& a, cudaStream_t st)
         count_launch();
         if ((e = cudaGetLastError()) != cudaSuccess) return e;
     }
+    if (phases & kBwdMain) {
     CUtensorMap tq, tk, tv, tdo;
     if ((e = encode_tmap_bf16_3d(&tq, a.q, D, s.Sq, s.B * s.Hq, 128)) != cudaSuccess) return e;
     if ((e = encode_tmap_bf16_3d(&tdo, a.dout, D, s.Sq, s.B * s.Hq, 128)) != cudaSuccess) return e;
@@ -747,6 +775,7 @@ cudaError_t launch_bwd(const TcArgs& a, cudaStream_t st)
     p.n_qt = n_qt; p.n_kt = n_kt;
     p.split_tiles = kSplit ? bwd_split_tiles(s) : 0;
     p.dkv_part = reinterpret_cast<float*>(reinterpret_cast<char*>(a.dq_accum) + align256(4 * (size_t)rows_padded * D));
+    p.dk_acc = a.dk_acc; p.dv_acc = a.dv_acc;
     p.scale = s.scale;
     p.scale_log2 = s.scale * 1.4426950408889634f;
     constexpr int kDoStages = (D == 128) ? 1 : 2;
@@ -766,6 +795,8 @@ cudaError_t launch_bwd(const TcArgs& a, cudaStream_t st)
         count_launch();
         if ((e = cudaGetLastError()) != cudaSuccess) return e;
     }
+    }   // kBwdMain
+    if (!(phases & kBwdPost)) return cudaSuccess;
     bwd_post_kernel<D><<<(unsigned)((long long)s.B * s.Hq * n_qt * 4), 256, 0, st>>>(a.dq_accum, a.dq, s.Sq, n_qt, s.scale);
     count_launch();
     return cudaGetLastError();
@@ -791,7 +822,8 @@ size_t tc_backward_workspace_bytes(const AttnShape& s)
 cudaError_t tc_backward(const TcArgs& a, cudaStream_t st)
 {
     const bool win = a.s.causal && a.s.window > 0;
-    if (bwd_split_tiles(a.s) > 0) {
+    // the accumulate form has no cut key tiles: their fp32 partials would need a second adding pass
+    if (a.dk_acc == nullptr && bwd_split_tiles(a.s) > 0) {
         if (a.s.D == 64) return win ? launch_bwd<64, true, true>(a, st) : launch_bwd<64, false, true>(a, st);
         return win ? launch_bwd<128, true, true>(a, st) : launch_bwd<128, false, true>(a, st);
     }

@@ -75,7 +75,17 @@ struct TcArgs {
     const float* lse;
     float* delta;      // [B][Hq][Sq_pad]
     float* dq_accum;   // [B][Hq][Sq_pad][D] fp32
+    // Backward in pieces (the ring schedule: one query block meets several key blocks).  phases selects which of the
+    // three launches run: kBwdPre (delta, LSE*log2e, dQ accumulator zeroed), kBwdMain (the tensor-core kernel, which
+    // ADDS this key block's dQ into the accumulator), kBwdPost (accumulator -> bf16 dQ).  0 = all three.
+    // dk_acc / dv_acc non-null: the main kernel adds its dK (times scale) / dV into these fp32 [B][Hkv][Skv][D]
+    // tensors instead of writing bf16 dk / dv (each element has one owning CTA per launch, so the read-modify-write
+    // needs no atomics and stays deterministic).
+    int phases = 0;
+    float* dk_acc = nullptr;
+    float* dv_acc = nullptr;
 };
+enum : int { kBwdPre = 1, kBwdMain = 2, kBwdPost = 4 };
 bool tc_fwd_supported(const AttnShape& s);
 bool tc_bwd_supported(const AttnShape& s);
 cudaError_t tc_forward(const TcArgs& a, cudaStream_t st);

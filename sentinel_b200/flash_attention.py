@@ -189,6 +189,59 @@ def attention_backward(q, k, v, o, lse, dout, *, causal=True, scale=None, flags=
     return dq, dk, dv
 
 
+class BackwardPieces:
+    """Backward of ONE block of queries against several blocks of keys in turn (sntl_attn_bwd_begin / _block / _end):
+    the work that depends only on the query block -- delta, the rescaled LSE, zeroing and converting the fp32 dQ
+    accumulator -- runs once, and each ``block`` call adds its dQ into that accumulator and its dK, dV into the
+    caller's fp32 accumulators.  ``lse`` must be the FINAL log-sum-exp of the query rows over all keys."""
+
+    def __init__(self, q, o, lse, dout, *, scale=None, workspace=None):
+        lib = _lib.load()
+        for t, n in ((q, "q"), (o, "o"), (lse, "lse"), (dout, "dout")):
+            _require(t, n)
+        if o.shape != q.shape or dout.shape != q.shape or lse.shape != q.shape[:3] or lse.dtype != torch.float32:
+            raise ValueError("o/dout must match q; lse must be fp32 [B,Hq,Sq]")
+        self.q, self.dout = q, dout
+        self.scale = q.shape[-1] ** -0.5 if scale is None else float(scale)
+        d = self._desc(q.shape[1], q.shape[2], False)
+        self.nbytes = lib.sntl_attn_bwd_pieces_workspace_bytes(C.byref(d))
+        if self.nbytes == 0:
+            _lib.check(_lib.ERR_UNSUPPORTED, "sntl_attn_bwd_begin")
+        if workspace is None:
+            workspace = torch.empty(self.nbytes, dtype=torch.uint8, device=q.device)
+        if workspace.numel() < self.nbytes:
+            raise ValueError("workspace too small")
+        self.ws = workspace
+        rc = lib.sntl_attn_bwd_begin(C.byref(d), o.data_ptr(), lse.data_ptr(), dout.data_ptr(), self.ws.data_ptr(), self.nbytes,
+                                     _stream_ptr())
+        _lib.check(rc, "sntl_attn_bwd_begin")
+
+    def _desc(self, kv_heads, seq_kv, causal):
+        B, Hq, Sq, D = self.q.shape
+        return _lib.Desc(_dtype_code(self.q), _lib.LAYOUT_BHSD, B, Hq, kv_heads, Sq, seq_kv, D, self.scale, int(bool(causal)), 0, 0,
+                         0, 0, 0)
+
+    def block(self, k, v, dk_acc, dv_acc, *, causal):
+        """Adds the (query block, this key block) pair: dQ into the accumulator, dK*scale / dV into fp32 dk_acc / dv_acc."""
+        for t, n in ((k, "k"), (v, "v"), (dk_acc, "dk_acc"), (dv_acc, "dv_acc")):
+            _require(t, n)
+        if k.shape != v.shape or dk_acc.shape != k.shape or dv_acc.shape != k.shape:
+            raise ValueError("k, v, dk_acc, dv_acc must share shape")
+        if dk_acc.dtype != torch.float32 or dv_acc.dtype != torch.float32:
+            raise ValueError("dk_acc / dv_acc must be fp32")
+        d = self._desc(k.shape[1], k.shape[2], causal)
+        rc = _lib.load().sntl_attn_bwd_block(C.byref(d), self.q.data_ptr(), k.data_ptr(), v.data_ptr(), self.dout.data_ptr(),
+                                             dk_acc.data_ptr(), dv_acc.data_ptr(), self.ws.data_ptr(), self.nbytes, _stream_ptr())
+        _lib.check(rc, "sntl_attn_bwd_block")
+
+    def end(self, dq=None):
+        dq = torch.empty_like(self.q) if dq is None else dq
+        d = self._desc(self.q.shape[1], self.q.shape[2], False)
+        rc = _lib.load().sntl_attn_bwd_end(C.byref(d), dq.data_ptr(), self.ws.data_ptr(), self.nbytes, _stream_ptr())
+        _lib.check(rc, "sntl_attn_bwd_end")
+        return dq
+
+
 def attention_forward_backward_host(q, k, v, dout, *, causal=True, scale=None, flags=0, device="cuda", chunks=None,
                                     window=0, global_tokens=0, out=None):
     """End-to-end call on HOST tensors (pinned memory recommended): uploads Q, K, V, dO, runs forward and

@@ -10,24 +10,40 @@ Schedule
 A plain ring over contiguous shards is badly unbalanced under a causal mask (rank r has r+0.5 blocks of work).
 So each shard is cut in two half-shards ("chunks", ``2W`` in total) and the chunks are first re-dealt in a zigzag:
 rank ``r`` works on chunks ``r`` and ``2W-1-r``.  Then for ``W`` steps the key/value chunks travel round the ring
-(rank r sends to r+1).  In every step every rank has exactly two visible (query chunk, key chunk) pairs -- a pair is
-visible iff ``key_chunk <= query_chunk``, causal inside iff equal -- so all ranks finish each step together.
-Forward: each visible pair is one call of the attention forward (non-causal, or causal on the diagonal) whose
-(O, LSE) partial is folded into fp32 running results with the log-sum-exp merge.  Backward: each visible pair is one
-call of the attention backward with the FINAL LSE and O of the query chunk, so its probabilities are already the
-global ones; dQ partials add up locally, dK/dV partials add into fp32 accumulators that travel with their key
-chunk and arrive home after ``W`` steps.  Results are dealt back to the contiguous layout at the end.
+(rank r sends to r+1).  In every step every rank has exactly two block units of visible (query chunk, key chunk)
+pairs -- a pair is visible iff ``key_chunk <= query_chunk``, causal inside iff equal -- so all ranks finish each step
+together.
 
-Communication is ``torch.distributed`` point-to-point (NCCL send/recv over NVLink on GPUs; gloo in the CPU tests),
-issued for step t+1 before the compute of step t so the transfer overlaps the kernels.
+Forward: each visible pair is one call of the attention forward (non-causal, or causal on the diagonal) whose
+(O, LSE) partial is folded into fp32 running results with the log-sum-exp merge.
+
+Backward: the work that belongs to a query chunk alone (delta, the rescaled FINAL log-sum-exp, zeroing and converting
+its fp32 dQ accumulator) runs once per chunk; each visible pair is then one launch of the tensor-core kernel that adds
+its dQ into that accumulator and its dK, dV into a per-pair fp32 partial.  dK/dV of a key chunk are summed in fp32
+accumulators that travel with the chunk: after a step's pairs the rank adds its partials to the accumulators that
+arrived from the previous rank and passes them on; that hop runs under the NEXT step's kernels (three buffer sets
+rotate: being sent, being received, being computed), as does the hop of K/V themselves, so in steady state no
+transfer is exposed.  After ``W`` steps one last hop brings the accumulators home.  Results are dealt back to the
+contiguous layout at the end.
+
+Communication is ``torch.distributed`` point-to-point (NCCL send/recv over NVLink on GPUs; gloo in the CPU tests).
+Every wait on a transfer has a deadline (``timeout_s``): a peer that left, stalled, or posted a different schedule
+makes ``RingAttention`` raise ``RingTimeout`` instead of waiting for ever.
 
 The arithmetic is supplied by a *backend* (``GpuBackend`` = this library's kernels).  The schedule itself touches
 no tensor values, which is what lets the CPU tests drive it with a reference backend.
 """
 from __future__ import annotations
 
+import time
+from datetime import timedelta
+
 import torch
 import torch.distributed as dist
+
+
+class RingTimeout(RuntimeError):
+    """A point-to-point transfer of the ring did not complete within the deadline."""
 
 
 def chunk_owner_contiguous(chunk: int) -> int:
@@ -65,11 +81,17 @@ class GpuBackend:
     def fwd(self, q, k, v, causal):
         return self.fa.attention_forward(q, k, v, causal=causal)
 
-    def bwd(self, q, k, v, o, lse, do, causal):
-        return self.fa.attention_backward(q, k, v, o, lse, do, causal=causal)
-
     def merge(self, o_acc, lse_acc, o_part, lse_part):
         self.fa.merge_partials(o_acc, lse_acc, o_part, lse_part)
+
+    def bwd_begin(self, q, o, lse, do):
+        return self.fa.BackwardPieces(q, o, lse, do)
+
+    def bwd_block(self, handle, k, v, dk_acc, dv_acc, causal):
+        handle.block(k, v, dk_acc, dv_acc, causal=causal)
+
+    def bwd_end(self, handle):
+        return handle.end()
 
     def accumulate(self, acc, part):
         self.fa.accumulate(acc, part)
@@ -80,45 +102,86 @@ class GpuBackend:
     def neg_inf(self, shape, like):
         return torch.full(shape, float("-inf"), dtype=torch.float32, device=like.device)
 
+    def check(self):
+        self.fa.raise_if_device_wait_timed_out()
+
 
 class RingAttention:
-    def __init__(self, backend, group=None):
+    def __init__(self, backend, group=None, timeout_s: float = 60.0, profile: bool = False):
         self.backend = backend
         self.group = group
         self.rank = dist.get_rank(group)
         self.world = dist.get_world_size(group)
+        self.timeout_s = timeout_s
+        self.profile = profile and torch.cuda.is_available()
+        self.timings: dict = {}
+        self._saved = None
+        self._side = None        # second compute stream: the two pairs of a step run side by side
 
-    # ------------------------------------------------------------------ redistribution
-    def _exchange(self, sends, recvs):
+    # ------------------------------------------------------------------ transfers
+    def _finish(self, works, what):
+        """Wait for posted transfers, with a deadline.  With NCCL ``wait()`` only makes the current stream wait (a dead
+        peer surfaces through the process group's own timeout); with a host-side backend (gloo) the wait itself takes
+        the deadline and its expiry is re-raised as ``RingTimeout``."""
+        if not works:
+            return
+        if torch.cuda.is_available() and dist.get_backend(self.group) == "nccl":
+            for w in works:
+                w.wait()
+            return
+        deadline = time.monotonic() + self.timeout_s
+        for w in works:
+            left = max(deadline - time.monotonic(), 0.001)
+            try:
+                w.wait(timedelta(seconds=left))
+            except RuntimeError as e:
+                if "imed out" in str(e) or "imeout" in str(e):
+                    raise RingTimeout(f"rank {self.rank}: {what} did not complete within {self.timeout_s} s "
+                                      "(a peer left, stalled, or posted a different schedule)") from e
+                raise
+
+    def _exchange(self, sends, recvs, what="redistribution"):
         """sends: [(tensor, dst)], recvs: [(tensor, src)]; one batched point-to-point round."""
         ops = [dist.P2POp(dist.isend, t, dst, self.group) for t, dst in sends]
         ops += [dist.P2POp(dist.irecv, t, src, self.group) for t, src in recvs]
         if ops:
-            for w in dist.batch_isend_irecv(ops):
-                w.wait()
+            self._finish(dist.batch_isend_irecv(ops), what)
+
+    def to_zigzag_many(self, xs):
+        """Contiguous shards [B,H,S_local,...] -> for each, the list of the two chunks this rank works on (zigzag deal).
+        All tensors travel in one batched round."""
+        r, W = self.rank, self.world
+        want = zigzag_chunks(r, W)
+        outs, sends, recvs = [], [], []
+        for x in xs:
+            half = x.shape[2] // 2
+            mine = {2 * r: x[:, :, :half].contiguous(), 2 * r + 1: x[:, :, half:].contiguous()}
+            out = {c: (mine[c] if c in mine else torch.empty_like(mine[2 * r])) for c in want}
+            sends += [(t, chunk_owner_zigzag(c, W)) for c, t in sorted(mine.items()) if chunk_owner_zigzag(c, W) != r]
+            recvs += [(out[c], chunk_owner_contiguous(c)) for c in want if chunk_owner_contiguous(c) != r]
+            outs.append([out[c] for c in want])
+        self._exchange(sends, recvs, "zigzag deal")
+        return outs
 
     def to_zigzag(self, x):
-        """[B,H,S_local,D] contiguous shard -> list of the two chunks this rank works on (zigzag deal)."""
+        return self.to_zigzag_many([x])[0]
+
+    def from_zigzag_many(self, chunk_lists):
+        """Inverse of ``to_zigzag_many``: per tensor, the two zigzag chunks -> this rank's contiguous shard."""
         r, W = self.rank, self.world
-        half = x.shape[2] // 2
-        mine = {2 * r: x[:, :, :half].contiguous(), 2 * r + 1: x[:, :, half:].contiguous()}
-        want = zigzag_chunks(r, W)
-        out = {c: (mine[c] if c in mine else torch.empty_like(mine[2 * r])) for c in want}
-        sends = [(t, chunk_owner_zigzag(c, W)) for c, t in sorted(mine.items()) if chunk_owner_zigzag(c, W) != r]
-        recvs = [(out[c], chunk_owner_contiguous(c)) for c in want if chunk_owner_contiguous(c) != r]
-        self._exchange(sends, recvs)
-        return [out[c] for c in want]
+        want = (2 * r, 2 * r + 1)
+        outs, sends, recvs = [], [], []
+        for chunks in chunk_lists:
+            have = dict(zip(zigzag_chunks(r, W), chunks))
+            out = {c: (have[c] if c in have else torch.empty_like(chunks[0])) for c in want}
+            sends += [(t.contiguous(), chunk_owner_contiguous(c)) for c, t in sorted(have.items()) if chunk_owner_contiguous(c) != r]
+            recvs += [(out[c], chunk_owner_zigzag(c, W)) for c in want if chunk_owner_zigzag(c, W) != r]
+            outs.append(out)
+        self._exchange(sends, recvs, "deal back")
+        return [torch.cat([out[want[0]], out[want[1]]], dim=2) for out in outs]
 
     def from_zigzag(self, chunks):
-        """Inverse of ``to_zigzag``: the two zigzag chunks -> this rank's contiguous shard."""
-        r, W = self.rank, self.world
-        have = dict(zip(zigzag_chunks(r, W), chunks))
-        want = (2 * r, 2 * r + 1)
-        out = {c: (have[c] if c in have else torch.empty_like(chunks[0])) for c in want}
-        sends = [(t.contiguous(), chunk_owner_contiguous(c)) for c, t in sorted(have.items()) if chunk_owner_contiguous(c) != r]
-        recvs = [(out[c], chunk_owner_zigzag(c, W)) for c in want if chunk_owner_zigzag(c, W) != r]
-        self._exchange(sends, recvs)
-        return torch.cat([out[want[0]], out[want[1]]], dim=2)
+        return self.from_zigzag_many([chunks])[0]
 
     def _rotate_start(self, tensors, buffers):
         """Post the ring shift of ``tensors`` (to rank+1) into ``buffers`` (from rank-1); returns work handles."""
@@ -129,74 +192,177 @@ class RingAttention:
         ops += [dist.P2POp(dist.irecv, b, prv, self.group) for b in buffers]
         return dist.batch_isend_irecv(ops)
 
-    @staticmethod
-    def _rotate_finish(works):
-        if works:
-            for w in works:
-                w.wait()
+    # ------------------------------------------------------------------ two compute lanes
+    def _lanes(self, like):
+        """(main stream, side stream) on CUDA, (None, None) on CPU."""
+        if not like.is_cuda:
+            return None, None
+        if self._side is None:
+            self._side = torch.cuda.Stream(device=like.device)
+        return torch.cuda.current_stream(like.device), self._side
+
+    def _mark(self, name):
+        if self.profile:
+            e = torch.cuda.Event(enable_timing=True)
+            e.record()
+            self.timings.setdefault("_events", []).append((name, e))
+
+    def _collect(self, prefix):
+        """Turns the recorded events into milliseconds: <prefix>_total, <prefix>_exposed_transfer (time the compute
+        stream spent waiting for transfers) and <prefix>_redistribution (zigzag deal and deal back)."""
+        evs = self.timings.pop("_events", [])
+        if not evs:
+            return
+        torch.cuda.synchronize()
+        total = evs[0][1].elapsed_time(evs[-1][1])
+        exposed = redis = 0.0
+        for (n0, e0), (n1, e1) in zip(evs, evs[1:]):
+            if n1 == "wait_done":
+                exposed += e0.elapsed_time(e1)
+            if n1 in ("dealt", "dealt_back"):
+                redis += e0.elapsed_time(e1)
+        self.timings[prefix] = {"total_ms": total, "exposed_transfer_ms": exposed, "redistribution_ms": redis,
+                                "kernel_ms": total - exposed - redis}
 
     # ------------------------------------------------------------------ forward
-    def forward(self, q, k, v):
-        """q,k,v: this rank's contiguous shards [B,H,S/W,D].  Returns (o, lse) for the same shard.
-        Also returns the zigzag-layout state the backward can reuse."""
+    def forward(self, q, k, v, keep_state: bool = False):
+        """q,k,v: this rank's contiguous shards [B,H,S/W,D].  Returns (o, lse) for the same shard.  With ``keep_state``
+        the zigzag-dealt Q, K, V, O, LSE are kept so that ``backward(..., use_saved_state=True)`` on the same tensors
+        does not deal them again (every rank must make the same choice: it changes what is exchanged)."""
         be, W, r = self.backend, self.world, self.rank
-        qz, kz, vz = self.to_zigzag(q), self.to_zigzag(k), self.to_zigzag(v)
+        self._mark("start")
+        qz, kz, vz = self.to_zigzag_many([q, k, v])
+        self._mark("dealt")
         q_ids = zigzag_chunks(r, W)
         o_acc = [be.zeros_f32(t) for t in qz]
         lse_acc = [be.neg_inf(t.shape[:3], t) for t in qz]
         kv = list(kz) + list(vz)
+        # two receive sets; the dealt chunks themselves are only ever read (they may alias the caller's tensors)
+        bufs = [[torch.empty_like(t) for t in kv] for _ in range(2 if W > 2 else 1)] if W > 1 else None
+        main, side = self._lanes(q)
         for step in range(W):
             src = (r - step) % W
             kv_ids = zigzag_chunks(src, W)
-            works, nxt_kv = None, None
+            works = None
             if step + 1 < W:
-                nxt_kv = [torch.empty_like(t) for t in kv]
-                works = self._rotate_start(kv, nxt_kv)
-            for qi, ki, causal in visible_pairs(q_ids, kv_ids):
-                o_p, lse_p = be.fwd(qz[qi], kv[ki], kv[2 + ki], causal)
-                be.merge(o_acc[qi], lse_acc[qi], o_p, lse_p)
+                works = self._rotate_start(kv, bufs[step % len(bufs)])
+            pairs = visible_pairs(q_ids, kv_ids)
+            # pairs on different query chunks touch disjoint running results: they run side by side on two streams
+            # so that one launch's last, partly filled wave of CTAs is covered by the other's
+            by_q = {}
+            for qi, ki, causal in pairs:
+                by_q.setdefault(qi, []).append((ki, causal))
+            lanes = [main, side] if (side is not None and len(by_q) > 1) else [main]
+            if len(lanes) > 1:
+                side.wait_stream(main)
+            for n, (qi, items) in enumerate(sorted(by_q.items())):
+                lane = lanes[n % len(lanes)]
+                ctx = torch.cuda.stream(lane) if lane is not None else _null()
+                with ctx:
+                    for ki, causal in items:
+                        o_p, lse_p = be.fwd(qz[qi], kv[ki], kv[2 + ki], causal)
+                        be.merge(o_acc[qi], lse_acc[qi], o_p, lse_p)
+            if len(lanes) > 1:
+                main.wait_stream(side)
             if step + 1 < W:
-                self._rotate_finish(works)
-                kv = nxt_kv
+                self._mark("compute_done")
+                self._finish(works, "K/V rotation")
+                self._mark("wait_done")
+                kv = bufs[step % len(bufs)]
         o_z = [t.to(q.dtype) for t in o_acc]
-        o = self.from_zigzag(o_z)
-        lse = self.from_zigzag([t.unsqueeze(-1).contiguous() for t in lse_acc]).squeeze(-1)
+        self._mark("computed")
+        o, lse4 = self.from_zigzag_many([o_z, [t.unsqueeze(-1).contiguous() for t in lse_acc]])
+        lse = lse4.squeeze(-1)
+        self._mark("dealt_back")
+        self._saved = {"qz": qz, "kz": kz, "vz": vz, "oz": o_z, "lsez": lse_acc} if keep_state else None
+        self._collect("forward")
         return o, lse
 
     # ------------------------------------------------------------------ backward
-    def backward(self, q, k, v, o, lse, do):
-        """All arguments are this rank's contiguous shards; returns (dq, dk, dv) for the same shards."""
+    def backward(self, q, k, v, o, lse, do, use_saved_state: bool = False):
+        """All arguments are this rank's contiguous shards; returns (dq, dk, dv) for the same shards.
+        ``use_saved_state``: q, k, v, o, lse are the tensors of the last ``forward(..., keep_state=True)``."""
         be, W, r = self.backend, self.world, self.rank
-        qz, kz, vz = self.to_zigzag(q), self.to_zigzag(k), self.to_zigzag(v)
-        oz, doz = self.to_zigzag(o), self.to_zigzag(do)
-        lsez = [t.squeeze(-1).contiguous() for t in self.to_zigzag(lse.unsqueeze(-1).contiguous())]
+        self._mark("start")
+        saved = self._saved
+        if use_saved_state:
+            if saved is None:
+                raise ValueError("no saved forward state: call forward(..., keep_state=True) first")
+            qz, kz, vz, oz, lsez = saved["qz"], saved["kz"], saved["vz"], saved["oz"], saved["lsez"]
+            (doz,) = self.to_zigzag_many([do])
+        else:
+            qz, kz, vz, oz, doz, lse4 = self.to_zigzag_many([q, k, v, o, do, lse.unsqueeze(-1).contiguous()])
+            lsez = [t.squeeze(-1).contiguous() for t in lse4]
+        self._saved = None
+        self._mark("dealt")
         q_ids = zigzag_chunks(r, W)
-        dq_acc = [be.zeros_f32(t) for t in qz]
+        handles = [be.bwd_begin(qz[i], oz[i], lsez[i], doz[i]) for i in range(2)]
         kv = list(kz) + list(vz)
-        dkv = [be.zeros_f32(t) for t in kv]          # travels with its key/value chunk
+        kv_bufs = [[torch.empty_like(t) for t in kv] for _ in range(2 if W > 2 else 1)] if W > 1 else None
+        # fp32 dK/dV: per-pair partials of this step, and the travelling accumulators in three rotating sets
+        part = [[be.zeros_f32(kv[0]), be.zeros_f32(kv[0])] for _ in range(3)]     # [pair slot][dk, dv]
+        acc = [be.zeros_f32(t) for t in kv]                                      # the set being completed this step
+        acc_recv = [torch.empty_like(t) for t in acc] if W > 1 else None
+        acc_send = [torch.empty_like(t) for t in acc] if W > 1 else None
+        recv_works = send_pending = None
+        main, side = self._lanes(q)
         for step in range(W):
             src = (r - step) % W
             kv_ids = zigzag_chunks(src, W)
-            works, nxt_kv = None, None
-            if step + 1 < W:                          # K/V of the next step can move while this step computes
-                nxt_kv = [torch.empty_like(t) for t in kv]
-                works = self._rotate_start(kv, nxt_kv)
-            for qi, ki, causal in visible_pairs(q_ids, kv_ids):
-                dq_p, dk_p, dv_p = be.bwd(qz[qi], kv[ki], kv[2 + ki], oz[qi], lsez[qi], doz[qi], causal)
-                be.accumulate(dq_acc[qi], dq_p)
-                be.accumulate(dkv[ki], dk_p)
-                be.accumulate(dkv[2 + ki], dv_p)
-            # the gradient accumulators follow their chunk (after this step's contributions), including the last
-            # hop that brings them home
+            kv_works = None
+            if step + 1 < W:                          # K/V of the next step move while this step computes
+                kv_works = self._rotate_start(kv, kv_bufs[step % len(kv_bufs)])
+            pairs = visible_pairs(q_ids, kv_ids)
+            lanes = [main, side] if (side is not None and len(pairs) > 1) else [main]
+            if len(lanes) > 1:
+                side.wait_stream(main)
+            for n, (qi, ki, causal) in enumerate(pairs):
+                lane = lanes[n % len(lanes)]
+                ctx = torch.cuda.stream(lane) if lane is not None else _null()
+                with ctx:
+                    part[n][0].zero_()
+                    part[n][1].zero_()
+                    be.bwd_block(handles[qi], kv[ki], kv[2 + ki], part[n][0], part[n][1], causal)
+            if len(lanes) > 1:
+                main.wait_stream(side)
+            self._mark("compute_done")
+            # the accumulators of this step's key chunks: zeros at step 0 (the chunks start here), else what the
+            # previous rank sent after its own previous step
+            if step > 0:
+                self._finish(recv_works, "dK/dV accumulator hop")
+                acc, acc_recv = acc_recv, acc
+            self._mark("wait_done")
+            for n, (qi, ki, causal) in enumerate(pairs):
+                be.accumulate(acc[ki], part[n][0])
+                be.accumulate(acc[2 + ki], part[n][1])
             if W > 1:
-                nxt_dkv = [torch.empty_like(t) for t in dkv]
-                w2 = self._rotate_start(dkv, nxt_dkv)
-                self._rotate_finish(w2)
-                dkv = nxt_dkv
+                # pass them on; the hop runs under the next step's kernels.  acc_send is free again once the hop
+                # posted a step ago has completed (same handles: a batched round completes as a whole)
+                acc, acc_send = acc_send, acc
+                recv_works = self._rotate_start(acc_send, acc_recv)
             if step + 1 < W:
-                self._rotate_finish(works)
-                kv = nxt_kv
-        dq = self.from_zigzag([t.to(q.dtype) for t in dq_acc])
-        dk = self.from_zigzag([t.to(k.dtype) for t in dkv[:2]])
-        dv = self.from_zigzag([t.to(v.dtype) for t in dkv[2:]])
+                self._mark("compute_done")
+                self._finish(kv_works, "K/V rotation")
+                self._mark("wait_done")
+                kv = kv_bufs[step % len(kv_bufs)]
+        if W > 1:
+            self._mark("compute_done")
+            self._finish(recv_works, "dK/dV accumulator hop home")   # the last hop brings this rank's own chunks home
+            self._mark("wait_done")
+            acc = acc_recv
+        dq_z = [be.bwd_end(h) for h in handles]
+        self._mark("computed")
+        dq, dk, dv = self.from_zigzag_many([dq_z, [t.to(k.dtype) for t in acc[:2]], [t.to(v.dtype) for t in acc[2:]]])
+        self._mark("dealt_back")
+        self._collect("backward")
+        if hasattr(be, "check"):
+            be.check()
         return dq, dk, dv
+
+
+class _null:
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *a):
+        return False

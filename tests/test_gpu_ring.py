@@ -1,9 +1,15 @@
-"""Multi-GPU test of the sequence-sharded ring schedule on the real kernels (needs >= 2 GPUs; skipped otherwise):
-every rank's shard of O, LSE, dQ, dK, dV from the ring must match single-GPU attention over the whole sequence."""
+"""Multi-GPU test of the sequence-sharded ring schedule on the real kernels (needs >= 2 GPUs; skipped otherwise).
+
+The reference has no sequence-parallel path, so the pin is the fp64 oracle over the WHOLE sequence: sampled query rows
+(O, LSE, dQ) and sampled key columns (dK, dV) of every rank's shard, held to the bf16 bounds of the single-GPU kernels
+(max abs 2e-2, relative L2 5e-3).  Early key columns need every later query -- S^2 oracle work -- so they are checked
+through linearity: a second backward with a dO that is zero outside a few hundred query rows has gradients the oracle
+can compute for ANY key.  A comparison with single-GPU attention over the whole sequence is kept as a second assert."""
 import os
 import socket
 import sys
 
+import numpy as np
 import pytest
 import torch
 
@@ -14,6 +20,11 @@ if ROOT not in sys.path:
 pytestmark = pytest.mark.gpu
 
 
+def _errs(got, want):
+    got, want = np.asarray(got, np.float64), np.asarray(want, np.float64)
+    return float(np.abs(got - want).max()), float(np.linalg.norm(got - want) / max(np.linalg.norm(want), 1e-30))
+
+
 def _worker(rank, world, port, shape, result_path):
     import torch.distributed as dist
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
@@ -21,21 +32,52 @@ def _worker(rank, world, port, shape, result_path):
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
     try:
         import sentinel_b200 as sb
+        from oracle import cpu
         from sentinel_b200.ring import GpuBackend, RingAttention
         B, Hq, Hkv, S, D = shape
         g = torch.Generator().manual_seed(99)
         q = (torch.randn(B, Hq, S, D, generator=g) * 0.5).bfloat16()
         k = (torch.randn(B, Hkv, S, D, generator=g) * 0.5).bfloat16()
-        v = torch.randn(B, Hkv, S, D, generator=g).bfloat16()
+        v = (torch.randn(B, Hkv, S, D, generator=g) * 0.5).bfloat16()
         do = (torch.randn(B, Hq, S, D, generator=g) * 1e-2).bfloat16()
-        sl = slice(rank * S // world, (rank + 1) * S // world)
-        sh = [t[:, :, sl].contiguous().cuda() for t in (q, k, v, do)]
+        # dO that is zero outside 192 query rows spread over the sequence (for the early-key-column check)
+        keep = torch.zeros(S, dtype=torch.bool)
+        keep[torch.linspace(0, S - 1, 192).long()] = True
+        do_sparse = torch.where(keep[None, None, :, None], do, torch.zeros_like(do))
+        S_loc = S // world
+        sl = slice(rank * S_loc, (rank + 1) * S_loc)
+        sh = [t[:, :, sl].contiguous().cuda() for t in (q, k, v, do, do_sparse)]
         ring = RingAttention(GpuBackend())
-        o, lse = ring.forward(sh[0], sh[1], sh[2])
-        dq, dk, dv = ring.backward(sh[0], sh[1], sh[2], o, lse, sh[3])
+        o, lse = ring.forward(sh[0], sh[1], sh[2], keep_state=True)
+        dq, dk, dv = ring.backward(sh[0], sh[1], sh[2], o, lse, sh[3], use_saved_state=True)
+        dq2, dk2, dv2 = ring.backward(sh[0], sh[1], sh[2], o, lse, sh[4])        # deals everything again: the other path
         torch.cuda.synchronize()
         assert sb.poll_device_status() == 0
-        # whole-sequence attention on this rank's GPU as the comparison
+        qf, kf, vf, dof, dosf = (t.float().numpy() for t in (q, k, v, do, do_sparse))
+        grp = Hq // Hkv
+        out = {}
+        # ---- fp64 oracle, sampled rows of this rank's shard (two heads) ----
+        rows = np.array(sorted({0, 1, S_loc // 2 - 1, S_loc // 2, S_loc - 130, S_loc - 1}), np.int32) + rank * S_loc
+        for h in (0, Hq - 1):
+            wo, wl, wdq = cpu.attn_rows(qf, kf, vf, dof, 0, h, rows)
+            loc = rows - rank * S_loc
+            out[f"o_h{h}"] = _errs(o[0, h, loc].float().cpu().numpy(), wo)
+            out[f"dq_h{h}"] = _errs(dq[0, h, loc].float().cpu().numpy(), wdq)
+            out[f"lse_h{h}"] = (float(np.abs(lse[0, h, loc].cpu().numpy() - wl).max()), 0.0)
+        # ---- fp64 oracle, key columns of this rank's shard: any key, through the sparse dO ----
+        cols = np.array(sorted({0, 5, S_loc // 2 - 1, S_loc // 2 + 3, S_loc - 1}), np.int32) + rank * S_loc
+        hk = Hkv - 1
+        wdk, wdv = cpu.attn_cols(qf, kf, vf, dosf, 0, hk, cols)
+        locc = cols - rank * S_loc
+        out["dk_sparse"] = _errs(dk2[0, hk, locc].float().cpu().numpy(), wdk)
+        out["dv_sparse"] = _errs(dv2[0, hk, locc].float().cpu().numpy(), wdv)
+        if rank == world - 1:     # the latest keys with the dense dO: few queries see them
+            late = np.array([S - 200, S - 129, S - 1], np.int32)
+            wdk, wdv = cpu.attn_cols(qf, kf, vf, dof, 0, 0, late)
+            ll = late - rank * S_loc
+            out["dk_late"] = _errs(dk[0, 0, ll].float().cpu().numpy(), wdk)
+            out["dv_late"] = _errs(dv[0, 0, ll].float().cpu().numpy(), wdv)
+        # ---- second assert: single-GPU attention over the whole sequence on this rank's GPU ----
         qa, ka, va, doa = (t.cuda() for t in (q, k, v, do))
         wo, wl = sb.attention_forward(qa, ka, va)
         wdq, wdk, wdv = sb.attention_backward(qa, ka, va, wo, wl, doa)
@@ -44,17 +86,17 @@ def _worker(rank, world, port, shape, result_path):
             a, b = a.float(), b.float()
             return float((a - b).norm() / b.norm().clamp_min(1e-30))
 
-        errs = {"o": rel(o, wo[:, :, sl]), "dq": rel(dq, wdq[:, :, sl]), "dk": rel(dk, wdk[:, :, sl]), "dv": rel(dv, wdv[:, :, sl]),
-                "lse": float((lse - wl[:, :, sl]).abs().max())}
+        out["self"] = {"o": rel(o, wo[:, :, sl]), "dq": rel(dq, wdq[:, :, sl]), "dk": rel(dk, wdk[:, :, sl]),
+                       "dv": rel(dv, wdv[:, :, sl]), "lse": float((lse - wl[:, :, sl]).abs().max())}
         gathered = [None] * world
-        dist.all_gather_object(gathered, errs)
+        dist.all_gather_object(gathered, out)
         if rank == 0:
             torch.save(gathered, result_path)
     finally:
         dist.destroy_process_group()
 
 
-def test_ring_on_gpus_matches_single_gpu_attention(tmp_path):
+def test_ring_on_gpus_matches_the_full_sequence_oracle(tmp_path):
     world = min(torch.cuda.device_count(), 4)
     if world < 2:
         pytest.skip("needs at least 2 GPUs")
@@ -63,7 +105,13 @@ def test_ring_on_gpus_matches_single_gpu_attention(tmp_path):
         s.bind(("127.0.0.1", 0))
         port = s.getsockname()[1]
     path = str(tmp_path / "errs.pt")
-    mp.spawn(_worker, args=(world, port, (1, 8, 2, 1024 * world, 128), path), nprocs=world, join=True)
+    mp.spawn(_worker, args=(world, port, (1, 8, 2, 4096 * world, 128), path), nprocs=world, join=True)
     for errs in torch.load(path):
-        # both sides are bf16 tensor-core results; the ring adds one more bf16 rounding per partial
-        assert errs["o"] < 5e-3 and errs["dq"] < 8e-3 and errs["dk"] < 8e-3 and errs["dv"] < 8e-3 and errs["lse"] < 1e-3, errs
+        for name, val in errs.items():
+            if name == "self":
+                continue
+            max_abs, rel_l2 = val
+            assert max_abs <= 2e-2 and rel_l2 <= 5e-3, (name, val)      # the bf16 bounds, against the fp64 oracle
+        s = errs["self"]
+        # both sides are bf16 tensor-core results; bf16 rounding of two different summation orders
+        assert s["o"] < 5e-3 and s["dq"] < 5e-3 and s["dk"] < 5e-3 and s["dv"] < 5e-3 and s["lse"] < 1e-3, s

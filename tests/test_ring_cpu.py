@@ -30,9 +30,8 @@ class OracleBackend:
         o, lse = self.cpu.attn_fwd(q.numpy(), k.numpy(), v.numpy(), causal=causal)
         return torch.from_numpy(o), torch.from_numpy(lse)
 
-    def bwd(self, q, k, v, o, lse, do, causal):
+    def _bwd(self, q, k, v, o, lse, do, causal):
         # global probabilities from the FINAL lse, exactly what the kernels do: P = exp(scale*qk - lse)
-        self.calls.append(("bwd", causal))
         qn, kn, vn, don = (t.double() for t in (q, k, v, do))
         B, Hq, Sq, D = qn.shape
         g = Hq // kn.shape[1]
@@ -48,6 +47,20 @@ class OracleBackend:
         dk = torch.einsum("bhqk,bhqd->bhkd", ds, qn).reshape(B, kn.shape[1], g, -1, D).sum(2)
         dv = torch.einsum("bhqk,bhqd->bhkd", p, don).reshape(B, kn.shape[1], g, -1, D).sum(2)
         return dq.float(), dk.float(), dv.float()
+
+    # the backward in pieces, as the C ABI offers it (sntl_attn_bwd_begin / _block / _end)
+    def bwd_begin(self, q, o, lse, do):
+        return {"q": q, "o": o, "lse": lse, "do": do, "dq": torch.zeros_like(q, dtype=torch.float32)}
+
+    def bwd_block(self, h, k, v, dk_acc, dv_acc, causal):
+        self.calls.append(("bwd", causal))
+        dq, dk, dv = self._bwd(h["q"], k, v, h["o"], h["lse"], h["do"], causal)
+        h["dq"] += dq
+        dk_acc += dk
+        dv_acc += dv
+
+    def bwd_end(self, h):
+        return h["dq"]
 
     def merge(self, o_acc, lse_acc, o_part, lse_part):
         m = torch.maximum(lse_acc, lse_part)
@@ -92,6 +105,12 @@ def _ring_worker(rank, world, port, shape, out_dir):
         # balance: every rank runs the same number of block pairs: 2 per step, 3 at step 0 (two of them diagonal halves)
         assert n_fwd == 2 * world + 1, n_fwd
         assert len(be.calls) - n_fwd == 2 * world + 1
+        # the same backward from the state the forward kept (no second deal of Q, K, V, O, LSE): identical results
+        qs, ks, vs, dos = (t[:, :, sl].contiguous() for t in (q, k, v, do))
+        o2, lse2 = ring.forward(qs, ks, vs, keep_state=True)
+        dq2, dk2, dv2 = ring.backward(qs, ks, vs, o2, lse2, dos, use_saved_state=True)
+        for a, b_, n in ((o2, o, 'o'), (dq2, dq, 'dq'), (dk2, dk, 'dk'), (dv2, dv, 'dv')):
+            assert float((a - b_).abs().max()) <= 1e-6 * float(b_.abs().max()), (n, float((a - b_).abs().max()))
         np.savez(os.path.join(out_dir, f"rank{rank}.npz"), o=o.numpy(), lse=lse.numpy(), dq=dq.numpy(), dk=dk.numpy(), dv=dv.numpy())
         # zigzag deal and its inverse are exact permutations
         x = torch.arange(B * Hq * (S // world) * D, dtype=torch.float32).reshape(B, Hq, S // world, D) + 1e6 * rank
@@ -115,6 +134,64 @@ def test_ring_schedule_matches_full_sequence_oracle(tmp_path, world, shape, orac
     got = {key: np.concatenate([np.load(tmp_path / f"rank{r}.npz")[key] for r in range(world)], axis=2) for key in ("o", "lse", "dq", "dk", "dv")}
     for key, want in (("o", wo), ("lse", wl), ("dq", wdq), ("dk", wdk), ("dv", wdv)):
         assert np.abs(got[key] - want).max() < 2e-5, key
+
+
+def _failure_worker(rank, world, port, mode, out_dir):
+    """Host-made failures only: a rank that never joins the step, a slow rank, a rank that rotates the wrong way."""
+    import time
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from sentinel_b200.ring import RingAttention, RingTimeout
+    B, Hq, Hkv, S, D = 1, 2, 1, 16 * world, 8
+    g = torch.Generator().manual_seed(5)
+    q = torch.randn(B, Hq, S, D, generator=g)
+    k = torch.randn(B, Hkv, S, D, generator=g)
+    v = torch.randn(B, Hkv, S, D, generator=g)
+    sl = slice(rank * S // world, (rank + 1) * S // world)
+    args = [t[:, :, sl].contiguous() for t in (q, k, v)]
+    outcome = "none"
+    t0 = time.monotonic()
+    try:
+        if mode == "leaves" and rank == world - 1:
+            outcome = "left"                    # leaves between steps: nothing of its own is in flight
+        else:
+            ring = RingAttention(OracleBackend(), timeout_s=10.0 if mode == "slow" else 2.0)
+            if mode == "slow" and rank == world - 1:
+                time.sleep(1.0)
+            if mode == "wrong_way" and rank == world - 1:
+                def wrong(tensors, buffers, self=ring):
+                    nxt, prv = (self.rank + 1) % self.world, (self.rank - 1) % self.world
+                    ops = [dist.P2POp(dist.isend, t, prv, self.group) for t in tensors]
+                    ops += [dist.P2POp(dist.irecv, b, nxt, self.group) for b in buffers]
+                    return dist.batch_isend_irecv(ops)
+                ring._rotate_start = wrong
+            ring.forward(*args)
+            outcome = "completed"
+    except RingTimeout:
+        outcome = "timeout"
+    except RuntimeError:                        # gloo reports a vanished peer as a connection error
+        outcome = "error"
+    with open(os.path.join(out_dir, f"outcome{rank}.txt"), "w") as f:
+        f.write(f"{outcome} {time.monotonic() - t0:.2f}")
+    os._exit(0)                                 # no collective teardown with a peer that may be gone
+
+
+@pytest.mark.parametrize("mode,world", [("leaves", 2), ("slow", 2), ("wrong_way", 3)])
+def test_ring_raises_within_a_deadline_when_a_peer_fails(tmp_path, mode, world):
+    ctx = mp.get_context("spawn")
+    port = _free_port()
+    procs = [ctx.Process(target=_failure_worker, args=(r, world, port, mode, str(tmp_path))) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(60)
+        assert not p.is_alive(), "a rank waited for ever"
+    got = [open(tmp_path / f"outcome{r}.txt").read().split() for r in range(world)]
+    if mode == "slow":
+        assert all(o == "completed" for o, _ in got), got          # a rank that is late but alive is waited for
+    else:
+        assert got[0][0] in ("timeout", "error"), got               # the healthy rank raised instead of hanging
+        assert float(got[0][1]) < 30.0
 
 
 def test_visible_pairs_cover_the_causal_mask_exactly_once():
