@@ -66,7 +66,18 @@ enum {
      * (CudaFlashAttention.cu:209-214), so this is the analogous trade. */
     SNTL_FLAG_ALLOW_BF16_COMPUTE = 1,
     /* never use the tensor-core kernels (diagnostics / cross-checks) */
-    SNTL_FLAG_FORCE_SIMT = 2
+    SNTL_FLAG_FORCE_SIMT = 2,
+    /* Backward: make dQ bit-reproducible from run to run.  The tensor-core kernel sums the dQ contributions of the
+     * key tiles in global memory in their order of arrival; fp32 addition is not associative, so without this flag
+     * the last bits of dQ vary between runs (dK, dV and the forward are always reproducible: each of their elements
+     * has one owner).  With it every contribution is converted exactly to 64-bit fixed point (2^-32 units) and
+     * summed as integers, which no order can change; the sum is rounded once at the end, so it is also slightly
+     * more accurate.  Cost: the dQ accumulator in the workspace and its reduction traffic double
+     * (sntl_attn_bwd_workspace_bytes accounts for it).  |dQ / scale| must stay below 2^31.  The reference's
+     * head_dim-64 backward has an exclusive dQ store (sentinel/NeuralNet/Cuda/CudaFlashAttention.cu:1434-1455);
+     * a caller that relies on bit-stable input gradients sets this flag.  Ignored by the exact kernels, whose
+     * dQ is reproducible already. */
+    SNTL_FLAG_DETERMINISTIC = 4
 };
 
 typedef struct sntl_attn_desc {

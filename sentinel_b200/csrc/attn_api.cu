@@ -48,7 +48,7 @@ AttnShape shape_of(const sntl_attn_desc* d)
     // a window that already covers the sequence is plain causal attention
     const int window = (d->window_size > 0 && d->window_size < d->seq_kv) ? d->window_size : 0;
     return AttnShape{d->batch, d->q_heads, d->kv_heads, d->seq_q, d->seq_kv, d->head_dim, d->scale, d->causal ? 1 : 0,
-                     window, window > 0 ? d->global_tokens : 0};
+                     window, window > 0 ? d->global_tokens : 0, (d->flags & SNTL_FLAG_DETERMINISTIC) ? 1 : 0};
 }
 
 // tensor-core path is taken for bf16 tensors, or fp32 tensors when the caller allows bf16 operands
@@ -380,7 +380,7 @@ int validate_pieces(const sntl_attn_desc* d)
     if (rc != SNTL_OK) return rc;
     if (d->dtype != SNTL_DTYPE_BF16 || d->layout != SNTL_LAYOUT_BHSD) return SNTL_ERR_UNSUPPORTED;
     if (d->window_size > 0 || d->global_tokens > 0) return SNTL_ERR_UNSUPPORTED;
-    if (d->flags & SNTL_FLAG_FORCE_SIMT) return SNTL_ERR_UNSUPPORTED;
+    if (d->flags & (SNTL_FLAG_FORCE_SIMT | SNTL_FLAG_DETERMINISTIC)) return SNTL_ERR_UNSUPPORTED;
     if (!tc_bwd_supported(shape_of(d))) return SNTL_ERR_UNSUPPORTED;
     return SNTL_OK;
 }

@@ -84,7 +84,7 @@ __host__ __device__ inline int bwd_tiles_per_head(int kt, int n_qt, int causal, 
 inline int bwd_split_tiles(const AttnShape& s)
 {
     const int group = s.Hq / s.Hkv;
-    if (group <= 1) return 0;
+    if (group <= 1 || s.deterministic) return 0;   // (the order-independent dQ form is not instantiated with cut tiles)
     const int n_qt = (s.Sq + kT - 1) / kT, n_kt = (s.Skv + kT - 1) / kT;
     const int window = s.causal ? s.window : 0;
     double total = 0.0;
@@ -105,7 +105,8 @@ struct BwdBarriers {
 
 // kSplit: the grid may hold key tiles cut by query head (a separate instantiation, so that the plain kernel carries none
 // of that bookkeeping)
-template <int D, bool kWin, bool kSplit>
+// kDet: dQ contributions leave as 64-bit fixed point (see the drain warpgroup)
+template <int D, bool kWin, bool kSplit, bool kDet>
 __global__ void __launch_bounds__(kBwdThreads, 1)
 attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                    const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_do, const BwdParams p)
@@ -400,7 +401,8 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
         for (int i = 0; i < n_iter; ++i) {
             const int g = i / per_head, qt = qt_first + (i - g * per_head);
             const int bh = b * p.Hq + hk * group + g0 + g;
-            float* tile = p.dq_accum + ((size_t)bh * p.n_qt + qt) * (size_t)(kT * D);
+            // fp32 accumulator: kT*D words per tile; fixed-point accumulator: kT*D 64-bit words per tile
+            float* tile = p.dq_accum + ((size_t)bh * p.n_qt + qt) * (size_t)(kT * D) * (kDet ? 2 : 1);
             ok = __all_sync(0xffffffffu, mbar_wait(&bars->dq_ready, (uint32_t)(i & 1), abort_flag, kSiteDQ));
             SNTL_TRACE_EV(tw, 3, tn, 1);
             if (!ok) break;
@@ -420,20 +422,48 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
             tc_fence_before();
             mbar_arrive(&bars->dq_drained);
             SNTL_TRACE_EV(tw, 3, tn, 2);
+            if constexpr (!kDet) {
 #pragma unroll
-            for (int c = 0; c < D / kStageCols; ++c) {
-                uint8_t* stage = sStage + (c % kStages) * kStageBytes;
-                if (elected) bulk_wait_read<kStages - 1>();
-                named_barrier_sync(1, 128);
+                for (int c = 0; c < D / kStageCols; ++c) {
+                    uint8_t* stage = sStage + (c % kStages) * kStageBytes;
+                    if (elected) bulk_wait_read<kStages - 1>();
+                    named_barrier_sync(1, 128);
 #pragma unroll
-                for (int v = 0; v < kStageCols / 4; ++v)
-                    *reinterpret_cast<uint4*>(stage + ((size_t)v * kT + row) * 16) =
-                        make_uint4(r[c * kStageCols + 4 * v], r[c * kStageCols + 4 * v + 1], r[c * kStageCols + 4 * v + 2], r[c * kStageCols + 4 * v + 3]);
-                fence_proxy_async_smem();
-                named_barrier_sync(1, 128);
-                if (elected) {
-                    bulk_reduce_add_f32(tile + (size_t)c * kStageCols * kT, stage, (uint32_t)kStageBytes);
-                    bulk_commit();
+                    for (int v = 0; v < kStageCols / 4; ++v)
+                        *reinterpret_cast<uint4*>(stage + ((size_t)v * kT + row) * 16) =
+                            make_uint4(r[c * kStageCols + 4 * v], r[c * kStageCols + 4 * v + 1], r[c * kStageCols + 4 * v + 2], r[c * kStageCols + 4 * v + 3]);
+                    fence_proxy_async_smem();
+                    named_barrier_sync(1, 128);
+                    if (elected) {
+                        bulk_reduce_add_f32(tile + (size_t)c * kStageCols * kT, stage, (uint32_t)kStageBytes);
+                        bulk_commit();
+                    }
+                }
+            } else {
+                // Order-independent form: each fp32 value times 2^32 is an integer that fits 64 bits exactly (24-bit
+                // mantissa, |value| < 2^31), and integer addition is associative, so the accumulated sum is the same
+                // whatever order the key tiles arrive in.  Same staging buffers, half as many columns per piece; the
+                // accumulator tile is [d/2][row][2] 64-bit words, so a piece is still one contiguous block.
+                constexpr int kDetCols = kStageCols / 2;
+                unsigned long long* tile64 = reinterpret_cast<unsigned long long*>(tile);
+#pragma unroll
+                for (int c = 0; c < D / kDetCols; ++c) {
+                    uint8_t* stage = sStage + (c % kStages) * kStageBytes;
+                    if (elected) bulk_wait_read<kStages - 1>();
+                    named_barrier_sync(1, 128);
+#pragma unroll
+                    for (int v = 0; v < kDetCols / 2; ++v) {
+                        const long long a = __float2ll_rn(__uint_as_float(r[c * kDetCols + 2 * v]) * 4294967296.0f);
+                        const long long b2 = __float2ll_rn(__uint_as_float(r[c * kDetCols + 2 * v + 1]) * 4294967296.0f);
+                        *reinterpret_cast<ulonglong2*>(stage + ((size_t)v * kT + row) * 16) =
+                            make_ulonglong2((unsigned long long)a, (unsigned long long)b2);
+                    }
+                    fence_proxy_async_smem();
+                    named_barrier_sync(1, 128);
+                    if (elected) {
+                        bulk_reduce_add_u64(tile64 + (size_t)c * kDetCols * kT, stage, (uint32_t)kStageBytes);
+                        bulk_commit();
+                    }
                 }
             }
             SNTL_TRACE_EV(tw, 3, tn, 3);
@@ -638,7 +668,7 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
 template <int D>
 __global__ void bwd_pre_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ dout,
                                const float* __restrict__ lse, float* __restrict__ lse2, float* __restrict__ delta,
-                               float* __restrict__ dq_accum, int Sq, int Sq_pad, long long rows_padded)
+                               float* __restrict__ dq_accum, int Sq, int Sq_pad, long long rows_padded, int acc_words_per_row)
 {
     const int lane = threadIdx.x & 31;
     const long long r = blockIdx.x * (long long)(blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -646,8 +676,9 @@ __global__ void bwd_pre_kernel(const __nv_bfloat16* __restrict__ o, const __nv_b
     const long long bh = r / Sq_pad;
     const int s = (int)(r - bh * Sq_pad);
     // the accumulator is tile-permuted but covers exactly D floats per padded row: zero it linearly
-    float4* z = reinterpret_cast<float4*>(dq_accum + r * D);
-    for (int i = lane; i < D / 4; i += 32) z[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+    // (D 32-bit words per row, or 2*D when the accumulator is 64-bit fixed point)
+    float4* z = reinterpret_cast<float4*>(dq_accum + r * acc_words_per_row);
+    for (int i = lane; i < acc_words_per_row / 4; i += 32) z[i] = make_float4(0.f, 0.f, 0.f, 0.f);
     if (s >= Sq) {
         if (lane == 0) { lse2[r] = -INFINITY; delta[r] = 0.0f; }
         return;
@@ -704,6 +735,40 @@ __global__ void __launch_bounds__(256) bwd_post_kernel(const float* __restrict__
     }
 }
 
+// The same for the 64-bit fixed-point accumulator (tiles of [d/2][row][2] words in units of 2^-32): the one rounding
+// of the exact integer sum happens here.
+template <int D>
+__global__ void __launch_bounds__(256) bwd_post_det_kernel(const unsigned long long* __restrict__ dq_accum, __nv_bfloat16* __restrict__ dq,
+                                                           int Sq, int n_qt, float scale)
+{
+    constexpr int kRows = 32;
+    __shared__ float tile[kRows][D + 4];
+    const size_t t = blockIdx.x >> 2;
+    const int r0 = (int)(blockIdx.x & 3) * kRows;
+    const size_t bh = t / n_qt;
+    const int qt = (int)(t - bh * n_qt);
+    const ulonglong2* src = reinterpret_cast<const ulonglong2*>(dq_accum + t * (size_t)(kT * D));
+    for (int e = threadIdx.x; e < kRows * D / 2; e += blockDim.x) {
+        const int chunk = e / kRows, row = e - chunk * kRows;   // consecutive threads -> consecutive 16-byte units
+        const ulonglong2 v = src[(size_t)chunk * kT + r0 + row];
+        tile[row][chunk * 2] = (float)((double)(long long)v.x * (1.0 / 4294967296.0));
+        tile[row][chunk * 2 + 1] = (float)((double)(long long)v.y * (1.0 / 4294967296.0));
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < kRows * D / 8; e += blockDim.x) {
+        const int row = e / (D / 8), d8 = (e - row * (D / 8)) * 8;
+        const int s = qt * kT + r0 + row;
+        if (s >= Sq) continue;
+        const float* x = &tile[row][d8];
+        uint4 w;
+        w.x = pack_bf16(x[0] * scale, x[1] * scale);
+        w.y = pack_bf16(x[2] * scale, x[3] * scale);
+        w.z = pack_bf16(x[4] * scale, x[5] * scale);
+        w.w = pack_bf16(x[6] * scale, x[7] * scale);
+        *reinterpret_cast<uint4*>(dq + (bh * Sq + s) * D + d8) = w;
+    }
+}
+
 inline size_t align256(size_t x) { return (x + 255) / 256 * 256; }
 
 // dV / dK of the key tiles that were cut by query head: the partials of a tile are added in head order and written as
@@ -741,7 +806,7 @@ __global__ void __launch_bounds__(256) bwd_dkv_reduce_kernel(const float* __rest
     *reinterpret_cast<uint4*>((which ? dk : dv) + ((size_t)slab * Skv + key) * D + d8) = w;
 }
 
-template <int D, bool kWin, bool kSplit>
+template <int D, bool kWin, bool kSplit, bool kDet>
 cudaError_t launch_bwd(const TcArgs& a, cudaStream_t st)
 {
     const AttnShape& s = a.s;
@@ -755,7 +820,7 @@ cudaError_t launch_bwd(const TcArgs& a, cudaStream_t st)
         const int warps = 8;
         const long long blocks = (rows_padded + warps - 1) / warps;
         bwd_pre_kernel<D><<<(unsigned)blocks, warps * 32, 0, st>>>(a.o, a.dout, a.lse, lse2, a.delta, a.dq_accum, s.Sq, Sq_pad,
-                                                                    rows_padded);
+                                                                    rows_padded, kDet ? 2 * D : D);
         count_launch();
         if ((e = cudaGetLastError()) != cudaSuccess) return e;
     }
@@ -774,18 +839,18 @@ cudaError_t launch_bwd(const TcArgs& a, cudaStream_t st)
     p.global_tokens = s.global_tokens;
     p.n_qt = n_qt; p.n_kt = n_kt;
     p.split_tiles = kSplit ? bwd_split_tiles(s) : 0;
-    p.dkv_part = reinterpret_cast<float*>(reinterpret_cast<char*>(a.dq_accum) + align256(4 * (size_t)rows_padded * D));
+    p.dkv_part = reinterpret_cast<float*>(reinterpret_cast<char*>(a.dq_accum) + align256((kDet ? 8 : 4) * (size_t)rows_padded * D));
     p.dk_acc = a.dk_acc; p.dv_acc = a.dv_acc;
     p.scale = s.scale;
     p.scale_log2 = s.scale * 1.4426950408889634f;
     constexpr int kDoStages = (D == 128) ? 1 : 2;
     const size_t smem = (size_t)(128 * D * 2) * (4 + kDoStages) + 128 * 128 * 2 + 2 * (32 * 128 * 4) + 4 * 128 * 4 + sizeof(BwdBarriers);
     static std::atomic<unsigned long long> configured{0};   // per instantiation, one bit per device
-    if ((e = ensure_dynamic_smem(attn_bwd_tc_kernel<D, kWin, kSplit>, smem, configured)) != cudaSuccess) return e;
+    if ((e = ensure_dynamic_smem(attn_bwd_tc_kernel<D, kWin, kSplit, kDet>, smem, configured)) != cudaSuccess) return e;
     const int group = s.Hq / s.Hkv, slabs = s.B * s.Hkv;
     const long long ctas = (long long)p.split_tiles * group * slabs + (long long)(n_kt - p.split_tiles) * slabs;
     if (ctas > 0x7fffffffLL) return cudaErrorInvalidConfiguration;
-    attn_bwd_tc_kernel<D, kWin, kSplit><<<(unsigned)ctas, kBwdThreads, smem, st>>>(tq, tk, tv, tdo, p);
+    attn_bwd_tc_kernel<D, kWin, kSplit, kDet><<<(unsigned)ctas, kBwdThreads, smem, st>>>(tq, tk, tv, tdo, p);
     count_launch();
     if ((e = cudaGetLastError()) != cudaSuccess) return e;
     if (p.split_tiles > 0) {
@@ -797,7 +862,11 @@ cudaError_t launch_bwd(const TcArgs& a, cudaStream_t st)
     }
     }   // kBwdMain
     if (!(phases & kBwdPost)) return cudaSuccess;
-    bwd_post_kernel<D><<<(unsigned)((long long)s.B * s.Hq * n_qt * 4), 256, 0, st>>>(a.dq_accum, a.dq, s.Sq, n_qt, s.scale);
+    if (kDet)
+        bwd_post_det_kernel<D><<<(unsigned)((long long)s.B * s.Hq * n_qt * 4), 256, 0, st>>>(
+            reinterpret_cast<const unsigned long long*>(a.dq_accum), a.dq, s.Sq, n_qt, s.scale);
+    else
+        bwd_post_kernel<D><<<(unsigned)((long long)s.B * s.Hq * n_qt * 4), 256, 0, st>>>(a.dq_accum, a.dq, s.Sq, n_qt, s.scale);
     count_launch();
     return cudaGetLastError();
 }
@@ -816,19 +885,23 @@ size_t tc_backward_workspace_bytes(const AttnShape& s)
     const size_t sq_pad = ((size_t)s.Sq + kT - 1) / kT * kT;
     const size_t rows = (size_t)s.B * s.Hq * sq_pad;
     const size_t part = (size_t)bwd_split_tiles(s) * s.B * s.Hq * 2 * kT * (size_t)s.D * 4;   // slabs * group = B * Hq
-    return align256(2 * 4 * rows) + align256(4 * rows * (size_t)s.D) + align256(part);
+    return align256(2 * 4 * rows) + align256((s.deterministic ? 8 : 4) * rows * (size_t)s.D) + align256(part);
 }
 
 cudaError_t tc_backward(const TcArgs& a, cudaStream_t st)
 {
     const bool win = a.s.causal && a.s.window > 0;
+    if (a.s.deterministic) {   // (bwd_split_tiles is 0 for this form)
+        if (a.s.D == 64) return win ? launch_bwd<64, true, false, true>(a, st) : launch_bwd<64, false, false, true>(a, st);
+        return win ? launch_bwd<128, true, false, true>(a, st) : launch_bwd<128, false, false, true>(a, st);
+    }
     // the accumulate form has no cut key tiles: their fp32 partials would need a second adding pass
     if (a.dk_acc == nullptr && bwd_split_tiles(a.s) > 0) {
-        if (a.s.D == 64) return win ? launch_bwd<64, true, true>(a, st) : launch_bwd<64, false, true>(a, st);
-        return win ? launch_bwd<128, true, true>(a, st) : launch_bwd<128, false, true>(a, st);
+        if (a.s.D == 64) return win ? launch_bwd<64, true, true, false>(a, st) : launch_bwd<64, false, true, false>(a, st);
+        return win ? launch_bwd<128, true, true, false>(a, st) : launch_bwd<128, false, true, false>(a, st);
     }
-    if (a.s.D == 64) return win ? launch_bwd<64, true, false>(a, st) : launch_bwd<64, false, false>(a, st);
-    return win ? launch_bwd<128, true, false>(a, st) : launch_bwd<128, false, false>(a, st);
+    if (a.s.D == 64) return win ? launch_bwd<64, true, false, false>(a, st) : launch_bwd<64, false, false, false>(a, st);
+    return win ? launch_bwd<128, true, false, false>(a, st) : launch_bwd<128, false, false, false>(a, st);
 }
 
 #ifdef SNTL_TRACE

@@ -26,6 +26,7 @@ struct AttnShape {
     int causal;
     int window;         // sliding window (keys a query sees counting itself); <= 0: unlimited.  Needs causal.
     int global_tokens;  // the first global_tokens keys stay visible to every later query
+    int deterministic;  // backward: dQ summed in 64-bit fixed point, so the result does not depend on the order of arrival
 };
 
 // The window part of the reference's CausalSelfAttention::allowsKey (CausalSelfAttention.cpp:95-100); the causal part

@@ -148,6 +148,13 @@ __device__ __forceinline__ void bulk_reduce_add_f32(float* gmem_dst, const void*
                  "r"(bytes)
                  : "memory");
 }
+// the same with 64-bit integer adds (two's complement: serves signed fixed-point sums)
+__device__ __forceinline__ void bulk_reduce_add_u64(unsigned long long* gmem_dst, const void* smem_src, uint32_t bytes)
+{
+    asm volatile("cp.reduce.async.bulk.global.shared::cta.bulk_group.add.u64 [%0], [%1], %2;" ::"l"(gmem_dst), "r"(smem_u32(smem_src)),
+                 "r"(bytes)
+                 : "memory");
+}
 __device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 // returns once at most N of this thread's bulk groups are still reading their shared-memory source
 template <int N> __device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory"); }

@@ -117,3 +117,40 @@ def test_bounded_wait_runs_out_reports_and_leaves_the_context_usable(sb):
     assert torch.equal(o1, o2) and torch.equal(lse1, lse2)
     assert lib.sntl_attn_selftest_wait_timeout(0, stream) == _lib.ERR_BAD_ARGUMENT
     assert lib.sntl_attn_selftest_wait_timeout(200000, stream) == _lib.ERR_BAD_ARGUMENT
+
+
+def test_deterministic_flag_makes_dq_bit_reproducible(sb):
+    """SNTL_FLAG_DETERMINISTIC: dQ is summed in 64-bit fixed point, so it is bit-identical from run to run, between the
+    one-stream and two-stream variants and through the chunked host-buffer pipeline -- and it meets the same oracle
+    bounds as the default path (it is the exact sum of the same fp32 contributions, rounded once)."""
+    import numpy as np
+    from oracle import cpu
+    from sentinel_b200 import _lib
+    from sentinel_b200.host_pipeline import forward_backward_host
+    det = _lib.FLAG_DETERMINISTIC
+    for name, kw in (("gqa7b_d128", dict(batch=2, q_heads=8, kv_heads=2, seq=1152)), ("llama1b_gqa", dict(batch=1, q_heads=8, kv_heads=4, seq=777))):
+        w = sb.WORKLOADS[name]
+        q, k, v, do = (t.pin_memory() for t in sb.make_inputs(w, **kw))
+        qd, kd, vd, dod = (t.cuda() for t in (q, k, v, do))
+        o, lse = sb.attention_forward(qd, kd, vd)
+        dq1, dk1, dv1 = sb.attention_backward(qd, kd, vd, o, lse, dod, flags=det)
+        runs = [sb.attention_backward(qd, kd, vd, o, lse, dod, flags=det) for _ in range(4)]
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            runs.append(sb.attention_backward(qd, kd, vd, o, lse, dod, flags=det))
+        runs.append(sb.attention_backward(qd, kd, vd, o, lse, dod, flags=det))     # overlaps the side stream's call
+        torch.cuda.synchronize()
+        for dq, dk, dv in runs:
+            assert torch.equal(dq, dq1) and torch.equal(dk, dk1) and torch.equal(dv, dv1)
+        for chunks in (None, 1, 2):
+            _, _, hdq, hdk, hdv = forward_backward_host(q, k, v, do, chunks=chunks, flags=det)
+            assert torch.equal(hdq, dq1.cpu()) and torch.equal(hdk, dk1.cpu()) and torch.equal(hdv, dv1.cpu())
+        # the default path differs from it only in the last bits, and both sit inside the oracle bounds
+        dq0, _, _ = sb.attention_backward(qd, kd, vd, o, lse, dod)
+        assert float((dq0.float() - dq1.float()).abs().max()) <= 1e-2 * float(dq1.float().abs().max())
+        wdq, wdk, wdv, _ = cpu.attn_bwd(*(t.float().numpy() for t in (q, k, v, do)))
+        got = dq1.float().cpu().numpy()
+        assert float(np.abs(got - wdq).max()) <= 2e-2
+        assert float(np.linalg.norm(got - wdq) / np.linalg.norm(wdq)) <= 5e-3
+    assert sb.poll_device_status() == 0

@@ -267,6 +267,11 @@ def test_forward_is_deterministic_and_recompute_stable(sb):
     _, dk1, dv1 = sb.attention_backward(q, k, v, o1, l1, do)
     _, dk2, dv2 = sb.attention_backward(q, k, v, o1, l1, do)
     assert torch.equal(dk1, dk2) and torch.equal(dv1, dv2)
+    # dQ is a sum over key tiles in arrival order unless SNTL_FLAG_DETERMINISTIC asks for the order-independent sum
+    from sentinel_b200 import _lib
+    dq1, dk3, dv3 = sb.attention_backward(q, k, v, o1, l1, do, flags=_lib.FLAG_DETERMINISTIC)
+    dq2, _, _ = sb.attention_backward(q, k, v, o1, l1, do, flags=_lib.FLAG_DETERMINISTIC)
+    assert torch.equal(dq1, dq2) and torch.equal(dk3, dk1) and torch.equal(dv3, dv1)
 
 
 def test_backward_long_key_tiles_cut_by_query_head(sb, oracle):
