@@ -46,7 +46,8 @@ enum {
     SNTL_ERR_CUDA = 4,           /* a CUDA runtime/driver call or a launch failed */
     SNTL_ERR_NO_DEVICE = 5,      /* current device is not compute capability 10.x */
     SNTL_ERR_DEVICE_TIMEOUT = 6, /* a bounded device-side wait ran out (reported by sntl_attn_poll_device_status) */
-    SNTL_ERR_SCRATCH_LIMIT = 7   /* sntl_attn_bwd_static_scratch: the problem needs more than the built-in scratch */
+    SNTL_ERR_SCRATCH_LIMIT = 7,  /* sntl_attn_bwd_static_scratch: the problem needs more than the built-in scratch */
+    SNTL_ERR_COMM = 8            /* sntl_ring_*: NCCL is not available, or an NCCL call failed */
 };
 
 enum { SNTL_DTYPE_BF16 = 0, SNTL_DTYPE_F32 = 1 };
@@ -214,6 +215,36 @@ int sntl_attn_merge(int32_t acc_dtype, int32_t part_dtype, int64_t rows, int32_t
 /* acc[i] += part[i] for `count` elements, acc fp32, part bf16 or fp32: the ring schedule's running sums of the
  * dQ / dK / dV partials of successive key blocks.  Asynchronous on `stream`.  No counterpart in the reference. */
 int sntl_attn_accumulate(int32_t part_dtype, int64_t count, float* acc, const void* part, void* stream);
+
+/* ---- Sequence-sharded attention over a ring of GPUs (the long-context workload) ----
+ * One process per GPU; rank r of `world` holds tokens [r*S/W, (r+1)*S/W) of ONE causal sequence: q, o, dout, dq
+ * [B][q_heads][S/W][D], k, v, dk, dv [B][kv_heads][S/W][D], lse [B][q_heads][S/W], all bf16 BHSD (lse fp32),
+ * head_dim 64 or 128, desc->seq_q = desc->seq_kv = S/W (even), desc->causal = 1.  The shards are dealt as half-shards in
+ * a zigzag so that every rank has the same work under the causal mask; K/V half-shards travel round the ring with
+ * grouped ncclSend / ncclRecv on the handle's own stream while the kernels of the current step run, and in the backward
+ * fp32 dK/dV accumulators travel with them.  Results come back in the contiguous layout.  Every rank makes the same
+ * calls in the same order.  All scratch comes from `workspace` (sntl_ring_attn_workspace_bytes; it must not be touched
+ * between a forward and a backward that reuses its state); streams and events belong to the handle.
+ *   sntl_ring_unique_id      rank 0 fills 128 bytes (an ncclUniqueId) that the host distributes to all ranks.
+ *   sntl_ring_comm_create    collective: makes the rank's handle (ncclCommInitRank on the current device).
+ *   sntl_ring_comm_adopt     the same around a communicator the host already has (an ncclComm_t; not destroyed with
+ *                            the handle).
+ *   sntl_ring_attn_bwd       reuse_forward_state != 0: q, k, v, o, lse are the tensors of the last sntl_ring_attn_fwd
+ *                            through this workspace, whose dealt copies are still there (only dout is dealt).
+ * NCCL is opened at run time (libnccl.so.2); SNTL_ERR_COMM when it is missing or a call fails.  A peer that stops
+ * answering is NCCL's to detect (its own time-outs / ncclCommAbort by the host); the device-side waits of the kernels
+ * stay bounded as everywhere.  No counterpart in the reference (it has no multi-GPU path at all). */
+typedef struct sntl_ring_comm sntl_ring_comm;
+int sntl_ring_unique_id(void* id128);
+int sntl_ring_comm_create(const void* id128, int rank, int world, sntl_ring_comm** out);
+int sntl_ring_comm_adopt(void* nccl_comm, int rank, int world, sntl_ring_comm** out);
+int sntl_ring_comm_destroy(sntl_ring_comm* comm);
+size_t sntl_ring_attn_workspace_bytes(const sntl_ring_comm* comm, const sntl_attn_desc* desc);
+int sntl_ring_attn_fwd(sntl_ring_comm* comm, const sntl_attn_desc* desc, const void* q, const void* k, const void* v, void* o,
+                       float* lse, void* workspace, size_t workspace_bytes, void* stream);
+int sntl_ring_attn_bwd(sntl_ring_comm* comm, const sntl_attn_desc* desc, const void* q, const void* k, const void* v,
+                       const void* o, const float* lse, const void* dout, void* dq, void* dk, void* dv,
+                       int reuse_forward_state, void* workspace, size_t workspace_bytes, void* stream);
 
 /* Name of the kernel family the most recent sntl_attn_fwd / sntl_attn_bwd call on this thread dispatched to
  * ("simt_f32", "tcgen05", ...), so a test can assert the path taken, like the reference's

@@ -19,8 +19,11 @@ EXPORTS = ["sntl_attn_version", "sntl_status_string", "sntl_attn_fwd_workspace_b
            "sntl_attn_poll_device_status", "sntl_attn_bwd_static_scratch", "sntl_attn_static_scratch_capacity", "sntl_attn_accumulate",
            "sntl_attn_cached_fwd", "sntl_attn_cached_fwd_workspace_bytes", "sntl_attn_pack_heads", "sntl_attn_unpack_heads",
            "sntl_attn_poll_device_status_words", "sntl_attn_selftest_wait_timeout",
-           "sntl_attn_bwd_pieces_workspace_bytes", "sntl_attn_bwd_begin", "sntl_attn_bwd_block", "sntl_attn_bwd_end"]
+           "sntl_attn_bwd_pieces_workspace_bytes", "sntl_attn_bwd_begin", "sntl_attn_bwd_block", "sntl_attn_bwd_end",
+           "sntl_ring_unique_id", "sntl_ring_comm_create", "sntl_ring_comm_adopt", "sntl_ring_comm_destroy",
+           "sntl_ring_attn_workspace_bytes", "sntl_ring_attn_fwd", "sntl_ring_attn_bwd"]
 ERR_SCRATCH_LIMIT = 7
+ERR_COMM = 8
 
 
 class Desc(C.Structure):
@@ -86,6 +89,20 @@ def load():
     lib.sntl_attn_bwd_block.argtypes = [dp, vp, vp, vp, vp, vp, vp, vp, sz, vp]
     lib.sntl_attn_bwd_end.restype = C.c_int
     lib.sntl_attn_bwd_end.argtypes = [dp, vp, vp, sz, vp]
+    lib.sntl_ring_unique_id.restype = C.c_int
+    lib.sntl_ring_unique_id.argtypes = [vp]
+    lib.sntl_ring_comm_create.restype = C.c_int
+    lib.sntl_ring_comm_create.argtypes = [vp, C.c_int, C.c_int, C.POINTER(vp)]
+    lib.sntl_ring_comm_adopt.restype = C.c_int
+    lib.sntl_ring_comm_adopt.argtypes = [vp, C.c_int, C.c_int, C.POINTER(vp)]
+    lib.sntl_ring_comm_destroy.restype = C.c_int
+    lib.sntl_ring_comm_destroy.argtypes = [vp]
+    lib.sntl_ring_attn_workspace_bytes.restype = sz
+    lib.sntl_ring_attn_workspace_bytes.argtypes = [vp, dp]
+    lib.sntl_ring_attn_fwd.restype = C.c_int
+    lib.sntl_ring_attn_fwd.argtypes = [vp, dp, vp, vp, vp, vp, vp, vp, sz, vp]
+    lib.sntl_ring_attn_bwd.restype = C.c_int
+    lib.sntl_ring_attn_bwd.argtypes = [vp, dp, vp, vp, vp, vp, vp, vp, vp, vp, vp, C.c_int, vp, sz, vp]
     lib.sntl_attn_poll_device_status_words.restype = C.c_int
     lib.sntl_attn_poll_device_status_words.argtypes = [vp, C.POINTER(C.c_uint32), C.POINTER(C.c_uint32)]
     lib.sntl_attn_selftest_wait_timeout.restype = C.c_int

@@ -19,7 +19,7 @@ LIB = os.path.join(LIB_DIR, "libsntl_attn.so")
 OBJ_DIR = os.path.join(HERE, "build")
 
 SOURCES = ["attn_api.cu", "attn_simt.cu", "layout_convert.cu", "attn_fwd_sm100.cu", "attn_bwd_sm100.cu",
-           "sentinel_compat.cu", "attn_bwd_static_scratch.cu"]
+           "sentinel_compat.cu", "attn_bwd_static_scratch.cu", "ring_nccl.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "-I", os.path.join(ROOT, "include"), "-I", CSRC]
 
@@ -59,7 +59,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
     with ThreadPoolExecutor(max_workers=min(8, len(srcs))) as ex:
         objs = list(ex.map(compile_one, srcs))
     if force or _stale(LIB, objs):
-        cmd = [nvcc(), "-shared", "-o", LIB] + objs + ["-gencode", "arch=compute_100a,code=sm_100a", "-cudart", "static"]
+        cmd = [nvcc(), "-shared", "-o", LIB] + objs + ["-gencode", "arch=compute_100a,code=sm_100a", "-cudart", "static", "-ldl"]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             sys.stderr.write(r.stdout + r.stderr)

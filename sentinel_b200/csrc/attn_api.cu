@@ -139,6 +139,7 @@ const char* sntl_status_string(int status)
         case SNTL_ERR_NO_DEVICE: return "no compute-capability-10.x device is current";
         case SNTL_ERR_DEVICE_TIMEOUT: return "a bounded device-side wait ran out";
         case SNTL_ERR_SCRATCH_LIMIT: return "problem needs more scratch than the library's built-in 32 MiB array";
+        case SNTL_ERR_COMM: return "NCCL is not available or an NCCL call failed";
         default: return "unknown status";
     }
 }

@@ -366,3 +366,65 @@ class _null:
 
     def __exit__(self, *a):
         return False
+
+
+class NativeRing:
+    """The same schedule run by the library itself (``sntl_ring_attn_fwd`` / ``sntl_ring_attn_bwd``): grouped
+    ncclSend / ncclRecv issued from C++ on the handle's own communication stream, every buffer carved from one
+    workspace, nothing allocated per call.  This is what a C / C++ host binds; here ``torch.distributed`` is only used
+    to hand the NCCL unique id from rank 0 to the other ranks.  bf16 ``[B, H, S/W, D]`` CUDA shards, head_dim 64 / 128."""
+
+    def __init__(self, group=None):
+        import ctypes as C
+        from . import _lib
+        self._C, self._lib = C, _lib
+        self.lib = _lib.load()
+        self.rank = dist.get_rank(group)
+        self.world = dist.get_world_size(group)
+        ident = [None]
+        if self.rank == 0:
+            buf = C.create_string_buffer(128)
+            _lib.check(self.lib.sntl_ring_unique_id(buf), "sntl_ring_unique_id")
+            ident[0] = buf.raw
+        dist.broadcast_object_list(ident, src=dist.get_global_rank(group, 0) if group is not None else 0, group=group)
+        handle = C.c_void_p()
+        _lib.check(self.lib.sntl_ring_comm_create(ident[0], self.rank, self.world, C.byref(handle)), "sntl_ring_comm_create")
+        self.handle = handle
+        self._ws = None
+
+    def _desc(self, q, k):
+        B, Hq, S, D = q.shape
+        return self._lib.Desc(self._lib.DTYPE_BF16, self._lib.LAYOUT_BHSD, B, Hq, k.shape[1], S, S, D, float(D ** -0.5), 1, 0, 0, 0, 0, 0)
+
+    def _workspace(self, d, device):
+        need = self.lib.sntl_ring_attn_workspace_bytes(self.handle, self._C.byref(d))
+        if need == 0:
+            self._lib.check(self._lib.ERR_UNSUPPORTED, "sntl_ring_attn_workspace_bytes")
+        if self._ws is None or self._ws.numel() < need:
+            self._ws = torch.empty(need, dtype=torch.uint8, device=device)
+        return self._ws, need
+
+    def forward(self, q, k, v, keep_state: bool = False):
+        d = self._desc(q, k)
+        ws, need = self._workspace(d, q.device)
+        o = torch.empty_like(q)
+        lse = torch.empty(q.shape[:3], dtype=torch.float32, device=q.device)
+        rc = self.lib.sntl_ring_attn_fwd(self.handle, self._C.byref(d), q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(),
+                                         lse.data_ptr(), ws.data_ptr(), need, torch.cuda.current_stream().cuda_stream)
+        self._lib.check(rc, "sntl_ring_attn_fwd")
+        return o, lse
+
+    def backward(self, q, k, v, o, lse, do, use_saved_state: bool = False):
+        d = self._desc(q, k)
+        ws, need = self._workspace(d, q.device)
+        dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+        rc = self.lib.sntl_ring_attn_bwd(self.handle, self._C.byref(d), q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(),
+                                         lse.data_ptr(), do.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
+                                         int(bool(use_saved_state)), ws.data_ptr(), need, torch.cuda.current_stream().cuda_stream)
+        self._lib.check(rc, "sntl_ring_attn_bwd")
+        return dq, dk, dv
+
+    def close(self):
+        if self.handle is not None:
+            self.lib.sntl_ring_comm_destroy(self.handle)
+            self.handle = None

@@ -270,8 +270,11 @@ def test_forward_is_deterministic_and_recompute_stable(sb):
     # dQ is a sum over key tiles in arrival order unless SNTL_FLAG_DETERMINISTIC asks for the order-independent sum
     from sentinel_b200 import _lib
     dq1, dk3, dv3 = sb.attention_backward(q, k, v, o1, l1, do, flags=_lib.FLAG_DETERMINISTIC)
-    dq2, _, _ = sb.attention_backward(q, k, v, o1, l1, do, flags=_lib.FLAG_DETERMINISTIC)
-    assert torch.equal(dq1, dq2) and torch.equal(dk3, dk1) and torch.equal(dv3, dv1)
+    dq2, dk4, dv4 = sb.attention_backward(q, k, v, o1, l1, do, flags=_lib.FLAG_DETERMINISTIC)
+    assert torch.equal(dq1, dq2) and torch.equal(dk3, dk4) and torch.equal(dv3, dv4)
+    # (on this small grid the default path cuts its long key tiles by query head and the flagged one does not, so their
+    # dK/dV are two different fixed summation orders of the same terms: close, not identical)
+    assert float((dk3.float() - dk1.float()).abs().max()) <= 2e-2 * float(dk1.float().abs().max())
 
 
 def test_backward_long_key_tiles_cut_by_query_head(sb, oracle):
