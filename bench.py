@@ -254,6 +254,63 @@ def run_cached_forward(args, w):
     print(json.dumps(line), flush=True)
 
 
+def run_pack_heads(args, w):
+    """Auxiliary mode (--pack-heads): the boundary kernels on the workload's Q tensor -- fp32 feature-major -> rotated
+    bf16 token-major (pack) and back with the inverse rotation (unpack).  HBM-bound: 6 bytes per element each way."""
+    import torch
+    import sentinel_b200 as sb
+    from oracle import cpu
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a B200 GPU: there is no CPU fallback for the product path")
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    sb._lib.load()
+    B, H, S, D = w.batch, w.q_heads, w.seq, w.head_dim
+    g = torch.Generator(device="cpu").manual_seed(20261125 + w.index)
+    matrix = torch.randn(H * D, B * S, generator=g, dtype=torch.float32).to(dev)
+    cos_t, sin_t = (torch.from_numpy(t).to(dev) for t in cpu.rope_tables(D, S, w.rope_base or 10000.0))
+    packed = torch.empty(B, H, S, D, dtype=torch.bfloat16, device=dev)
+    back = torch.empty_like(matrix)
+
+    def pack():
+        sb.pack_heads(matrix, B, H, S, D, cos_table=cos_t, sin_table=sin_t, out=packed)
+
+    def unpack():
+        sb.unpack_heads(packed, back, cos_table=cos_t, sin_table=sin_t, inverse=True)
+
+    def ms_of(fn):
+        for _ in range(args.warmup):
+            fn()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(args.steps):
+            fn()
+        e1.record()
+        e1.synchronize()
+        return e0.elapsed_time(e1) / args.steps
+
+    launches0 = sb.launch_count()
+    with ClockSampler(0) as clocks:
+        t_pack, t_unpack = ms_of(pack), ms_of(unpack)
+    n = matrix.numel()
+    peaks = load_peaks()
+    peak = float(peaks.get("hbm_gbs", FALLBACK_PEAKS["hbm_gbs"]))
+    gbs = lambda ms: 6.0 * n / (ms * 1e-3) / 1e9
+    line = {"metric": "attention_pack_heads_hbm_gbs", "value": gbs(t_pack), "unit": "GB/s", "n_gpus": 1, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": t_pack, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f32->bf16", "data": "synthetic",
+            "config": {"workload": w.name + "_pack_heads", "B": B, "H": H, "S": S, "D": D, "elements": n,
+                       "l2": f"{6 * n / 1e6:.0f} MB moved per call, larger than the 126 MB L2"},
+            "roofline": {"bound": "hbm", "kernel": "pack64_kernel (rotary embedding + cast + relayout)", "achieved": gbs(t_pack),
+                         "peak": peak, "unit": "GB/s", "frac": gbs(t_pack) / peak, "peak_source": f"{peaks['_source']} hbm_gbs",
+                         "traffic": None, "algorithmic_bytes": 6.0 * n},
+            "unpack": {"ms": t_unpack, "achieved": gbs(t_unpack), "frac": gbs(t_unpack) / peak,
+                       "kernel": "unpack64_kernel (inverse rotation)"},
+            "gpu_launches": int(sb.launch_count() - launches0), "clocks": clocks.summary()}
+    print(json.dumps(line), flush=True)
+
+
 def _make_timed(torch, dist, dev, world, local):
     def barrier():
         if world > 1:
@@ -491,6 +548,8 @@ def main():
                     help="headline timing only: no sustained loop, other workloads, strong-scaling or ring legs (profiling captures)")
     ap.add_argument("--cached-tokens", type=int, default=0,
                     help="auxiliary mode: this many new tokens per sequence against a KV cache of the workload's length")
+    ap.add_argument("--pack-heads", action="store_true",
+                    help="auxiliary mode: the rotary + cast + relayout boundary kernels on the workload's Q tensor")
     ap.add_argument("--window", type=int, default=0, help="sliding window (keys per query); 0 = the workload's plain causal mask")
     ap.add_argument("--global-tokens", type=int, default=0, help="always-visible first keys (with --window)")
     args = ap.parse_args()
@@ -506,6 +565,9 @@ def main():
         return
     if args.cached_tokens > 0:
         run_cached_forward(args, w)
+        return
+    if args.pack_heads:
+        run_pack_heads(args, w)
         return
 
     import torch
