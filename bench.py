@@ -453,7 +453,8 @@ def ring_oracle_check(torch, w_local, rank, world, o, lse, dq, dk, dv):
     base = rank * S_local
     out = {}
     # rows: head h against its KV head (index 0 of the kept pair)
-    rows = np.array(sorted({0, 1, S_local // 2 - 1, S_local // 2, S_local - 129, S_local - 1}), dtype=np.int32) + base
+    rows = np.unique(np.concatenate([np.array([0, 1, S_local // 2 - 1, S_local // 2, S_local - 129, S_local - 1]),
+                                     np.linspace(7, S_local - 9, 42).astype(np.int64)])).astype(np.int32) + base
     hi = hs.index(h)
     wo, wl, wdq = cpu.attn_rows(qf[:, hi:hi + 1], kf[:, 0:1], vf[:, 0:1], dof[:, hi:hi + 1], 0, 0, rows)
     loc = rows - base
@@ -515,8 +516,10 @@ def run_ring(torch, dist, sb, dev, rank, world, timed, steps, per_gpu_value):
     # the same schedule driven from Python over torch.distributed (the form the CPU tests pin), and one profiled step of it
     py_res, py_total, py_fwd_ms = measure(RingAttention(GpuBackend()))
     prof = RingAttention(GpuBackend(), profile=True)
-    o_, l_ = prof.forward(q, k, v, keep_state=True)
-    prof.backward(q, k, v, o_, l_, do, use_saved_state=True)
+    for _ in range(2):                     # the second pass is the one kept: the first pays for this object's first allocations
+        prof.timings.clear()
+        o_, l_ = prof.forward(q, k, v, keep_state=True)
+        prof.backward(q, k, v, o_, l_, do, use_saved_state=True)
     value = flops / (total * 1e-3) / 1e12
     check = ring_oracle_check(torch, w_local, rank, world, res["o"], res["lse"], *res["g"]) if rank in (0, world - 1) else None
     gathered = [None] * world

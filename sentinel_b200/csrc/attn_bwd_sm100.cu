@@ -69,7 +69,19 @@ struct BwdParams {
     float scale, scale_log2;
 };
 
-constexpr int kSmCount = 148;
+// SMs of the current device (148 on a B200), read once per device ordinal
+inline int sm_count()
+{
+    static std::atomic<int> cached[64];
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    int n = cached[dev].load(std::memory_order_relaxed);
+    if (n == 0) {
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+        cached[dev].store(n, std::memory_order_relaxed);
+    }
+    return n;
+}
 
 // Query tiles per head that key tile kt visits (the kernel's own rule)
 __host__ __device__ inline int bwd_tiles_per_head(int kt, int n_qt, int causal, int window, int global_tokens)
@@ -89,7 +101,7 @@ inline int bwd_split_tiles(const AttnShape& s)
     const int window = s.causal ? s.window : 0;
     double total = 0.0;
     for (int kt = 0; kt < n_kt; ++kt) total += bwd_tiles_per_head(kt, n_qt, s.causal, window, s.global_tokens);
-    const double avg = total * group * s.B * s.Hkv / kSmCount;
+    const double avg = total * group * s.B * s.Hkv / sm_count();
     int n = 0;
     while (n < n_kt && (double)bwd_tiles_per_head(n, n_qt, s.causal, window, s.global_tokens) * group > avg) ++n;
     return n;

@@ -356,26 +356,6 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t* r)
         "r"(r[31])
         : "memory");
 }
-// the same shapes, 16 columns at a time (for code that is short of registers)
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* r)
-{
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
-        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
-          "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-        : "r"(taddr)
-        : "memory");
-}
-__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t* r)
-{
-    asm volatile(
-        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
-        "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};" ::"r"(taddr),
-        "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]),
-        "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
-        : "memory");
-}
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
@@ -404,5 +384,6 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi)
 // Host side: encode a 3-D tiled tensor map over a bf16 [slabs][rows][D] tensor with a {64, box_rows, 1} box and
 // 128-byte swizzle.  The driver entry point is looked up at run time, so the library does not link libcuda.
 cudaError_t encode_tmap_bf16_3d(CUtensorMap* out, const void* base, int D, int rows, int slabs, int box_rows, int slab_rows = 0);
+cudaError_t encode_tmap_bf16_3d_uncached(CUtensorMap* out, const void* base, int D, int rows, int slabs, int box_rows, int slab_rows);
 
 }  // namespace sntl

@@ -388,7 +388,19 @@ class NativeRing:
             ident[0] = buf.raw
         dist.broadcast_object_list(ident, src=dist.get_global_rank(group, 0) if group is not None else 0, group=group)
         handle = C.c_void_p()
-        _lib.check(self.lib.sntl_ring_comm_create(ident[0], self.rank, self.world, C.byref(handle)), "sntl_ring_comm_create")
+        # NCCL may print a version banner on standard output when a communicator is made; programs that print their
+        # results there (bench.py's one JSON line) must not get it mixed in, so it goes to standard error
+        import os
+        import sys
+        sys.stdout.flush()
+        saved = os.dup(1)
+        os.dup2(2, 1)
+        try:
+            rc = self.lib.sntl_ring_comm_create(ident[0], self.rank, self.world, C.byref(handle))
+        finally:
+            os.dup2(saved, 1)
+            os.close(saved)
+        _lib.check(rc, "sntl_ring_comm_create")
         self.handle = handle
         self._ws = None
 
