@@ -633,23 +633,40 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
             const int key = k0 + row;
             const bool store = key < p.Skv;
             const float mul = wg == 0 ? 1.0f : p.scale;
-            __nv_bfloat16* dst = (wg == 0 ? p.dv : p.dk) + ((size_t)slab * p.Skv + (size_t)(store ? key : 0)) * D;
+            // Coalesced bf16 store: a thread holds one whole key row, so the warp's 32 rows go through shared memory (the V
+            // tile's buffer for dV, the K tile's for dK: every product has retired) and leave with each store instruction
+            // covering whole rows; 16-byte units are XOR-swizzled by the row against bank conflicts.
+            (void)store;
+            __nv_bfloat16* out = (wg == 0 ? p.dv : p.dk) + (size_t)slab * p.Skv * D;
             const uint32_t src = (wg == 0 ? tm_dV : tm_dK) + lane_off;
+            constexpr int kUnits = D / 8;
+            uint8_t* stage = (wg == 0 ? sV : sK) + (warp & 3) * 32 * (D * 2);
 #pragma unroll
             for (int c = 0; c < D / 32; ++c) {
                 uint32_t r[32];
                 tmem_ld32(src + (uint32_t)(c * 32), r);
                 tmem_ld_wait();
-                if (store) {
 #pragma unroll
-                    for (int v = 0; v < 4; ++v) {
-                        uint4 w;
-                        w.x = pack_bf16(__uint_as_float(r[8 * v + 0]) * mul, __uint_as_float(r[8 * v + 1]) * mul);
-                        w.y = pack_bf16(__uint_as_float(r[8 * v + 2]) * mul, __uint_as_float(r[8 * v + 3]) * mul);
-                        w.z = pack_bf16(__uint_as_float(r[8 * v + 4]) * mul, __uint_as_float(r[8 * v + 5]) * mul);
-                        w.w = pack_bf16(__uint_as_float(r[8 * v + 6]) * mul, __uint_as_float(r[8 * v + 7]) * mul);
-                        *reinterpret_cast<uint4*>(dst + c * 32 + v * 8) = w;
-                    }
+                for (int v = 0; v < 4; ++v) {
+                    uint4 w;
+                    w.x = pack_bf16(__uint_as_float(r[8 * v + 0]) * mul, __uint_as_float(r[8 * v + 1]) * mul);
+                    w.y = pack_bf16(__uint_as_float(r[8 * v + 2]) * mul, __uint_as_float(r[8 * v + 3]) * mul);
+                    w.z = pack_bf16(__uint_as_float(r[8 * v + 4]) * mul, __uint_as_float(r[8 * v + 5]) * mul);
+                    w.w = pack_bf16(__uint_as_float(r[8 * v + 6]) * mul, __uint_as_float(r[8 * v + 7]) * mul);
+                    const int unit = c * 4 + v;
+                    *reinterpret_cast<uint4*>(stage + lane * (D * 2) + ((unit ^ (lane & 7)) << 4)) = w;
+                }
+            }
+            __syncwarp();
+            {
+                constexpr int kRowsPerStore = 32 / kUnits;
+                const int sub = lane / kUnits, unit = lane % kUnits;
+                const int key_warp0 = key - lane;               // first key row of this warp
+#pragma unroll
+                for (int i = 0; i < 32 / kRowsPerStore; ++i) {
+                    const int rr = i * kRowsPerStore + sub;
+                    const uint4 w = *reinterpret_cast<const uint4*>(stage + rr * (D * 2) + ((unit ^ (rr & 7)) << 4));
+                    if (key_warp0 + rr < p.Skv) *reinterpret_cast<uint4*>(out + (size_t)(key_warp0 + rr) * D + unit * 8) = w;
                 }
             }
         } else if (n_iter == 0 && p.dk_acc == nullptr) {

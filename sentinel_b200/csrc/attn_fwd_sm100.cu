@@ -408,22 +408,45 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
             // cache mode: each stream of each split writes its own partial result, [2 * split + t][slab][row]
             const size_t part = kMode == kCache ? (size_t)(2 * split + t) : 0;
             const size_t out_row = (part * bh_count + bh) * p.Sq + (size_t)(store ? grow : 0);
-            __nv_bfloat16* orow = p.o + out_row * D;
+            // Coalesced store of O.  A thread holds one whole row (2*D bytes); written straight from there a warp's store
+            // instruction would touch 32 rows, 16 bytes each.  So the warp's 32 rows go through shared memory -- this tile's
+            // Q buffer, free since the last S product of this tile retired (o_ready of the last step implies it) -- and
+            // come back out with each store instruction covering whole
+            // rows: 16 lanes x 16 bytes = one 256-byte row at head_dim 128, 8 lanes per 128-byte row at 64.  Only the rows of
+            // this warp are exchanged, so a warp-level sync is all it takes; 16-byte units are XOR-swizzled by the row so
+            // that both the row-wise writes and the row-wise reads spread over the banks.
+            // (Cache mode: the two streams share ONE query tile, which the other stream may still be reading, but each owns
+            // K stage t, and that stage gets no further load once the stream's last tile is done.)
+            constexpr int kUnits = D / 8;                       // 16-byte units per row
+            uint8_t* stage = (kMode == kCache ? sK : sQ) + t * kTileBytes + (warp & 3) * 32 * (D * 2);
 #pragma unroll
             for (int c = 0; c < D / 32; ++c) {
                 uint32_t o[32];
                 tmem_ld32(tmem_O[t] + lane_off + (uint32_t)(c * 32), o);
                 tmem_ld_wait();
-                if (store) {
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        uint4 w;
-                        w.x = pack_bf16(__uint_as_float(o[8 * i + 0]) * inv, __uint_as_float(o[8 * i + 1]) * inv);
-                        w.y = pack_bf16(__uint_as_float(o[8 * i + 2]) * inv, __uint_as_float(o[8 * i + 3]) * inv);
-                        w.z = pack_bf16(__uint_as_float(o[8 * i + 4]) * inv, __uint_as_float(o[8 * i + 5]) * inv);
-                        w.w = pack_bf16(__uint_as_float(o[8 * i + 6]) * inv, __uint_as_float(o[8 * i + 7]) * inv);
-                        *reinterpret_cast<uint4*>(orow + c * 32 + i * 8) = w;
-                    }
+                for (int i = 0; i < 4; ++i) {
+                    uint4 w;
+                    w.x = pack_bf16(__uint_as_float(o[8 * i + 0]) * inv, __uint_as_float(o[8 * i + 1]) * inv);
+                    w.y = pack_bf16(__uint_as_float(o[8 * i + 2]) * inv, __uint_as_float(o[8 * i + 3]) * inv);
+                    w.z = pack_bf16(__uint_as_float(o[8 * i + 4]) * inv, __uint_as_float(o[8 * i + 5]) * inv);
+                    w.w = pack_bf16(__uint_as_float(o[8 * i + 6]) * inv, __uint_as_float(o[8 * i + 7]) * inv);
+                    const int unit = c * 4 + i;
+                    *reinterpret_cast<uint4*>(stage + lane * (D * 2) + ((unit ^ (lane & (kUnits - 1) & 7)) << 4)) = w;
+                }
+            }
+            __syncwarp();
+            {
+                constexpr int kRowsPerStore = 32 / kUnits;       // rows one store instruction of the warp covers
+                const int sub = lane / kUnits, unit = lane % kUnits;
+                const int warp_row0 = grow - lane;                // first row of this warp inside the slab
+                const size_t part_base = (part * bh_count + bh) * (size_t)p.Sq;
+#pragma unroll
+                for (int i = 0; i < 32 / kRowsPerStore; ++i) {
+                    const int r = i * kRowsPerStore + sub;        // row inside the warp's 32
+                    const uint4 w = *reinterpret_cast<const uint4*>(stage + r * (D * 2) + ((unit ^ (r & (kUnits - 1) & 7)) << 4));
+                    if (warp_row0 + r < p.Sq)
+                        *reinterpret_cast<uint4*>(p.o + (part_base + (size_t)(warp_row0 + r)) * D + unit * 8) = w;
                 }
             }
             if (store)

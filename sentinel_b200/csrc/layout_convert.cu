@@ -129,67 +129,128 @@ __device__ __forceinline__ void rotate_pair(float& even, float& odd, float c, fl
     }
 }
 
-template <int kRot>
+// Tiles of kTok tokens x 64 features, every global access 16 bytes wide: on the fp32 side a thread moves four
+// consecutive tokens of one feature (rows of kTok * 4 = 512 contiguous bytes per feature), on the bf16 side eight
+// consecutive features of one token (the 128-byte half row of a token leaves as eight such units), the angle tables
+// come as float4 (four pairs).  kVec = false is the same kernel with 4-byte accesses on the fp32 side, for windows
+// whose first column or row pitch is not a multiple of four elements.
+constexpr int kTok = 128;
+
+template <int kRot, bool kVec>
 __global__ void __launch_bounds__(256) pack64_kernel(const float* __restrict__ src, __nv_bfloat16* __restrict__ dst, int H, int S, int D,
                                                      int stride_columns, int column_start, const float* __restrict__ cos_t,
                                                      const float* __restrict__ sin_t, int position_offset)
 {
-    __shared__ float tile[64][65];   // [token][feature]
+    __shared__ float tile[kTok][65];   // [token][feature]
     const int bh = blockIdx.z, b = bh / H, h = bh % H;
-    const int s0 = blockIdx.x * 64, d0 = blockIdx.y * 64;
+    const int s0 = blockIdx.x * kTok, d0 = blockIdx.y * 64;
     const float* base = src + (long long)(h * D + d0) * stride_columns + column_start + (long long)b * S + s0;
+    if (kVec) {
 #pragma unroll
-    for (int r = 0; r < 16; ++r) {
-        const int idx = r * 256 + threadIdx.x, d = idx >> 6, sl = idx & 63;
-        tile[sl][d] = (s0 + sl < S) ? base[(long long)d * stride_columns + sl] : 0.0f;
+        for (int r = 0; r < kTok * 64 / 4 / 256; ++r) {
+            // a warp takes 8 token quads x 4 features: four full 128-byte lines from global memory, and with the odd
+            // row pitch of the tile its 32 lanes hit 32 different banks on every one of the four transposing writes
+            const int idx = r * 256 + threadIdx.x, rest = idx >> 5;
+            const int s4 = (rest & 3) * 32 + (idx & 7) * 4, d = (rest >> 2) * 4 + ((idx >> 3) & 3);
+            float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (s0 + s4 + 3 < S) x = *reinterpret_cast<const float4*>(base + (long long)d * stride_columns + s4);
+            else {
+                const float* row = base + (long long)d * stride_columns + s4;
+                if (s0 + s4 < S) x.x = row[0];
+                if (s0 + s4 + 1 < S) x.y = row[1];
+                if (s0 + s4 + 2 < S) x.z = row[2];
+            }
+            tile[s4][d] = x.x; tile[s4 + 1][d] = x.y; tile[s4 + 2][d] = x.z; tile[s4 + 3][d] = x.w;
+        }
+    } else {
+#pragma unroll 4
+        for (int r = 0; r < kTok * 64 / 256; ++r) {
+            const int idx = r * 256 + threadIdx.x, d = idx / kTok, sl = idx % kTok;
+            tile[sl][d] = (s0 + sl < S) ? base[(long long)d * stride_columns + sl] : 0.0f;
+        }
     }
     __syncthreads();
     const int pairs = D >> 1;
 #pragma unroll
-    for (int r = 0; r < 8; ++r) {
-        const int idx = r * 256 + threadIdx.x, sl = idx >> 5, pr = idx & 31;
+    for (int r = 0; r < kTok * 8 / 256; ++r) {
+        const int idx = r * 256 + threadIdx.x, sl = idx >> 3, u = idx & 7;    // token, 8-feature unit
         const int s = s0 + sl;
         if (s >= S) continue;
-        float even = tile[sl][2 * pr], odd = tile[sl][2 * pr + 1];
+        float x[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) x[i] = tile[sl][8 * u + i];
         if (kRot != 0) {
-            const long long ti = (long long)(position_offset + s) * pairs + (d0 >> 1) + pr;
-            rotate_pair<kRot>(even, odd, cos_t[ti], sin_t[ti]);
+            const long long ti = (long long)(position_offset + s) * pairs + (d0 >> 1) + 4 * u;   // a multiple of 4: 16-byte aligned
+            const float4 c = *reinterpret_cast<const float4*>(cos_t + ti), sn = *reinterpret_cast<const float4*>(sin_t + ti);
+            rotate_pair<kRot>(x[0], x[1], c.x, sn.x);
+            rotate_pair<kRot>(x[2], x[3], c.y, sn.y);
+            rotate_pair<kRot>(x[4], x[5], c.z, sn.z);
+            rotate_pair<kRot>(x[6], x[7], c.w, sn.w);
         }
-        reinterpret_cast<__nv_bfloat162*>(dst + ((long long)bh * S + s) * D + d0)[pr] = __floats2bfloat162_rn(even, odd);
+        __nv_bfloat162 o0 = __floats2bfloat162_rn(x[0], x[1]), o1 = __floats2bfloat162_rn(x[2], x[3]);
+        __nv_bfloat162 o2 = __floats2bfloat162_rn(x[4], x[5]), o3 = __floats2bfloat162_rn(x[6], x[7]);
+        uint4 w;
+        w.x = *reinterpret_cast<uint32_t*>(&o0); w.y = *reinterpret_cast<uint32_t*>(&o1);
+        w.z = *reinterpret_cast<uint32_t*>(&o2); w.w = *reinterpret_cast<uint32_t*>(&o3);
+        *reinterpret_cast<uint4*>(dst + ((long long)bh * S + s) * D + d0 + 8 * u) = w;
     }
 }
 
-template <int kRot>
+template <int kRot, bool kVec>
 __global__ void __launch_bounds__(256) unpack64_kernel(const __nv_bfloat16* __restrict__ src, float* __restrict__ dst, int H, int S, int D,
                                                        int stride_columns, int column_start, const float* __restrict__ cos_t,
                                                        const float* __restrict__ sin_t, int position_offset)
 {
-    __shared__ float tile[64][65];
+    __shared__ float tile[kTok][65];
     const int bh = blockIdx.z, b = bh / H, h = bh % H;
-    const int s0 = blockIdx.x * 64, d0 = blockIdx.y * 64;
+    const int s0 = blockIdx.x * kTok, d0 = blockIdx.y * 64;
     const int pairs = D >> 1;
 #pragma unroll
-    for (int r = 0; r < 8; ++r) {
-        const int idx = r * 256 + threadIdx.x, sl = idx >> 5, pr = idx & 31;
+    for (int r = 0; r < kTok * 8 / 256; ++r) {
+        const int idx = r * 256 + threadIdx.x, sl = idx >> 3, u = idx & 7;
         const int s = s0 + sl;
-        float even = 0.0f, odd = 0.0f;
+        float x[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
         if (s < S) {
-            const float2 x = __bfloat1622float2(reinterpret_cast<const __nv_bfloat162*>(src + ((long long)bh * S + s) * D + d0)[pr]);
-            even = x.x; odd = x.y;
+            const uint4 w = *reinterpret_cast<const uint4*>(src + ((long long)bh * S + s) * D + d0 + 8 * u);
+            const uint32_t ws[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                x[2 * i] = __uint_as_float(ws[i] << 16);
+                x[2 * i + 1] = __uint_as_float(ws[i] & 0xffff0000u);
+            }
             if (kRot != 0) {
-                const long long ti = (long long)(position_offset + s) * pairs + (d0 >> 1) + pr;
-                rotate_pair<kRot>(even, odd, cos_t[ti], sin_t[ti]);
+                const long long ti = (long long)(position_offset + s) * pairs + (d0 >> 1) + 4 * u;
+                const float4 c = *reinterpret_cast<const float4*>(cos_t + ti), sn = *reinterpret_cast<const float4*>(sin_t + ti);
+                rotate_pair<kRot>(x[0], x[1], c.x, sn.x);
+                rotate_pair<kRot>(x[2], x[3], c.y, sn.y);
+                rotate_pair<kRot>(x[4], x[5], c.z, sn.z);
+                rotate_pair<kRot>(x[6], x[7], c.w, sn.w);
             }
         }
-        tile[sl][2 * pr] = even;
-        tile[sl][2 * pr + 1] = odd;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) tile[sl][8 * u + i] = x[i];
     }
     __syncthreads();
     float* base = dst + (long long)(h * D + d0) * stride_columns + column_start + (long long)b * S + s0;
+    if (kVec) {
 #pragma unroll
-    for (int r = 0; r < 16; ++r) {
-        const int idx = r * 256 + threadIdx.x, d = idx >> 6, sl = idx & 63;
-        if (s0 + sl < S) base[(long long)d * stride_columns + sl] = tile[sl][d];
+        for (int r = 0; r < kTok * 64 / 4 / 256; ++r) {
+            const int idx = r * 256 + threadIdx.x, rest = idx >> 5;      // same lane map as the pack kernel's loads
+            const int s4 = (rest & 3) * 32 + (idx & 7) * 4, d = (rest >> 2) * 4 + ((idx >> 3) & 3);
+            float* row = base + (long long)d * stride_columns + s4;
+            if (s0 + s4 + 3 < S) *reinterpret_cast<float4*>(row) = make_float4(tile[s4][d], tile[s4 + 1][d], tile[s4 + 2][d], tile[s4 + 3][d]);
+            else {
+                if (s0 + s4 < S) row[0] = tile[s4][d];
+                if (s0 + s4 + 1 < S) row[1] = tile[s4 + 1][d];
+                if (s0 + s4 + 2 < S) row[2] = tile[s4 + 2][d];
+            }
+        }
+    } else {
+#pragma unroll 4
+        for (int r = 0; r < kTok * 64 / 256; ++r) {
+            const int idx = r * 256 + threadIdx.x, d = idx / kTok, sl = idx % kTok;
+            if (s0 + sl < S) base[(long long)d * stride_columns + sl] = tile[sl][d];
+        }
     }
 }
 
@@ -282,13 +343,28 @@ cudaError_t bhsd_bf16_to_sentinel(const __nv_bfloat16* src, float* dst, int B, i
     return cudaGetLastError();
 }
 
+// the fp32 side can be accessed 16 bytes at a time when every row of the window starts on a 16-byte boundary
+static bool f32_rows_aligned(const void* p, int S, int stride_columns, int column_start)
+{
+    return ((uintptr_t)p & 15u) == 0 && stride_columns % 4 == 0 && column_start % 4 == 0 && S % 4 == 0;
+}
+static bool tables_aligned(const float* cos_t, const float* sin_t) { return (((uintptr_t)cos_t | (uintptr_t)sin_t) & 15u) == 0; }
+
 cudaError_t rope_pack_bf16(const float* src, __nv_bfloat16* dst, int B, int H, int S, int D, int stride_columns,
                            int column_start, const float* cos_t, const float* sin_t, int position_offset, cudaStream_t st)
 {
     if (D % 64 == 0) {
-        dim3 grid((S + 63) / 64, D / 64, B * H);
-        if (cos_t) pack64_kernel<1><<<grid, 256, 0, st>>>(src, dst, H, S, D, stride_columns, column_start, cos_t, sin_t, position_offset);
-        else pack64_kernel<0><<<grid, 256, 0, st>>>(src, dst, H, S, D, stride_columns, column_start, nullptr, nullptr, 0);
+        // the bf16 side and the angle tables are accessed 16 bytes at a time (as are all bf16 tensors of the tensor-core kernels)
+        if (((uintptr_t)dst & 15u) != 0 || (cos_t && !tables_aligned(cos_t, sin_t))) return cudaErrorMisalignedAddress;
+        dim3 grid((S + kTok - 1) / kTok, D / 64, B * H);
+        const bool vec = f32_rows_aligned(src, S, stride_columns, column_start);
+        if (cos_t) {
+            if (vec) pack64_kernel<1, true><<<grid, 256, 0, st>>>(src, dst, H, S, D, stride_columns, column_start, cos_t, sin_t, position_offset);
+            else pack64_kernel<1, false><<<grid, 256, 0, st>>>(src, dst, H, S, D, stride_columns, column_start, cos_t, sin_t, position_offset);
+        } else {
+            if (vec) pack64_kernel<0, true><<<grid, 256, 0, st>>>(src, dst, H, S, D, stride_columns, column_start, nullptr, nullptr, 0);
+            else pack64_kernel<0, false><<<grid, 256, 0, st>>>(src, dst, H, S, D, stride_columns, column_start, nullptr, nullptr, 0);
+        }
         count_launch();
         return cudaGetLastError();
     }
@@ -304,10 +380,18 @@ cudaError_t rope_unpack_f32(const __nv_bfloat16* src, float* dst, int B, int H, 
                             cudaStream_t st)
 {
     if (D % 64 == 0) {
-        dim3 grid((S + 63) / 64, D / 64, B * H);
-        if (!cos_t) unpack64_kernel<0><<<grid, 256, 0, st>>>(src, dst, H, S, D, stride_columns, column_start, nullptr, nullptr, 0);
-        else if (inverse) unpack64_kernel<2><<<grid, 256, 0, st>>>(src, dst, H, S, D, stride_columns, column_start, cos_t, sin_t, position_offset);
-        else unpack64_kernel<1><<<grid, 256, 0, st>>>(src, dst, H, S, D, stride_columns, column_start, cos_t, sin_t, position_offset);
+        if (((uintptr_t)src & 15u) != 0 || (cos_t && !tables_aligned(cos_t, sin_t))) return cudaErrorMisalignedAddress;
+        dim3 grid((S + kTok - 1) / kTok, D / 64, B * H);
+        const bool vec = f32_rows_aligned(dst, S, stride_columns, column_start);
+#define SNTL_UNPACK(ROT, C, SN, PO)                                                                                                   \
+        do {                                                                                                                          \
+            if (vec) unpack64_kernel<ROT, true><<<grid, 256, 0, st>>>(src, dst, H, S, D, stride_columns, column_start, C, SN, PO);    \
+            else unpack64_kernel<ROT, false><<<grid, 256, 0, st>>>(src, dst, H, S, D, stride_columns, column_start, C, SN, PO);       \
+        } while (0)
+        if (!cos_t) SNTL_UNPACK(0, nullptr, nullptr, 0);
+        else if (inverse) SNTL_UNPACK(2, cos_t, sin_t, position_offset);
+        else SNTL_UNPACK(1, cos_t, sin_t, position_offset);
+#undef SNTL_UNPACK
         count_launch();
         return cudaGetLastError();
     }
