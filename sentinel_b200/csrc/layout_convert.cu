@@ -129,130 +129,223 @@ __device__ __forceinline__ void rotate_pair(float& even, float& odd, float c, fl
     }
 }
 
-// Tiles of kTok tokens x 64 features, every global access 16 bytes wide: on the fp32 side a thread moves four
-// consecutive tokens of one feature (rows of kTok * 4 = 512 contiguous bytes per feature), on the bf16 side eight
-// consecutive features of one token (the 128-byte half row of a token leaves as eight such units), the angle tables
-// come as float4 (four pairs).  kVec = false is the same kernel with 4-byte accesses on the fp32 side, for windows
-// whose first column or row pitch is not a multiple of four elements.
+// Tiles of kTok tokens x DT = 64 features, every global access 16 bytes wide: on the bf16 side a thread moves eight
+// consecutive features of one token, on the fp32 side four consecutive tokens of one feature (runs of kTok * 4 = 512
+// contiguous bytes per feature).  (A tile covering a whole 128-feature head makes the bf16 side one contiguous block,
+// but its 66 KB of shared memory leave three CTAs per SM and it measured 35 % slower.)  The angle tables come as float4 (four
+// pairs).  Lane maps are chosen so that, with the tile's odd row pitch, the 32 lanes of a warp hit 32 different banks in
+// both transposing directions: 8 token quads x 4 features on the fp32 side, 8 tokens x 4 eight-feature units on the
+// bf16 side.  kVec = false is the same kernel with 4-byte accesses on the fp32 side, for windows whose first column,
+// length or row pitch is not a multiple of four elements.
 constexpr int kTok = 128;
+constexpr int kHeadsPerCta = 4;   // heads one CTA converts in turn: the angle tables then cost a quarter of the L2 traffic
 
-template <int kRot, bool kVec>
-__global__ void __launch_bounds__(256) pack64_kernel(const float* __restrict__ src, __nv_bfloat16* __restrict__ dst, int H, int S, int D,
-                                                     int stride_columns, int column_start, const float* __restrict__ cos_t,
-                                                     const float* __restrict__ sin_t, int position_offset)
-{
-    __shared__ float tile[kTok][65];   // [token][feature]
-    const int bh = blockIdx.z, b = bh / H, h = bh % H;
-    const int s0 = blockIdx.x * kTok, d0 = blockIdx.y * 64;
-    const float* base = src + (long long)(h * D + d0) * stride_columns + column_start + (long long)b * S + s0;
-    if (kVec) {
-#pragma unroll
-        for (int r = 0; r < kTok * 64 / 4 / 256; ++r) {
-            // a warp takes 8 token quads x 4 features: four full 128-byte lines from global memory, and with the odd
-            // row pitch of the tile its 32 lanes hit 32 different banks on every one of the four transposing writes
-            const int idx = r * 256 + threadIdx.x, rest = idx >> 5;
-            const int s4 = (rest & 3) * 32 + (idx & 7) * 4, d = (rest >> 2) * 4 + ((idx >> 3) & 3);
-            float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (s0 + s4 + 3 < S) x = *reinterpret_cast<const float4*>(base + (long long)d * stride_columns + s4);
-            else {
-                const float* row = base + (long long)d * stride_columns + s4;
-                if (s0 + s4 < S) x.x = row[0];
-                if (s0 + s4 + 1 < S) x.y = row[1];
-                if (s0 + s4 + 2 < S) x.z = row[2];
-            }
-            tile[s4][d] = x.x; tile[s4 + 1][d] = x.y; tile[s4 + 2][d] = x.z; tile[s4 + 3][d] = x.w;
-        }
-    } else {
-#pragma unroll 4
-        for (int r = 0; r < kTok * 64 / 256; ++r) {
-            const int idx = r * 256 + threadIdx.x, d = idx / kTok, sl = idx % kTok;
-            tile[sl][d] = (s0 + sl < S) ? base[(long long)d * stride_columns + sl] : 0.0f;
-        }
+// lane maps (see above): fp32 side -> (first of four tokens, feature); bf16 side -> (token, 8-feature unit)
+template <int DT> struct PackMap {
+    static constexpr int kQuads = kTok * DT / 4 / 256;        // float4 accesses per thread on the fp32 side
+    static constexpr int kUnits = kTok * (DT / 8) / 256;      // 16-byte units per thread on the bf16 side
+    static constexpr int kUnitGroups = DT / 32;
+    __device__ static void quad(int r, int& s4, int& d)
+    {
+        const int idx = r * 256 + threadIdx.x, rest = idx >> 5;
+        s4 = (rest & 3) * 32 + (idx & 7) * 4;
+        d = (rest >> 2) * 4 + ((idx >> 3) & 3);
     }
-    __syncthreads();
-    const int pairs = D >> 1;
+    __device__ static void unit(int r, int& sl, int& u)
+    {
+        const int idx = r * 256 + threadIdx.x, rest = idx >> 5;
+        sl = (rest / kUnitGroups) * 8 + ((idx >> 2) & 7);
+        u = (rest % kUnitGroups) * 4 + (idx & 3);
+    }
+};
+
+// The angles depend on the token and the feature pair only: a thread fetches those of its (token, unit) slots once
+// and keeps them in registers for all the heads its CTA converts.
+template <int kRot, int DT>
+__device__ __forceinline__ void load_angles(float4* cs, float4* sn, const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                                            int s0, int d0, int S, int pairs, int position_offset)
+{
+    if (kRot == 0) return;
 #pragma unroll
-    for (int r = 0; r < kTok * 8 / 256; ++r) {
-        const int idx = r * 256 + threadIdx.x, sl = idx >> 3, u = idx & 7;    // token, 8-feature unit
-        const int s = s0 + sl;
-        if (s >= S) continue;
-        float x[8];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) x[i] = tile[sl][8 * u + i];
-        if (kRot != 0) {
-            const long long ti = (long long)(position_offset + s) * pairs + (d0 >> 1) + 4 * u;   // a multiple of 4: 16-byte aligned
-            const float4 c = *reinterpret_cast<const float4*>(cos_t + ti), sn = *reinterpret_cast<const float4*>(sin_t + ti);
-            rotate_pair<kRot>(x[0], x[1], c.x, sn.x);
-            rotate_pair<kRot>(x[2], x[3], c.y, sn.y);
-            rotate_pair<kRot>(x[4], x[5], c.z, sn.z);
-            rotate_pair<kRot>(x[6], x[7], c.w, sn.w);
-        }
-        __nv_bfloat162 o0 = __floats2bfloat162_rn(x[0], x[1]), o1 = __floats2bfloat162_rn(x[2], x[3]);
-        __nv_bfloat162 o2 = __floats2bfloat162_rn(x[4], x[5]), o3 = __floats2bfloat162_rn(x[6], x[7]);
-        uint4 w;
-        w.x = *reinterpret_cast<uint32_t*>(&o0); w.y = *reinterpret_cast<uint32_t*>(&o1);
-        w.z = *reinterpret_cast<uint32_t*>(&o2); w.w = *reinterpret_cast<uint32_t*>(&o3);
-        *reinterpret_cast<uint4*>(dst + ((long long)bh * S + s) * D + d0 + 8 * u) = w;
+    for (int r = 0; r < PackMap<DT>::kUnits; ++r) {
+        int sl, u;
+        PackMap<DT>::unit(r, sl, u);
+        const int s = min(s0 + sl, S - 1);
+        const long long ti = (long long)(position_offset + s) * pairs + (d0 >> 1) + 4 * u;   // a multiple of 4: 16-byte aligned
+        cs[r] = __ldg(reinterpret_cast<const float4*>(cos_t + ti));
+        sn[r] = __ldg(reinterpret_cast<const float4*>(sin_t + ti));
     }
 }
 
-template <int kRot, bool kVec>
-__global__ void __launch_bounds__(256) unpack64_kernel(const __nv_bfloat16* __restrict__ src, float* __restrict__ dst, int H, int S, int D,
+template <int kRot, bool kVec, int DT>
+__global__ void __launch_bounds__(256, 4) pack64_kernel(const float* __restrict__ src, __nv_bfloat16* __restrict__ dst, int H, int S, int D,
+                                                     int stride_columns, int column_start, const float* __restrict__ cos_t,
+                                                     const float* __restrict__ sin_t, int position_offset)
+{
+    using M = PackMap<DT>;
+    extern __shared__ float tile_raw[];
+    float (*tile)[DT + 1] = reinterpret_cast<float (*)[DT + 1]>(tile_raw);   // [token][feature]
+    const int groups = (H + kHeadsPerCta - 1) / kHeadsPerCta;
+    const int b = blockIdx.z / groups, h_first = (blockIdx.z % groups) * kHeadsPerCta;
+    const int s0 = blockIdx.x * kTok, d0 = blockIdx.y * DT;
+    float4 cs[M::kUnits], sn[M::kUnits];
+    load_angles<kRot, DT>(cs, sn, cos_t, sin_t, s0, d0, S, D >> 1, position_offset);
+    for (int h = h_first; h < min(H, h_first + kHeadsPerCta); ++h) {
+        const float* base = src + (long long)(h * D + d0) * stride_columns + column_start + (long long)b * S + s0;
+        if (kVec) {
+            // all of a thread's loads are issued before the first one is used (S is a multiple of four here, so a quad
+            // of tokens is inside the sequence or outside it as a whole)
+            float4 x[M::kQuads];
+#pragma unroll
+            for (int r = 0; r < M::kQuads; ++r) {
+                int s4, d;
+                M::quad(r, s4, d);
+                x[r] = (s0 + s4 < S) ? __ldg(reinterpret_cast<const float4*>(base + (long long)d * stride_columns + s4))
+                                     : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+#pragma unroll
+            for (int r = 0; r < M::kQuads; ++r) {
+                int s4, d;
+                M::quad(r, s4, d);
+                tile[s4][d] = x[r].x; tile[s4 + 1][d] = x[r].y; tile[s4 + 2][d] = x[r].z; tile[s4 + 3][d] = x[r].w;
+            }
+        } else {
+#pragma unroll 4
+            for (int r = 0; r < kTok * DT / 256; ++r) {
+                const int idx = r * 256 + threadIdx.x, d = idx / kTok, sl = idx % kTok;
+                tile[sl][d] = (s0 + sl < S) ? base[(long long)d * stride_columns + sl] : 0.0f;
+            }
+        }
+        __syncthreads();
+        __nv_bfloat16* out = dst + ((long long)(b * H + h) * S + s0) * D + d0;
+#pragma unroll
+        for (int r = 0; r < M::kUnits; ++r) {
+            int sl, u;
+            M::unit(r, sl, u);
+            if (s0 + sl >= S) continue;
+            float x[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) x[i] = tile[sl][8 * u + i];
+            if (kRot != 0) {
+                rotate_pair<kRot>(x[0], x[1], cs[r].x, sn[r].x);
+                rotate_pair<kRot>(x[2], x[3], cs[r].y, sn[r].y);
+                rotate_pair<kRot>(x[4], x[5], cs[r].z, sn[r].z);
+                rotate_pair<kRot>(x[6], x[7], cs[r].w, sn[r].w);
+            }
+            __nv_bfloat162 o0 = __floats2bfloat162_rn(x[0], x[1]), o1 = __floats2bfloat162_rn(x[2], x[3]);
+            __nv_bfloat162 o2 = __floats2bfloat162_rn(x[4], x[5]), o3 = __floats2bfloat162_rn(x[6], x[7]);
+            uint4 w;
+            w.x = *reinterpret_cast<uint32_t*>(&o0); w.y = *reinterpret_cast<uint32_t*>(&o1);
+            w.z = *reinterpret_cast<uint32_t*>(&o2); w.w = *reinterpret_cast<uint32_t*>(&o3);
+            *reinterpret_cast<uint4*>(out + (long long)sl * D + 8 * u) = w;
+        }
+        __syncthreads();      // the tile is refilled for the next head
+    }
+}
+
+template <int kRot, bool kVec, int DT>
+__global__ void __launch_bounds__(256, 4) unpack64_kernel(const __nv_bfloat16* __restrict__ src, float* __restrict__ dst, int H, int S, int D,
                                                        int stride_columns, int column_start, const float* __restrict__ cos_t,
                                                        const float* __restrict__ sin_t, int position_offset)
 {
-    __shared__ float tile[kTok][65];
-    const int bh = blockIdx.z, b = bh / H, h = bh % H;
-    const int s0 = blockIdx.x * kTok, d0 = blockIdx.y * 64;
-    const int pairs = D >> 1;
+    using M = PackMap<DT>;
+    extern __shared__ float tile_raw[];
+    float (*tile)[DT + 1] = reinterpret_cast<float (*)[DT + 1]>(tile_raw);
+    const int groups = (H + kHeadsPerCta - 1) / kHeadsPerCta;
+    const int b = blockIdx.z / groups, h_first = (blockIdx.z % groups) * kHeadsPerCta;
+    const int s0 = blockIdx.x * kTok, d0 = blockIdx.y * DT;
+    float4 cs[M::kUnits], sn[M::kUnits];
+    load_angles<kRot, DT>(cs, sn, cos_t, sin_t, s0, d0, S, D >> 1, position_offset);
+    for (int h = h_first; h < min(H, h_first + kHeadsPerCta); ++h) {
+        const __nv_bfloat16* in = src + ((long long)(b * H + h) * S + s0) * D + d0;
+        uint4 win[M::kUnits];
 #pragma unroll
-    for (int r = 0; r < kTok * 8 / 256; ++r) {
-        const int idx = r * 256 + threadIdx.x, sl = idx >> 3, u = idx & 7;
-        const int s = s0 + sl;
-        float x[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-        if (s < S) {
-            const uint4 w = *reinterpret_cast<const uint4*>(src + ((long long)bh * S + s) * D + d0 + 8 * u);
-            const uint32_t ws[4] = {w.x, w.y, w.z, w.w};
+        for (int r = 0; r < M::kUnits; ++r) {      // all loads first
+            int sl, u;
+            M::unit(r, sl, u);
+            win[r] = (s0 + sl < S) ? __ldg(reinterpret_cast<const uint4*>(in + (long long)sl * D + 8 * u)) : make_uint4(0, 0, 0, 0);
+        }
+#pragma unroll
+        for (int r = 0; r < M::kUnits; ++r) {
+            int sl, u;
+            M::unit(r, sl, u);
+            const uint32_t ws[4] = {win[r].x, win[r].y, win[r].z, win[r].w};
+            float x[8];
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
                 x[2 * i] = __uint_as_float(ws[i] << 16);
                 x[2 * i + 1] = __uint_as_float(ws[i] & 0xffff0000u);
             }
-            if (kRot != 0) {
-                const long long ti = (long long)(position_offset + s) * pairs + (d0 >> 1) + 4 * u;
-                const float4 c = *reinterpret_cast<const float4*>(cos_t + ti), sn = *reinterpret_cast<const float4*>(sin_t + ti);
-                rotate_pair<kRot>(x[0], x[1], c.x, sn.x);
-                rotate_pair<kRot>(x[2], x[3], c.y, sn.y);
-                rotate_pair<kRot>(x[4], x[5], c.z, sn.z);
-                rotate_pair<kRot>(x[6], x[7], c.w, sn.w);
+            if (kRot != 0) {      // (rows past the end are zeros and stay zeros under the rotation)
+                rotate_pair<kRot>(x[0], x[1], cs[r].x, sn[r].x);
+                rotate_pair<kRot>(x[2], x[3], cs[r].y, sn[r].y);
+                rotate_pair<kRot>(x[4], x[5], cs[r].z, sn[r].z);
+                rotate_pair<kRot>(x[6], x[7], cs[r].w, sn[r].w);
             }
+#pragma unroll
+            for (int i = 0; i < 8; ++i) tile[sl][8 * u + i] = x[i];
         }
+        __syncthreads();
+        float* base = dst + (long long)(h * D + d0) * stride_columns + column_start + (long long)b * S + s0;
+        if (kVec) {
 #pragma unroll
-        for (int i = 0; i < 8; ++i) tile[sl][8 * u + i] = x[i];
-    }
-    __syncthreads();
-    float* base = dst + (long long)(h * D + d0) * stride_columns + column_start + (long long)b * S + s0;
-    if (kVec) {
-#pragma unroll
-        for (int r = 0; r < kTok * 64 / 4 / 256; ++r) {
-            const int idx = r * 256 + threadIdx.x, rest = idx >> 5;      // same lane map as the pack kernel's loads
-            const int s4 = (rest & 3) * 32 + (idx & 7) * 4, d = (rest >> 2) * 4 + ((idx >> 3) & 3);
-            float* row = base + (long long)d * stride_columns + s4;
-            if (s0 + s4 + 3 < S) *reinterpret_cast<float4*>(row) = make_float4(tile[s4][d], tile[s4 + 1][d], tile[s4 + 2][d], tile[s4 + 3][d]);
-            else {
-                if (s0 + s4 < S) row[0] = tile[s4][d];
-                if (s0 + s4 + 1 < S) row[1] = tile[s4 + 1][d];
-                if (s0 + s4 + 2 < S) row[2] = tile[s4 + 2][d];
+            for (int r = 0; r < M::kQuads; ++r) {
+                int s4, d;
+                M::quad(r, s4, d);
+                if (s0 + s4 < S)
+                    *reinterpret_cast<float4*>(base + (long long)d * stride_columns + s4) =
+                        make_float4(tile[s4][d], tile[s4 + 1][d], tile[s4 + 2][d], tile[s4 + 3][d]);
             }
-        }
-    } else {
+        } else {
 #pragma unroll 4
-        for (int r = 0; r < kTok * 64 / 256; ++r) {
-            const int idx = r * 256 + threadIdx.x, d = idx / kTok, sl = idx % kTok;
-            if (s0 + sl < S) base[(long long)d * stride_columns + sl] = tile[sl][d];
+            for (int r = 0; r < kTok * DT / 256; ++r) {
+                const int idx = r * 256 + threadIdx.x, d = idx / kTok, sl = idx % kTok;
+                if (s0 + sl < S) base[(long long)d * stride_columns + sl] = tile[sl][d];
+            }
         }
+        __syncthreads();      // the tile is refilled for the next head
     }
 }
+
+// launches pack64_kernel / unpack64_kernel (one tile column of 64 features per blockIdx.y)
+#define SNTL_PACK_CASE(KERNEL, ROT, VEC, DTV)                                                                                      \
+    do {                                                                                                                           \
+        constexpr size_t smem = (size_t)kTok * (DTV + 1) * sizeof(float);                                                          \
+        static std::atomic<unsigned long long> configured{0};                                                                      \
+        if ((e = ensure_dynamic_smem(KERNEL<ROT, VEC, DTV>, smem, configured)) != cudaSuccess) return e;                           \
+        dim3 grid((S + kTok - 1) / kTok, D / DTV, B * ((H + kHeadsPerCta - 1) / kHeadsPerCta));                                    \
+        KERNEL<ROT, VEC, DTV><<<grid, 256, smem, st>>>(src, dst, H, S, D, stride_columns, column_start, cos_t, sin_t, position_offset); \
+    } while (0)
+#define SNTL_PACK_ROT(KERNEL, VEC, DTV)                                 \
+    do {                                                                \
+        if (rot == 0) SNTL_PACK_CASE(KERNEL, 0, VEC, DTV);              \
+        else if (rot == 1) SNTL_PACK_CASE(KERNEL, 1, VEC, DTV);         \
+        else SNTL_PACK_CASE(KERNEL, 2, VEC, DTV);                       \
+    } while (0)
+#define SNTL_PACK_ALL(KERNEL)                                                            \
+    do {                                                                                 \
+        if (vec) SNTL_PACK_ROT(KERNEL, true, 64); else SNTL_PACK_ROT(KERNEL, false, 64);                         \
+    } while (0)
+
+cudaError_t launch_pack64(int rot, bool vec, const float* src, __nv_bfloat16* dst, int B, int H, int S, int D, int stride_columns,
+                          int column_start, const float* cos_t, const float* sin_t, int position_offset, cudaStream_t st)
+{
+    cudaError_t e;
+    SNTL_PACK_ALL(pack64_kernel);
+    count_launch();
+    return cudaGetLastError();
+}
+cudaError_t launch_unpack64(int rot, bool vec, const __nv_bfloat16* src, float* dst, int B, int H, int S, int D, int stride_columns,
+                            int column_start, const float* cos_t, const float* sin_t, int position_offset, cudaStream_t st)
+{
+    cudaError_t e;
+    SNTL_PACK_ALL(unpack64_kernel);
+    count_launch();
+    return cudaGetLastError();
+}
+#undef SNTL_PACK_ALL
+#undef SNTL_PACK_ROT
+#undef SNTL_PACK_CASE
 
 __global__ void f32_to_bf16_kernel(const float* __restrict__ src, __nv_bfloat16* __restrict__ dst, size_t n)
 {
@@ -356,17 +449,8 @@ cudaError_t rope_pack_bf16(const float* src, __nv_bfloat16* dst, int B, int H, i
     if (D % 64 == 0) {
         // the bf16 side and the angle tables are accessed 16 bytes at a time (as are all bf16 tensors of the tensor-core kernels)
         if (((uintptr_t)dst & 15u) != 0 || (cos_t && !tables_aligned(cos_t, sin_t))) return cudaErrorMisalignedAddress;
-        dim3 grid((S + kTok - 1) / kTok, D / 64, B * H);
-        const bool vec = f32_rows_aligned(src, S, stride_columns, column_start);
-        if (cos_t) {
-            if (vec) pack64_kernel<1, true><<<grid, 256, 0, st>>>(src, dst, H, S, D, stride_columns, column_start, cos_t, sin_t, position_offset);
-            else pack64_kernel<1, false><<<grid, 256, 0, st>>>(src, dst, H, S, D, stride_columns, column_start, cos_t, sin_t, position_offset);
-        } else {
-            if (vec) pack64_kernel<0, true><<<grid, 256, 0, st>>>(src, dst, H, S, D, stride_columns, column_start, nullptr, nullptr, 0);
-            else pack64_kernel<0, false><<<grid, 256, 0, st>>>(src, dst, H, S, D, stride_columns, column_start, nullptr, nullptr, 0);
-        }
-        count_launch();
-        return cudaGetLastError();
+        return launch_pack64(cos_t ? 1 : 0, f32_rows_aligned(src, S, stride_columns, column_start), src, dst, B, H, S, D, stride_columns,
+                             column_start, cos_t, sin_t, position_offset, st);
     }
     if (!cos_t) return sentinel_to_bhsd_bf16(src, dst, B, H, S, D, stride_columns, column_start, st);
     dim3 grid((S + 31) / 32, (D + 31) / 32, B * H), block(32, 8);
@@ -381,19 +465,8 @@ cudaError_t rope_unpack_f32(const __nv_bfloat16* src, float* dst, int B, int H, 
 {
     if (D % 64 == 0) {
         if (((uintptr_t)src & 15u) != 0 || (cos_t && !tables_aligned(cos_t, sin_t))) return cudaErrorMisalignedAddress;
-        dim3 grid((S + kTok - 1) / kTok, D / 64, B * H);
-        const bool vec = f32_rows_aligned(dst, S, stride_columns, column_start);
-#define SNTL_UNPACK(ROT, C, SN, PO)                                                                                                   \
-        do {                                                                                                                          \
-            if (vec) unpack64_kernel<ROT, true><<<grid, 256, 0, st>>>(src, dst, H, S, D, stride_columns, column_start, C, SN, PO);    \
-            else unpack64_kernel<ROT, false><<<grid, 256, 0, st>>>(src, dst, H, S, D, stride_columns, column_start, C, SN, PO);       \
-        } while (0)
-        if (!cos_t) SNTL_UNPACK(0, nullptr, nullptr, 0);
-        else if (inverse) SNTL_UNPACK(2, cos_t, sin_t, position_offset);
-        else SNTL_UNPACK(1, cos_t, sin_t, position_offset);
-#undef SNTL_UNPACK
-        count_launch();
-        return cudaGetLastError();
+        return launch_unpack64(!cos_t ? 0 : (inverse ? 2 : 1), f32_rows_aligned(dst, S, stride_columns, column_start), src, dst, B, H, S, D,
+                               stride_columns, column_start, cos_t, sin_t, position_offset, st);
     }
     if (!cos_t) return bhsd_bf16_to_sentinel(src, dst, B, H, S, D, stride_columns, column_start, st);
     dim3 grid((S + 31) / 32, (D + 31) / 32, B * H), block(32, 8);

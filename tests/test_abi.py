@@ -178,3 +178,33 @@ def test_dropin_smoke_binaries_resolve_their_libraries():
         r = subprocess.run([exe, "gqa"], capture_output=True, text=True, timeout=120)
         assert f"maxHeadDimension={want}" in r.stdout, (r.stdout, r.stderr)
         assert r.returncode in (0, 4), (r.returncode, r.stdout, r.stderr)
+
+
+def test_pieces_ring_and_selftest_entry_points_validate_without_a_gpu(lib):
+    """The entry points added for the ring schedule and for failure detection refuse bad input before touching a device."""
+    d = _desc()
+    need = lib.sntl_attn_bwd_pieces_workspace_bytes(C.byref(d))
+    assert need >= 4 * 2 * 8 * 256 * 128                                     # at least the fp32 dQ accumulator
+    assert lib.sntl_attn_bwd_pieces_workspace_bytes(C.byref(_desc(dtype=_lib.DTYPE_F32))) == 0
+    assert lib.sntl_attn_bwd_pieces_workspace_bytes(C.byref(_desc(window_size=64))) == 0
+    assert lib.sntl_attn_bwd_pieces_workspace_bytes(C.byref(_desc(flags=_lib.FLAG_DETERMINISTIC))) == 0
+    dummy = C.c_void_p(16)
+    assert lib.sntl_attn_bwd_begin(C.byref(_desc(dtype=_lib.DTYPE_F32)), dummy, dummy, dummy, dummy, 1 << 30, None) == _lib.ERR_UNSUPPORTED
+    assert lib.sntl_attn_bwd_begin(C.byref(d), dummy, dummy, dummy, dummy, 16, None) == _lib.ERR_WORKSPACE
+    assert lib.sntl_attn_bwd_block(C.byref(d), dummy, dummy, dummy, dummy, None, dummy, dummy, need, None) == _lib.ERR_BAD_ARGUMENT
+    assert lib.sntl_attn_bwd_end(C.byref(d), None, dummy, need, None) == _lib.ERR_BAD_ARGUMENT
+    # deterministic flag: the backward scratch doubles its dQ accumulator
+    # (kv_heads == q_heads: no key tiles cut by query head, whose partials the default form would add to its scratch)
+    plain = lib.sntl_attn_bwd_workspace_bytes(C.byref(_desc(kv_heads=8)))
+    det = lib.sntl_attn_bwd_workspace_bytes(C.byref(_desc(kv_heads=8, flags=_lib.FLAG_DETERMINISTIC)))
+    assert det - plain == 4 * 2 * 8 * 256 * 128
+    # ring: no handle, no work
+    assert lib.sntl_ring_unique_id(None) == _lib.ERR_BAD_ARGUMENT
+    assert lib.sntl_ring_attn_workspace_bytes(None, C.byref(d)) == 0
+    assert lib.sntl_ring_attn_fwd(None, C.byref(d), dummy, dummy, dummy, dummy, dummy, dummy, 1 << 30, None) == _lib.ERR_BAD_ARGUMENT
+    assert lib.sntl_ring_comm_create(None, 0, 1, None) == _lib.ERR_BAD_ARGUMENT
+    assert lib.sntl_ring_comm_destroy(None) == _lib.OK
+    # self-test hook: limits are checked first
+    assert lib.sntl_attn_selftest_wait_timeout(0, None) == _lib.ERR_BAD_ARGUMENT
+    assert lib.sntl_attn_selftest_wait_timeout(10 ** 6, None) == _lib.ERR_BAD_ARGUMENT
+    assert lib.sntl_status_string(_lib.ERR_COMM).decode().startswith("NCCL")
