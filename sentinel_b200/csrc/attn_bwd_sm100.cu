@@ -693,41 +693,44 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
 
 // -delta = -rowsum(dO o O), lse2 = -LSE * log2(e) (-inf for padded rows and for rows without visible keys, so that
 // they produce P = 0; both are stored negated so the main kernel can use them as FMA/ADD addends), and the dQ
-// accumulator zeroed.  One warp per (b, h, padded row).
+// accumulator zeroed.  D/4 lanes per (b, h, padded row), 8 bytes of O and of dO per lane: a warp covers one row at
+// head_dim 128 and two at 64, every lane busy either way.
 template <int D>
 __global__ void bwd_pre_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ dout,
                                const float* __restrict__ lse, float* __restrict__ lse2, float* __restrict__ delta,
                                float* __restrict__ dq_accum, int Sq, int Sq_pad, long long rows_padded, int acc_words_per_row)
 {
-    const int lane = threadIdx.x & 31;
-    const long long r = blockIdx.x * (long long)(blockDim.x >> 5) + (threadIdx.x >> 5);
-    if (r >= rows_padded) return;
-    const long long bh = r / Sq_pad;
-    const int s = (int)(r - bh * Sq_pad);
-    // the accumulator is tile-permuted but covers exactly D floats per padded row: zero it linearly
-    // (D 32-bit words per row, or 2*D when the accumulator is 64-bit fixed point)
-    float4* z = reinterpret_cast<float4*>(dq_accum + r * acc_words_per_row);
-    for (int i = lane; i < acc_words_per_row / 4; i += 32) z[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (s >= Sq) {
-        if (lane == 0) { lse2[r] = -INFINITY; delta[r] = 0.0f; }
-        return;
+    constexpr int kLanesPerRow = D / 4, kRowsPerWarp = 32 / kLanesPerRow;
+    const int lane = threadIdx.x & 31, sub = lane / kLanesPerRow, l = lane % kLanesPerRow;
+    const long long r = (blockIdx.x * (long long)(blockDim.x >> 5) + (threadIdx.x >> 5)) * kRowsPerWarp + sub;
+    const bool live = r < rows_padded;
+    const long long bh = live ? r / Sq_pad : 0;
+    const int s = live ? (int)(r - bh * Sq_pad) : 0;
+    if (live) {
+        // the accumulator is tile-permuted but covers exactly acc_words_per_row 32-bit words per padded row (D, or 2*D
+        // when it is 64-bit fixed point): zero it linearly
+        float4* z = reinterpret_cast<float4*>(dq_accum + r * acc_words_per_row);
+        for (int i = l; i < acc_words_per_row / 4; i += kLanesPerRow) z[i] = make_float4(0.f, 0.f, 0.f, 0.f);
     }
-    const size_t off = ((size_t)bh * Sq + s) * D;
     float acc = 0.0f;
-    for (int d = lane * 4; d < D; d += 128) {      // 8 bytes per lane: a row of head_dim 128 is one load per tensor
-        const uint2 a = *reinterpret_cast<const uint2*>(o + off + d);
-        const uint2 g = *reinterpret_cast<const uint2*>(dout + off + d);
+    if (live && s < Sq) {
+        const size_t off = ((size_t)bh * Sq + s) * D + l * 4;
+        const uint2 a = __ldg(reinterpret_cast<const uint2*>(o + off));
+        const uint2 g = __ldg(reinterpret_cast<const uint2*>(dout + off));
         acc = fmaf(__uint_as_float(a.x << 16), __uint_as_float(g.x << 16), acc);
         acc = fmaf(__uint_as_float(a.x & 0xffff0000u), __uint_as_float(g.x & 0xffff0000u), acc);
         acc = fmaf(__uint_as_float(a.y << 16), __uint_as_float(g.y << 16), acc);
         acc = fmaf(__uint_as_float(a.y & 0xffff0000u), __uint_as_float(g.y & 0xffff0000u), acc);
     }
 #pragma unroll
-    for (int m = 16; m > 0; m >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, m);
-    if (lane == 0) {
-        const float l = lse[(size_t)bh * Sq + s];
-        lse2[r] = (l == -INFINITY) ? -INFINITY : -l * 1.4426950408889634f;
-        delta[r] = -acc;
+    for (int m = kLanesPerRow / 2; m > 0; m >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, m);
+    if (live && l == 0) {
+        if (s >= Sq) { lse2[r] = -INFINITY; delta[r] = 0.0f; }
+        else {
+            const float lv = lse[(size_t)bh * Sq + s];
+            lse2[r] = (lv == -INFINITY) ? -INFINITY : -lv * 1.4426950408889634f;
+            delta[r] = -acc;
+        }
     }
 }
 
@@ -847,7 +850,8 @@ cudaError_t launch_bwd(const TcArgs& a, cudaStream_t st)
     const int phases = a.phases ? a.phases : (kBwdPre | kBwdMain | kBwdPost);
     if (phases & kBwdPre) {
         const int warps = 8;
-        const long long blocks = (rows_padded + warps - 1) / warps;
+        const long long rows_per_block = (long long)warps * (32 / (D / 4));
+        const long long blocks = (rows_padded + rows_per_block - 1) / rows_per_block;
         bwd_pre_kernel<D><<<(unsigned)blocks, warps * 32, 0, st>>>(a.o, a.dout, a.lse, lse2, a.delta, a.dq_accum, s.Sq, Sq_pad,
                                                                     rows_padded, kDet ? 2 * D : D);
         count_launch();
