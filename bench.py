@@ -453,20 +453,33 @@ def ring_oracle_check(torch, w_local, rank, world, o, lse, dq, dk, dv):
     base = rank * S_local
     out = {}
     # rows: head h against its KV head (index 0 of the kept pair)
-    rows = np.unique(np.concatenate([np.array([0, 1, S_local // 2 - 1, S_local // 2, S_local - 129, S_local - 1]),
-                                     np.linspace(7, S_local - 9, 42).astype(np.int64)])).astype(np.int32) + base
+    # The bound is stated for whole tensors, and dQ's norm is far from uniform over the rows: a row with n visible keys
+    # has |dQ|^2 ~ 1/n, so the first rows of the sequence carry much of it (and, with two or three keys and no averaging
+    # of the bf16 roundings of P and dS, the largest relative error).  A stratified sample estimates the whole-shard
+    # figure without bias: every one of the first 256 rows of the sequence (weight 1; they cost next to nothing) plus
+    # uniformly spaced rows of the rest, each standing for the rows between it and the next (weight = spacing).
+    # A row costs (its position) x D oracle work: many rows on the early shards, fewer at the end of a long sequence.
+    n_uniform = 256 if base + S_local <= 32768 else 90
+    head_rows = np.arange(min(256, S_local)) if rank == 0 else np.zeros(0, dtype=np.int64)
+    lo = len(head_rows)
+    uni = np.unique(np.linspace(lo, S_local - 1, n_uniform).astype(np.int64))
+    rows = (np.concatenate([head_rows, uni]) + base).astype(np.int32)
+    weights = np.concatenate([np.ones(lo), np.full(len(uni), (S_local - lo) / len(uni))])
     hi = hs.index(h)
     wo, wl, wdq = cpu.attn_rows(qf[:, hi:hi + 1], kf[:, 0:1], vf[:, 0:1], dof[:, hi:hi + 1], 0, 0, rows)
     loc = rows - base
     got_o, got_dq = o[0, h, loc].float().cpu().numpy(), dq[0, h, loc].float().cpu().numpy()
     got_l = lse[0, h, loc].float().cpu().numpy()
 
-    def errs(got, want):
-        return {"max_abs": float(np.abs(got - want).max()), "rel_l2": float(np.linalg.norm(got - want) / max(np.linalg.norm(want), 1e-30))}
+    def errs(got, want, w=None):
+        d2 = ((got - want) ** 2).sum(axis=-1)
+        r2 = (want ** 2).sum(axis=-1)
+        w = np.ones(len(d2)) if w is None else w
+        return {"max_abs": float(np.abs(got - want).max()), "rel_l2": float(np.sqrt((w * d2).sum() / max((w * r2).sum(), 1e-60)))}
 
-    out["o"], out["dq"] = errs(got_o, wo), errs(got_dq, wdq)
+    out["o"], out["dq"] = errs(got_o, wo, weights), errs(got_dq, wdq, weights)
     out["lse_max_abs"] = float(np.abs(got_l - wl).max())
-    out["rows"] = [int(x) for x in rows]
+    out["rows_sampled"] = int(len(rows))
     if rank == world - 1:
         S = S_local * world
         cols = np.array([S - 385, S - 130, S - 1], dtype=np.int32)
