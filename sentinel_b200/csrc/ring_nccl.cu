@@ -336,7 +336,11 @@ static int make_handle(ncclComm_t comm, bool owns, int rank, int world, sntl_rin
     if (!c) return SNTL_ERR_CUDA;
     c->comm = comm; c->owns_comm = owns; c->rank = rank; c->world = world;
     bool ok = cudaGetDevice(&c->device) == cudaSuccess;
-    ok = ok && cudaStreamCreateWithFlags(&c->comm_stream, cudaStreamNonBlocking) == cudaSuccess;
+    // the communication stream gets the highest priority: its few CTAs must get onto an SM as soon as one frees up, not
+    // after every CTA of the compute kernels queued before them has been dispatched, or the transfers stop hiding
+    int prio_least = 0, prio_greatest = 0;
+    ok = ok && cudaDeviceGetStreamPriorityRange(&prio_least, &prio_greatest) == cudaSuccess;
+    ok = ok && cudaStreamCreateWithPriority(&c->comm_stream, cudaStreamNonBlocking, prio_greatest) == cudaSuccess;
     ok = ok && cudaStreamCreateWithFlags(&c->side_stream, cudaStreamNonBlocking) == cudaSuccess;
     cudaEvent_t* evs[] = {&c->ev_main, &c->ev_side, &c->ev_kv, &c->ev_acc, &c->ev_deal};
     for (cudaEvent_t* e : evs) ok = ok && cudaEventCreateWithFlags(e, cudaEventDisableTiming) == cudaSuccess;
