@@ -37,6 +37,23 @@ NCU_DRAM_BYTES_PER_BATCH = {"gqa7b_d128": (1870.9e6 + 988.1e6) / 2}
 NCU_CACHED_DRAM_BYTES_PER_BATCH = {"gqa7b_d128": (268640768 + 5306880) / 16.0}
 
 
+class stdout_to_stderr:
+    """File-descriptor-level redirect of standard output to standard error.  NCCL prints a version banner on standard
+    output when the first communicator of a process is made; this program's standard output carries ONE JSON line, so
+    communicator set-up runs inside this."""
+
+    def __enter__(self):
+        sys.stdout.flush()
+        self.saved = os.dup(1)
+        os.dup2(2, 1)
+        return self
+
+    def __exit__(self, *a):
+        sys.stdout.flush()
+        os.dup2(self.saved, 1)
+        os.close(self.saved)
+
+
 def load_peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -100,6 +117,7 @@ class ClockSampler:
         return {"sm_mhz": s[len(s) // 2], "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": len(s)}
 
 
+EXTRA_LEGS_LIMIT_S = 300      # strong-scaling + ring legs (N > 1) or the other workloads (N = 1) together
 CPU_SAMPLE_MAX_SEQ = 8192     # one head at S = 8192 keeps two S x S fp32 matrices (2 x 268 MB): the largest length sampled
 CPU_SAMPLE_PASSES = 3         # about 4 s per pass at S = 8192 on 16-32 cores
 
@@ -598,7 +616,10 @@ def main():
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+        with stdout_to_stderr():
+            dist.init_process_group("nccl", device_id=dev)
+            dist.barrier(device_ids=[local])       # the communicator exists (and has said so) before anything is printed
+            torch.cuda.synchronize()
     sb._lib.load()
     barrier, timed = _make_timed(torch, dist, dev, world, local)
 
@@ -734,23 +755,7 @@ def main():
                 "bwd_ms": bwd_ms,
                 "fwd_bwd_frac_of_burst_peak": flops_rank / (ms_per_step * 1e-3) / 1e12 / burst}
 
-    extras = {}
-    plain_headline = ring is None and not mask and args.batch == 0 and not args.lean
-    if plain_headline and world == 1:
-        extras["other_workloads"] = [run_other_workload(torch, sb, n, dev, peaks) for n in ("llama1b_gqa", "gpt2_small")]
-    if plain_headline and world > 1:
-        extras["strong"] = run_strong_scaling(torch, dist, sb, w, dev, rank, world, timed, args.steps, ms_per_step)
-        extras["ring"] = run_ring(torch, dist, sb, dev, rank, world, timed, max(3, min(args.steps, 5)), value / world)
-    status = status or sb.poll_device_status()
-
-    if rank == 0:
-        cpu_base = None
-        if not args.no_cpu_baseline and world == 1:
-            try:
-                r = cpu_reference_sample(w)
-                cpu_base = {kk: r[kk] for kk in ("value", "unit", "cores", "kind", "sample")}
-            except Exception as exc:  # the checker is optional for the bench line, never for the product path
-                cpu_base = {"value": None, "unit": UNIT, "cores": 0, "kind": "port", "sample": f"unavailable: {exc}"}
+    def make_line(extras, status_now):
         line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
                 "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
                 "dtype": "bf16" if w.dtype == "bf16" else "f32", "data": "synthetic",
@@ -768,12 +773,51 @@ def main():
                         "frac_of_copy_bound": (copy_ms / e2e_ms) if (copy_ms and not args.skip_e2e) else None,
                         "copy_bound": "the same bytes as plain pinned copies, both directions at once, all ranks at once, no kernels"},
                 "gpu_launches": int(launches), "clocks": clock_summary, "roofline": roofline,
-                "device_status": status}
+                "device_status": status_now}
         if sustained is not None:
             line["sustained"] = sustained
         line.update(extras)
-        if cpu_base is not None:
-            line["cpu_baseline"] = cpu_base
+        return line
+
+    # The extra legs (other workloads; strong scaling and the ring at N > 1) come after every number of the headline
+    # line is in hand.  Should one of them stall -- a peer that died, an NCCL set-up problem on the box -- a watchdog
+    # prints the headline line without it and ends the process, so that the main measurement is never lost to them.
+    extras = {}
+    done = threading.Event()
+
+    def watchdog():
+        if done.wait(EXTRA_LEGS_LIMIT_S):
+            return
+        if rank == 0:
+            late = dict(extras)
+            late["extra_legs"] = {"unavailable": f"not finished within {EXTRA_LEGS_LIMIT_S} s; the headline figures above are complete"}
+            print(json.dumps(make_line(late, status)), flush=True)
+        os._exit(0)
+
+    threading.Thread(target=watchdog, daemon=True).start()
+    plain_headline = ring is None and not mask and args.batch == 0 and not args.lean
+    if plain_headline and world == 1:
+        extras["other_workloads"] = [run_other_workload(torch, sb, n, dev, peaks) for n in ("llama1b_gqa", "gpt2_small")]
+    if plain_headline and world > 1:
+        try:
+            extras["strong"] = run_strong_scaling(torch, dist, sb, w, dev, rank, world, timed, args.steps, ms_per_step)
+        except Exception as exc:
+            extras["strong"] = {"unavailable": f"{type(exc).__name__}: {exc}"}
+        try:
+            extras["ring"] = run_ring(torch, dist, sb, dev, rank, world, timed, max(3, min(args.steps, 5)), value / world)
+        except Exception as exc:
+            extras["ring"] = {"unavailable": f"{type(exc).__name__}: {exc}"}
+    status = status or sb.poll_device_status()
+    done.set()
+
+    if rank == 0:
+        line = make_line(extras, status)
+        if not args.no_cpu_baseline and world == 1:
+            try:
+                r = cpu_reference_sample(w)
+                line["cpu_baseline"] = {kk: r[kk] for kk in ("value", "unit", "cores", "kind", "sample")}
+            except Exception as exc:  # the checker is optional for the bench line, never for the product path
+                line["cpu_baseline"] = {"value": None, "unit": UNIT, "cores": 0, "kind": "port", "sample": f"unavailable: {exc}"}
         if world == 1 and ring is None and not args.no_cpu_baseline:
             try:
                 line["reference_cuda"] = reference_cuda_sample(w, q, k, v, do)
