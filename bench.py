@@ -31,7 +31,7 @@ UNIT = "TFLOP/s"
 FALLBACK_PEAKS = {"bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "hbm_gbs": 6650.0}
 # DRAM bytes (read + write) of one launch of the dominant kernel per batch element, from the ncu capture summarised in
 # profiles/attn_bwd_tc_kernel_gqa7b_d128.md (captured on the full workload, batch 2; traffic grows in proportion to the batch)
-NCU_DRAM_BYTES_PER_BATCH = {"gqa7b_d128": (1870.9e6 + 988.1e6) / 2}
+NCU_DRAM_BYTES_PER_BATCH = {"gqa7b_d128": (1823.955e6 + 987.866e6) / 2}
 # the same for the cache-mode forward kernel, one new token, no window (profiles/attn_fwd_tc_kernel_cache_mode_gqa7b_d128.md,
 # captured at batch 16)
 NCU_CACHED_DRAM_BYTES_PER_BATCH = {"gqa7b_d128": (268640768 + 5306880) / 16.0}
