@@ -334,7 +334,7 @@ int sntl_attn_bwd(const sntl_attn_desc* d, const void* q, const void* k, const v
     if (!c.ok) return SNTL_ERR_WORKSPACE;
     const size_t sq_pad = ((size_t)d->seq_q + 127) / 128 * 128;
     t.delta = (float*)tcws;
-    t.dq_accum = (float*)(tcws + align_up(2 * 4 * (size_t)d->batch * d->q_heads * sq_pad));  // after [delta | lse*log2e]
+    t.dq_accum = (float*)(tcws + align_up(kBwdRowAuxBytes * (size_t)d->batch * d->q_heads * sq_pad));  // after the per-row records
     g_last_path = "tcgen05";
     if (!needs_staging(d)) {
         t.q = (const __nv_bfloat16*)q; t.k = (const __nv_bfloat16*)k; t.v = (const __nv_bfloat16*)v;
@@ -389,14 +389,14 @@ size_t pieces_workspace_bytes(const sntl_attn_desc* d)
 {
     const size_t sq_pad = ((size_t)d->seq_q + 127) / 128 * 128;
     const size_t rows = (size_t)d->batch * d->q_heads * sq_pad;
-    return align_up(2 * 4 * rows) + align_up(4 * rows * (size_t)d->head_dim);
+    return align_up(kBwdRowAuxBytes * rows) + align_up(4 * rows * (size_t)d->head_dim);
 }
 void pieces_args(const sntl_attn_desc* d, void* workspace, TcArgs& t)
 {
     t.s = shape_of(d);
     const size_t sq_pad = ((size_t)d->seq_q + 127) / 128 * 128;
     t.delta = (float*)workspace;
-    t.dq_accum = (float*)((char*)workspace + align_up(2 * 4 * (size_t)d->batch * d->q_heads * sq_pad));
+    t.dq_accum = (float*)((char*)workspace + align_up(kBwdRowAuxBytes * (size_t)d->batch * d->q_heads * sq_pad));
 }
 }  // namespace
 }  // namespace sntl

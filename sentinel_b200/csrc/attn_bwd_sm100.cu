@@ -11,11 +11,13 @@
 //     materialises repeated K/V and reduces afterwards, CudaCausalSelfAttention.cu:27-44);
 //   * everything is computed transposed (rows = keys) so that both P^T and dS^T are consumed by the next MMA
 //     straight from TMEM as the A operand:
-//         S^T  = K  Q^T          (K, Q  K-major from shared memory)      -> TMEM
-//         dP^T = V  dO^T         (V, dO K-major from shared memory)      -> TMEM
-//         P^T  = exp2(S^T*scale*log2e - LSE*log2e), causal mask on the diagonal tile, bf16 back over S^T
+//         S^T  = K  Q^T  - 1 (LSE/scale)^T    (K, Q  K-major from shared memory)      -> TMEM
+//         dP^T = V  dO^T - 1 delta^T          (V, dO K-major from shared memory)      -> TMEM
+//           (the rank-one terms ride along as one extra 16-wide contraction step: a constant block of ones on the key
+//            side, a 16-byte record per query on the other, so no per-column operand reaches the compute warps)
+//         P^T  = exp2(scale*log2e * that), causal mask on the diagonal tile, bf16 back over S^T
 //         dV  += P^T  dO         (A = P^T in TMEM,  B = dO tile MN-major)
-//         dS^T = P^T o (dP^T - delta), bf16 into a shared-memory tile [key][query]
+//         dS^T = P^T o that, a packed bf16 product, into a shared-memory tile [key][query]
 //         dQ_i = dS   K          (A = that tile read MN-major, B = K tile MN-major)
 //         dK  += dS^T Q          (A = the same tile read K-major, B = Q tile MN-major)
 //     the softmax scale is folded into the final dK store and the dQ conversion pass;
@@ -27,8 +29,9 @@
 //     (setmaxnreg).  Q (+LSE, delta) is double-buffered; dO is double-buffered for D=64 and single-buffered for
 //     D=128 (shared-memory capacity).
 //
-// A pre-pass computes delta = rowsum(dO o O), LSE*log2e (padded rows get +inf so they produce P = 0) and
-// zeroes the dQ accumulator; a post-pass converts the accumulator to bf16 dQ (times scale).
+// A pre-pass computes the per-query records (delta = rowsum(dO o O) and LSE/scale, each split in two bf16; padded rows get a
+// huge LSE so they produce P = 0) and zeroes the dQ accumulator; a post-pass converts the accumulator to bf16 dQ (times
+// scale).
 //
 // Long key tiles.  The CTA of key tile 0 visits every query tile of every head of its group; when the grid is small
 // (few batch elements x KV heads, as in the chunks of the host-buffer pipeline) or a sliding window leaves only the
@@ -56,8 +59,8 @@ enum BwdSite : uint32_t {
 
 struct BwdParams {
     __nv_bfloat16 *dk, *dv;
-    const float* lse2;     // [B][Hq][Sq_pad]  -LSE * log2(e), -inf on padded rows
-    const float* delta;    // [B][Hq][Sq_pad]  -rowsum(dO o O)
+    const uint4* qaug;     // [B][Hq][Sq_pad] one 16-byte record per query: bf16 (hi, lo, 0 x 6) of -LSE / scale
+    const uint4* doaug;    // the same for -delta = -rowsum(dO o O)
     float* dq_accum;       // [B*Hq][n_qt][D/4][128][4]
     int B, Hq, Hkv, Sq, Skv, Sq_pad;
     int causal;
@@ -115,6 +118,175 @@ struct BwdBarriers {
     uint32_t abort_flag;
 };
 
+// Shared-memory descriptor of an unswizzled K-major operand of ONE contraction step (16 bf16 = two 8-element column
+// blocks): a column block is rows of 16 bytes, eight rows forming one 128-byte core matrix (SBO = 128 to the next eight
+// rows); LBO is the distance from the first column block to the second.
+__device__ __forceinline__ uint64_t make_sdesc_plain(uint32_t smem_addr, uint32_t lbo_bytes)
+{
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3ffffu) >> 4);
+    d |= (uint64_t)((lbo_bytes >> 4) & 0x3fffu) << 16;
+    d |= (uint64_t)(128u >> 4) << 32;
+    d |= (uint64_t)1 << 46;  // descriptor version (Blackwell); swizzle field 0 = none
+    return d;
+}
+
+// One dQ tile (this thread's row in registers) -> staging buffers -> asynchronous bulk add-reductions into the accumulator
+// tile, kStageCols columns per piece.  Called by all 128 threads of the drain warpgroup (named barrier 1); `elected` is the
+// one thread that owns the bulk groups.  kStagingBytes of staging in all; `piece` counts pieces over the CTA's lifetime, so
+// that the rotation carries on from tile to tile (a buffer is rewritten only after the kStages - 1 groups issued since
+// its last use are all that may still be reading).
+template <int D, bool kDet, int kStageCols, int kStagingBytes>
+__device__ __forceinline__ void push_dq_tile(const uint32_t (&r)[D], float* tile, uint8_t* sStage, int row, bool elected, uint32_t& piece)
+{
+    constexpr int kStageBytes = kStageCols * kT * 4;
+    constexpr int kStages = kStagingBytes / kStageBytes;
+    static_assert(kStages >= 2 && kStages * kStageBytes == kStagingBytes, "staging must hold whole pieces");
+    if constexpr (!kDet) {
+#pragma unroll
+        for (int c = 0; c < D / kStageCols; ++c) {
+            uint8_t* stage = sStage + (piece++ % kStages) * kStageBytes;
+            if (elected) bulk_wait_read<kStages - 1>();
+            named_barrier_sync(1, 128);
+#pragma unroll
+            for (int v = 0; v < kStageCols / 4; ++v)
+                *reinterpret_cast<uint4*>(stage + ((size_t)v * kT + row) * 16) =
+                    make_uint4(r[c * kStageCols + 4 * v], r[c * kStageCols + 4 * v + 1], r[c * kStageCols + 4 * v + 2], r[c * kStageCols + 4 * v + 3]);
+            fence_proxy_async_smem();
+            named_barrier_sync(1, 128);
+            if (elected) {
+                bulk_reduce_add_f32(tile + (size_t)c * kStageCols * kT, stage, (uint32_t)kStageBytes);
+                bulk_commit();
+            }
+        }
+    } else {
+        // Order-independent form: each fp32 value times 2^32 is an integer that fits 64 bits exactly (24-bit
+        // mantissa, |value| < 2^31), and integer addition is associative, so the accumulated sum is the same
+        // whatever order the key tiles arrive in.  Same staging buffers, half as many columns per piece; the
+        // accumulator tile is [d/2][row][2] 64-bit words, so a piece is still one contiguous block.
+        constexpr int kDetCols = kStageCols / 2;
+        unsigned long long* tile64 = reinterpret_cast<unsigned long long*>(tile);
+#pragma unroll
+        for (int c = 0; c < D / kDetCols; ++c) {
+            uint8_t* stage = sStage + (piece++ % kStages) * kStageBytes;
+            if (elected) bulk_wait_read<kStages - 1>();
+            named_barrier_sync(1, 128);
+#pragma unroll
+            for (int v = 0; v < kDetCols / 2; ++v) {
+                const long long a = __float2ll_rn(__uint_as_float(r[c * kDetCols + 2 * v]) * 4294967296.0f);
+                const long long b2 = __float2ll_rn(__uint_as_float(r[c * kDetCols + 2 * v + 1]) * 4294967296.0f);
+                *reinterpret_cast<ulonglong2*>(stage + ((size_t)v * kT + row) * 16) =
+                    make_ulonglong2((unsigned long long)a, (unsigned long long)b2);
+            }
+            fence_proxy_async_smem();
+            named_barrier_sync(1, 128);
+            if (elected) {
+                bulk_reduce_add_u64(tile64 + (size_t)c * kDetCols * kT, stage, (uint32_t)kStageBytes);
+                bulk_commit();
+            }
+        }
+    }
+}
+
+// Epilogue of a compute warpgroup: its accumulator (dV for warpgroup 0, dK for warpgroup 1; `src` = TMEM address of this
+// thread's row) leaves as an fp32 partial (cut tiles), is added into the caller's fp32 accumulators, or is stored as bf16
+// through `stage_base` (a shared-memory tile no product reads any more).
+template <int D>
+__device__ __forceinline__ void write_dkv(const BwdParams& p, bool ok, bool split, int n_iter, int wg, int warp, int lane, int row,
+                                          uint32_t src, int kt, int slab, int slabs, int group, int g0, int k0, uint8_t* stage_base)
+{
+    if (split) {
+        // this CTA's share of dV (warpgroup 0) / dK (warpgroup 1) as an fp32 partial; zeros if it saw no query
+        float* dst = p.dkv_part + ((((size_t)kt * slabs + slab) * group + g0) * 2 + wg) * (size_t)(kT * D) + (size_t)row * D;
+        if (ok) tc_fence_after();
+#pragma unroll
+        for (int c = 0; c < D / 32; ++c) {
+            uint32_t r[32];
+            if (ok) {
+                tmem_ld32(src + (uint32_t)(c * 32), r);
+                tmem_ld_wait();
+            } else {
+#pragma unroll
+                for (int v = 0; v < 32; ++v) r[v] = 0u;
+            }
+#pragma unroll
+            for (int v = 0; v < 8; ++v)
+                *reinterpret_cast<uint4*>(dst + c * 32 + v * 4) = make_uint4(r[4 * v], r[4 * v + 1], r[4 * v + 2], r[4 * v + 3]);
+        }
+    } else if (ok && p.dk_acc != nullptr) {
+        // accumulate form: this CTA is the only writer of its 128 key rows in this launch
+        tc_fence_after();
+        const int key = k0 + row;
+        const bool store = key < p.Skv;
+        const float mul = wg == 0 ? 1.0f : p.scale;
+        float* dst = (wg == 0 ? p.dv_acc : p.dk_acc) + ((size_t)slab * p.Skv + (size_t)(store ? key : 0)) * D;
+#pragma unroll
+        for (int c = 0; c < D / 32; ++c) {
+            uint32_t r[32];
+            tmem_ld32(src + (uint32_t)(c * 32), r);
+            tmem_ld_wait();
+            if (store) {
+#pragma unroll
+                for (int v = 0; v < 8; ++v) {
+                    float4 a = *reinterpret_cast<const float4*>(dst + c * 32 + v * 4);
+                    a.x = fmaf(__uint_as_float(r[4 * v + 0]), mul, a.x);
+                    a.y = fmaf(__uint_as_float(r[4 * v + 1]), mul, a.y);
+                    a.z = fmaf(__uint_as_float(r[4 * v + 2]), mul, a.z);
+                    a.w = fmaf(__uint_as_float(r[4 * v + 3]), mul, a.w);
+                    *reinterpret_cast<float4*>(dst + c * 32 + v * 4) = a;
+                }
+            }
+        }
+    } else if (ok) {
+        tc_fence_after();
+        const int key = k0 + row;
+        const bool store = key < p.Skv;
+        const float mul = wg == 0 ? 1.0f : p.scale;
+        // Coalesced bf16 store: a thread holds one whole key row, so the warp's 32 rows go through shared memory (the V
+        // tile's buffer for dV, the K tile's for dK: every product has retired) and leave with each store instruction
+        // covering whole rows; 16-byte units are XOR-swizzled by the row against bank conflicts.
+        (void)store;
+        __nv_bfloat16* out = (wg == 0 ? p.dv : p.dk) + (size_t)slab * p.Skv * D;
+        constexpr int kUnits = D / 8;
+        uint8_t* stage = stage_base + (warp & 3) * 32 * (D * 2);
+#pragma unroll
+        for (int c = 0; c < D / 32; ++c) {
+            uint32_t r[32];
+            tmem_ld32(src + (uint32_t)(c * 32), r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+                uint4 w;
+                w.x = pack_bf16(__uint_as_float(r[8 * v + 0]) * mul, __uint_as_float(r[8 * v + 1]) * mul);
+                w.y = pack_bf16(__uint_as_float(r[8 * v + 2]) * mul, __uint_as_float(r[8 * v + 3]) * mul);
+                w.z = pack_bf16(__uint_as_float(r[8 * v + 4]) * mul, __uint_as_float(r[8 * v + 5]) * mul);
+                w.w = pack_bf16(__uint_as_float(r[8 * v + 6]) * mul, __uint_as_float(r[8 * v + 7]) * mul);
+                const int unit = c * 4 + v;
+                *reinterpret_cast<uint4*>(stage + lane * (D * 2) + ((unit ^ (lane & 7)) << 4)) = w;
+            }
+        }
+        __syncwarp();
+        {
+            constexpr int kRowsPerStore = 32 / kUnits;
+            const int sub = lane / kUnits, unit = lane % kUnits;
+            const int key_warp0 = key - lane;               // first key row of this warp
+#pragma unroll
+            for (int i = 0; i < 32 / kRowsPerStore; ++i) {
+                const int rr = i * kRowsPerStore + sub;
+                const uint4 w = *reinterpret_cast<const uint4*>(stage + rr * (D * 2) + ((unit ^ (rr & 7)) << 4));
+                if (key_warp0 + rr < p.Skv) *reinterpret_cast<uint4*>(out + (size_t)(key_warp0 + rr) * D + unit * 8) = w;
+            }
+        }
+    } else if (n_iter == 0 && p.dk_acc == nullptr) {
+        // a key tile no query can see (cannot happen for causal with Sq == Skv; kept for safety): zero grads
+        const int key = k0 + row;
+        if (key < p.Skv) {
+            __nv_bfloat16* dst = (wg == 0 ? p.dv : p.dk) + ((size_t)slab * p.Skv + key) * D;
+            for (int d = 0; d < D; d += 8) *reinterpret_cast<uint4*>(dst + d) = make_uint4(0, 0, 0, 0);
+        }
+    }
+}
+
 // kSplit: the grid may hold key tiles cut by query head (a separate instantiation, so that the plain kernel carries none
 // of that bookkeeping)
 // kDet: dQ contributions leave as 64-bit fixed point (see the drain warpgroup)
@@ -127,12 +299,20 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
     constexpr int kChunkBytes = kT * 128;          // 128 rows x 128 B
     constexpr int kChunks = D / 64;
     constexpr int kDoStages = (D == 128) ? 1 : 2;  // shared-memory capacity: 227 KB
-    // columns of a dQ tile per bulk reduction: 8 KB pieces (four in flight) at head_dim 128, where the tile loads of Q and
-    // dO queue behind the reductions in the TMA engine and shorter pieces let them through sooner (-3 % kernel time);
-    // 16 KB pieces at head_dim 64 (there the finer split costs 1 %, and 4 KB pieces cost 10-20 % at either size)
+    // columns of a dQ tile per bulk reduction (kStageCols columns x 128 rows fp32 = one piece): 8 KB pieces at head_dim 128,
+    // where the tile loads of Q and dO queue behind the reductions on the SM's path to L2 and shorter pieces let them through
+    // sooner (-3 % kernel time); 16 KB pieces at head_dim 64 (there the finer split costs 1 %, and 4 KB pieces cost 10-20 %
+    // at either size)
     constexpr int kStageCols = (D == 128) ? 16 : 32;
-    constexpr int kStageBytes = kStageCols * kT * 4;   // dQ staging: kStageCols columns x 128 rows fp32 = one bulk reduction
-    constexpr int kStages = 2 * 32 * kT * 4 / kStageBytes;   // 32 KB of staging in all
+    // staging in all: 32 KB at head_dim 64; 24 KB (three pieces) at 128, where shared memory is full
+    constexpr int kStagingBytes = (D == 128) ? 24 * 1024 : 32 * 1024;
+    // The extra contraction step.  S^T and dP^T each get one more 16-wide k-step whose operands are not tile data: on the
+    // key side a constant block (1, 1, 0, ...), on the query side a 16-byte record per query, (hi, lo, 0, ...) with
+    // hi + lo = -LSE/scale (for S^T) or -delta (for dP^T) split in two bf16.  The tensor core then delivers
+    // S^T - LSE/scale and dP^T - delta, and the compute warps need no per-column operand from shared memory at all:
+    // P^T = exp2(scale*log2e * that) and dS^T = P^T o that.  One column block (8 bf16) per operand is real; the second
+    // block of the constant operand is zeros, so the second block of the record operand may alias the first (LBO 0).
+    constexpr int kAugBytes = kT * 16;             // 128 records
     constexpr int kDsBytes = kT * kT * 2;          // dS^T tile: [128 keys][128 queries] bf16 as two 64-query chunks
     // The layout uses every byte of the 227 KB a CTA may have (D = 128), so there is no room for an alignment
     // pad: the kernel has no static shared memory, which puts the dynamic window at the 1024-byte aligned start
@@ -144,10 +324,11 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
     uint8_t* sQ = sV + kTileBytes;                 // [2]
     uint8_t* sDo = sQ + 2 * kTileBytes;            // [kDoStages]
     uint8_t* sDs = sDo + kDoStages * kTileBytes;
-    uint8_t* sStage = sDs + kDsBytes;              // [kStages][kStageBytes]
-    float* sLse = (float*)(sStage + kStages * kStageBytes);   // [2][128]
-    float* sDelta = sLse + 2 * kT;                 // [2][128]
-    BwdBarriers* bars = (BwdBarriers*)(sDelta + 2 * kT);
+    uint8_t* sStage = sDs + kDsBytes;              // kStagingBytes
+    uint8_t* sOnes = sStage + kStagingBytes;       // [2][kAugBytes]: the constant block, then zeros
+    uint8_t* sQaug = sOnes + 2 * kAugBytes;        // [2][kAugBytes]
+    uint8_t* sDoaug = sQaug + 2 * kAugBytes;       // [kDoStages][kAugBytes]
+    BwdBarriers* bars = (BwdBarriers*)(sDoaug + kDoStages * kAugBytes);
     volatile uint32_t* abort_flag = &bars->abort_flag;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -209,6 +390,11 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
         tmem_alloc(&bars->tmem_base, kTmemCols);
         tmem_relinquish();
     }
+    if (threadIdx.x < kT) {
+        reinterpret_cast<uint4*>(sOnes)[threadIdx.x] = make_uint4(0x3f803f80u, 0u, 0u, 0u);   // bf16 (1, 1, 0, 0, 0, 0, 0, 0)
+        reinterpret_cast<uint4*>(sOnes + kAugBytes)[threadIdx.x] = make_uint4(0u, 0u, 0u, 0u);
+        fence_proxy_async_smem();
+    }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -236,16 +422,16 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
                 const int bh = b * p.Hq + hk * group + g0 + g;
                 const int sq = i & 1;
                 if (i >= 2 && !mbar_wait(&bars->q_empty[sq], (uint32_t)(((i >> 1) - 1) & 1), abort_flag, kSiteQEmpty)) break;
-                mbar_arrive_expect_tx(&bars->q_full[sq], (uint32_t)(kTileBytes + 2 * kT * 4));
+                mbar_arrive_expect_tx(&bars->q_full[sq], (uint32_t)(kTileBytes + kAugBytes));
                 for (int c = 0; c < kChunks; ++c)
                     tma_load_3d(sQ + sq * kTileBytes + c * kChunkBytes, &tmap_q, &bars->q_full[sq], c * 64, qt * kT, bh);
-                bulk_load_1d(sLse + sq * kT, p.lse2 + (size_t)bh * p.Sq_pad + (size_t)qt * kT, kT * 4, &bars->q_full[sq]);
-                bulk_load_1d(sDelta + sq * kT, p.delta + (size_t)bh * p.Sq_pad + (size_t)qt * kT, kT * 4, &bars->q_full[sq]);
+                bulk_load_1d(sQaug + sq * kAugBytes, p.qaug + (size_t)bh * p.Sq_pad + (size_t)qt * kT, kAugBytes, &bars->q_full[sq]);
                 const int sd = i % kDoStages;
                 if (i >= kDoStages &&
                     !mbar_wait(&bars->do_empty[sd], (uint32_t)(((i / kDoStages) - 1) & 1), abort_flag, kSiteDoEmpty))
                     break;
-                mbar_arrive_expect_tx(&bars->do_full[sd], (uint32_t)kTileBytes);
+                mbar_arrive_expect_tx(&bars->do_full[sd], (uint32_t)(kTileBytes + kAugBytes));
+                bulk_load_1d(sDoaug + sd * kAugBytes, p.doaug + (size_t)bh * p.Sq_pad + (size_t)qt * kT, kAugBytes, &bars->do_full[sd]);
                 for (int c = 0; c < kChunks; ++c)
                     tma_load_3d(sDo + sd * kTileBytes + c * kChunkBytes, &tmap_do, &bars->do_full[sd], c * 64, qt * kT, bh);
             }
@@ -274,13 +460,16 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
             auto wait = [&](uint64_t* bar, uint32_t parity, uint32_t site) {
                 return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag, site));
             };
-            auto issue_kmajor = [&](uint32_t d_tmem, uint64_t a, uint64_t b) {
+            const uint64_t d_ones = make_sdesc_plain(smem_u32(sOnes), kAugBytes), d_qaug0 = make_sdesc_plain(smem_u32(sQaug), 0);
+            // the D/16 steps over the head dimension, then the extra step that subtracts LSE/scale (see kAugBytes)
+            auto issue_kmajor = [&](uint32_t d_tmem, uint64_t a, uint64_t b, uint64_t aug) {
                 mma_ss_e<false>(d_tmem, a, b, idesc_st);
 #pragma unroll
                 for (int ks = 1; ks < D / 16; ++ks) {
                     const uint32_t off = (uint32_t)((ks >> 2) * kChunkBytes + (ks & 3) * 32);
                     mma_ss_e<true>(d_tmem, sdesc_advance(a, off), sdesc_advance(b, off), idesc_st);
                 }
+                mma_ss_e<true>(d_tmem, d_ones, aug, idesc_st);
             };
             auto issue_from_tmem = [&](uint32_t d_tmem, uint32_t a_tmem, uint64_t b, bool accumulate) {
                 if (accumulate) mma_ts_e<true>(d_tmem, a_tmem, b, idesc_kv);
@@ -295,7 +484,7 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
             ok = ok && wait(&bars->q_full[0], 0, kSiteQFull);
             if (ok) {
                 tc_fence_after();
-                issue_kmajor(tm_S, dK_k, dQ_k0);
+                issue_kmajor(tm_S, dK_k, dQ_k0, d_qaug0);
                 tc_commit_e(&bars->s_ready);
             }
             for (int i = 0; ok && i < n_iter; ++i) {
@@ -312,7 +501,7 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
                     const int nq = (i + 1) & 1;
                     if (!(ok = wait(&bars->q_full[nq], (uint32_t)(((i + 1) >> 1) & 1), kSiteQFull))) break;
                     tc_fence_after();
-                    issue_kmajor(tm_S, dK_k, sdesc_advance(dQ_k0, nq * kTileBytes));
+                    issue_kmajor(tm_S, dK_k, sdesc_advance(dQ_k0, nq * kTileBytes), sdesc_advance(d_qaug0, nq * kAugBytes));
                     tc_commit_e(&bars->s_ready);
                     SNTL_TRACE_EV(tl, 0, tn, 9);
                 }
@@ -327,14 +516,17 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
             // C[128 x 128] = A[128 x D] * B[128 x D]^T, both K-major tiles; one descriptor per tile, advanced per k-step
             // by a 64-bit add (the empty asm keeps the compiler from hoisting every advanced descriptor out of the main
             // loop, which would cost this warp more registers than it is allotted)
-            auto issue_kmajor = [&](uint32_t d_tmem, uint64_t a, uint64_t b) {
-                asm volatile("" : "+l"(a), "+l"(b));
+            const uint64_t d_ones = make_sdesc_plain(smem_u32(sOnes), kAugBytes), d_doaug0 = make_sdesc_plain(smem_u32(sDoaug), 0);
+            // the D/16 steps over the head dimension, then the extra step that subtracts delta (see kAugBytes)
+            auto issue_kmajor = [&](uint32_t d_tmem, uint64_t a, uint64_t b, uint64_t aug) {
+                asm volatile("" : "+l"(a), "+l"(b), "+l"(aug));
                 mma_ss_c<false>(d_tmem, a, b, idesc_st);
 #pragma unroll
                 for (int ks = 1; ks < D / 16; ++ks) {
                     const uint32_t off = (uint32_t)((ks >> 2) * kChunkBytes + (ks & 3) * 32);
                     mma_ss_c<true>(d_tmem, sdesc_advance(a, off), sdesc_advance(b, off), idesc_st);
                 }
+                mma_ss_c<true>(d_tmem, d_ones, aug, idesc_st);
             };
             bool ok = mbar_wait(&bars->kv_full, 0, abort_flag, kSiteKV);
             {
@@ -345,7 +537,7 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
                 ok = ok && mbar_wait(&bars->do_full[0], 0, abort_flag, kSiteDoFull);
                 if (ok) {
                     tc_fence_after();
-                    issue_kmajor(tm_dP, dV_k, dDo_k0);
+                    issue_kmajor(tm_dP, dV_k, dDo_k0, d_doaug0);
                     tc_commit(&bars->dp_ready);
                     tc_commit(&bars->do_empty[0]);   // this warp's share of releasing dO_0: dP^T_0
                 }
@@ -387,7 +579,7 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
                         SNTL_TRACE_EV(true, 4, tn, 5);
                         if (!(ok = mbar_wait(&bars->do_full[nd], (uint32_t)(((i + 1) / kDoStages) & 1), abort_flag, kSiteDoFull))) break;
                         tc_fence_after();
-                        issue_kmajor(tm_dP, dV_k, sdesc_advance(dDo_k0, nd * kTileBytes));
+                        issue_kmajor(tm_dP, dV_k, sdesc_advance(dDo_k0, nd * kTileBytes), sdesc_advance(d_doaug0, nd * kAugBytes));
                         tc_commit(&bars->dp_ready);
                         // this warp's share of releasing dO_{i+1}, committed at once: with a single dO stage the load of the
                         // next tile starts as soon as this product and dV_{i+1} have read the stage
@@ -410,6 +602,7 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
         const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;
         const bool elected = warp == 8 && lane == 0;
         bool ok = true;
+        uint32_t piece = 0;
         for (int i = 0; i < n_iter; ++i) {
             const int g = i / per_head, qt = qt_first + (i - g * per_head);
             const int bh = b * p.Hq + hk * group + g0 + g;
@@ -434,50 +627,7 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
             tc_fence_before();
             mbar_arrive(&bars->dq_drained);
             SNTL_TRACE_EV(tw, 3, tn, 2);
-            if constexpr (!kDet) {
-#pragma unroll
-                for (int c = 0; c < D / kStageCols; ++c) {
-                    uint8_t* stage = sStage + (c % kStages) * kStageBytes;
-                    if (elected) bulk_wait_read<kStages - 1>();
-                    named_barrier_sync(1, 128);
-#pragma unroll
-                    for (int v = 0; v < kStageCols / 4; ++v)
-                        *reinterpret_cast<uint4*>(stage + ((size_t)v * kT + row) * 16) =
-                            make_uint4(r[c * kStageCols + 4 * v], r[c * kStageCols + 4 * v + 1], r[c * kStageCols + 4 * v + 2], r[c * kStageCols + 4 * v + 3]);
-                    fence_proxy_async_smem();
-                    named_barrier_sync(1, 128);
-                    if (elected) {
-                        bulk_reduce_add_f32(tile + (size_t)c * kStageCols * kT, stage, (uint32_t)kStageBytes);
-                        bulk_commit();
-                    }
-                }
-            } else {
-                // Order-independent form: each fp32 value times 2^32 is an integer that fits 64 bits exactly (24-bit
-                // mantissa, |value| < 2^31), and integer addition is associative, so the accumulated sum is the same
-                // whatever order the key tiles arrive in.  Same staging buffers, half as many columns per piece; the
-                // accumulator tile is [d/2][row][2] 64-bit words, so a piece is still one contiguous block.
-                constexpr int kDetCols = kStageCols / 2;
-                unsigned long long* tile64 = reinterpret_cast<unsigned long long*>(tile);
-#pragma unroll
-                for (int c = 0; c < D / kDetCols; ++c) {
-                    uint8_t* stage = sStage + (c % kStages) * kStageBytes;
-                    if (elected) bulk_wait_read<kStages - 1>();
-                    named_barrier_sync(1, 128);
-#pragma unroll
-                    for (int v = 0; v < kDetCols / 2; ++v) {
-                        const long long a = __float2ll_rn(__uint_as_float(r[c * kDetCols + 2 * v]) * 4294967296.0f);
-                        const long long b2 = __float2ll_rn(__uint_as_float(r[c * kDetCols + 2 * v + 1]) * 4294967296.0f);
-                        *reinterpret_cast<ulonglong2*>(stage + ((size_t)v * kT + row) * 16) =
-                            make_ulonglong2((unsigned long long)a, (unsigned long long)b2);
-                    }
-                    fence_proxy_async_smem();
-                    named_barrier_sync(1, 128);
-                    if (elected) {
-                        bulk_reduce_add_u64(tile64 + (size_t)c * kDetCols * kT, stage, (uint32_t)kStageBytes);
-                        bulk_commit();
-                    }
-                }
-            }
+            push_dq_tile<D, kDet, kStageCols, kStagingBytes>(r, tile, sStage, row, elected, piece);
             SNTL_TRACE_EV(tw, 3, tn, 3);
         }
         if (elected) bulk_wait_all();   // the reductions read shared memory and must land before the CTA retires
@@ -495,11 +645,9 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
         bool ok = true;
         for (int i = 0; i < n_iter; ++i) {
             const int qt = qt_first + (i % per_head);
-            const int sq = i & 1;
             const uint32_t ph = (uint32_t)(i & 1);
             // ---- P^T ----
-            ok = __all_sync(0xffffffffu, mbar_wait(&bars->q_full[sq], (uint32_t)((i >> 1) & 1), abort_flag, kSiteQFull) &&
-                                             mbar_wait(&bars->s_ready, ph, abort_flag, kSiteS));
+            ok = __all_sync(0xffffffffu, mbar_wait(&bars->s_ready, ph, abort_flag, kSiteS));
             SNTL_TRACE_EV(tw, 1 + wg, tn, 1);
             if (!ok) break;
             tc_fence_after();
@@ -508,7 +656,6 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
             tmem_ld32(tm_S + lane_off + col0 + 32u, s + 32);
             tmem_ld_wait();
             SNTL_TRACE_EV(tw, 1 + wg, tn, 2);
-            const float4* lse4 = reinterpret_cast<const float4*>(sLse + sq * kT + col0);
             // tiles the mask cuts through: the diagonal one and, with a window, those reaching past (first key + window - 1)
             const bool diag = (p.causal && qt == kt) || (kWin && qt * kT + kT - 1 > k0 + p.window - 1);
             uint32_t pk[32];
@@ -518,9 +665,9 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
             if (!diag) {
 #pragma unroll
                 for (int c = 0; c < 16; ++c) {
-                    const float4 l = lse4[c];   // holds -LSE*log2(e): x = s*scale*log2(e) - LSE*log2(e) in one packed FMA per pair
-                    const float2 x01 = ffma2(make_float2(__uint_as_float(s[4 * c + 0]), __uint_as_float(s[4 * c + 1])), sc2, make_float2(l.x, l.y));
-                    const float2 x23 = ffma2(make_float2(__uint_as_float(s[4 * c + 2]), __uint_as_float(s[4 * c + 3])), sc2, make_float2(l.z, l.w));
+                    // the product already holds S^T - LSE/scale: one packed multiply gives the exponent
+                    const float2 x01 = fmul2(make_float2(__uint_as_float(s[4 * c + 0]), __uint_as_float(s[4 * c + 1])), sc2);
+                    const float2 x23 = fmul2(make_float2(__uint_as_float(s[4 * c + 2]), __uint_as_float(s[4 * c + 3])), sc2);
                     pk[2 * c] = pack_bf16(ex2(x01.x), ex2(x01.y));
                     pk[2 * c + 1] = pack_bf16(ex2(x23.x), ex2(x23.y));
                 }
@@ -531,9 +678,8 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
                 const int last_q = (kWin && key >= p.global_tokens) ? key + p.window - 1 - qt * kT : kT;
 #pragma unroll
                 for (int c = 0; c < 16; ++c) {
-                    const float4 l = lse4[c];
-                    const float2 x01 = ffma2(make_float2(__uint_as_float(s[4 * c + 0]), __uint_as_float(s[4 * c + 1])), sc2, make_float2(l.x, l.y));
-                    const float2 x23 = ffma2(make_float2(__uint_as_float(s[4 * c + 2]), __uint_as_float(s[4 * c + 3])), sc2, make_float2(l.z, l.w));
+                    const float2 x01 = fmul2(make_float2(__uint_as_float(s[4 * c + 0]), __uint_as_float(s[4 * c + 1])), sc2);
+                    const float2 x23 = fmul2(make_float2(__uint_as_float(s[4 * c + 2]), __uint_as_float(s[4 * c + 3])), sc2);
                     const int q = (int)col0 + 4 * c;   // visible: first_q <= query (column) <= last_q
                     const float p0 = (q + 0 < first_q || q + 0 > last_q) ? 0.0f : ex2(x01.x);
                     const float p1 = (q + 1 < first_q || q + 1 > last_q) ? 0.0f : ex2(x01.y);
@@ -558,16 +704,22 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
             tmem_ld32(tm_dP + lane_off + col0 + 32u, s + 32);
             tmem_ld_wait();
             SNTL_TRACE_EV(tw, 1 + wg, tn, 6);
-            const float4* dl4 = reinterpret_cast<const float4*>(sDelta + sq * kT + col0);
+            // the product already holds dP^T - delta
 #pragma unroll
             for (int c = 0; c < 16; ++c) {
-                const float4 dl = dl4[c];   // holds -delta
+#ifdef SNTL_DS_F32
                 const float2 pa = make_float2(__uint_as_float(pk[2 * c] << 16), __uint_as_float(pk[2 * c] & 0xffff0000u));
                 const float2 pb = make_float2(__uint_as_float(pk[2 * c + 1] << 16), __uint_as_float(pk[2 * c + 1] & 0xffff0000u));
-                const float2 da = fmul2(pa, fadd2(make_float2(__uint_as_float(s[4 * c + 0]), __uint_as_float(s[4 * c + 1])), make_float2(dl.x, dl.y)));
-                const float2 db = fmul2(pb, fadd2(make_float2(__uint_as_float(s[4 * c + 2]), __uint_as_float(s[4 * c + 3])), make_float2(dl.z, dl.w)));
+                const float2 da = fmul2(pa, make_float2(__uint_as_float(s[4 * c + 0]), __uint_as_float(s[4 * c + 1])));
+                const float2 db = fmul2(pb, make_float2(__uint_as_float(s[4 * c + 2]), __uint_as_float(s[4 * c + 3])));
                 pk[2 * c] = pack_bf16(da.x, da.y);
                 pk[2 * c + 1] = pack_bf16(db.x, db.y);
+#else
+                // dS^T = P^T o (dP^T - delta) as a packed bf16 product: the second factor is rounded to bf16 first, the
+                // product once more (dS^T is a bf16 MMA operand either way)
+                pk[2 * c] = mul_bf16x2(pk[2 * c], pack_bf16(__uint_as_float(s[4 * c + 0]), __uint_as_float(s[4 * c + 1])));
+                pk[2 * c + 1] = mul_bf16x2(pk[2 * c + 1], pack_bf16(__uint_as_float(s[4 * c + 2]), __uint_as_float(s[4 * c + 3])));
+#endif
             }
             // into shared memory, rows of 128 bytes with the 128-byte swizzle the MMA expects (both the dQ and the dK
             // product read this tile)
@@ -584,99 +736,8 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
         }
         // ---- epilogue: dV (warpgroup 0) and dK (warpgroup 1) ----
         ok = __all_sync(0xffffffffu, ok && n_iter > 0 && mbar_wait(&bars->final_bar, 0, abort_flag, kSiteFinal));
-        if (split) {
-            // this CTA's share of dV (warpgroup 0) / dK (warpgroup 1) as an fp32 partial; zeros if it saw no query
-            float* dst = p.dkv_part + ((((size_t)kt * slabs + slab) * group + g0) * 2 + wg) * (size_t)(kT * D) + (size_t)row * D;
-            const uint32_t src = (wg == 0 ? tm_dV : tm_dK) + lane_off;
-            if (ok) tc_fence_after();
-#pragma unroll
-            for (int c = 0; c < D / 32; ++c) {
-                uint32_t r[32];
-                if (ok) {
-                    tmem_ld32(src + (uint32_t)(c * 32), r);
-                    tmem_ld_wait();
-                } else {
-#pragma unroll
-                    for (int v = 0; v < 32; ++v) r[v] = 0u;
-                }
-#pragma unroll
-                for (int v = 0; v < 8; ++v)
-                    *reinterpret_cast<uint4*>(dst + c * 32 + v * 4) = make_uint4(r[4 * v], r[4 * v + 1], r[4 * v + 2], r[4 * v + 3]);
-            }
-        } else if (ok && p.dk_acc != nullptr) {
-            // accumulate form: this CTA is the only writer of its 128 key rows in this launch
-            tc_fence_after();
-            const int key = k0 + row;
-            const bool store = key < p.Skv;
-            const float mul = wg == 0 ? 1.0f : p.scale;
-            float* dst = (wg == 0 ? p.dv_acc : p.dk_acc) + ((size_t)slab * p.Skv + (size_t)(store ? key : 0)) * D;
-            const uint32_t src = (wg == 0 ? tm_dV : tm_dK) + lane_off;
-#pragma unroll
-            for (int c = 0; c < D / 32; ++c) {
-                uint32_t r[32];
-                tmem_ld32(src + (uint32_t)(c * 32), r);
-                tmem_ld_wait();
-                if (store) {
-#pragma unroll
-                    for (int v = 0; v < 8; ++v) {
-                        float4 a = *reinterpret_cast<const float4*>(dst + c * 32 + v * 4);
-                        a.x = fmaf(__uint_as_float(r[4 * v + 0]), mul, a.x);
-                        a.y = fmaf(__uint_as_float(r[4 * v + 1]), mul, a.y);
-                        a.z = fmaf(__uint_as_float(r[4 * v + 2]), mul, a.z);
-                        a.w = fmaf(__uint_as_float(r[4 * v + 3]), mul, a.w);
-                        *reinterpret_cast<float4*>(dst + c * 32 + v * 4) = a;
-                    }
-                }
-            }
-        } else if (ok) {
-            tc_fence_after();
-            const int key = k0 + row;
-            const bool store = key < p.Skv;
-            const float mul = wg == 0 ? 1.0f : p.scale;
-            // Coalesced bf16 store: a thread holds one whole key row, so the warp's 32 rows go through shared memory (the V
-            // tile's buffer for dV, the K tile's for dK: every product has retired) and leave with each store instruction
-            // covering whole rows; 16-byte units are XOR-swizzled by the row against bank conflicts.
-            (void)store;
-            __nv_bfloat16* out = (wg == 0 ? p.dv : p.dk) + (size_t)slab * p.Skv * D;
-            const uint32_t src = (wg == 0 ? tm_dV : tm_dK) + lane_off;
-            constexpr int kUnits = D / 8;
-            uint8_t* stage = (wg == 0 ? sV : sK) + (warp & 3) * 32 * (D * 2);
-#pragma unroll
-            for (int c = 0; c < D / 32; ++c) {
-                uint32_t r[32];
-                tmem_ld32(src + (uint32_t)(c * 32), r);
-                tmem_ld_wait();
-#pragma unroll
-                for (int v = 0; v < 4; ++v) {
-                    uint4 w;
-                    w.x = pack_bf16(__uint_as_float(r[8 * v + 0]) * mul, __uint_as_float(r[8 * v + 1]) * mul);
-                    w.y = pack_bf16(__uint_as_float(r[8 * v + 2]) * mul, __uint_as_float(r[8 * v + 3]) * mul);
-                    w.z = pack_bf16(__uint_as_float(r[8 * v + 4]) * mul, __uint_as_float(r[8 * v + 5]) * mul);
-                    w.w = pack_bf16(__uint_as_float(r[8 * v + 6]) * mul, __uint_as_float(r[8 * v + 7]) * mul);
-                    const int unit = c * 4 + v;
-                    *reinterpret_cast<uint4*>(stage + lane * (D * 2) + ((unit ^ (lane & 7)) << 4)) = w;
-                }
-            }
-            __syncwarp();
-            {
-                constexpr int kRowsPerStore = 32 / kUnits;
-                const int sub = lane / kUnits, unit = lane % kUnits;
-                const int key_warp0 = key - lane;               // first key row of this warp
-#pragma unroll
-                for (int i = 0; i < 32 / kRowsPerStore; ++i) {
-                    const int rr = i * kRowsPerStore + sub;
-                    const uint4 w = *reinterpret_cast<const uint4*>(stage + rr * (D * 2) + ((unit ^ (rr & 7)) << 4));
-                    if (key_warp0 + rr < p.Skv) *reinterpret_cast<uint4*>(out + (size_t)(key_warp0 + rr) * D + unit * 8) = w;
-                }
-            }
-        } else if (n_iter == 0 && p.dk_acc == nullptr) {
-            // a key tile no query can see (cannot happen for causal with Sq == Skv; kept for safety): zero grads
-            const int key = k0 + row;
-            if (key < p.Skv) {
-                __nv_bfloat16* dst = (wg == 0 ? p.dv : p.dk) + ((size_t)slab * p.Skv + key) * D;
-                for (int d = 0; d < D; d += 8) *reinterpret_cast<uint4*>(dst + d) = make_uint4(0, 0, 0, 0);
-            }
-        }
+        write_dkv<D>(p, ok, split, n_iter, wg, warp, lane, row, (wg == 0 ? tm_dV : tm_dK) + lane_off, kt, slab, slabs, group, g0, k0,
+                     wg == 0 ? sV : sK);
     }
 
     // ---- teardown ----
@@ -691,14 +752,15 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
     }
 }
 
-// -delta = -rowsum(dO o O), lse2 = -LSE * log2(e) (-inf for padded rows and for rows without visible keys, so that
-// they produce P = 0; both are stored negated so the main kernel can use them as FMA/ADD addends), and the dQ
-// accumulator zeroed.  D/4 lanes per (b, h, padded row), 8 bytes of O and of dO per lane: a warp covers one row at
-// head_dim 128 and two at 64, every lane busy either way.
+// Per padded query row: the two 16-byte records the main kernel feeds to its extra contraction step -- bf16 (hi, lo, 0 x 6)
+// with hi + lo = -rowsum(dO o O) (delta) and = -LSE / scale (a large negative number for padded rows and for rows without
+// visible keys, so that they produce P = 0) -- and the dQ accumulator zeroed.  D/4 lanes per (b, h, padded row), 8 bytes of O
+// and of dO per lane: a warp covers one row at head_dim 128 and two at 64, every lane busy either way.
 template <int D>
 __global__ void bwd_pre_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ dout,
-                               const float* __restrict__ lse, float* __restrict__ lse2, float* __restrict__ delta,
-                               float* __restrict__ dq_accum, int Sq, int Sq_pad, long long rows_padded, int acc_words_per_row)
+                               const float* __restrict__ lse, uint4* __restrict__ qaug, uint4* __restrict__ doaug,
+                               float* __restrict__ dq_accum, int Sq, int Sq_pad, long long rows_padded, int acc_words_per_row,
+                               float inv_scale)
 {
     constexpr int kLanesPerRow = D / 4, kRowsPerWarp = 32 / kLanesPerRow;
     const int lane = threadIdx.x & 31, sub = lane / kLanesPerRow, l = lane % kLanesPerRow;
@@ -725,11 +787,18 @@ __global__ void bwd_pre_kernel(const __nv_bfloat16* __restrict__ o, const __nv_b
 #pragma unroll
     for (int m = kLanesPerRow / 2; m > 0; m >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, m);
     if (live && l == 0) {
-        if (s >= Sq) { lse2[r] = -INFINITY; delta[r] = 0.0f; }
+        // value -> bf16 pair (hi, lo) with hi + lo = value to 16 significant bits, as the low word of a record
+        auto split = [](float x) {
+            const __nv_bfloat16 hi = __float2bfloat16_rn(x);
+            const __nv_bfloat16 lo = __float2bfloat16_rn(x - __bfloat162float(hi));
+            return make_uint4((uint32_t)__bfloat16_as_ushort(hi) | ((uint32_t)__bfloat16_as_ushort(lo) << 16), 0u, 0u, 0u);
+        };
+        constexpr float kMasked = -1.0e30f;   // times scale*log2(e) still far below the exponent range: P = 0, and finite
+        if (s >= Sq) { qaug[r] = split(kMasked); doaug[r] = make_uint4(0u, 0u, 0u, 0u); }
         else {
             const float lv = lse[(size_t)bh * Sq + s];
-            lse2[r] = (lv == -INFINITY) ? -INFINITY : -lv * 1.4426950408889634f;
-            delta[r] = -acc;
+            qaug[r] = split((lv == -INFINITY) ? kMasked : -lv * inv_scale);
+            doaug[r] = split(-acc);
         }
     }
 }
@@ -845,15 +914,17 @@ cudaError_t launch_bwd(const TcArgs& a, cudaStream_t st)
     const int n_qt = (s.Sq + kT - 1) / kT, n_kt = (s.Skv + kT - 1) / kT;
     const int Sq_pad = n_qt * kT;
     const long long rows_padded = (long long)s.B * s.Hq * Sq_pad;
-    float* lse2 = a.delta + rows_padded;   // workspace: [delta | lse2] then the accumulator (see tc_backward_workspace_bytes)
+    // workspace: [delta records | LSE records] then the accumulator (see tc_backward_workspace_bytes)
+    uint4* doaug = reinterpret_cast<uint4*>(a.delta);
+    uint4* qaug = doaug + rows_padded;
     cudaError_t e;
     const int phases = a.phases ? a.phases : (kBwdPre | kBwdMain | kBwdPost);
     if (phases & kBwdPre) {
         const int warps = 8;
         const long long rows_per_block = (long long)warps * (32 / (D / 4));
         const long long blocks = (rows_padded + rows_per_block - 1) / rows_per_block;
-        bwd_pre_kernel<D><<<(unsigned)blocks, warps * 32, 0, st>>>(a.o, a.dout, a.lse, lse2, a.delta, a.dq_accum, s.Sq, Sq_pad,
-                                                                    rows_padded, kDet ? 2 * D : D);
+        bwd_pre_kernel<D><<<(unsigned)blocks, warps * 32, 0, st>>>(a.o, a.dout, a.lse, qaug, doaug, a.dq_accum, s.Sq, Sq_pad,
+                                                                    rows_padded, kDet ? 2 * D : D, 1.0f / s.scale);
         count_launch();
         if ((e = cudaGetLastError()) != cudaSuccess) return e;
     }
@@ -865,7 +936,7 @@ cudaError_t launch_bwd(const TcArgs& a, cudaStream_t st)
     if ((e = encode_tmap_bf16_3d(&tv, a.v, D, s.Skv, s.B * s.Hkv, 128)) != cudaSuccess) return e;
     BwdParams p{};
     p.dk = a.dk; p.dv = a.dv;
-    p.lse2 = lse2; p.delta = a.delta; p.dq_accum = a.dq_accum;
+    p.qaug = qaug; p.doaug = doaug; p.dq_accum = a.dq_accum;
     p.B = s.B; p.Hq = s.Hq; p.Hkv = s.Hkv; p.Sq = s.Sq; p.Skv = s.Skv; p.Sq_pad = Sq_pad;
     p.causal = s.causal;
     p.window = s.causal ? s.window : 0;
@@ -876,14 +947,18 @@ cudaError_t launch_bwd(const TcArgs& a, cudaStream_t st)
     p.dk_acc = a.dk_acc; p.dv_acc = a.dv_acc;
     p.scale = s.scale;
     p.scale_log2 = s.scale * 1.4426950408889634f;
-    constexpr int kDoStages = (D == 128) ? 1 : 2;
-    const size_t smem = (size_t)(128 * D * 2) * (4 + kDoStages) + 128 * 128 * 2 + 2 * (32 * 128 * 4) + 4 * 128 * 4 + sizeof(BwdBarriers);
-    static std::atomic<unsigned long long> configured{0};   // per instantiation, one bit per device
-    if ((e = ensure_dynamic_smem(attn_bwd_tc_kernel<D, kWin, kSplit, kDet>, smem, configured)) != cudaSuccess) return e;
     const int group = s.Hq / s.Hkv, slabs = s.B * s.Hkv;
     const long long ctas = (long long)p.split_tiles * group * slabs + (long long)(n_kt - p.split_tiles) * slabs;
     if (ctas > 0x7fffffffLL) return cudaErrorInvalidConfiguration;
-    attn_bwd_tc_kernel<D, kWin, kSplit, kDet><<<(unsigned)ctas, kBwdThreads, smem, st>>>(tq, tk, tv, tdo, p);
+    static std::atomic<unsigned long long> configured{0};   // per instantiation, one bit per device
+    {
+        constexpr int kDoStages = (D == 128) ? 1 : 2;
+        // K, V, Q x 2, dO stages; the dS tile; dQ staging; the constant block and its zeros; one record block per Q / dO stage
+        const size_t smem = (size_t)(128 * D * 2) * (4 + kDoStages) + 128 * 128 * 2 + (D == 128 ? 24 : 32) * 1024 +
+                            (size_t)(2 + 2 + kDoStages) * 128 * 16 + sizeof(BwdBarriers);
+        if ((e = ensure_dynamic_smem(attn_bwd_tc_kernel<D, kWin, kSplit, kDet>, smem, configured)) != cudaSuccess) return e;
+        attn_bwd_tc_kernel<D, kWin, kSplit, kDet><<<(unsigned)ctas, kBwdThreads, smem, st>>>(tq, tk, tv, tdo, p);
+    }
     count_launch();
     if ((e = cudaGetLastError()) != cudaSuccess) return e;
     if (p.split_tiles > 0) {
@@ -911,14 +986,14 @@ bool tc_bwd_supported(const AttnShape& s)
     return (s.D == 64 || s.D == 128) && (!s.causal || s.Sq == s.Skv);
 }
 
-// [delta: B*Hq*Sq_pad fp32][lse2: same], 256-byte aligned, then the fp32 dQ accumulator B*Hq*Sq_pad*D, then the fp32
+// [delta records: B*Hq*Sq_pad x 16 bytes][LSE records: same], 256-byte aligned, then the fp32 dQ accumulator B*Hq*Sq_pad*D, then the fp32
 // dK/dV partials of the key tiles that are cut by query head (none for most shapes)
 size_t tc_backward_workspace_bytes(const AttnShape& s)
 {
     const size_t sq_pad = ((size_t)s.Sq + kT - 1) / kT * kT;
     const size_t rows = (size_t)s.B * s.Hq * sq_pad;
     const size_t part = (size_t)bwd_split_tiles(s) * s.B * s.Hq * 2 * kT * (size_t)s.D * 4;   // slabs * group = B * Hq
-    return align256(2 * 4 * rows) + align256((s.deterministic ? 8 : 4) * rows * (size_t)s.D) + align256(part);
+    return align256(kBwdRowAuxBytes * rows) + align256((s.deterministic ? 8 : 4) * rows * (size_t)s.D) + align256(part);
 }
 
 cudaError_t tc_backward(const TcArgs& a, cudaStream_t st)

@@ -74,10 +74,10 @@ struct TcArgs {
     __nv_bfloat16 *o_out, *dq, *dk, *dv;
     float* lse_out;
     const float* lse;
-    float* delta;      // [B][Hq][Sq_pad]
+    float* delta;      // start of the backward workspace: the per-row records (kBwdRowAuxBytes per padded query row)
     float* dq_accum;   // [B][Hq][Sq_pad][D] fp32
     // Backward in pieces (the ring schedule: one query block meets several key blocks).  phases selects which of the
-    // three launches run: kBwdPre (delta, LSE*log2e, dQ accumulator zeroed), kBwdMain (the tensor-core kernel, which
+    // three launches run: kBwdPre (per-row records, dQ accumulator zeroed), kBwdMain (the tensor-core kernel, which
     // ADDS this key block's dQ into the accumulator), kBwdPost (accumulator -> bf16 dQ).  0 = all three.
     // dk_acc / dv_acc non-null: the main kernel adds its dK (times scale) / dV into these fp32 [B][Hkv][Skv][D]
     // tensors instead of writing bf16 dk / dv (each element has one owning CTA per launch, so the read-modify-write
@@ -100,6 +100,9 @@ bool tc_cache_supported(const AttnShape& s);
 cudaError_t tc_cache_forward(const TcArgs& a, int capacity, void* workspace, cudaStream_t st);
 cudaError_t tc_backward(const TcArgs& a, cudaStream_t st);
 size_t tc_backward_workspace_bytes(const AttnShape& s);
+// Bytes per padded query row at the head of the tensor-core backward workspace: two 16-byte records (the extra
+// contraction-step operands that carry -delta and -LSE/scale into the dP^T and S^T products)
+constexpr size_t kBwdRowAuxBytes = 2 * 16;
 
 // Layout / dtype staging (layout_convert.cu): SENTINEL fp32 feature-major <-> bf16 BHSD.
 // The same relayouts with the rotary embedding applied on the way (cos_t == nullptr: plain relayout).

@@ -116,7 +116,7 @@ size_t pieces_bytes_for(int B, int Hq, int Sc, int D)
 {
     const size_t sq_pad = ((size_t)Sc + 127) / 128 * 128;
     const size_t rows = (size_t)B * Hq * sq_pad;
-    return up256(2 * 4 * rows) + up256(4 * rows * (size_t)D);
+    return up256(kBwdRowAuxBytes * rows) + up256(4 * rows * (size_t)D);
 }
 
 // Lays the buffers out from `base` (null: only sizes are wanted).
@@ -492,7 +492,7 @@ int sntl_ring_attn_bwd(sntl_ring_comm* c, const sntl_attn_desc* d, const void* q
         TcArgs t{};
         t.s = pair_shape(r, 0);
         t.delta = (float*)r.pieces[i];
-        t.dq_accum = (float*)((char*)r.pieces[i] + up256(2 * 4 * (size_t)r.B * r.Hq * (((size_t)r.Sc + 127) / 128 * 128)));
+        t.dq_accum = (float*)((char*)r.pieces[i] + up256(kBwdRowAuxBytes * (size_t)r.B * r.Hq * (((size_t)r.Sc + 127) / 128 * 128)));
         t.o = r.oz[i]; t.dout = r.doz[i]; t.lse = r.lsez[i];
         t.phases = kBwdPre;
         f.cuda(tc_backward(t, main));
@@ -523,7 +523,7 @@ int sntl_ring_attn_bwd(sntl_ring_comm* c, const sntl_attn_desc* d, const void* q
             TcArgs t{};
             t.s = pair_shape(r, p.causal);
             t.delta = (float*)r.pieces[p.qi];
-            t.dq_accum = (float*)((char*)r.pieces[p.qi] + up256(2 * 4 * (size_t)r.B * r.Hq * (((size_t)r.Sc + 127) / 128 * 128)));
+            t.dq_accum = (float*)((char*)r.pieces[p.qi] + up256(kBwdRowAuxBytes * (size_t)r.B * r.Hq * (((size_t)r.Sc + 127) / 128 * 128)));
             t.q = r.qz[p.qi]; t.k = cur[p.ki]; t.v = cur[2 + p.ki]; t.dout = r.doz[p.qi];
             t.dk_acc = r.part[i][0]; t.dv_acc = r.part[i][1];
             t.phases = kBwdMain;
@@ -566,7 +566,7 @@ int sntl_ring_attn_bwd(sntl_ring_comm* c, const sntl_attn_desc* d, const void* q
         TcArgs t{};
         t.s = pair_shape(r, 0);
         t.delta = (float*)r.pieces[i];
-        t.dq_accum = (float*)((char*)r.pieces[i] + up256(2 * 4 * (size_t)r.B * r.Hq * (((size_t)r.Sc + 127) / 128 * 128)));
+        t.dq_accum = (float*)((char*)r.pieces[i] + up256(kBwdRowAuxBytes * (size_t)r.B * r.Hq * (((size_t)r.Sc + 127) / 128 * 128)));
         t.dq = r.dqz[i];
         t.phases = kBwdPost;
         f.cuda(tc_backward(t, main));

@@ -378,6 +378,13 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi)
     asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
     return r;
 }
+// element-wise product of two bf16 pairs, rounded to nearest even
+__device__ __forceinline__ uint32_t mul_bf16x2(uint32_t a, uint32_t b)
+{
+    uint32_t r;
+    asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+    return r;
+}
 
 }  // namespace ptx
 
