@@ -26,8 +26,8 @@
 //     per-tile [d/4][row][4] order so that the 32 rows of a warp hit consecutive addresses;
 //   * warp roles: 2 compute warpgroups (each owns 64 of the 128 query columns, one thread per key row),
 //     1 drain warpgroup, 2 MMA-issuing warps, 1 TMA-producer warp; registers are re-allocated per role
-//     (setmaxnreg).  Q (+LSE, delta) is double-buffered; dO is double-buffered for D=64 and single-buffered for
-//     D=128 (shared-memory capacity).
+//     (setmaxnreg).  Q (with its LSE records) has two stages and dO (with its delta records) one at D=128
+//     (shared-memory capacity); three and two at D=64.
 //
 // A pre-pass computes the per-query records (delta = rowsum(dO o O) and LSE/scale, each split in two bf16; padded rows get a
 // huge LSE so they produce P = 0) and zeroes the dQ accumulator; a post-pass converts the accumulator to bf16 dQ (times
@@ -38,7 +38,8 @@
 // global-token tiles long, that one CTA outlasts the average SM's whole load and bounds the kernel.  Such tiles are
 // cut by query head: one CTA per (key tile, KV head, query head of the group), each leaving its dK/dV as an fp32
 // partial in scratch, and a small kernel adds the partials in head order (deterministic) and writes bf16.
-// TMEM map (512 columns): S^T/P^T [0,128)  dP^T/dS^T/dQ [128,256)  dV [256,256+D)  dK [384,384+D).
+// TMEM map (512 columns): S^T/P^T [0,128)  dP^T/dQ [128,256)  then dV [256,384) dK [384,512) at head_dim 128, and
+// dV [256,320) dK [320,384) plus a second S^T/P^T buffer [384,512) at head_dim 64.
 #include "common.cuh"
 #include "sm100_ptx.cuh"
 
@@ -112,8 +113,8 @@ inline int bwd_split_tiles(const AttnShape& s)
 
 struct BwdBarriers {
     uint64_t kv_full;
-    uint64_t q_full[2], q_empty[2], do_full[2], do_empty[2];
-    uint64_t s_ready, p_ready, dp_ready, ds_ready, dq_ready, dq_drained, final_bar;
+    uint64_t q_full[3], q_empty[3], do_full[2], do_empty[2];
+    uint64_t s_ready[2], p_ready, dp_ready, ds_ready, dq_ready, dq_drained, final_bar;
     uint32_t tmem_base;
     uint32_t abort_flag;
 };
@@ -299,6 +300,11 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
     constexpr int kChunkBytes = kT * 128;          // 128 rows x 128 B
     constexpr int kChunks = D / 64;
     constexpr int kDoStages = (D == 128) ? 1 : 2;  // shared-memory capacity: 227 KB
+    // head_dim 64 leaves 128 TMEM columns and 60 KB of shared memory unused: S^T gets a second buffer there, so that
+    // S^T_{i+2} is computed while the compute warps are still busy with step i+1 and they never wait for the dV_i, S^T_{i+1}
+    // pair behind their own P^T_i; Q then needs a third stage (Q_{i+2} is loaded while dK_i still reads Q_i)
+    constexpr int kSBufs = (D == 128) ? 1 : 2;
+    constexpr int kQStages = (D == 128) ? 2 : 3;
     // columns of a dQ tile per bulk reduction (kStageCols columns x 128 rows fp32 = one piece): 8 KB pieces at head_dim 128,
     // where the tile loads of Q and dO queue behind the reductions on the SM's path to L2 and shorter pieces let them through
     // sooner (-3 % kernel time); 16 KB pieces at head_dim 64 (there the finer split costs 1 %, and 4 KB pieces cost 10-20 %
@@ -321,13 +327,13 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
     uint8_t* smem = smem_raw;
     uint8_t* sK = smem;
     uint8_t* sV = sK + kTileBytes;
-    uint8_t* sQ = sV + kTileBytes;                 // [2]
-    uint8_t* sDo = sQ + 2 * kTileBytes;            // [kDoStages]
+    uint8_t* sQ = sV + kTileBytes;                 // [kQStages]
+    uint8_t* sDo = sQ + kQStages * kTileBytes;     // [kDoStages]
     uint8_t* sDs = sDo + kDoStages * kTileBytes;
     uint8_t* sStage = sDs + kDsBytes;              // kStagingBytes
     uint8_t* sOnes = sStage + kStagingBytes;       // [2][kAugBytes]: the constant block, then zeros
-    uint8_t* sQaug = sOnes + 2 * kAugBytes;        // [2][kAugBytes]
-    uint8_t* sDoaug = sQaug + 2 * kAugBytes;       // [kDoStages][kAugBytes]
+    uint8_t* sQaug = sOnes + 2 * kAugBytes;        // [kQStages][kAugBytes]
+    uint8_t* sDoaug = sQaug + kQStages * kAugBytes;   // [kDoStages][kAugBytes]
     BwdBarriers* bars = (BwdBarriers*)(sDoaug + kDoStages * kAugBytes);
     volatile uint32_t* abort_flag = &bars->abort_flag;
 
@@ -370,13 +376,15 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
         prefetch_tensormap(&tmap_v);
         prefetch_tensormap(&tmap_do);
         mbar_init(&bars->kv_full, 1);
-        for (int i = 0; i < 2; ++i) {
+        for (int i = 0; i < 3; ++i) {
             mbar_init(&bars->q_full[i], 1);
             mbar_init(&bars->q_empty[i], 2);
+        }
+        for (int i = 0; i < 2; ++i) {
             mbar_init(&bars->do_full[i], 1);
             mbar_init(&bars->do_empty[i], 2);
+            mbar_init(&bars->s_ready[i], 1);
         }
-        mbar_init(&bars->s_ready, 1);
         mbar_init(&bars->p_ready, 256);
         mbar_init(&bars->dp_ready, 1);
         mbar_init(&bars->ds_ready, 256);
@@ -399,7 +407,9 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = bars->tmem_base;
-    const uint32_t tm_S = tmem, tm_dP = tmem + 128u, tm_dV = tmem + 256u, tm_dK = tmem + 384u;
+    // S^T / P^T [0,128)   dP^T / dQ [128,256)   head_dim 128: dV [256,384) dK [384,512)   64: dV [256,320) dK [320,384) 2nd S^T [384,512)
+    const uint32_t tm_S = tmem, tm_dP = tmem + 128u, tm_dV = tmem + 256u, tm_dK = tmem + (D == 128 ? 384u : 320u);
+    constexpr uint32_t kSBufStride = 384u;         // columns from the first S^T buffer to the second
 
     // 512 threads start with 128 registers each; the issuing/producer warpgroup needs few, the others get the rest
     // (each role re-allocates registers inside its own branch so that the compiler sees which register count applies where)
@@ -420,8 +430,8 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
             for (int i = 0; i < n_iter; ++i) {
                 const int g = i / per_head, qt = qt_first + (i - g * per_head);
                 const int bh = b * p.Hq + hk * group + g0 + g;
-                const int sq = i & 1;
-                if (i >= 2 && !mbar_wait(&bars->q_empty[sq], (uint32_t)(((i >> 1) - 1) & 1), abort_flag, kSiteQEmpty)) break;
+                const int sq = i % kQStages;
+                if (i >= kQStages && !mbar_wait(&bars->q_empty[sq], (uint32_t)(((i / kQStages) - 1) & 1), abort_flag, kSiteQEmpty)) break;
                 mbar_arrive_expect_tx(&bars->q_full[sq], (uint32_t)(kTileBytes + kAugBytes));
                 for (int c = 0; c < kChunks; ++c)
                     tma_load_3d(sQ + sq * kTileBytes + c * kChunkBytes, &tmap_q, &bars->q_full[sq], c * 64, qt * kT, bh);
@@ -481,28 +491,30 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
             bool ok = wait(&bars->kv_full, 0, kSiteKV);
             const uint64_t dK_k = make_sdesc(smem_u32(sK), 16, 1024);
             const uint64_t dQ_k0 = make_sdesc(smem_u32(sQ), 16, 1024), dDo_mn0 = make_sdesc(smem_u32(sDo), kChunkBytes, 1024);
-            ok = ok && wait(&bars->q_full[0], 0, kSiteQFull);
-            if (ok) {
+            // S^T of the first kSBufs steps; after that S^T_{i+kSBufs} follows dV_i into the buffer that P^T_i leaves
+            for (int j = 0; ok && j < kSBufs && j < n_iter; ++j) {
+                if (!(ok = wait(&bars->q_full[j], 0, kSiteQFull))) break;
                 tc_fence_after();
-                issue_kmajor(tm_S, dK_k, dQ_k0, d_qaug0);
-                tc_commit_e(&bars->s_ready);
+                issue_kmajor(tm_S + (uint32_t)j * kSBufStride, dK_k, sdesc_advance(dQ_k0, j * kTileBytes), sdesc_advance(d_qaug0, j * kAugBytes));
+                tc_commit_e(&bars->s_ready[j]);
             }
             for (int i = 0; ok && i < n_iter; ++i) {
-                const int sq = i & 1, sd = i % kDoStages;
+                const int sq = i % kQStages, sd = i % kDoStages, sb = i % kSBufs;
+                const uint32_t tm_Si = tm_S + (uint32_t)sb * kSBufStride;
                 if (!(ok = wait(&bars->p_ready, (uint32_t)(i & 1), kSiteP))) break;
                 if (!(ok = wait(&bars->do_full[sd], (uint32_t)((i / kDoStages) & 1), kSiteDoFull))) break;
                 SNTL_TRACE_EV(tl, 0, tn, 1);
                 tc_fence_after();
-                issue_from_tmem(tm_dV, tm_S, sdesc_advance(dDo_mn0, sd * kTileBytes), i > 0);
+                issue_from_tmem(tm_dV, tm_Si, sdesc_advance(dDo_mn0, sd * kTileBytes), i > 0);
                 tc_commit_e(&bars->do_empty[sd]);
                 tc_commit_e(&bars->q_empty[sq]);
                 SNTL_TRACE_EV(tl, 0, tn, 2);
-                if (i + 1 < n_iter) {
-                    const int nq = (i + 1) & 1;
-                    if (!(ok = wait(&bars->q_full[nq], (uint32_t)(((i + 1) >> 1) & 1), kSiteQFull))) break;
+                if (i + kSBufs < n_iter) {
+                    const int nq = (i + kSBufs) % kQStages;
+                    if (!(ok = wait(&bars->q_full[nq], (uint32_t)(((i + kSBufs) / kQStages) & 1), kSiteQFull))) break;
                     tc_fence_after();
-                    issue_kmajor(tm_S, dK_k, sdesc_advance(dQ_k0, nq * kTileBytes), sdesc_advance(d_qaug0, nq * kAugBytes));
-                    tc_commit_e(&bars->s_ready);
+                    issue_kmajor(tm_Si, dK_k, sdesc_advance(dQ_k0, nq * kTileBytes), sdesc_advance(d_qaug0, nq * kAugBytes));
+                    tc_commit_e(&bars->s_ready[sb]);
                     SNTL_TRACE_EV(tl, 0, tn, 9);
                 }
             }
@@ -543,7 +555,7 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
                 }
                 for (int i = 0; ok && i < n_iter; ++i) {
                     const uint32_t ph = (uint32_t)(i & 1);
-                    const int sq = i & 1;
+                    const int sq = i % kQStages;
                     if (!(ok = mbar_wait(&bars->ds_ready, ph, abort_flag, kSiteDS))) break;
                     SNTL_TRACE_EV(true, 4, tn, 3);
                     tc_fence_after();
@@ -647,13 +659,14 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
             const int qt = qt_first + (i % per_head);
             const uint32_t ph = (uint32_t)(i & 1);
             // ---- P^T ----
-            ok = __all_sync(0xffffffffu, mbar_wait(&bars->s_ready, ph, abort_flag, kSiteS));
+            const uint32_t tm_Si = tm_S + (uint32_t)(i % kSBufs) * kSBufStride;
+            ok = __all_sync(0xffffffffu, mbar_wait(&bars->s_ready[i % kSBufs], (uint32_t)((i / kSBufs) & 1), abort_flag, kSiteS));
             SNTL_TRACE_EV(tw, 1 + wg, tn, 1);
             if (!ok) break;
             tc_fence_after();
             uint32_t s[64];
-            tmem_ld32(tm_S + lane_off + col0, s);
-            tmem_ld32(tm_S + lane_off + col0 + 32u, s + 32);
+            tmem_ld32(tm_Si + lane_off + col0, s);
+            tmem_ld32(tm_Si + lane_off + col0 + 32u, s + 32);
             tmem_ld_wait();
             SNTL_TRACE_EV(tw, 1 + wg, tn, 2);
             // tiles the mask cuts through: the diagonal one and, with a window, those reaching past (first key + window - 1)
@@ -690,7 +703,7 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
                 }
             }
             SNTL_TRACE_EV(tw, 1 + wg, tn, 3);
-            tmem_st32(tm_S + lane_off + col0, pk);
+            tmem_st32(tm_Si + lane_off + col0, pk);
             tmem_st_wait();
             tc_fence_before();
             mbar_arrive(&bars->p_ready);
@@ -953,9 +966,10 @@ cudaError_t launch_bwd(const TcArgs& a, cudaStream_t st)
     static std::atomic<unsigned long long> configured{0};   // per instantiation, one bit per device
     {
         constexpr int kDoStages = (D == 128) ? 1 : 2;
-        // K, V, Q x 2, dO stages; the dS tile; dQ staging; the constant block and its zeros; one record block per Q / dO stage
-        const size_t smem = (size_t)(128 * D * 2) * (4 + kDoStages) + 128 * 128 * 2 + (D == 128 ? 24 : 32) * 1024 +
-                            (size_t)(2 + 2 + kDoStages) * 128 * 16 + sizeof(BwdBarriers);
+        // K, V, Q stages, dO stages; the dS tile; dQ staging; the constant block and its zeros; one record block per Q / dO stage
+        constexpr int kQStages = (D == 128) ? 2 : 3;
+        const size_t smem = (size_t)(128 * D * 2) * (2 + kQStages + kDoStages) + 128 * 128 * 2 + (D == 128 ? 24 : 32) * 1024 +
+                            (size_t)(2 + kQStages + kDoStages) * 128 * 16 + sizeof(BwdBarriers);
         if ((e = ensure_dynamic_smem(attn_bwd_tc_kernel<D, kWin, kSplit, kDet>, smem, configured)) != cudaSuccess) return e;
         attn_bwd_tc_kernel<D, kWin, kSplit, kDet><<<(unsigned)ctas, kBwdThreads, smem, st>>>(tq, tk, tv, tdo, p);
     }
