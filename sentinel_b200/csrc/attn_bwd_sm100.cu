@@ -60,8 +60,12 @@ enum BwdSite : uint32_t {
 
 struct BwdParams {
     __nv_bfloat16 *dk, *dv;
+    // head_dim 64 (see bwd_folds_row_terms):
     const uint4* qaug;     // [B][Hq][Sq_pad] one 16-byte record per query: bf16 (hi, lo, 0 x 6) of -LSE / scale
     const uint4* doaug;    // the same for -delta = -rowsum(dO o O)
+    // head_dim 128:
+    const float* lse2;     // [B][Hq][Sq_pad]  -LSE * log2(e), -inf on padded rows
+    const float* delta;    // [B][Hq][Sq_pad]  -rowsum(dO o O)
     float* dq_accum;       // [B*Hq][n_qt][D/4][128][4]
     int B, Hq, Hkv, Sq, Skv, Sq_pad;
     int causal;
@@ -118,6 +122,12 @@ struct BwdBarriers {
     uint32_t tmem_base;
     uint32_t abort_flag;
 };
+
+// Whether the per-query terms (LSE, delta) are folded into the S^T and dP^T products as one extra contraction step (see
+// kAugBytes in the kernel).  That trades shared-memory loads and arithmetic in the compute warps for 2 x 65 tensor-pipe
+// cycles per step on the two chains of products: a clear gain at head_dim 64, where the compute warps set the pace
+// (-11 % kernel time), a loss at 128, where the chains do (+3 %).
+__host__ __device__ constexpr bool bwd_folds_row_terms(int D) { return D == 64; }
 
 // Shared-memory descriptor of an unswizzled K-major operand of ONE contraction step (16 bf16 = two 8-element column
 // blocks): a column block is rows of 16 bytes, eight rows forming one 128-byte core matrix (SBO = 128 to the next eight
@@ -310,14 +320,14 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
     // sooner (-3 % kernel time); 16 KB pieces at head_dim 64 (there the finer split costs 1 %, and 4 KB pieces cost 10-20 %
     // at either size)
     constexpr int kStageCols = (D == 128) ? 16 : 32;
-    // staging in all: 32 KB at head_dim 64; 24 KB (three pieces) at 128, where shared memory is full
-    constexpr int kStagingBytes = (D == 128) ? 24 * 1024 : 32 * 1024;
-    // The extra contraction step.  S^T and dP^T each get one more 16-wide k-step whose operands are not tile data: on the
+    constexpr int kStagingBytes = 32 * 1024;       // dQ staging in all
+    // The extra contraction step (head_dim 64).  S^T and dP^T each get one more 16-wide k-step whose operands are not tile data: on the
     // key side a constant block (1, 1, 0, ...), on the query side a 16-byte record per query, (hi, lo, 0, ...) with
     // hi + lo = -LSE/scale (for S^T) or -delta (for dP^T) split in two bf16.  The tensor core then delivers
     // S^T - LSE/scale and dP^T - delta, and the compute warps need no per-column operand from shared memory at all:
     // P^T = exp2(scale*log2e * that) and dS^T = P^T o that.  One column block (8 bf16) per operand is real; the second
     // block of the constant operand is zeros, so the second block of the record operand may alias the first (LBO 0).
+    constexpr bool kAug = bwd_folds_row_terms(D);
     constexpr int kAugBytes = kT * 16;             // 128 records
     constexpr int kDsBytes = kT * kT * 2;          // dS^T tile: [128 keys][128 queries] bf16 as two 64-query chunks
     // The layout uses every byte of the 227 KB a CTA may have (D = 128), so there is no room for an alignment
@@ -331,10 +341,15 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
     uint8_t* sDo = sQ + kQStages * kTileBytes;     // [kDoStages]
     uint8_t* sDs = sDo + kDoStages * kTileBytes;
     uint8_t* sStage = sDs + kDsBytes;              // kStagingBytes
-    uint8_t* sOnes = sStage + kStagingBytes;       // [2][kAugBytes]: the constant block, then zeros
+    // per-query terms: with the extra contraction step its operands, else -LSE*log2e and -delta as plain fp32 columns
+    uint8_t* sTail = sStage + kStagingBytes;
+    uint8_t* sOnes = sTail;                        // [2][kAugBytes]: the constant block, then zeros
     uint8_t* sQaug = sOnes + 2 * kAugBytes;        // [kQStages][kAugBytes]
     uint8_t* sDoaug = sQaug + kQStages * kAugBytes;   // [kDoStages][kAugBytes]
-    BwdBarriers* bars = (BwdBarriers*)(sDoaug + kDoStages * kAugBytes);
+    float* sLse = (float*)sTail;                   // [kQStages][128]
+    float* sDelta = sLse + kQStages * kT;          // [kQStages][128]
+    constexpr int kTailBytes = kAug ? (2 + kQStages + kDoStages) * kAugBytes : 2 * kQStages * kT * 4;
+    BwdBarriers* bars = (BwdBarriers*)(sTail + kTailBytes);
     volatile uint32_t* abort_flag = &bars->abort_flag;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -398,7 +413,7 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
         tmem_alloc(&bars->tmem_base, kTmemCols);
         tmem_relinquish();
     }
-    if (threadIdx.x < kT) {
+    if (kAug && threadIdx.x < kT) {
         reinterpret_cast<uint4*>(sOnes)[threadIdx.x] = make_uint4(0x3f803f80u, 0u, 0u, 0u);   // bf16 (1, 1, 0, 0, 0, 0, 0, 0)
         reinterpret_cast<uint4*>(sOnes + kAugBytes)[threadIdx.x] = make_uint4(0u, 0u, 0u, 0u);
         fence_proxy_async_smem();
@@ -432,16 +447,22 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
                 const int bh = b * p.Hq + hk * group + g0 + g;
                 const int sq = i % kQStages;
                 if (i >= kQStages && !mbar_wait(&bars->q_empty[sq], (uint32_t)(((i / kQStages) - 1) & 1), abort_flag, kSiteQEmpty)) break;
-                mbar_arrive_expect_tx(&bars->q_full[sq], (uint32_t)(kTileBytes + kAugBytes));
+                mbar_arrive_expect_tx(&bars->q_full[sq], (uint32_t)(kTileBytes + (kAug ? kAugBytes : 2 * kT * 4)));
                 for (int c = 0; c < kChunks; ++c)
                     tma_load_3d(sQ + sq * kTileBytes + c * kChunkBytes, &tmap_q, &bars->q_full[sq], c * 64, qt * kT, bh);
-                bulk_load_1d(sQaug + sq * kAugBytes, p.qaug + (size_t)bh * p.Sq_pad + (size_t)qt * kT, kAugBytes, &bars->q_full[sq]);
+                if constexpr (kAug) {
+                    bulk_load_1d(sQaug + sq * kAugBytes, p.qaug + (size_t)bh * p.Sq_pad + (size_t)qt * kT, kAugBytes, &bars->q_full[sq]);
+                } else {
+                    bulk_load_1d(sLse + sq * kT, p.lse2 + (size_t)bh * p.Sq_pad + (size_t)qt * kT, kT * 4, &bars->q_full[sq]);
+                    bulk_load_1d(sDelta + sq * kT, p.delta + (size_t)bh * p.Sq_pad + (size_t)qt * kT, kT * 4, &bars->q_full[sq]);
+                }
                 const int sd = i % kDoStages;
                 if (i >= kDoStages &&
                     !mbar_wait(&bars->do_empty[sd], (uint32_t)(((i / kDoStages) - 1) & 1), abort_flag, kSiteDoEmpty))
                     break;
-                mbar_arrive_expect_tx(&bars->do_full[sd], (uint32_t)(kTileBytes + kAugBytes));
-                bulk_load_1d(sDoaug + sd * kAugBytes, p.doaug + (size_t)bh * p.Sq_pad + (size_t)qt * kT, kAugBytes, &bars->do_full[sd]);
+                mbar_arrive_expect_tx(&bars->do_full[sd], (uint32_t)(kTileBytes + (kAug ? kAugBytes : 0)));
+                if constexpr (kAug)
+                    bulk_load_1d(sDoaug + sd * kAugBytes, p.doaug + (size_t)bh * p.Sq_pad + (size_t)qt * kT, kAugBytes, &bars->do_full[sd]);
                 for (int c = 0; c < kChunks; ++c)
                     tma_load_3d(sDo + sd * kTileBytes + c * kChunkBytes, &tmap_do, &bars->do_full[sd], c * 64, qt * kT, bh);
             }
@@ -479,7 +500,7 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
                     const uint32_t off = (uint32_t)((ks >> 2) * kChunkBytes + (ks & 3) * 32);
                     mma_ss_e<true>(d_tmem, sdesc_advance(a, off), sdesc_advance(b, off), idesc_st);
                 }
-                mma_ss_e<true>(d_tmem, d_ones, aug, idesc_st);
+                if constexpr (kAug) mma_ss_e<true>(d_tmem, d_ones, aug, idesc_st);
             };
             auto issue_from_tmem = [&](uint32_t d_tmem, uint32_t a_tmem, uint64_t b, bool accumulate) {
                 if (accumulate) mma_ts_e<true>(d_tmem, a_tmem, b, idesc_kv);
@@ -538,7 +559,7 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
                     const uint32_t off = (uint32_t)((ks >> 2) * kChunkBytes + (ks & 3) * 32);
                     mma_ss_c<true>(d_tmem, sdesc_advance(a, off), sdesc_advance(b, off), idesc_st);
                 }
-                mma_ss_c<true>(d_tmem, d_ones, aug, idesc_st);
+                if constexpr (kAug) mma_ss_c<true>(d_tmem, d_ones, aug, idesc_st);
             };
             bool ok = mbar_wait(&bars->kv_full, 0, abort_flag, kSiteKV);
             {
@@ -660,7 +681,9 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
             const uint32_t ph = (uint32_t)(i & 1);
             // ---- P^T ----
             const uint32_t tm_Si = tm_S + (uint32_t)(i % kSBufs) * kSBufStride;
-            ok = __all_sync(0xffffffffu, mbar_wait(&bars->s_ready[i % kSBufs], (uint32_t)((i / kSBufs) & 1), abort_flag, kSiteS));
+            // (the Q stage's barrier also covers the LSE and delta columns this warp reads when they come as plain columns)
+            ok = __all_sync(0xffffffffu, (kAug || mbar_wait(&bars->q_full[i % kQStages], (uint32_t)((i / kQStages) & 1), abort_flag, kSiteQFull)) &&
+                                             mbar_wait(&bars->s_ready[i % kSBufs], (uint32_t)((i / kSBufs) & 1), abort_flag, kSiteS));
             SNTL_TRACE_EV(tw, 1 + wg, tn, 1);
             if (!ok) break;
             tc_fence_after();
@@ -673,14 +696,28 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
             const bool diag = (p.causal && qt == kt) || (kWin && qt * kT + kT - 1 > k0 + p.window - 1);
             uint32_t pk[32];
             const float2 sc2 = make_float2(p.scale_log2, p.scale_log2);
+            const float4* lse4 = reinterpret_cast<const float4*>(sLse + (i % kQStages) * kT + col0);
+            // exponents of four columns: with the extra contraction step the product already holds S^T - LSE/scale and one
+            // packed multiply per pair gives them; else x = s*scale*log2(e) - LSE*log2(e) is one packed FMA per pair
+            auto exponents = [&](int c, float2& x01, float2& x23) {
+                const float2 s01 = make_float2(__uint_as_float(s[4 * c + 0]), __uint_as_float(s[4 * c + 1]));
+                const float2 s23 = make_float2(__uint_as_float(s[4 * c + 2]), __uint_as_float(s[4 * c + 3]));
+                if constexpr (kAug) {
+                    x01 = fmul2(s01, sc2);
+                    x23 = fmul2(s23, sc2);
+                } else {
+                    const float4 l = lse4[c];
+                    x01 = ffma2(s01, sc2, make_float2(l.x, l.y));
+                    x23 = ffma2(s23, sc2, make_float2(l.z, l.w));
+                }
+            };
             // branch-free main body (the mask test lives in its own copy of the loop, taken only on the diagonal tile,
             // so that the common copy is one basic block the compiler can software-pipeline)
             if (!diag) {
 #pragma unroll
                 for (int c = 0; c < 16; ++c) {
-                    // the product already holds S^T - LSE/scale: one packed multiply gives the exponent
-                    const float2 x01 = fmul2(make_float2(__uint_as_float(s[4 * c + 0]), __uint_as_float(s[4 * c + 1])), sc2);
-                    const float2 x23 = fmul2(make_float2(__uint_as_float(s[4 * c + 2]), __uint_as_float(s[4 * c + 3])), sc2);
+                    float2 x01, x23;
+                    exponents(c, x01, x23);
                     pk[2 * c] = pack_bf16(ex2(x01.x), ex2(x01.y));
                     pk[2 * c + 1] = pack_bf16(ex2(x23.x), ex2(x23.y));
                 }
@@ -691,8 +728,8 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
                 const int last_q = (kWin && key >= p.global_tokens) ? key + p.window - 1 - qt * kT : kT;
 #pragma unroll
                 for (int c = 0; c < 16; ++c) {
-                    const float2 x01 = fmul2(make_float2(__uint_as_float(s[4 * c + 0]), __uint_as_float(s[4 * c + 1])), sc2);
-                    const float2 x23 = fmul2(make_float2(__uint_as_float(s[4 * c + 2]), __uint_as_float(s[4 * c + 3])), sc2);
+                    float2 x01, x23;
+                    exponents(c, x01, x23);
                     const int q = (int)col0 + 4 * c;   // visible: first_q <= query (column) <= last_q
                     const float p0 = (q + 0 < first_q || q + 0 > last_q) ? 0.0f : ex2(x01.x);
                     const float p1 = (q + 1 < first_q || q + 1 > last_q) ? 0.0f : ex2(x01.y);
@@ -717,22 +754,23 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
             tmem_ld32(tm_dP + lane_off + col0 + 32u, s + 32);
             tmem_ld_wait();
             SNTL_TRACE_EV(tw, 1 + wg, tn, 6);
-            // the product already holds dP^T - delta
+            const float4* dl4 = reinterpret_cast<const float4*>(sDelta + (i % kQStages) * kT + col0);
 #pragma unroll
             for (int c = 0; c < 16; ++c) {
-#ifdef SNTL_DS_F32
-                const float2 pa = make_float2(__uint_as_float(pk[2 * c] << 16), __uint_as_float(pk[2 * c] & 0xffff0000u));
-                const float2 pb = make_float2(__uint_as_float(pk[2 * c + 1] << 16), __uint_as_float(pk[2 * c + 1] & 0xffff0000u));
-                const float2 da = fmul2(pa, make_float2(__uint_as_float(s[4 * c + 0]), __uint_as_float(s[4 * c + 1])));
-                const float2 db = fmul2(pb, make_float2(__uint_as_float(s[4 * c + 2]), __uint_as_float(s[4 * c + 3])));
-                pk[2 * c] = pack_bf16(da.x, da.y);
-                pk[2 * c + 1] = pack_bf16(db.x, db.y);
-#else
-                // dS^T = P^T o (dP^T - delta) as a packed bf16 product: the second factor is rounded to bf16 first, the
-                // product once more (dS^T is a bf16 MMA operand either way)
-                pk[2 * c] = mul_bf16x2(pk[2 * c], pack_bf16(__uint_as_float(s[4 * c + 0]), __uint_as_float(s[4 * c + 1])));
-                pk[2 * c + 1] = mul_bf16x2(pk[2 * c + 1], pack_bf16(__uint_as_float(s[4 * c + 2]), __uint_as_float(s[4 * c + 3])));
-#endif
+                if constexpr (kAug) {
+                    // the product already holds dP^T - delta, and dS^T = P^T o that is a packed bf16 product: the second
+                    // factor is rounded to bf16 first, the product once more (dS^T is a bf16 MMA operand either way)
+                    pk[2 * c] = mul_bf16x2(pk[2 * c], pack_bf16(__uint_as_float(s[4 * c + 0]), __uint_as_float(s[4 * c + 1])));
+                    pk[2 * c + 1] = mul_bf16x2(pk[2 * c + 1], pack_bf16(__uint_as_float(s[4 * c + 2]), __uint_as_float(s[4 * c + 3])));
+                } else {
+                    const float4 dl = dl4[c];   // holds -delta
+                    const float2 pa = make_float2(__uint_as_float(pk[2 * c] << 16), __uint_as_float(pk[2 * c] & 0xffff0000u));
+                    const float2 pb = make_float2(__uint_as_float(pk[2 * c + 1] << 16), __uint_as_float(pk[2 * c + 1] & 0xffff0000u));
+                    const float2 da = fmul2(pa, fadd2(make_float2(__uint_as_float(s[4 * c + 0]), __uint_as_float(s[4 * c + 1])), make_float2(dl.x, dl.y)));
+                    const float2 db = fmul2(pb, fadd2(make_float2(__uint_as_float(s[4 * c + 2]), __uint_as_float(s[4 * c + 3])), make_float2(dl.z, dl.w)));
+                    pk[2 * c] = pack_bf16(da.x, da.y);
+                    pk[2 * c + 1] = pack_bf16(db.x, db.y);
+                }
             }
             // into shared memory, rows of 128 bytes with the 128-byte swizzle the MMA expects (both the dQ and the dK
             // product read this tile)
@@ -771,7 +809,7 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
 // and of dO per lane: a warp covers one row at head_dim 128 and two at 64, every lane busy either way.
 template <int D>
 __global__ void bwd_pre_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ dout,
-                               const float* __restrict__ lse, uint4* __restrict__ qaug, uint4* __restrict__ doaug,
+                               const float* __restrict__ lse, void* __restrict__ lse_out, void* __restrict__ delta_out,
                                float* __restrict__ dq_accum, int Sq, int Sq_pad, long long rows_padded, int acc_words_per_row,
                                float inv_scale)
 {
@@ -800,18 +838,31 @@ __global__ void bwd_pre_kernel(const __nv_bfloat16* __restrict__ o, const __nv_b
 #pragma unroll
     for (int m = kLanesPerRow / 2; m > 0; m >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, m);
     if (live && l == 0) {
-        // value -> bf16 pair (hi, lo) with hi + lo = value to 16 significant bits, as the low word of a record
-        auto split = [](float x) {
-            const __nv_bfloat16 hi = __float2bfloat16_rn(x);
-            const __nv_bfloat16 lo = __float2bfloat16_rn(x - __bfloat162float(hi));
-            return make_uint4((uint32_t)__bfloat16_as_ushort(hi) | ((uint32_t)__bfloat16_as_ushort(lo) << 16), 0u, 0u, 0u);
-        };
-        constexpr float kMasked = -1.0e30f;   // times scale*log2(e) still far below the exponent range: P = 0, and finite
-        if (s >= Sq) { qaug[r] = split(kMasked); doaug[r] = make_uint4(0u, 0u, 0u, 0u); }
-        else {
-            const float lv = lse[(size_t)bh * Sq + s];
-            qaug[r] = split((lv == -INFINITY) ? kMasked : -lv * inv_scale);
-            doaug[r] = split(-acc);
+        if constexpr (bwd_folds_row_terms(D)) {
+            uint4* qaug = static_cast<uint4*>(lse_out);
+            uint4* doaug = static_cast<uint4*>(delta_out);
+            // value -> bf16 pair (hi, lo) with hi + lo = value to 16 significant bits, as the low word of a record
+            auto split = [](float x) {
+                const __nv_bfloat16 hi = __float2bfloat16_rn(x);
+                const __nv_bfloat16 lo = __float2bfloat16_rn(x - __bfloat162float(hi));
+                return make_uint4((uint32_t)__bfloat16_as_ushort(hi) | ((uint32_t)__bfloat16_as_ushort(lo) << 16), 0u, 0u, 0u);
+            };
+            constexpr float kMasked = -1.0e30f;   // times scale*log2(e) still far below the exponent range: P = 0, and finite
+            if (s >= Sq) { qaug[r] = split(kMasked); doaug[r] = make_uint4(0u, 0u, 0u, 0u); }
+            else {
+                const float lv = lse[(size_t)bh * Sq + s];
+                qaug[r] = split((lv == -INFINITY) ? kMasked : -lv * inv_scale);
+                doaug[r] = split(-acc);
+            }
+        } else {
+            float* lse2 = static_cast<float*>(lse_out);
+            float* delta = static_cast<float*>(delta_out);
+            if (s >= Sq) { lse2[r] = -INFINITY; delta[r] = 0.0f; }
+            else {
+                const float lv = lse[(size_t)bh * Sq + s];
+                lse2[r] = (lv == -INFINITY) ? -INFINITY : -lv * 1.4426950408889634f;
+                delta[r] = -acc;
+            }
         }
     }
 }
@@ -928,15 +979,18 @@ cudaError_t launch_bwd(const TcArgs& a, cudaStream_t st)
     const int Sq_pad = n_qt * kT;
     const long long rows_padded = (long long)s.B * s.Hq * Sq_pad;
     // workspace: [delta records | LSE records] then the accumulator (see tc_backward_workspace_bytes)
+    constexpr bool kAug = bwd_folds_row_terms(D);
     uint4* doaug = reinterpret_cast<uint4*>(a.delta);
     uint4* qaug = doaug + rows_padded;
+    float* lse2 = a.delta + rows_padded;           // the plain-column form takes the head of the same region
     cudaError_t e;
     const int phases = a.phases ? a.phases : (kBwdPre | kBwdMain | kBwdPost);
     if (phases & kBwdPre) {
         const int warps = 8;
         const long long rows_per_block = (long long)warps * (32 / (D / 4));
         const long long blocks = (rows_padded + rows_per_block - 1) / rows_per_block;
-        bwd_pre_kernel<D><<<(unsigned)blocks, warps * 32, 0, st>>>(a.o, a.dout, a.lse, qaug, doaug, a.dq_accum, s.Sq, Sq_pad,
+        bwd_pre_kernel<D><<<(unsigned)blocks, warps * 32, 0, st>>>(a.o, a.dout, a.lse, kAug ? (void*)qaug : (void*)lse2,
+                                                                    kAug ? (void*)doaug : (void*)a.delta, a.dq_accum, s.Sq, Sq_pad,
                                                                     rows_padded, kDet ? 2 * D : D, 1.0f / s.scale);
         count_launch();
         if ((e = cudaGetLastError()) != cudaSuccess) return e;
@@ -949,7 +1003,7 @@ cudaError_t launch_bwd(const TcArgs& a, cudaStream_t st)
     if ((e = encode_tmap_bf16_3d(&tv, a.v, D, s.Skv, s.B * s.Hkv, 128)) != cudaSuccess) return e;
     BwdParams p{};
     p.dk = a.dk; p.dv = a.dv;
-    p.qaug = qaug; p.doaug = doaug; p.dq_accum = a.dq_accum;
+    p.qaug = qaug; p.doaug = doaug; p.lse2 = lse2; p.delta = a.delta; p.dq_accum = a.dq_accum;
     p.B = s.B; p.Hq = s.Hq; p.Hkv = s.Hkv; p.Sq = s.Sq; p.Skv = s.Skv; p.Sq_pad = Sq_pad;
     p.causal = s.causal;
     p.window = s.causal ? s.window : 0;
@@ -966,10 +1020,10 @@ cudaError_t launch_bwd(const TcArgs& a, cudaStream_t st)
     static std::atomic<unsigned long long> configured{0};   // per instantiation, one bit per device
     {
         constexpr int kDoStages = (D == 128) ? 1 : 2;
-        // K, V, Q stages, dO stages; the dS tile; dQ staging; the constant block and its zeros; one record block per Q / dO stage
+        // K, V, Q stages, dO stages; the dS tile; dQ staging; the per-query terms (see sTail in the kernel)
         constexpr int kQStages = (D == 128) ? 2 : 3;
-        const size_t smem = (size_t)(128 * D * 2) * (2 + kQStages + kDoStages) + 128 * 128 * 2 + (D == 128 ? 24 : 32) * 1024 +
-                            (size_t)(2 + kQStages + kDoStages) * 128 * 16 + sizeof(BwdBarriers);
+        const size_t smem = (size_t)(128 * D * 2) * (2 + kQStages + kDoStages) + 128 * 128 * 2 + 32 * 1024 +
+                            (kAug ? (size_t)(2 + kQStages + kDoStages) * 128 * 16 : (size_t)2 * kQStages * 128 * 4) + sizeof(BwdBarriers);
         if ((e = ensure_dynamic_smem(attn_bwd_tc_kernel<D, kWin, kSplit, kDet>, smem, configured)) != cudaSuccess) return e;
         attn_bwd_tc_kernel<D, kWin, kSplit, kDet><<<(unsigned)ctas, kBwdThreads, smem, st>>>(tq, tk, tv, tdo, p);
     }
