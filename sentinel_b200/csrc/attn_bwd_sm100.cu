@@ -315,6 +315,10 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
     // pair behind their own P^T_i; Q then needs a third stage (Q_{i+2} is loaded while dK_i still reads Q_i)
     constexpr int kSBufs = (D == 128) ? 1 : 2;
     constexpr int kQStages = (D == 128) ? 2 : 3;
+    // ... and the dS tile a second buffer, which lets dK_i be issued after the next dP^T instead of before it: the chain
+    // dS_i -> dQ_i -> drain -> dP^T_{i+1} -> dS_{i+1} then no longer carries the issue time of dK_i (with one buffer dK_i must
+    // have read the tile before dP^T_{i+1} lets the compute warps overwrite it)
+    constexpr int kDsBufs = (D == 128) ? 1 : 2;
     // columns of a dQ tile per bulk reduction (kStageCols columns x 128 rows fp32 = one piece): 8 KB pieces at head_dim 128,
     // where the tile loads of Q and dO queue behind the reductions on the SM's path to L2 and shorter pieces let them through
     // sooner (-3 % kernel time); 16 KB pieces at head_dim 64 (there the finer split costs 1 %, and 4 KB pieces cost 10-20 %
@@ -339,8 +343,8 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
     uint8_t* sV = sK + kTileBytes;
     uint8_t* sQ = sV + kTileBytes;                 // [kQStages]
     uint8_t* sDo = sQ + kQStages * kTileBytes;     // [kDoStages]
-    uint8_t* sDs = sDo + kDoStages * kTileBytes;
-    uint8_t* sStage = sDs + kDsBytes;              // kStagingBytes
+    uint8_t* sDs = sDo + kDoStages * kTileBytes;   // [kDsBufs]
+    uint8_t* sStage = sDs + kDsBufs * kDsBytes;    // kStagingBytes
     // per-query terms: with the extra contraction step its operands, else -LSE*log2e and -delta as plain fp32 columns
     uint8_t* sTail = sStage + kStagingBytes;
     uint8_t* sOnes = sTail;                        // [2][kAugBytes]: the constant block, then zeros
@@ -580,10 +584,10 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
                     if (!(ok = mbar_wait(&bars->ds_ready, ph, abort_flag, kSiteDS))) break;
                     SNTL_TRACE_EV(true, 4, tn, 3);
                     tc_fence_after();
-                    // dQ first: it gates the drain and with it the next dP^T; dK only has to finish before the dS tile
-                    // is rewritten, which the in-order issue of this thread already guarantees
+                    // dQ first: it gates the drain and with it the next dP^T
+                    const uint32_t ds_off = (uint32_t)((i % kDsBufs) * kDsBytes);
                     {
-                        uint64_t a = dDs_mn, bq = dK_mn;
+                        uint64_t a = sdesc_advance(dDs_mn, ds_off), bq = dK_mn;
                         asm volatile("" : "+l"(a), "+l"(bq));
                         mma_ss_c<false>(tm_dP, a, bq, idesc_dq);
 #pragma unroll
@@ -593,19 +597,21 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
                     tc_commit(&bars->dq_ready);
                     SNTL_TRACE_EV(true, 4, tn, 4);
                     // dK += dS^T Q with dS^T read from its shared-memory tile as a K-major A operand (rows = keys, the 64
-                    // contiguous elements run along the queries).  It is issued before the next dP^T, so by the time the
-                    // compute warps see that dP^T and rewrite the dS tile this product has read it (one thread's MMAs run
-                    // in order).  Q_i is ready: ds_ready implies its load was seen.
-                    {
-                        uint64_t a = dDs_k, bq = sdesc_advance(dQ_mn0, sq * kTileBytes);
+                    // contiguous elements run along the queries).  Q_i is ready: ds_ready implies its load was seen.  With
+                    // one dS buffer it goes before the next dP^T: by the time the compute warps see that dP^T and rewrite the
+                    // tile, this product has read it (one thread's MMAs run in order).  With two it goes after, and the
+                    // buffer it reads is rewritten only behind dP^T_{i+2}, which this thread issues later still.
+                    auto issue_dk = [&]() {
+                        uint64_t a = sdesc_advance(dDs_k, ds_off), bq = sdesc_advance(dQ_mn0, sq * kTileBytes);
                         asm volatile("" : "+l"(a), "+l"(bq));
                         if (i > 0) mma_ss_c<true>(tm_dK, a, bq, idesc_kv);
                         else mma_ss_c<false>(tm_dK, a, bq, idesc_kv);
 #pragma unroll
                         for (int ks = 1; ks < kT / 16; ++ks)
                             mma_ss_c<true>(tm_dK, sdesc_advance(a, (ks >> 2) * kChunkBytes + (ks & 3) * 32), sdesc_advance(bq, ks * 2048), idesc_kv);
-                    }
-                    tc_commit(&bars->q_empty[sq]);    // this warp's share: dK_i
+                        tc_commit(&bars->q_empty[sq]);    // this warp's share: dK_i
+                    };
+                    if constexpr (kDsBufs == 1) issue_dk();
                     if (i + 1 < n_iter) {
                         const int nd = (i + 1) % kDoStages;
                         if (!(ok = mbar_wait(&bars->dq_drained, ph, abort_flag, kSiteDrained))) break;
@@ -619,6 +625,7 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
                         tc_commit(&bars->do_empty[nd]);
                         SNTL_TRACE_EV(true, 4, tn, 6);
                     }
+                    if constexpr (kDsBufs == 2) issue_dk();
                 }
             }
             // every MMA of this thread has retired once its commit lands; the epilogue waits for both issuers
@@ -674,7 +681,7 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
         (void)tw;
         const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;
         const uint32_t col0 = (uint32_t)(wg * 64);
-        uint8_t* ds_row = sDs + wg * kChunkBytes + row * 128;    // this thread's 128-byte row of its 64-query chunk
+        uint8_t* ds_row0 = sDs + wg * kChunkBytes + row * 128;   // this thread's 128-byte row of its 64-query chunk
         bool ok = true;
         for (int i = 0; i < n_iter; ++i) {
             const int qt = qt_first + (i % per_head);
@@ -774,6 +781,7 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
             }
             // into shared memory, rows of 128 bytes with the 128-byte swizzle the MMA expects (both the dQ and the dK
             // product read this tile)
+            uint8_t* ds_row = ds_row0 + (i % kDsBufs) * kDsBytes;
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
                 uint4 w = make_uint4(pk[4 * j], pk[4 * j + 1], pk[4 * j + 2], pk[4 * j + 3]);
@@ -1020,9 +1028,9 @@ cudaError_t launch_bwd(const TcArgs& a, cudaStream_t st)
     static std::atomic<unsigned long long> configured{0};   // per instantiation, one bit per device
     {
         constexpr int kDoStages = (D == 128) ? 1 : 2;
-        // K, V, Q stages, dO stages; the dS tile; dQ staging; the per-query terms (see sTail in the kernel)
+        // K, V, Q stages, dO stages; the dS tile (two at head_dim 64); dQ staging; the per-query terms (see sTail in the kernel)
         constexpr int kQStages = (D == 128) ? 2 : 3;
-        const size_t smem = (size_t)(128 * D * 2) * (2 + kQStages + kDoStages) + 128 * 128 * 2 + 32 * 1024 +
+        const size_t smem = (size_t)(128 * D * 2) * (2 + kQStages + kDoStages) + (D == 128 ? 1 : 2) * 128 * 128 * 2 + 32 * 1024 +
                             (kAug ? (size_t)(2 + kQStages + kDoStages) * 128 * 16 : (size_t)2 * kQStages * 128 * 4) + sizeof(BwdBarriers);
         if ((e = ensure_dynamic_smem(attn_bwd_tc_kernel<D, kWin, kSplit, kDet>, smem, configured)) != cudaSuccess) return e;
         attn_bwd_tc_kernel<D, kWin, kSplit, kDet><<<(unsigned)ctas, kBwdThreads, smem, st>>>(tq, tk, tv, tdo, p);
