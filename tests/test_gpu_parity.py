@@ -309,6 +309,35 @@ def test_backward_long_key_tiles_cut_by_query_head(sb, oracle):
         _check_bf16(_np(got), _np(want), what + " slice vs exact kernels")
 
 
+def test_backward_head_dim_64_buffers_and_cut_tiles_vs_oracle(sb, oracle):
+    """head_dim 64 takes a path of its own inside the backward kernel (LSE and delta folded into the S^T / dP^T products,
+    two S^T buffers, three Q stages, two dS tiles).  B1 / Hq8 / Hkv2 / S1400 is a grid small enough that every key tile is
+    cut by query head, with more steps per CTA than there are buffers of any kind and a ragged last tile: whole tensors
+    against the fp64 oracle, two runs bit-identical in dK/dV; then a single-tile case (fewer steps than buffers)."""
+    w = sb.WORKLOADS["llama1b_gqa"]
+    q, k, v, do = _bf16_case(w, batch=1, q_heads=8, kv_heads=2, seq=1400)
+    wo, wl, wdq, wdk, wdv = _oracle_full(oracle, q, k, v, do)
+    qd, kd, vd, dod = (t.cuda() for t in (q, k, v, do))
+    o, lse = sb.attention_forward(qd, kd, vd)
+    dq, dk, dv = sb.attention_backward(qd, kd, vd, o, lse, dod)
+    assert sb.last_path() == "tcgen05" and sb.poll_device_status() == 0
+    _check_bf16(_np(dq), wdq, "dq")
+    _check_bf16(_np(dk), wdk, "dk")
+    _check_bf16(_np(dv), wdv, "dv")
+    _, dk2, dv2 = sb.attention_backward(qd, kd, vd, o, lse, dod)
+    assert torch.equal(dk, dk2) and torch.equal(dv, dv2)
+    # one key tile only (a single step per head: fewer steps than buffers)
+    q, k, v, do = _bf16_case(w, batch=2, q_heads=4, kv_heads=4, seq=100)
+    wo, wl, wdq, wdk, wdv = _oracle_full(oracle, q, k, v, do)
+    qd, kd, vd, dod = (t.cuda() for t in (q, k, v, do))
+    o, lse = sb.attention_forward(qd, kd, vd)
+    dq, dk, dv = sb.attention_backward(qd, kd, vd, o, lse, dod)
+    assert sb.poll_device_status() == 0
+    _check_bf16(_np(dq), wdq, "dq (one tile)")
+    _check_bf16(_np(dk), wdk, "dk (one tile)")
+    _check_bf16(_np(dv), wdv, "dv (one tile)")
+
+
 @pytest.mark.parametrize("wname", ["gpt2_small", "llama1b_gqa", "gqa7b_d128"])
 def test_full_size_workloads_sampled_oracle_and_cross_check(sb, oracle, wname):
     """At the benchmark's full sizes: sampled fp64-oracle rows/columns, plus size-independent properties
