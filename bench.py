@@ -544,6 +544,11 @@ def run_ring(torch, dist, sb, dev, rank, world, timed, steps, per_gpu_value):
     native = NativeRing()
     res, total, fwd_ms = measure(native)
     bwd_ms = total - fwd_ms                # the backward consumes the state its forward kept, so it is not timed alone
+    # the same calls for a host that keeps its shards in the zigzag order (SNTL_FLAG_RING_ZIGZAG): nothing is redistributed.
+    # The same device tensors serve (which tokens they stand for does not change the time).
+    zz = NativeRing(zigzag_layout=True)
+    _, zz_total, zz_fwd_ms = measure(zz)
+    zz.close()
     # the same schedule driven from Python over torch.distributed (the form the CPU tests pin), and one profiled step of it
     py_res, py_total, py_fwd_ms = measure(RingAttention(GpuBackend()))
     prof = RingAttention(GpuBackend(), profile=True)
@@ -562,6 +567,10 @@ def run_ring(torch, dist, sb, dev, rank, world, timed, steps, per_gpu_value):
             "bytes_sent_per_gpu_per_step": {"forward": (world - 1) * kv_bytes, "backward": (world - 1) * kv_bytes + world * acc_bytes,
                                             "redistribution": "one of the two half-shards of Q,K,V,O,dO,LSE each way, once"},
             "driver": "sntl_ring_attn_fwd / sntl_ring_attn_bwd (C ABI, NCCL send/recv issued by the library)",
+            "zigzag_layout": {"value": flops / (zz_total * 1e-3) / 1e12, "ms_per_step": zz_total, "fwd_ms": zz_fwd_ms,
+                              "bwd_ms": zz_total - zz_fwd_ms,
+                              "efficiency_vs_n_times_one_gpu": flops / (zz_total * 1e-3) / 1e12 / (world * per_gpu_value),
+                              "note": "shards passed and returned in the zigzag order (SNTL_FLAG_RING_ZIGZAG): no redistribution round"},
             "python_schedule": {"value": flops / (py_total * 1e-3) / 1e12, "ms_per_step": py_total, "fwd_ms": py_fwd_ms,
                                 "bwd_ms": py_total - py_fwd_ms, "compute_stream_breakdown_ms": prof.timings},
             "oracle": {"first_rank": gathered[0], "last_rank": gathered[world - 1],

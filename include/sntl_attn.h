@@ -78,7 +78,13 @@ enum {
      * head_dim-64 backward has an exclusive dQ store (sentinel/NeuralNet/Cuda/CudaFlashAttention.cu:1434-1455);
      * a caller that relies on bit-stable input gradients sets this flag.  Ignored by the exact kernels, whose
      * dQ is reproducible already. */
-    SNTL_FLAG_DETERMINISTIC = 4
+    SNTL_FLAG_DETERMINISTIC = 4,
+    /* sntl_ring_attn_fwd / _bwd only: the shard a rank passes is already its two zigzag chunks.  The sequence is cut in
+     * 2*world equal chunks; tokens [0, S/2W) of rank r's shard are chunk r and tokens [S/2W, S/W) are chunk
+     * 2*world-1-r (results come back in the same order).  A host that keeps its activations in this order for the whole
+     * model -- the usual arrangement of causal sequence parallelism -- saves the redistribution round before and after
+     * every call: the deal becomes a local copy. */
+    SNTL_FLAG_RING_ZIGZAG = 8
 };
 
 typedef struct sntl_attn_desc {
@@ -222,7 +228,8 @@ int sntl_attn_accumulate(int32_t part_dtype, int64_t count, float* acc, const vo
  * head_dim 64 or 128, desc->seq_q = desc->seq_kv = S/W (even), desc->causal = 1.  The shards are dealt as half-shards in
  * a zigzag so that every rank has the same work under the causal mask; K/V half-shards travel round the ring with
  * grouped ncclSend / ncclRecv on the handle's own stream while the kernels of the current step run, and in the backward
- * fp32 dK/dV accumulators travel with them.  Results come back in the contiguous layout.  Every rank makes the same
+ * fp32 dK/dV accumulators travel with them.  Results come back in the contiguous layout (with SNTL_FLAG_RING_ZIGZAG the
+ * shards are taken and returned in the zigzag order itself and nothing is redistributed).  Every rank makes the same
  * calls in the same order.  All scratch comes from `workspace` (sntl_ring_attn_workspace_bytes; it must not be touched
  * between a forward and a backward that reuses its state); streams and events belong to the handle.
  *   sntl_ring_unique_id      rank 0 fills 128 bytes (an ncclUniqueId) that the host distributes to all ranks.

@@ -11,7 +11,7 @@ LIB_PATH = os.environ.get("SNTL_ATTN_LIB") or os.path.join(HERE, "lib", "libsntl
 OK, ERR_BAD_ARGUMENT, ERR_UNSUPPORTED, ERR_WORKSPACE, ERR_CUDA, ERR_NO_DEVICE, ERR_DEVICE_TIMEOUT = range(7)
 DTYPE_BF16, DTYPE_F32 = 0, 1
 LAYOUT_BHSD, LAYOUT_SENTINEL = 0, 1
-FLAG_ALLOW_BF16_COMPUTE, FLAG_FORCE_SIMT, FLAG_DETERMINISTIC = 1, 2, 4
+FLAG_ALLOW_BF16_COMPUTE, FLAG_FORCE_SIMT, FLAG_DETERMINISTIC, FLAG_RING_ZIGZAG = 1, 2, 4, 8
 
 # every symbol include/sntl_attn.h declares
 EXPORTS = ["sntl_attn_version", "sntl_status_string", "sntl_attn_fwd_workspace_bytes", "sntl_attn_bwd_workspace_bytes",

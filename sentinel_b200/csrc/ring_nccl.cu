@@ -89,6 +89,7 @@ namespace {
 // Everything one call touches, carved from the caller's workspace.  Sizes in elements of one chunk (half a shard).
 struct Ring {
     sntl_ring_comm* c;
+    bool zigzag;                  // the caller's shards are the two zigzag chunks already (SNTL_FLAG_RING_ZIGZAG)
     int B, Hq, Hkv, Sc, D;        // Sc = tokens per chunk
     float scale;
     size_t n_q, n_kv, n_l;        // elements per chunk of a Q-like tensor, a K-like tensor, an LSE-like tensor
@@ -185,6 +186,7 @@ int validate_ring(const sntl_ring_comm* c, const sntl_attn_desc* d)
 void make_ring(Ring& r, sntl_ring_comm* c, const sntl_attn_desc* d, void* workspace)
 {
     r.c = c;
+    r.zigzag = (d->flags & SNTL_FLAG_RING_ZIGZAG) != 0;
     r.B = d->batch; r.Hq = d->q_heads; r.Hkv = d->kv_heads; r.Sc = d->seq_q / 2; r.D = d->head_dim;
     r.scale = d->scale;
     r.n_q = (size_t)r.B * r.Hq * r.Sc * r.D;
@@ -218,6 +220,19 @@ void deal(Ring& r, DealItem* items, int n, bool reverse, cudaStream_t main, Fail
     const int mine[2] = {2 * me, 2 * me + 1};            // chunks of the contiguous shard
     const int work[2] = {me, 2 * W - 1 - me};            // chunks this rank works on
     NcclApi& api = nccl();
+    if (r.zigzag) {
+        // the shard is the two chunks this rank works on, one after the other inside every slab: a local (un)packing
+        for (int t = 0; t < n; ++t) {
+            DealItem& it = items[t];
+            const size_t chunk_bytes = (size_t)r.Sc * it.row_bytes, pitch = 2 * chunk_bytes;
+            for (int h = 0; h < 2; ++h) {
+                char* half = const_cast<char*>(it.x) + (size_t)h * chunk_bytes;
+                if (!reverse) f.cuda(cudaMemcpy2DAsync(it.z[h], chunk_bytes, half, pitch, chunk_bytes, it.slabs, cudaMemcpyDeviceToDevice, main));
+                else f.cuda(cudaMemcpy2DAsync(half, pitch, it.z[h], chunk_bytes, chunk_bytes, it.slabs, cudaMemcpyDeviceToDevice, main));
+            }
+        }
+        return;
+    }
     // 1. local copies and packing of what leaves
     for (int t = 0; t < n; ++t) {
         DealItem& it = items[t];

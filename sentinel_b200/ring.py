@@ -59,6 +59,14 @@ def zigzag_chunks(rank: int, world: int):
     return (rank, 2 * world - 1 - rank)
 
 
+def zigzag_shard(x_full, rank: int, world: int):
+    """Rank ``rank``'s shard of a whole-sequence tensor ``[B, H, S, ...]`` in the zigzag layout: chunk ``rank`` followed by
+    chunk ``2*world-1-rank`` of the ``2*world`` equal chunks of the sequence (what ``zigzag_layout=True`` expects)."""
+    chunks = x_full.chunk(2 * world, dim=2)
+    a, b = zigzag_chunks(rank, world)
+    return torch.cat([chunks[a], chunks[b]], dim=2).contiguous()
+
+
 def visible_pairs(q_chunks, kv_chunks):
     """[(qi, ki, causal)] over local slot indices for the pairs the causal mask lets through."""
     out = []
@@ -107,7 +115,10 @@ class GpuBackend:
 
 
 class RingAttention:
-    def __init__(self, backend, group=None, timeout_s: float = 60.0, profile: bool = False):
+    def __init__(self, backend, group=None, timeout_s: float = 60.0, profile: bool = False, zigzag_layout: bool = False):
+        """``zigzag_layout``: every shard passed in (and returned) is already the rank's two zigzag chunks, first half of
+        the shard = chunk ``rank``, second half = chunk ``2W-1-rank`` (see ``zigzag_shard``); nothing is redistributed."""
+        self.zigzag_layout = zigzag_layout
         self.backend = backend
         self.group = group
         self.rank = dist.get_rank(group)
@@ -151,6 +162,8 @@ class RingAttention:
         """Contiguous shards [B,H,S_local,...] -> for each, the list of the two chunks this rank works on (zigzag deal).
         All tensors travel in one batched round."""
         r, W = self.rank, self.world
+        if self.zigzag_layout:
+            return [[x[:, :, :x.shape[2] // 2].contiguous(), x[:, :, x.shape[2] // 2:].contiguous()] for x in xs]
         want = zigzag_chunks(r, W)
         outs, sends, recvs = [], [], []
         for x in xs:
@@ -169,6 +182,8 @@ class RingAttention:
     def from_zigzag_many(self, chunk_lists):
         """Inverse of ``to_zigzag_many``: per tensor, the two zigzag chunks -> this rank's contiguous shard."""
         r, W = self.rank, self.world
+        if self.zigzag_layout:
+            return [torch.cat(list(chunks), dim=2) for chunks in chunk_lists]
         want = (2 * r, 2 * r + 1)
         outs, sends, recvs = [], [], []
         for chunks in chunk_lists:
@@ -374,10 +389,13 @@ class NativeRing:
     workspace, nothing allocated per call.  This is what a C / C++ host binds; here ``torch.distributed`` is only used
     to hand the NCCL unique id from rank 0 to the other ranks.  bf16 ``[B, H, S/W, D]`` CUDA shards, head_dim 64 / 128."""
 
-    def __init__(self, group=None):
+    def __init__(self, group=None, zigzag_layout: bool = False):
+        """``zigzag_layout``: shards come and go as the rank's two zigzag chunks (``SNTL_FLAG_RING_ZIGZAG``,
+        ``zigzag_shard``); the library then redistributes nothing."""
         import ctypes as C
         from . import _lib
         self._C, self._lib = C, _lib
+        self.zigzag_layout = zigzag_layout
         self.lib = _lib.load()
         self.rank = dist.get_rank(group)
         self.world = dist.get_world_size(group)
@@ -406,7 +424,8 @@ class NativeRing:
 
     def _desc(self, q, k):
         B, Hq, S, D = q.shape
-        return self._lib.Desc(self._lib.DTYPE_BF16, self._lib.LAYOUT_BHSD, B, Hq, k.shape[1], S, S, D, float(D ** -0.5), 1, 0, 0, 0, 0, 0)
+        flags = self._lib.FLAG_RING_ZIGZAG if self.zigzag_layout else 0
+        return self._lib.Desc(self._lib.DTYPE_BF16, self._lib.LAYOUT_BHSD, B, Hq, k.shape[1], S, S, D, float(D ** -0.5), 1, 0, 0, flags, 0, 0)
 
     def _workspace(self, d, device):
         need = self.lib.sntl_ring_attn_workspace_bytes(self.handle, self._C.byref(d))

@@ -115,6 +115,21 @@ def _ring_worker(rank, world, port, shape, out_dir):
         # zigzag deal and its inverse are exact permutations
         x = torch.arange(B * Hq * (S // world) * D, dtype=torch.float32).reshape(B, Hq, S // world, D) + 1e6 * rank
         assert torch.equal(ring.from_zigzag(ring.to_zigzag(x)), x)
+        # shards handed over in the zigzag layout itself (nothing is redistributed: no exchange before the first step):
+        # the same numbers, in that layout
+        from sentinel_b200.ring import zigzag_shard
+        zring = RingAttention(OracleBackend(), zigzag_layout=True)
+        qz, kz, vz, doz = (zigzag_shard(t, rank, world) for t in (q, k, v, do))
+        oz, lsez = zring.forward(qz, kz, vz)
+        dqz, dkz, dvz = zring.backward(qz, kz, vz, oz, lsez, doz)
+        full = {}
+        for name, mine in (("o", o), ("lse", lse.unsqueeze(-1)), ("dq", dq), ("dk", dk), ("dv", dv)):
+            parts = [torch.empty_like(mine) for _ in range(world)]
+            dist.all_gather(parts, mine.contiguous())
+            full[name] = torch.cat(parts, dim=2)
+        for name, got in (("o", oz), ("lse", lsez.unsqueeze(-1)), ("dq", dqz), ("dk", dkz), ("dv", dvz)):
+            want = zigzag_shard(full[name], rank, world)
+            assert float((got - want).abs().max()) <= 1e-6 * max(1.0, float(want.abs().max())), name
     finally:
         dist.destroy_process_group()
 
