@@ -8,6 +8,9 @@
 //   * K/V chunks and the dK/dV accumulators move with grouped ncclSend / ncclRecv on a communication stream of the
 //     handle's own, ordered against the compute streams with events; received data lands in local HBM first and is then
 //     read by ordinary per-CTA TMA loads (no kernel here ever reads a peer's memory);
+//   * the K/V chunks do not wait for anybody's kernels: all world - 1 hops of their journey are posted at the start of a
+//     call, each into a receive set of its own, and run back to back at link speed (the Python schedule posts one hop per
+//     step instead); the accumulators, which need every rank's contribution on the way, still hop once per step;
 //   * the two block pairs of a step run on two compute streams (the caller's and one of the handle's), so that the
 //     last, partly filled wave of CTAs of one launch is covered by the other;
 //   * nothing is allocated per call: every buffer is carved from the caller's workspace
@@ -69,6 +72,7 @@ NcclApi& nccl()
 }
 
 inline size_t up256(size_t x) { return (x + 255) / 256 * 256; }
+constexpr int kMaxWorld = 64;     // ranks of one ring
 
 }  // namespace
 }  // namespace sntl
@@ -80,7 +84,8 @@ struct sntl_ring_comm {
     bool owns_comm = false;
     int rank = 0, world = 1, device = 0;
     cudaStream_t comm_stream = nullptr, side_stream = nullptr;
-    cudaEvent_t ev_main = nullptr, ev_side = nullptr, ev_kv = nullptr, ev_acc = nullptr, ev_deal = nullptr;
+    cudaEvent_t ev_main = nullptr, ev_side = nullptr, ev_acc = nullptr, ev_deal = nullptr;
+    cudaEvent_t* ev_hop = nullptr;   // [world - 1]: K/V of step h + 1 have arrived
 };
 
 namespace sntl {
@@ -99,7 +104,7 @@ struct Ring {
     // staging for the deal (room for both halves of a tensor: either may leave, and either work chunk may arrive)
     __nv_bfloat16 *st_q, *st_k, *st_v, *st_o, *st_do;
     float* st_l;
-    __nv_bfloat16* kvbuf[2][4];   // two receive sets of (k0, k1, v0, v1)
+    __nv_bfloat16* kvbuf[kMaxWorld][4];   // world - 1 receive sets of (k0, k1, v0, v1): one per hop of the K/V chain
     // forward
     float *o_acc[2], *lse_acc[2];
     __nv_bfloat16* o_part[2];
@@ -143,7 +148,7 @@ void lay_out(Ring& r, char* base)
     r.st_k = (__nv_bfloat16*)take(2 * 2 * r.n_kv);
     r.st_v = (__nv_bfloat16*)take(2 * 2 * r.n_kv);
     r.st_l = (float*)take(2 * 4 * r.n_l);
-    for (int s = 0; s < 2; ++s)
+    for (int s = 0; s + 1 < r.c->world; ++s)
         for (int i = 0; i < 4; ++i) r.kvbuf[s][i] = (__nv_bfloat16*)take(2 * r.n_kv);
     // forward-only and backward-only buffers share one region: a call is one or the other
     const size_t shared0 = off;
@@ -173,6 +178,7 @@ void lay_out(Ring& r, char* base)
 int validate_ring(const sntl_ring_comm* c, const sntl_attn_desc* d)
 {
     if (!c || !d) return SNTL_ERR_BAD_ARGUMENT;
+    if (c->world > kMaxWorld) return SNTL_ERR_UNSUPPORTED;
     if (d->dtype != SNTL_DTYPE_BF16 || d->layout != SNTL_LAYOUT_BHSD) return SNTL_ERR_UNSUPPORTED;
     if (d->batch <= 0 || d->q_heads <= 0 || d->kv_heads <= 0 || d->seq_q <= 0 || d->q_heads % d->kv_heads != 0) return SNTL_ERR_BAD_ARGUMENT;
     if (d->seq_kv != d->seq_q || !d->causal) return SNTL_ERR_BAD_ARGUMENT;     // every rank holds seq_q tokens of one causal sequence
@@ -305,6 +311,26 @@ void rotate(Ring& r, void* const* send, void* const* recv, int count, size_t byt
     f.cuda(cudaEventRecord(done, c->comm_stream));
 }
 
+// Posts the whole journey of the K/V chunks round the ring at once: hop h sends what hop h - 1 received (hop 0: this
+// rank's own chunks) to rank + 1 and receives the chunks of step h + 1 from rank - 1 into receive set h.  The hops run
+// back to back on the communication stream, at link speed, without waiting for any rank's kernels -- every rank holds a
+// buffer per hop -- so a rank that runs late delays nobody's K/V, and only the first steps can ever wait for a hop.
+void post_kv_chain(Ring& r, __nv_bfloat16* const own[4], cudaStream_t main, Fail& f)
+{
+    sntl_ring_comm* c = r.c;
+    if (c->world < 2) return;
+    f.cuda(cudaEventRecord(c->ev_main, main));
+    for (int h = 0; h + 1 < c->world && !f.bad(); ++h) {
+        void* s4[4];
+        void* r4[4];
+        for (int i = 0; i < 4; ++i) {
+            s4[i] = h == 0 ? own[i] : r.kvbuf[h - 1][i];
+            r4[i] = r.kvbuf[h][i];
+        }
+        rotate(r, s4, r4, 4, 2 * r.n_kv, c->ev_main, c->ev_hop[h], f);   // (waiting for ev_main again is free)
+    }
+}
+
 struct Pair { int qi, ki, causal; };
 int visible_pairs(const int q_ids[2], const int kv_ids[2], Pair out[4])
 {
@@ -357,8 +383,13 @@ static int make_handle(ncclComm_t comm, bool owns, int rank, int world, sntl_rin
     ok = ok && cudaDeviceGetStreamPriorityRange(&prio_least, &prio_greatest) == cudaSuccess;
     ok = ok && cudaStreamCreateWithPriority(&c->comm_stream, cudaStreamNonBlocking, prio_greatest) == cudaSuccess;
     ok = ok && cudaStreamCreateWithFlags(&c->side_stream, cudaStreamNonBlocking) == cudaSuccess;
-    cudaEvent_t* evs[] = {&c->ev_main, &c->ev_side, &c->ev_kv, &c->ev_acc, &c->ev_deal};
+    cudaEvent_t* evs[] = {&c->ev_main, &c->ev_side, &c->ev_acc, &c->ev_deal};
     for (cudaEvent_t* e : evs) ok = ok && cudaEventCreateWithFlags(e, cudaEventDisableTiming) == cudaSuccess;
+    if (world > 1) {
+        c->ev_hop = new (std::nothrow) cudaEvent_t[world - 1]();
+        ok = ok && c->ev_hop != nullptr;
+        for (int i = 0; ok && i + 1 < world; ++i) ok = cudaEventCreateWithFlags(&c->ev_hop[i], cudaEventDisableTiming) == cudaSuccess;
+    }
     if (!ok) { delete c; return SNTL_ERR_CUDA; }
     *out = c;
     return SNTL_OK;
@@ -391,8 +422,12 @@ int sntl_ring_comm_destroy(sntl_ring_comm* c)
     cudaStreamSynchronize(c->comm_stream);
     cudaStreamSynchronize(c->side_stream);
     if (c->owns_comm && c->comm) nccl().CommDestroy(c->comm);
-    cudaEvent_t evs[] = {c->ev_main, c->ev_side, c->ev_kv, c->ev_acc, c->ev_deal};
+    cudaEvent_t evs[] = {c->ev_main, c->ev_side, c->ev_acc, c->ev_deal};
     for (cudaEvent_t e : evs) if (e) cudaEventDestroy(e);
+    if (c->ev_hop) {
+        for (int i = 0; i + 1 < c->world; ++i) if (c->ev_hop[i]) cudaEventDestroy(c->ev_hop[i]);
+        delete[] c->ev_hop;
+    }
     cudaStreamDestroy(c->comm_stream);
     cudaStreamDestroy(c->side_stream);
     delete c;
@@ -430,16 +465,15 @@ int sntl_ring_attn_fwd(sntl_ring_comm* c, const sntl_attn_desc* d, const void* q
     }
     const int q_ids[2] = {me, 2 * W - 1 - me};
     __nv_bfloat16* cur[4] = {r.kz[0], r.kz[1], r.vz[0], r.vz[1]};
+    post_kv_chain(r, cur, main, f);
     for (int step = 0; step < W && !f.bad(); ++step) {
         const int src = ((me - step) % W + W) % W;
         const int kv_ids[2] = {src, 2 * W - 1 - src};
-        __nv_bfloat16** nxt = r.kvbuf[step & 1];
-        f.cuda(cudaEventRecord(c->ev_main, main));
-        if (step + 1 < W) {
-            void* s4[4] = {cur[0], cur[1], cur[2], cur[3]};
-            void* r4[4] = {nxt[0], nxt[1], nxt[2], nxt[3]};
-            rotate(r, s4, r4, 4, 2 * r.n_kv, c->ev_main, c->ev_kv, f);
+        if (step > 0) {
+            f.cuda(cudaStreamWaitEvent(main, c->ev_hop[step - 1], 0));
+            for (int i = 0; i < 4; ++i) cur[i] = r.kvbuf[step - 1][i];
         }
+        f.cuda(cudaEventRecord(c->ev_main, main));
         Pair pairs[4];
         const int n = visible_pairs(q_ids, kv_ids, pairs);
         // the pairs of query chunk 0 on the caller's stream, those of query chunk 1 on the side stream (when both have some)
@@ -461,10 +495,6 @@ int sntl_ring_attn_fwd(sntl_ring_comm* c, const sntl_attn_desc* d, const void* q
         if (two) {
             f.cuda(cudaEventRecord(c->ev_side, side));
             f.cuda(cudaStreamWaitEvent(main, c->ev_side, 0));
-        }
-        if (step + 1 < W) {
-            f.cuda(cudaStreamWaitEvent(main, c->ev_kv, 0));
-            for (int i = 0; i < 4; ++i) cur[i] = nxt[i];
         }
     }
     for (int i = 0; i < 2; ++i) f.cuda(f32_to_bf16(r.o_acc[i], r.oz[i], r.n_q, main));
@@ -516,16 +546,15 @@ int sntl_ring_attn_bwd(sntl_ring_comm* c, const sntl_attn_desc* d, const void* q
     __nv_bfloat16* cur[4] = {r.kz[0], r.kz[1], r.vz[0], r.vz[1]};
     int a_cur = 0, a_recv = 1, a_send = 2;         // indices into r.acc: being completed, being received, being sent
     for (int i = 0; i < 4; ++i) f.cuda(cudaMemsetAsync(r.acc[a_cur][i], 0, 4 * r.n_kv, main));
+    post_kv_chain(r, cur, main, f);
     for (int step = 0; step < W && !f.bad(); ++step) {
         const int src = ((me - step) % W + W) % W;
         const int kv_ids[2] = {src, 2 * W - 1 - src};
-        __nv_bfloat16** nxt = r.kvbuf[step & 1];
-        f.cuda(cudaEventRecord(c->ev_main, main));
-        if (step + 1 < W) {
-            void* s4[4] = {cur[0], cur[1], cur[2], cur[3]};
-            void* r4[4] = {nxt[0], nxt[1], nxt[2], nxt[3]};
-            rotate(r, s4, r4, 4, 2 * r.n_kv, c->ev_main, c->ev_kv, f);
+        if (step > 0) {
+            f.cuda(cudaStreamWaitEvent(main, c->ev_hop[step - 1], 0));
+            for (int i = 0; i < 4; ++i) cur[i] = r.kvbuf[step - 1][i];
         }
+        f.cuda(cudaEventRecord(c->ev_main, main));
         Pair pairs[4];
         const int n = visible_pairs(q_ids, kv_ids, pairs);
         const bool two = n > 1;
@@ -566,10 +595,6 @@ int sntl_ring_attn_bwd(sntl_ring_comm* c, const sntl_attn_desc* d, const void* q
             void* s4[4] = {r.acc[a_send][0], r.acc[a_send][1], r.acc[a_send][2], r.acc[a_send][3]};
             void* r4[4] = {r.acc[a_recv][0], r.acc[a_recv][1], r.acc[a_recv][2], r.acc[a_recv][3]};
             rotate(r, s4, r4, 4, 4 * r.n_kv, c->ev_main, c->ev_acc, f);
-        }
-        if (step + 1 < W) {
-            f.cuda(cudaStreamWaitEvent(main, c->ev_kv, 0));
-            for (int i = 0; i < 4; ++i) cur[i] = nxt[i];
         }
     }
     int home = a_cur;
