@@ -319,6 +319,7 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
     // dS_i -> dQ_i -> drain -> dP^T_{i+1} -> dS_{i+1} then no longer carries the issue time of dK_i (with one buffer dK_i must
     // have read the tile before dP^T_{i+1} lets the compute warps overwrite it)
     constexpr int kDsBufs = (D == 128) ? 1 : 2;
+    constexpr bool kElect14 = D == 64;             // issue form of the dS-side warp (see there)
     // columns of a dQ tile per bulk reduction (kStageCols columns x 128 rows fp32 = one piece): 8 KB pieces at head_dim 128,
     // where the tile loads of Q and dO queue behind the reductions on the SM's path to L2 and shorter pieces let them through
     // sooner (-3 % kernel time); 16 KB pieces at head_dim 64 (there the finer split costs 1 %, and 4 KB pieces cost 10-20 %
@@ -547,7 +548,16 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
             }
             tc_commit_e(&bars->final_bar);
             wait(&bars->final_bar, 0, kSiteFinal);
-        } else if (warp == 14 && lane == 0 && n_iter > 0) {
+        } else if (warp == 14 && (kElect14 || lane == 0) && n_iter > 0) {
+            // dS side.  At head_dim 64 it takes the same warp-uniform form as the P side (-4 % kernel time); at 128 a single
+            // lane walks the loop: there the faster form costs 8 % (2.81 vs 2.59 ms) -- these products then get into the
+            // tensor pipe ahead of the P side's, whose chain sets the step at that head size.
+            const bool tl14 = lane == 0;
+            (void)tl14;
+            auto wait = [&](uint64_t* bar, uint32_t parity, uint32_t site) {
+                if constexpr (kElect14) return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag, site));
+                else return mbar_wait(bar, parity, abort_flag, site);
+            };
             SNTL_TRACE_DECL(tn);
             constexpr uint32_t idesc_st = make_idesc(kT, kT, false, false);   // S^T, dP^T
             constexpr uint32_t idesc_kv = make_idesc(kT, D, false, true);     // dV, dK: A in TMEM, B MN-major
@@ -559,45 +569,45 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
             // the D/16 steps over the head dimension, then the extra step that subtracts delta (see kAugBytes)
             auto issue_kmajor = [&](uint32_t d_tmem, uint64_t a, uint64_t b, uint64_t aug) {
                 asm volatile("" : "+l"(a), "+l"(b), "+l"(aug));
-                mma_ss_c<false>(d_tmem, a, b, idesc_st);
+                mma_ss_x<kElect14, false>(d_tmem, a, b, idesc_st);
 #pragma unroll
                 for (int ks = 1; ks < D / 16; ++ks) {
                     const uint32_t off = (uint32_t)((ks >> 2) * kChunkBytes + (ks & 3) * 32);
-                    mma_ss_c<true>(d_tmem, sdesc_advance(a, off), sdesc_advance(b, off), idesc_st);
+                    mma_ss_x<kElect14, true>(d_tmem, sdesc_advance(a, off), sdesc_advance(b, off), idesc_st);
                 }
-                if constexpr (kAug) mma_ss_c<true>(d_tmem, d_ones, aug, idesc_st);
+                if constexpr (kAug) mma_ss_x<kElect14, true>(d_tmem, d_ones, aug, idesc_st);
             };
-            bool ok = mbar_wait(&bars->kv_full, 0, abort_flag, kSiteKV);
+            bool ok = wait(&bars->kv_full, 0, kSiteKV);
             {
                 const uint64_t dV_k = make_sdesc(smem_u32(sV), 16, 1024), dDo_k0 = make_sdesc(smem_u32(sDo), 16, 1024);
                 const uint64_t dK_mn = make_sdesc(smem_u32(sK), kChunkBytes, 1024), dDs_mn = make_sdesc(smem_u32(sDs), kChunkBytes, 1024);
                 const uint64_t dDs_k = make_sdesc(smem_u32(sDs), 16, 1024);
                 const uint64_t dQ_mn0 = make_sdesc(smem_u32(sQ), kChunkBytes, 1024);
-                ok = ok && mbar_wait(&bars->do_full[0], 0, abort_flag, kSiteDoFull);
+                ok = ok && wait(&bars->do_full[0], 0, kSiteDoFull);
                 if (ok) {
                     tc_fence_after();
                     issue_kmajor(tm_dP, dV_k, dDo_k0, d_doaug0);
-                    tc_commit(&bars->dp_ready);
-                    tc_commit(&bars->do_empty[0]);   // this warp's share of releasing dO_0: dP^T_0
+                    tc_commit_x<kElect14>(&bars->dp_ready);
+                    tc_commit_x<kElect14>(&bars->do_empty[0]);   // this warp's share of releasing dO_0: dP^T_0
                 }
                 for (int i = 0; ok && i < n_iter; ++i) {
                     const uint32_t ph = (uint32_t)(i & 1);
                     const int sq = i % kQStages;
-                    if (!(ok = mbar_wait(&bars->ds_ready, ph, abort_flag, kSiteDS))) break;
-                    SNTL_TRACE_EV(true, 4, tn, 3);
+                    if (!(ok = wait(&bars->ds_ready, ph, kSiteDS))) break;
+                    SNTL_TRACE_EV(tl14, 4, tn, 3);
                     tc_fence_after();
                     // dQ first: it gates the drain and with it the next dP^T
                     const uint32_t ds_off = (uint32_t)((i % kDsBufs) * kDsBytes);
                     {
                         uint64_t a = sdesc_advance(dDs_mn, ds_off), bq = dK_mn;
                         asm volatile("" : "+l"(a), "+l"(bq));
-                        mma_ss_c<false>(tm_dP, a, bq, idesc_dq);
+                        mma_ss_x<kElect14, false>(tm_dP, a, bq, idesc_dq);
 #pragma unroll
                         for (int ks = 1; ks < kT / 16; ++ks)
-                            mma_ss_c<true>(tm_dP, sdesc_advance(a, ks * 2048), sdesc_advance(bq, ks * 2048), idesc_dq);
+                            mma_ss_x<kElect14, true>(tm_dP, sdesc_advance(a, ks * 2048), sdesc_advance(bq, ks * 2048), idesc_dq);
                     }
-                    tc_commit(&bars->dq_ready);
-                    SNTL_TRACE_EV(true, 4, tn, 4);
+                    tc_commit_x<kElect14>(&bars->dq_ready);
+                    SNTL_TRACE_EV(tl14, 4, tn, 4);
                     // dK += dS^T Q with dS^T read from its shared-memory tile as a K-major A operand (rows = keys, the 64
                     // contiguous elements run along the queries).  Q_i is ready: ds_ready implies its load was seen.  With
                     // one dS buffer it goes before the next dP^T: by the time the compute warps see that dP^T and rewrite the
@@ -606,33 +616,33 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
                     auto issue_dk = [&]() {
                         uint64_t a = sdesc_advance(dDs_k, ds_off), bq = sdesc_advance(dQ_mn0, sq * kTileBytes);
                         asm volatile("" : "+l"(a), "+l"(bq));
-                        if (i > 0) mma_ss_c<true>(tm_dK, a, bq, idesc_kv);
-                        else mma_ss_c<false>(tm_dK, a, bq, idesc_kv);
+                        if (i > 0) mma_ss_x<kElect14, true>(tm_dK, a, bq, idesc_kv);
+                        else mma_ss_x<kElect14, false>(tm_dK, a, bq, idesc_kv);
 #pragma unroll
                         for (int ks = 1; ks < kT / 16; ++ks)
-                            mma_ss_c<true>(tm_dK, sdesc_advance(a, (ks >> 2) * kChunkBytes + (ks & 3) * 32), sdesc_advance(bq, ks * 2048), idesc_kv);
-                        tc_commit(&bars->q_empty[sq]);    // this warp's share: dK_i
+                            mma_ss_x<kElect14, true>(tm_dK, sdesc_advance(a, (ks >> 2) * kChunkBytes + (ks & 3) * 32), sdesc_advance(bq, ks * 2048), idesc_kv);
+                        tc_commit_x<kElect14>(&bars->q_empty[sq]);    // this warp's share: dK_i
                     };
                     if constexpr (kDsBufs == 1) issue_dk();
                     if (i + 1 < n_iter) {
                         const int nd = (i + 1) % kDoStages;
-                        if (!(ok = mbar_wait(&bars->dq_drained, ph, abort_flag, kSiteDrained))) break;
-                        SNTL_TRACE_EV(true, 4, tn, 5);
-                        if (!(ok = mbar_wait(&bars->do_full[nd], (uint32_t)(((i + 1) / kDoStages) & 1), abort_flag, kSiteDoFull))) break;
+                        if (!(ok = wait(&bars->dq_drained, ph, kSiteDrained))) break;
+                        SNTL_TRACE_EV(tl14, 4, tn, 5);
+                        if (!(ok = wait(&bars->do_full[nd], (uint32_t)(((i + 1) / kDoStages) & 1), kSiteDoFull))) break;
                         tc_fence_after();
                         issue_kmajor(tm_dP, dV_k, sdesc_advance(dDo_k0, nd * kTileBytes), sdesc_advance(d_doaug0, nd * kAugBytes));
-                        tc_commit(&bars->dp_ready);
+                        tc_commit_x<kElect14>(&bars->dp_ready);
                         // this warp's share of releasing dO_{i+1}, committed at once: with a single dO stage the load of the
                         // next tile starts as soon as this product and dV_{i+1} have read the stage
-                        tc_commit(&bars->do_empty[nd]);
-                        SNTL_TRACE_EV(true, 4, tn, 6);
+                        tc_commit_x<kElect14>(&bars->do_empty[nd]);
+                        SNTL_TRACE_EV(tl14, 4, tn, 6);
                     }
                     if constexpr (kDsBufs == 2) issue_dk();
                 }
             }
             // every MMA of this thread has retired once its commit lands; the epilogue waits for both issuers
-            tc_commit(&bars->final_bar);
-            mbar_wait(&bars->final_bar, 0, abort_flag, kSiteFinal);
+            tc_commit_x<kElect14>(&bars->final_bar);
+            wait(&bars->final_bar, 0, kSiteFinal);
         }
     } else if (warp >= 8) {
         setmaxnreg_inc<152>();

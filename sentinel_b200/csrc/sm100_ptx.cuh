@@ -327,6 +327,19 @@ __device__ __forceinline__ void tc_commit_e(uint64_t* bar)
 {
     if (elect_one()) tc_commit(bar);
 }
+// either form, chosen at compile time: kElect = a fully active warp with an elected lane, else the calling thread itself
+template <bool kElect, bool kAccumulate>
+__device__ __forceinline__ void mma_ss_x(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc)
+{
+    if constexpr (kElect) mma_ss_e<kAccumulate>(d_tmem, a_desc, b_desc, idesc);
+    else mma_ss_c<kAccumulate>(d_tmem, a_desc, b_desc, idesc);
+}
+template <bool kElect>
+__device__ __forceinline__ void tc_commit_x(uint64_t* bar)
+{
+    if constexpr (kElect) tc_commit_e(bar);
+    else tc_commit(bar);
+}
 
 // ---------------------------------------------------------------------------------------------------
 // TMEM <-> registers.  32x32b shape: thread `lane` of warp w touches TMEM lane 32*(w%4)+lane and 32 (or 16)
