@@ -41,7 +41,7 @@ constexpr uint32_t kTmemCols = 512;
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
 
 enum WaitSite : uint32_t {
-    kSiteQ = 1, kSiteKFull, kSiteVFull, kSiteKEmpty, kSiteVEmpty, kSiteSReady, kSitePReady, kSiteOReady, kSiteFinal
+    kSiteQ = 1, kSiteKFull, kSiteVFull, kSiteKEmpty, kSiteVEmpty, kSiteSReady, kSitePReady, kSiteOReady, kSiteFinal, kSiteIssue
 };
 
 struct FwdParams {
@@ -65,6 +65,7 @@ struct FwdBarriers {
     uint64_t final_bar;
     uint32_t tmem_base;
     uint32_t abort_flag;
+    uint64_t s_free[2];      // head_dim 64 (plain / window): the softmax warps have read S_j of tile t
 };
 
 // kMode: kPlain = causal / full attention of a whole sequence; kWindow adds the sliding window (separate so that the
@@ -152,6 +153,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
             mbar_init(&bars->v_full[i], 1);
             mbar_init(&bars->v_empty[i], 1);
             mbar_init(&bars->s_ready[i], 1);
+            if (D == 64 && kMode != kCache) mbar_init(&bars->s_free[i], 128);
             mbar_init(&bars->p_ready[i], 128);
             mbar_init(&bars->o_ready[i], 1);
         }
@@ -167,8 +169,16 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = bars->tmem_base;
-    const uint32_t tmem_S[2] = {tmem + 0u, tmem + 128u};
-    const uint32_t tmem_O[2] = {tmem + 256u, tmem + 384u};
+    // head_dim 64 (plain / window kernels) leaves room for P in columns of its own: S_t [192t, 192t+128), P_t the next 64,
+    // O_t [384+64t, +64).  The next S of a tile is then issued as soon as the softmax warps have READ the current one
+    // instead of behind the P V product that consumes P, which takes a tile's two products out of the chain between two of
+    // its softmax passes.  Otherwise (512 columns full at head_dim 128): S_t [128t, +128) with P written over it,
+    // O_t [256+128t, +128).
+    constexpr bool kOwnP = D == 64 && kMode != kCache;
+    // (computed, not looked up: a two-element array indexed by the warp's tile would live in local memory)
+    auto tmem_S = [&](int t) { return tmem + (uint32_t)t * (kOwnP ? 192u : 128u); };
+    constexpr uint32_t kPOff = kOwnP ? 128u : 0u;   // P relative to the S of its tile
+    auto tmem_O = [&](int t) { return tmem + (kOwnP ? 384u : 256u) + (uint32_t)t * (kOwnP ? 64u : 128u); };
 
     // 384 threads start with 168 registers each; each role re-allocates inside its own branch
     if (warp >= 10) {
@@ -214,7 +224,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
             auto issue_s = [&](int t, int st) {
                 uint64_t a = (t && kMode != kCache) ? dq1 : dq0, b = st ? dk1 : dk0;
                 asm volatile("" : "+l"(a), "+l"(b));   // keeps the advanced descriptors from being hoisted into registers
-                const uint32_t d = tmem_S[t];
+                const uint32_t d = tmem_S(t);
                 mma_ss_c<false>(d, a, b, idesc_s);
 #pragma unroll
                 for (int ks = 1; ks < D / 16; ++ks) {
@@ -226,7 +236,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
             auto issue_pv = [&](int t, int st, bool accumulate) {
                 uint64_t b = st ? dv1 : dv0;
                 asm volatile("" : "+l"(b));
-                const uint32_t d = tmem_O[t], a = tmem_S[t];
+                const uint32_t d = tmem_O(t), a = tmem_S(t) + kPOff;
                 if (accumulate) mma_ts_c<true>(d, a, b, idesc_pv);
                 else mma_ts_c<false>(d, a, b, idesc_pv);
 #pragma unroll
@@ -259,6 +269,41 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
                             tc_commit(&bars->k_empty[t]);
                         }
                     }
+                }
+            } else if constexpr (kOwnP) {
+                // With P in columns of its own the next S of a tile no longer waits for the P V product that consumes P:
+                // per key tile j the thread first issues S_{j+1} of both query tiles, each as soon as its softmax warps have
+                // READ S_j (s_free, early in their pass), then the two P V products of step j as their P arrive.
+                bool ok = n_max > 0 && mbar_wait(&bars->q_full, 0, abort_flag, kSiteQ) &&
+                          mbar_wait(&bars->k_full[0], 0, abort_flag, kSiteKFull);
+                if (ok) {
+                    tc_fence_after();
+                    if (n_t[0] > 0) issue_s(0, 0);
+                    if (n_t[1] > 0) issue_s(1, 0);
+                    tc_commit(&bars->k_empty[0]);
+                }
+                for (int j = 0; ok && j < n_max; ++j) {
+                    const int st = j & 1, nst = st ^ 1;
+                    if (j + 1 < n_max) {
+                        if (!(ok = mbar_wait(&bars->k_full[nst], (uint32_t)(((j + 1) >> 1) & 1), abort_flag, kSiteKFull))) break;
+                        for (int t = 0; t < 2 && ok; ++t) {
+                            if (j + 1 >= n_t[t]) continue;
+                            if (!(ok = mbar_wait(&bars->s_free[t], (uint32_t)(j & 1), abort_flag, kSiteIssue))) break;
+                            tc_fence_after();
+                            issue_s(t, nst);
+                        }
+                        if (!ok) break;
+                        tc_commit(&bars->k_empty[nst]);
+                    }
+                    if (!(ok = mbar_wait(&bars->v_full[st], (uint32_t)((j >> 1) & 1), abort_flag, kSiteVFull))) break;
+                    for (int t = 0; t < 2 && ok; ++t) {
+                        if (j >= n_t[t]) continue;
+                        if (!(ok = mbar_wait(&bars->p_ready[t], (uint32_t)(j & 1), abort_flag, kSitePReady))) break;
+                        tc_fence_after();
+                        issue_pv(t, st, j > 0);
+                    }
+                    if (!ok) break;
+                    tc_commit(&bars->v_empty[st]);
                 }
             } else {
             bool ok = n_max > 0 && mbar_wait(&bars->q_full, 0, abort_flag, kSiteQ) &&
@@ -321,8 +366,12 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
             tc_fence_after();
             uint32_t s[128];
 #pragma unroll
-            for (int c = 0; c < 4; ++c) tmem_ld32(tmem_S[t] + lane_off + (uint32_t)(c * 32), s + c * 32);
+            for (int c = 0; c < 4; ++c) tmem_ld32(tmem_S(t) + lane_off + (uint32_t)(c * 32), s + c * 32);
             tmem_ld_wait();
+            if constexpr (kOwnP) {      // S_j is in registers: the next S of this tile may overwrite it
+                tc_fence_before();
+                mbar_arrive(&bars->s_free[t]);
+            }
             SNTL_TRACE_EV(tw, 1 + t, tn, 2);
             // number of visible keys of this row inside this tile
             const int key0 = key_tile(kMode == kCache ? 2 * j + t : j) * kN;
@@ -357,10 +406,16 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
             const float m_new = fmaxf(m_ref, mx * p.scale_log2);
             SNTL_TRACE_EV(tw, 1 + t, tn, 3);
             const bool need = (m_new - m_ref) > kRescaleThreshold;   // false when both are -inf (NaN compare)
+            if constexpr (kOwnP) {      // P_{j-1} has been consumed (and O holds its product): P_j may be written
+                if (j > 0) {
+                    if (!(ok = __all_sync(0xffffffffu, mbar_wait(&bars->o_ready[t], (uint32_t)((j - 1) & 1), abort_flag, kSiteOReady)))) break;
+                    tc_fence_after();
+                }
+            }
             if (j == 0) {
                 m_ref = m_new;
             } else if (__any_sync(0xffffffffu, need)) {
-                if (!(ok = __all_sync(0xffffffffu, mbar_wait(&bars->o_ready[t], (uint32_t)((j - 1) & 1), abort_flag, kSiteOReady)))) break;
+                if (!kOwnP && !(ok = __all_sync(0xffffffffu, mbar_wait(&bars->o_ready[t], (uint32_t)((j - 1) & 1), abort_flag, kSiteOReady)))) break;
                 tc_fence_after();
                 const float factor = need ? ex2(m_ref - m_new) : 1.0f;
                 if (need) m_ref = m_new;
@@ -368,11 +423,11 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
 #pragma unroll
                 for (int c = 0; c < D / 32; ++c) {
                     uint32_t o[32];
-                    tmem_ld32(tmem_O[t] + lane_off + (uint32_t)(c * 32), o);
+                    tmem_ld32(tmem_O(t) + lane_off + (uint32_t)(c * 32), o);
                     tmem_ld_wait();
 #pragma unroll
                     for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * factor);
-                    tmem_st32(tmem_O[t] + lane_off + (uint32_t)(c * 32), o);
+                    tmem_st32(tmem_O(t) + lane_off + (uint32_t)(c * 32), o);
                 }
                 tmem_st_wait();
             }
@@ -392,7 +447,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
                     l4[c & 3] += p0 + p1;
                     pk[c] = pack_bf16(p0, p1);
                 }
-                tmem_st32(tmem_S[t] + lane_off + (uint32_t)(h * 32), pk);
+                tmem_st32(tmem_S(t) + kPOff + lane_off + (uint32_t)(h * 32), pk);
             }
             l += (l4[0] + l4[1]) + (l4[2] + l4[3]);
             SNTL_TRACE_EV(tw, 1 + t, tn, 5);
@@ -422,7 +477,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
 #pragma unroll
             for (int c = 0; c < D / 32; ++c) {
                 uint32_t o[32];
-                tmem_ld32(tmem_O[t] + lane_off + (uint32_t)(c * 32), o);
+                tmem_ld32(tmem_O(t) + lane_off + (uint32_t)(c * 32), o);
                 tmem_ld_wait();
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
