@@ -9,9 +9,11 @@
 //     own softmax warpgroup (one thread per query row: tcgen05.ld's 32x32b shape hands thread i row i, so the
 //     row max / row sum need no shuffles) while a single MMA-issuing thread feeds the tensor core for both,
 //     so one tile's softmax overlaps the other tile's MMAs;
-//   * S (fp32, 128 columns) and O (fp32, D columns) live in TMEM; P is written back over S as packed bf16 and
-//     consumed by the PV MMA straight from TMEM (A operand in TMEM), V is consumed from shared memory as an
-//     MN-major operand, so nothing is transposed and P never touches shared memory;
+//   * S (fp32, 128 columns) and O (fp32, D columns) live in TMEM; P is written back as packed bf16 -- over S at
+//     head_dim 128, into 64 columns of its own at head_dim 64, where the next S of the tile is then issued as soon as
+//     the softmax warps have read the current one -- and consumed by the PV MMA straight from TMEM (A operand in
+//     TMEM), V is consumed from shared memory as an MN-major operand, so nothing is transposed and P never touches
+//     shared memory;
 //   * Q/K/V tiles arrive by per-CTA TMA (128-byte swizzle, no multicast) into two-stage K and V rings
 //     guarded by mbarriers; stages are released by tcgen05.commit;
 //   * the softmax works in the exp2 domain with scale*log2(e) folded into one FMA, and rescales O lazily:
@@ -21,7 +23,8 @@
 //     heads of one group are adjacent in launch order so they share K/V tiles in L2.
 //
 // Layout: bf16 token-major [B][H][S][D], D in {64,128}; LSE [B][Hq][Sq] fp32 (natural log).
-// TMEM map (512 columns): S0 [0,128) S1 [128,256) O0 [256,256+D) O1 [384,384+D).
+// TMEM map (512 columns): head_dim 128 and KV-cache mode S0 [0,128) S1 [128,256) O0 [256,256+D) O1 [384,384+D);
+// head_dim 64 S0 [0,128) P0 [128,192) S1 [192,320) P1 [320,384) O0 [384,448) O1 [448,512).
 #include "common.cuh"
 #include "sm100_ptx.cuh"
 
