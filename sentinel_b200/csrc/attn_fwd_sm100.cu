@@ -7,7 +7,7 @@
 //
 //   * one CTA owns 256 consecutive query rows of one (batch, head) as two 128-row tiles; each tile has its
 //     own softmax warpgroup (one thread per query row: tcgen05.ld's 32x32b shape hands thread i row i, so the
-//     row max / row sum need no shuffles) while a single MMA-issuing thread feeds the tensor core for both,
+//     row max / row sum need no shuffles) while a single MMA-issuing warp (one elected lane) feeds the tensor core for both,
 //     so one tile's softmax overlaps the other tile's MMAs;
 //   * S (fp32, 128 columns) and O (fp32, D columns) live in TMEM; P is written back as packed bf16 -- over S at
 //     head_dim 128, into 64 columns of its own at head_dim 64, where the next S of the tile is then issued as soon as
@@ -216,7 +216,19 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
     } else if (warp == 8) {
         setmaxnreg_dec<72>();
         // =========================== MMA issuer ===========================
-        if (lane == 0) {
+        // All 32 lanes walk the loops (warp-uniform control flow keeps descriptors and addresses in uniform registers) and
+        // one elected lane issues each tcgen05 instruction: the warp shares its scheduler with two softmax warps and this
+        // form needs fewer of the issue slots it is given per MMA than a single-lane loop (-3.7 % at head_dim 64, where
+        // the issue order below makes this warp's pace count; no change at 128).  The KV-cache kernel, which is bound by
+        // HBM, keeps a single lane.
+        constexpr bool kElectF = kMode != kCache;
+        if (kElectF || lane == 0) {
+            auto wait = [&](uint64_t* bar, uint32_t parity, uint32_t site) {
+                if constexpr (kElectF) return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag, site));
+                else return mbar_wait(bar, parity, abort_flag, site);
+            };
+            const bool tl8 = lane == 0;
+            (void)tl8;
             SNTL_TRACE_DECL(tn);
             constexpr uint32_t idesc_s = make_idesc(kM, kN, false, false);
             constexpr uint32_t idesc_pv = make_idesc(kM, D, false, true);
@@ -228,48 +240,48 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
                 uint64_t a = (t && kMode != kCache) ? dq1 : dq0, b = st ? dk1 : dk0;
                 asm volatile("" : "+l"(a), "+l"(b));   // keeps the advanced descriptors from being hoisted into registers
                 const uint32_t d = tmem_S(t);
-                mma_ss_c<false>(d, a, b, idesc_s);
+                mma_ss_x<kElectF, false>(d, a, b, idesc_s);
 #pragma unroll
                 for (int ks = 1; ks < D / 16; ++ks) {
                     const uint32_t off = (uint32_t)((ks >> 2) * kChunkBytes + (ks & 3) * 32);
-                    mma_ss_c<true>(d, sdesc_advance(a, off), sdesc_advance(b, off), idesc_s);
+                    mma_ss_x<kElectF, true>(d, sdesc_advance(a, off), sdesc_advance(b, off), idesc_s);
                 }
-                tc_commit(&bars->s_ready[t]);
+                tc_commit_x<kElectF>(&bars->s_ready[t]);
             };
             auto issue_pv = [&](int t, int st, bool accumulate) {
                 uint64_t b = st ? dv1 : dv0;
                 asm volatile("" : "+l"(b));
                 const uint32_t d = tmem_O(t), a = tmem_S(t) + kPOff;
-                if (accumulate) mma_ts_c<true>(d, a, b, idesc_pv);
-                else mma_ts_c<false>(d, a, b, idesc_pv);
+                if (accumulate) mma_ts_x<kElectF, true>(d, a, b, idesc_pv);
+                else mma_ts_x<kElectF, false>(d, a, b, idesc_pv);
 #pragma unroll
-                for (int ks = 1; ks < kN / 16; ++ks) mma_ts_c<true>(d, a + (uint32_t)(ks * 8), sdesc_advance(b, ks * 2048), idesc_pv);
-                tc_commit(&bars->o_ready[t]);
+                for (int ks = 1; ks < kN / 16; ++ks) mma_ts_x<kElectF, true>(d, a + (uint32_t)(ks * 8), sdesc_advance(b, ks * 2048), idesc_pv);
+                tc_commit_x<kElectF>(&bars->o_ready[t]);
             };
             if constexpr (kMode == kCache) {
                 // two independent streams: stream t owns K/V stage t, S_t and O_t; its jj-th key tile is load 2*jj + t
-                bool ok = n_max > 0 && mbar_wait(&bars->q_full, 0, abort_flag, kSiteQ);
+                bool ok = n_max > 0 && wait(&bars->q_full, 0, kSiteQ);
                 for (int t = 0; t < 2 && ok; ++t) {
                     if (n_t[t] == 0) continue;
-                    if (!(ok = mbar_wait(&bars->k_full[t], 0, abort_flag, kSiteKFull))) break;
+                    if (!(ok = wait(&bars->k_full[t], 0, kSiteKFull))) break;
                     tc_fence_after();
                     issue_s(t, t);
-                    tc_commit(&bars->k_empty[t]);
+                    tc_commit_x<kElectF>(&bars->k_empty[t]);
                 }
                 for (int jj = 0; ok && jj < n_max; ++jj) {
                     const uint32_t ph = (uint32_t)(jj & 1), nph = ph ^ 1u;
                     for (int t = 0; t < 2 && ok; ++t) {
                         if (jj >= n_t[t]) continue;
-                        if (!(ok = mbar_wait(&bars->v_full[t], ph, abort_flag, kSiteVFull))) break;
-                        if (!(ok = mbar_wait(&bars->p_ready[t], ph, abort_flag, kSitePReady))) break;
+                        if (!(ok = wait(&bars->v_full[t], ph, kSiteVFull))) break;
+                        if (!(ok = wait(&bars->p_ready[t], ph, kSitePReady))) break;
                         tc_fence_after();
                         issue_pv(t, t, jj > 0);
-                        tc_commit(&bars->v_empty[t]);
+                        tc_commit_x<kElectF>(&bars->v_empty[t]);
                         if (jj + 1 < n_t[t]) {
-                            if (!(ok = mbar_wait(&bars->k_full[t], nph, abort_flag, kSiteKFull))) break;
+                            if (!(ok = wait(&bars->k_full[t], nph, kSiteKFull))) break;
                             tc_fence_after();
                             issue_s(t, t);
-                            tc_commit(&bars->k_empty[t]);
+                            tc_commit_x<kElectF>(&bars->k_empty[t]);
                         }
                     }
                 }
@@ -277,78 +289,78 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
                 // With P in columns of its own the next S of a tile no longer waits for the P V product that consumes P:
                 // per key tile j the thread first issues S_{j+1} of both query tiles, each as soon as its softmax warps have
                 // READ S_j (s_free, early in their pass), then the two P V products of step j as their P arrive.
-                bool ok = n_max > 0 && mbar_wait(&bars->q_full, 0, abort_flag, kSiteQ) &&
-                          mbar_wait(&bars->k_full[0], 0, abort_flag, kSiteKFull);
+                bool ok = n_max > 0 && wait(&bars->q_full, 0, kSiteQ) &&
+                          wait(&bars->k_full[0], 0, kSiteKFull);
                 if (ok) {
                     tc_fence_after();
                     if (n_t[0] > 0) issue_s(0, 0);
                     if (n_t[1] > 0) issue_s(1, 0);
-                    tc_commit(&bars->k_empty[0]);
+                    tc_commit_x<kElectF>(&bars->k_empty[0]);
                 }
                 for (int j = 0; ok && j < n_max; ++j) {
                     const int st = j & 1, nst = st ^ 1;
                     if (j + 1 < n_max) {
-                        if (!(ok = mbar_wait(&bars->k_full[nst], (uint32_t)(((j + 1) >> 1) & 1), abort_flag, kSiteKFull))) break;
+                        if (!(ok = wait(&bars->k_full[nst], (uint32_t)(((j + 1) >> 1) & 1), kSiteKFull))) break;
                         for (int t = 0; t < 2 && ok; ++t) {
                             if (j + 1 >= n_t[t]) continue;
-                            if (!(ok = mbar_wait(&bars->s_free[t], (uint32_t)(j & 1), abort_flag, kSiteIssue))) break;
+                            if (!(ok = wait(&bars->s_free[t], (uint32_t)(j & 1), kSiteIssue))) break;
                             tc_fence_after();
                             issue_s(t, nst);
                         }
                         if (!ok) break;
-                        tc_commit(&bars->k_empty[nst]);
+                        tc_commit_x<kElectF>(&bars->k_empty[nst]);
                     }
-                    if (!(ok = mbar_wait(&bars->v_full[st], (uint32_t)((j >> 1) & 1), abort_flag, kSiteVFull))) break;
+                    if (!(ok = wait(&bars->v_full[st], (uint32_t)((j >> 1) & 1), kSiteVFull))) break;
                     for (int t = 0; t < 2 && ok; ++t) {
                         if (j >= n_t[t]) continue;
-                        if (!(ok = mbar_wait(&bars->p_ready[t], (uint32_t)(j & 1), abort_flag, kSitePReady))) break;
+                        if (!(ok = wait(&bars->p_ready[t], (uint32_t)(j & 1), kSitePReady))) break;
                         tc_fence_after();
                         issue_pv(t, st, j > 0);
                     }
                     if (!ok) break;
-                    tc_commit(&bars->v_empty[st]);
+                    tc_commit_x<kElectF>(&bars->v_empty[st]);
                 }
             } else {
-            bool ok = n_max > 0 && mbar_wait(&bars->q_full, 0, abort_flag, kSiteQ) &&
-                      mbar_wait(&bars->k_full[0], 0, abort_flag, kSiteKFull);
+            bool ok = n_max > 0 && wait(&bars->q_full, 0, kSiteQ) &&
+                      wait(&bars->k_full[0], 0, kSiteKFull);
             if (ok) {
                 tc_fence_after();
                 if (n_t[0] > 0) issue_s(0, 0);
                 if (n_t[1] > 0) issue_s(1, 0);
-                tc_commit(&bars->k_empty[0]);
+                tc_commit_x<kElectF>(&bars->k_empty[0]);
             }
             for (int j = 0; ok && j < n_max; ++j) {
                 const int st = j & 1, nst = st ^ 1;
                 const uint32_t ph = (uint32_t)((j >> 1) & 1), nph = (uint32_t)(((j + 1) >> 1) & 1);
-                if (!(ok = mbar_wait(&bars->v_full[st], ph, abort_flag, kSiteVFull))) break;
+                if (!(ok = wait(&bars->v_full[st], ph, kSiteVFull))) break;
                 bool next_k_ready = false;
                 for (int t = 0; t < 2 && ok; ++t) {
                     if (j >= n_t[t]) continue;
-                    if (!(ok = mbar_wait(&bars->p_ready[t], (uint32_t)(j & 1), abort_flag, kSitePReady))) break;
-                    SNTL_TRACE_EV(true, 0, tn, 10 + t);
+                    if (!(ok = wait(&bars->p_ready[t], (uint32_t)(j & 1), kSitePReady))) break;
+                    SNTL_TRACE_EV(tl8, 0, tn, 10 + t);
                     tc_fence_after();
                     issue_pv(t, st, j > 0);
-                    SNTL_TRACE_EV(true, 0, tn, 20 + t);
+                    SNTL_TRACE_EV(tl8, 0, tn, 20 + t);
                     if (j + 1 < n_t[t]) {
                         if (!next_k_ready) {
-                            SNTL_TRACE_EV(true, 0, tn, 40);
-                            if (!(ok = mbar_wait(&bars->k_full[nst], nph, abort_flag, kSiteKFull))) break;
+                            SNTL_TRACE_EV(tl8, 0, tn, 40);
+                            if (!(ok = wait(&bars->k_full[nst], nph, kSiteKFull))) break;
                             tc_fence_after();
-                            SNTL_TRACE_EV(true, 0, tn, 41);
+                            SNTL_TRACE_EV(tl8, 0, tn, 41);
                             next_k_ready = true;
                         }
                         issue_s(t, nst);
-                        SNTL_TRACE_EV(true, 0, tn, 30 + t);
+                        SNTL_TRACE_EV(tl8, 0, tn, 30 + t);
                     }
                 }
                 if (!ok) break;
-                if (j + 1 < n_max) tc_commit(&bars->k_empty[nst]);
-                tc_commit(&bars->v_empty[st]);
+                if (j + 1 < n_max) tc_commit_x<kElectF>(&bars->k_empty[nst]);
+                tc_commit_x<kElectF>(&bars->v_empty[st]);
             }
             }
             // every MMA issued above must have retired before shared memory / TMEM are given up
-            tc_commit(&bars->final_bar);
-            mbar_wait(&bars->final_bar, 0, abort_flag, kSiteFinal);
+            tc_commit_x<kElectF>(&bars->final_bar);
+            wait(&bars->final_bar, 0, kSiteFinal);
         }
     } else {
         // =========================== softmax + epilogue warpgroups ===========================

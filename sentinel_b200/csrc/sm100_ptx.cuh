@@ -334,6 +334,12 @@ __device__ __forceinline__ void mma_ss_x(uint32_t d_tmem, uint64_t a_desc, uint6
     if constexpr (kElect) mma_ss_e<kAccumulate>(d_tmem, a_desc, b_desc, idesc);
     else mma_ss_c<kAccumulate>(d_tmem, a_desc, b_desc, idesc);
 }
+template <bool kElect, bool kAccumulate>
+__device__ __forceinline__ void mma_ts_x(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc)
+{
+    if constexpr (kElect) mma_ts_e<kAccumulate>(d_tmem, a_tmem, b_desc, idesc);
+    else mma_ts_c<kAccumulate>(d_tmem, a_tmem, b_desc, idesc);
+}
 template <bool kElect>
 __device__ __forceinline__ void tc_commit_x(uint64_t* bar)
 {
