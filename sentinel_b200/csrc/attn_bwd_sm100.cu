@@ -14,7 +14,8 @@
 //         S^T  = K  Q^T  - 1 (LSE/scale)^T    (K, Q  K-major from shared memory)      -> TMEM
 //         dP^T = V  dO^T - 1 delta^T          (V, dO K-major from shared memory)      -> TMEM
 //           (the rank-one terms ride along as one extra 16-wide contraction step: a constant block of ones on the key
-//            side, a 16-byte record per query on the other, so no per-column operand reaches the compute warps)
+//            side, a 16-byte record per query on the other -- the fp32 value split exactly in three bf16 -- so no
+//            per-column operand reaches the compute warps)
 //         P^T  = exp2(scale*log2e * that), causal mask on the diagonal tile, bf16 back over S^T
 //         dV  += P^T  dO         (A = P^T in TMEM,  B = dO tile MN-major)
 //         dS^T = P^T o that, a packed bf16 product, into a shared-memory tile [key][query]
@@ -61,7 +62,7 @@ enum BwdSite : uint32_t {
 struct BwdParams {
     __nv_bfloat16 *dk, *dv;
     // head_dim 64 (see bwd_folds_row_terms):
-    const uint4* qaug;     // [B][Hq][Sq_pad] one 16-byte record per query: bf16 (hi, lo, 0 x 6) of -LSE / scale
+    const uint4* qaug;     // [B][Hq][Sq_pad] one 16-byte record per query: bf16 (hi, mid, lo, 0 x 5) of -LSE / scale
     const uint4* doaug;    // the same for -delta = -rowsum(dO o O)
     // head_dim 128:
     const float* lse2;     // [B][Hq][Sq_pad]  -LSE * log2(e), -inf on padded rows
@@ -327,8 +328,8 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
     constexpr int kStageCols = (D == 128) ? 16 : 32;
     constexpr int kStagingBytes = 32 * 1024;       // dQ staging in all
     // The extra contraction step (head_dim 64).  S^T and dP^T each get one more 16-wide k-step whose operands are not tile data: on the
-    // key side a constant block (1, 1, 0, ...), on the query side a 16-byte record per query, (hi, lo, 0, ...) with
-    // hi + lo = -LSE/scale (for S^T) or -delta (for dP^T) split in two bf16.  The tensor core then delivers
+    // key side a constant block (1, 1, 1, 0, ...), on the query side a 16-byte record per query, (hi, mid, lo, 0, ...) with
+    // hi + mid + lo = -LSE/scale (for S^T) or -delta (for dP^T): the fp32 value split exactly in three bf16.  The tensor core then delivers
     // S^T - LSE/scale and dP^T - delta, and the compute warps need no per-column operand from shared memory at all:
     // P^T = exp2(scale*log2e * that) and dS^T = P^T o that.  One column block (8 bf16) per operand is real; the second
     // block of the constant operand is zeros, so the second block of the record operand may alias the first (LBO 0).
@@ -419,7 +420,7 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
         tmem_relinquish();
     }
     if (kAug && threadIdx.x < kT) {
-        reinterpret_cast<uint4*>(sOnes)[threadIdx.x] = make_uint4(0x3f803f80u, 0u, 0u, 0u);   // bf16 (1, 1, 0, 0, 0, 0, 0, 0)
+        reinterpret_cast<uint4*>(sOnes)[threadIdx.x] = make_uint4(0x3f803f80u, 0x00003f80u, 0u, 0u);   // bf16 (1, 1, 1, 0, 0, 0, 0, 0)
         reinterpret_cast<uint4*>(sOnes + kAugBytes)[threadIdx.x] = make_uint4(0u, 0u, 0u, 0u);
         fence_proxy_async_smem();
     }
@@ -823,8 +824,8 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
     }
 }
 
-// Per padded query row: the two 16-byte records the main kernel feeds to its extra contraction step -- bf16 (hi, lo, 0 x 6)
-// with hi + lo = -rowsum(dO o O) (delta) and = -LSE / scale (a large negative number for padded rows and for rows without
+// Per padded query row: the two 16-byte records the main kernel feeds to its extra contraction step -- bf16 (hi, mid, lo, 0 x 5)
+// with hi + mid + lo = -rowsum(dO o O) (delta) and = -LSE / scale (a large negative number for padded rows and for rows without
 // visible keys, so that they produce P = 0) -- and the dQ accumulator zeroed.  D/4 lanes per (b, h, padded row), 8 bytes of O
 // and of dO per lane: a warp covers one row at head_dim 128 and two at 64, every lane busy either way.
 template <int D>
@@ -861,11 +862,15 @@ __global__ void bwd_pre_kernel(const __nv_bfloat16* __restrict__ o, const __nv_b
         if constexpr (bwd_folds_row_terms(D)) {
             uint4* qaug = static_cast<uint4*>(lse_out);
             uint4* doaug = static_cast<uint4*>(delta_out);
-            // value -> bf16 pair (hi, lo) with hi + lo = value to 16 significant bits, as the low word of a record
+            // value -> three bf16 (hi, mid, lo) whose sum is the fp32 value exactly (3 x 8 significant bits), as the first
+            // three slots of a record
             auto split = [](float x) {
                 const __nv_bfloat16 hi = __float2bfloat16_rn(x);
-                const __nv_bfloat16 lo = __float2bfloat16_rn(x - __bfloat162float(hi));
-                return make_uint4((uint32_t)__bfloat16_as_ushort(hi) | ((uint32_t)__bfloat16_as_ushort(lo) << 16), 0u, 0u, 0u);
+                const float r1 = x - __bfloat162float(hi);
+                const __nv_bfloat16 mid = __float2bfloat16_rn(r1);
+                const __nv_bfloat16 lo = __float2bfloat16_rn(r1 - __bfloat162float(mid));
+                return make_uint4((uint32_t)__bfloat16_as_ushort(hi) | ((uint32_t)__bfloat16_as_ushort(mid) << 16),
+                                  (uint32_t)__bfloat16_as_ushort(lo), 0u, 0u);
             };
             constexpr float kMasked = -1.0e30f;   // times scale*log2(e) still far below the exponent range: P = 0, and finite
             if (s >= Sq) { qaug[r] = split(kMasked); doaug[r] = make_uint4(0u, 0u, 0u, 0u); }
