@@ -427,6 +427,7 @@ def test_sliding_window_matches_reference_golden(sb, name):
     ("gqa7b_d128", dict(batch=1, q_heads=2, kv_heads=1, seq=640), 1, 0),         # every query sees only itself
     ("gqa7b_d128", dict(batch=1, q_heads=2, kv_heads=1, seq=640), 64, 640),      # every key global: plain causal
     ("llama1b_gqa", dict(batch=1, q_heads=8, kv_heads=2, seq=1536), 300, 7),
+    ("llama1b_gqa", dict(batch=1, q_heads=4, kv_heads=2, seq=300), 1, 0),         # head_dim 64, every query sees only itself: dQ = dK = 0
     ("gpt2_small", dict(batch=1, q_heads=2, kv_heads=2, seq=77), 20, 2),         # shorter than one tile
     ("gpt2_small", dict(batch=1, q_heads=2, kv_heads=2, seq=520), 5000, 9),      # window wider than the sequence: plain causal
 ])
