@@ -338,6 +338,37 @@ def test_backward_head_dim_64_buffers_and_cut_tiles_vs_oracle(sb, oracle):
     _check_bf16(_np(dv), wdv, "dv (one tile)")
 
 
+@pytest.mark.parametrize("wname,kw", [
+    ("llama1b_gqa", dict(batch=2, q_heads=8, kv_heads=2, seq=768)),      # head_dim 64
+    ("gqa7b_d128", dict(batch=1, q_heads=6, kv_heads=2, seq=512)),       # head_dim 128
+])
+def test_backward_in_pieces_matches_the_whole_backward(sb, wname, kw):
+    """sntl_attn_bwd_begin / _block / _end (the form the ring schedule uses): the sequence cut in two chunks, every visible
+    (query chunk, key chunk) pair one call -- non-causal below the diagonal, causal on it -- with dQ summed in the query
+    chunk's accumulator and dK*scale / dV added into fp32 accumulators per key chunk.  The sums must equal the whole causal
+    backward (same kernels, fp32 sums rounded once at the end instead of per pair)."""
+    w = sb.WORKLOADS[wname]
+    q, k, v, do = (t.cuda() for t in _bf16_case(w, **kw))
+    o, lse = sb.attention_forward(q, k, v)
+    wdq, wdk, wdv = sb.attention_backward(q, k, v, o, lse, do)
+    Sc = q.shape[2] // 2
+    ch = [slice(0, Sc), slice(Sc, 2 * Sc)]
+    dk_acc = [torch.zeros(k[:, :, c].shape, dtype=torch.float32, device="cuda") for c in ch]
+    dv_acc = [torch.zeros_like(t) for t in dk_acc]
+    dq = []
+    for qi, qc in enumerate(ch):
+        pieces = sb.BackwardPieces(q[:, :, qc].contiguous(), o[:, :, qc].contiguous(), lse[:, :, qc].contiguous(), do[:, :, qc].contiguous())
+        for ki in range(qi + 1):
+            pieces.block(k[:, :, ch[ki]].contiguous(), v[:, :, ch[ki]].contiguous(), dk_acc[ki], dv_acc[ki], causal=(ki == qi))
+        dq.append(pieces.end())
+    assert sb.poll_device_status() == 0
+    got = {"dq": torch.cat(dq, dim=2), "dk": torch.cat(dk_acc, dim=2), "dv": torch.cat(dv_acc, dim=2)}
+    for name, want in (("dq", wdq), ("dk", wdk), ("dv", wdv)):
+        g, x = got[name].float(), want.float()
+        assert float((g - x).norm() / x.norm()) <= 3e-3, (name, float((g - x).norm() / x.norm()))    # bf16 rounding of `want`
+        assert float((g - x).abs().max()) <= 2e-2, name
+
+
 @pytest.mark.parametrize("wname", ["gpt2_small", "llama1b_gqa", "gqa7b_d128"])
 def test_full_size_workloads_sampled_oracle_and_cross_check(sb, oracle, wname):
     """At the benchmark's full sizes: sampled fp64-oracle rows/columns, plus size-independent properties
