@@ -65,6 +65,7 @@ struct FwdBarriers {
     uint64_t q_full;
     uint64_t k_full[2], k_empty[2], v_full[2], v_empty[2];
     uint64_t s_ready[2], p_ready[2], o_ready[2];
+    uint64_t p_half[2];      // the first 64 columns of P_t are written
     uint64_t final_bar;
     uint32_t tmem_base;
     uint32_t abort_flag;
@@ -158,6 +159,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
             mbar_init(&bars->s_ready[i], 1);
             if (D == 64 && kMode != kCache) mbar_init(&bars->s_free[i], 128);
             mbar_init(&bars->p_ready[i], 128);
+            mbar_init(&bars->p_half[i], 128);
             mbar_init(&bars->o_ready[i], 1);
         }
         mbar_init(&bars->final_bar, 1);
@@ -181,6 +183,9 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
     // (computed, not looked up: a two-element array indexed by the warp's tile would live in local memory)
     auto tmem_S = [&](int t) { return tmem + (uint32_t)t * (kOwnP ? 192u : 128u); };
     constexpr uint32_t kPOff = kOwnP ? 128u : 0u;   // P relative to the S of its tile
+    // head_dim 128 (plain / window): P is written over S, so a tile's P V product and next S stay in the chain between two of
+    // its softmax passes; there the first half of P V is issued as soon as the first 64 columns of P are written (-6 %)
+    constexpr bool kHalfP = !kOwnP && kMode != kCache;
     auto tmem_O = [&](int t) { return tmem + (kOwnP ? 384u : 256u) + (uint32_t)t * (kOwnP ? 64u : 128u); };
 
     // 384 threads start with 168 registers each; each role re-allocates inside its own branch
@@ -248,15 +253,26 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
                 }
                 tc_commit_x<kElectF>(&bars->s_ready[t]);
             };
-            auto issue_pv = [&](int t, int st, bool accumulate) {
+            // With kHalfP, P V in two halves of the contraction: the first four k-steps need only the first 64 columns of P
+            // (p_half, which the caller has waited for), the rest the whole of it (p_ready) -- so half the product is issued
+            // while the softmax warps still compute the second half of their exponentials.  Otherwise the caller has waited
+            // for the whole of P.  Returns false when a wait gave up.
+            auto issue_pv = [&](int t, int st, bool accumulate, uint32_t parity) {
                 uint64_t b = st ? dv1 : dv0;
                 asm volatile("" : "+l"(b));
                 const uint32_t d = tmem_O(t), a = tmem_S(t) + kPOff;
                 if (accumulate) mma_ts_x<kElectF, true>(d, a, b, idesc_pv);
                 else mma_ts_x<kElectF, false>(d, a, b, idesc_pv);
 #pragma unroll
-                for (int ks = 1; ks < kN / 16; ++ks) mma_ts_x<kElectF, true>(d, a + (uint32_t)(ks * 8), sdesc_advance(b, ks * 2048), idesc_pv);
+                for (int ks = 1; ks < kN / 32; ++ks) mma_ts_x<kElectF, true>(d, a + (uint32_t)(ks * 8), sdesc_advance(b, ks * 2048), idesc_pv);
+                if constexpr (kHalfP) {
+                    if (!wait(&bars->p_ready[t], parity, kSitePReady)) return false;
+                    tc_fence_after();
+                }
+#pragma unroll
+                for (int ks = kN / 32; ks < kN / 16; ++ks) mma_ts_x<kElectF, true>(d, a + (uint32_t)(ks * 8), sdesc_advance(b, ks * 2048), idesc_pv);
                 tc_commit_x<kElectF>(&bars->o_ready[t]);
+                return true;
             };
             if constexpr (kMode == kCache) {
                 // two independent streams: stream t owns K/V stage t, S_t and O_t; its jj-th key tile is load 2*jj + t
@@ -273,9 +289,9 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
                     for (int t = 0; t < 2 && ok; ++t) {
                         if (jj >= n_t[t]) continue;
                         if (!(ok = wait(&bars->v_full[t], ph, kSiteVFull))) break;
-                        if (!(ok = wait(&bars->p_ready[t], ph, kSitePReady))) break;
+                        if (!(ok = wait(kHalfP ? &bars->p_half[t] : &bars->p_ready[t], ph, kSitePReady))) break;
                         tc_fence_after();
-                        issue_pv(t, t, jj > 0);
+                        if (!(ok = issue_pv(t, t, jj > 0, ph))) break;
                         tc_commit_x<kElectF>(&bars->v_empty[t]);
                         if (jj + 1 < n_t[t]) {
                             if (!(ok = wait(&bars->k_full[t], nph, kSiteKFull))) break;
@@ -313,9 +329,9 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
                     if (!(ok = wait(&bars->v_full[st], (uint32_t)((j >> 1) & 1), kSiteVFull))) break;
                     for (int t = 0; t < 2 && ok; ++t) {
                         if (j >= n_t[t]) continue;
-                        if (!(ok = wait(&bars->p_ready[t], (uint32_t)(j & 1), kSitePReady))) break;
+                        if (!(ok = wait(kHalfP ? &bars->p_half[t] : &bars->p_ready[t], (uint32_t)(j & 1), kSitePReady))) break;
                         tc_fence_after();
-                        issue_pv(t, st, j > 0);
+                        if (!(ok = issue_pv(t, st, j > 0, (uint32_t)(j & 1)))) break;
                     }
                     if (!ok) break;
                     tc_commit_x<kElectF>(&bars->v_empty[st]);
@@ -336,10 +352,10 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
                 bool next_k_ready = false;
                 for (int t = 0; t < 2 && ok; ++t) {
                     if (j >= n_t[t]) continue;
-                    if (!(ok = wait(&bars->p_ready[t], (uint32_t)(j & 1), kSitePReady))) break;
+                    if (!(ok = wait(kHalfP ? &bars->p_half[t] : &bars->p_ready[t], (uint32_t)(j & 1), kSitePReady))) break;
                     SNTL_TRACE_EV(tl8, 0, tn, 10 + t);
                     tc_fence_after();
-                    issue_pv(t, st, j > 0);
+                    if (!(ok = issue_pv(t, st, j > 0, (uint32_t)(j & 1)))) break;
                     SNTL_TRACE_EV(tl8, 0, tn, 20 + t);
                     if (j + 1 < n_t[t]) {
                         if (!next_k_ready) {
@@ -463,6 +479,11 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
                     pk[c] = pack_bf16(p0, p1);
                 }
                 tmem_st32(tmem_S(t) + kPOff + lane_off + (uint32_t)(h * 32), pk);
+                if (kHalfP && h == 0) {   // the P V product may start on the first 64 keys while the rest is computed
+                    tmem_st_wait();
+                    tc_fence_before();
+                    mbar_arrive(&bars->p_half[t]);
+                }
             }
             l += (l4[0] + l4[1]) + (l4[2] + l4[3]);
             SNTL_TRACE_EV(tw, 1 + t, tn, 5);
