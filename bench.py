@@ -206,8 +206,10 @@ def run_reference_arm(args, workload):
     line = {"impl": "reference", "metric": METRIC, "value": res["value"], "unit": UNIT, "n_gpus": args.gpus,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": res["ms_per_step"], "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": workload.name, "B": workload.batch, "Hq": workload.q_heads, "Hkv": workload.kv_heads,
-                       "S": workload.seq, "D": workload.head_dim, "causal": True},
+            # the product arm's workload keys, value for value; what the CPU actually ran is in cpu_baseline.sample
+            "config": {"workload": workload.name, "B_per_gpu": workload.batch, "global_batch": workload.batch * max(1, args.gpus),
+                       "Hq": workload.q_heads, "Hkv": workload.kv_heads, "S": workload.seq, "D": workload.head_dim, "causal": True,
+                       "parallelism": "host cores of rank 0 only (OpenMP); the other ranks exit without work"},
             "cpu_baseline": {k: res[k] for k in ("value", "unit", "cores", "kind", "sample")},
             "e2e": {"value": res["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
