@@ -54,6 +54,21 @@ def _require(t: torch.Tensor, name: str) -> None:
         raise ValueError(f"{name} must be contiguous")
 
 
+def _check_out(t: torch.Tensor, shape, dtype, like: torch.Tensor, name: str) -> torch.Tensor:
+    """A caller-supplied result tensor is written by the kernels through its raw pointer: it must be exactly what the
+    call would have allocated itself."""
+    _require(t, name)
+    if tuple(t.shape) != tuple(shape) or t.dtype != dtype or t.device != like.device:
+        raise ValueError(f"{name} must be a {dtype} tensor of shape {tuple(shape)} on {like.device}")
+    return t
+
+
+def _same_device(ref: torch.Tensor, *named) -> None:
+    for t, n in named:
+        if t.device != ref.device:
+            raise ValueError(f"{n} is on {t.device}, q on {ref.device}")
+
+
 def _bhsd_desc(q, k, causal, scale, flags, window=0, global_tokens=0) -> _lib.Desc:
     if q.dim() != 4 or k.dim() != 4:
         raise ValueError("expected [B, H, S, D] tensors")
@@ -78,9 +93,11 @@ def attention_forward(q, k, v, *, causal=True, scale=None, flags=0, out=None, ls
         _require(t, n)
     if k.shape != v.shape or k.dtype != q.dtype or v.dtype != q.dtype:
         raise ValueError("k and v must share shape; q, k, v must share dtype")
+    _same_device(q, (k, "k"), (v, "v"))
     d = _bhsd_desc(q, k, causal, scale, flags, window, global_tokens)
-    o = torch.empty_like(q) if out is None else out
-    lse = torch.empty(q.shape[:3], dtype=torch.float32, device=q.device) if lse is None else lse
+    o = torch.empty_like(q) if out is None else _check_out(out, q.shape, q.dtype, q, "out")
+    lse = (torch.empty(q.shape[:3], dtype=torch.float32, device=q.device) if lse is None
+           else _check_out(lse, q.shape[:3], torch.float32, q, "lse"))
     nbytes = lib.sntl_attn_fwd_workspace_bytes(C.byref(d))
     ws = _workspace(nbytes, q.device)
     rc = lib.sntl_attn_fwd(C.byref(d), q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(),
@@ -109,8 +126,10 @@ def attention_cached_forward(q, k_cache, v_cache, cache_length, *, scale=None, f
         scale = D ** -0.5
     d = _lib.Desc(_dtype_code(q), _lib.LAYOUT_BHSD, B, Hq, Hkv, T, int(cache_length), D, float(scale), 1, 0, 0, int(flags),
                   int(window), int(global_tokens))
-    o = torch.empty_like(q) if out is None else out
-    lse = torch.empty(q.shape[:3], dtype=torch.float32, device=q.device) if lse is None else lse
+    _same_device(q, (k_cache, "k_cache"), (v_cache, "v_cache"))
+    o = torch.empty_like(q) if out is None else _check_out(out, q.shape, q.dtype, q, "out")
+    lse = (torch.empty(q.shape[:3], dtype=torch.float32, device=q.device) if lse is None
+           else _check_out(lse, q.shape[:3], torch.float32, q, "lse"))
     nbytes = lib.sntl_attn_cached_fwd_workspace_bytes(C.byref(d), capacity)
     ws = _workspace(nbytes, q.device)
     rc = lib.sntl_attn_cached_fwd(C.byref(d), q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), capacity, o.data_ptr(),
@@ -143,7 +162,8 @@ def pack_heads(matrix, batch, heads, seq, head_dim, *, column_start=0, cos_table
     if matrix.dtype != torch.float32 or matrix.dim() != 2 or matrix.shape[0] != heads * head_dim:
         raise ValueError("matrix must be fp32 (heads*head_dim) x stride")
     cp, sp, positions = _tables(cos_table, sin_table, head_dim, matrix.device)
-    dst = torch.empty(batch, heads, seq, head_dim, dtype=torch.bfloat16, device=matrix.device) if out is None else out
+    dst = (torch.empty(batch, heads, seq, head_dim, dtype=torch.bfloat16, device=matrix.device) if out is None
+           else _check_out(out, (batch, heads, seq, head_dim), torch.bfloat16, matrix, "out"))
     rc = lib.sntl_attn_pack_heads(matrix.data_ptr(), dst.data_ptr(), batch, heads, seq, head_dim, matrix.shape[1], column_start,
                                   cp, sp, position_offset, positions, _stream_ptr())
     _lib.check(rc, "sntl_attn_pack_heads")
@@ -176,10 +196,13 @@ def attention_backward(q, k, v, o, lse, dout, *, causal=True, scale=None, flags=
         _require(t, n)
     if o.shape != q.shape or dout.shape != q.shape or lse.shape != q.shape[:3] or lse.dtype != torch.float32:
         raise ValueError("o/dout must match q; lse must be fp32 [B,Hq,Sq]")
+    if k.shape != v.shape or any(t.dtype != q.dtype for t in (k, v, o, dout)):
+        raise ValueError("k and v must share shape; q, k, v, o, dout must share dtype")
+    _same_device(q, (k, "k"), (v, "v"), (o, "o"), (lse, "lse"), (dout, "dout"))
     d = _bhsd_desc(q, k, causal, scale, flags, window, global_tokens)
-    dq = torch.empty_like(q) if dq is None else dq
-    dk = torch.empty_like(k) if dk is None else dk
-    dv = torch.empty_like(v) if dv is None else dv
+    dq = torch.empty_like(q) if dq is None else _check_out(dq, q.shape, q.dtype, q, "dq")
+    dk = torch.empty_like(k) if dk is None else _check_out(dk, k.shape, k.dtype, q, "dk")
+    dv = torch.empty_like(v) if dv is None else _check_out(dv, v.shape, v.dtype, q, "dv")
     nbytes = lib.sntl_attn_bwd_workspace_bytes(C.byref(d))
     ws = _workspace(nbytes, q.device)
     rc = lib.sntl_attn_bwd(C.byref(d), q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(),
@@ -201,6 +224,9 @@ class BackwardPieces:
             _require(t, n)
         if o.shape != q.shape or dout.shape != q.shape or lse.shape != q.shape[:3] or lse.dtype != torch.float32:
             raise ValueError("o/dout must match q; lse must be fp32 [B,Hq,Sq]")
+        if o.dtype != q.dtype or dout.dtype != q.dtype:
+            raise ValueError("q, o, dout must share dtype")
+        _same_device(q, (o, "o"), (lse, "lse"), (dout, "dout"))
         self.q, self.dout = q, dout
         self.scale = q.shape[-1] ** -0.5 if scale is None else float(scale)
         d = self._desc(q.shape[1], q.shape[2], False)
@@ -229,13 +255,16 @@ class BackwardPieces:
             raise ValueError("k, v, dk_acc, dv_acc must share shape")
         if dk_acc.dtype != torch.float32 or dv_acc.dtype != torch.float32:
             raise ValueError("dk_acc / dv_acc must be fp32")
+        if k.dtype != self.q.dtype or v.dtype != self.q.dtype or k.dim() != 4 or k.shape[0] != self.q.shape[0] or k.shape[3] != self.q.shape[3]:
+            raise ValueError("k, v must be [B, Hkv, Skv, D] tensors of q's dtype, batch and head_dim")
+        _same_device(self.q, (k, "k"), (v, "v"), (dk_acc, "dk_acc"), (dv_acc, "dv_acc"))
         d = self._desc(k.shape[1], k.shape[2], causal)
         rc = _lib.load().sntl_attn_bwd_block(C.byref(d), self.q.data_ptr(), k.data_ptr(), v.data_ptr(), self.dout.data_ptr(),
                                              dk_acc.data_ptr(), dv_acc.data_ptr(), self.ws.data_ptr(), self.nbytes, _stream_ptr())
         _lib.check(rc, "sntl_attn_bwd_block")
 
     def end(self, dq=None):
-        dq = torch.empty_like(self.q) if dq is None else dq
+        dq = torch.empty_like(self.q) if dq is None else _check_out(dq, self.q.shape, self.q.dtype, self.q, "dq")
         d = self._desc(self.q.shape[1], self.q.shape[2], False)
         rc = _lib.load().sntl_attn_bwd_end(C.byref(d), dq.data_ptr(), self.ws.data_ptr(), self.nbytes, _stream_ptr())
         _lib.check(rc, "sntl_attn_bwd_end")
@@ -259,6 +288,11 @@ def merge_partials(o_acc, lse_acc, o_part, lse_part):
         _require(t, n)
     D = o_acc.shape[-1]
     rows = o_acc.numel() // D
+    if o_part.shape != o_acc.shape or lse_acc.numel() != rows or lse_part.numel() != rows:
+        raise ValueError("o_part must match o_acc; lse_acc / lse_part hold one value per row")
+    if lse_acc.dtype != torch.float32 or lse_part.dtype != torch.float32:
+        raise ValueError("lse_acc / lse_part must be fp32")
+    _same_device(o_acc, (lse_acc, "lse_acc"), (o_part, "o_part"), (lse_part, "lse_part"))
     rc = lib.sntl_attn_merge(_dtype_code(o_acc), _dtype_code(o_part), rows, D, o_acc.data_ptr(), lse_acc.data_ptr(),
                              o_part.data_ptr(), lse_part.data_ptr(), _stream_ptr())
     _lib.check(rc, "sntl_attn_merge")
@@ -325,6 +359,8 @@ class CudaFlashAttention:
         op = "CudaFlashAttention"
         if query.numel() == 0 or key.numel() == 0:
             raise ValueError(f"{op} empty input")
+        if query.dim() != 2 or key.dim() != 2 or query.dtype != torch.float32 or key.dtype != torch.float32:
+            raise ValueError(f"{op} expects fp32 matrices")
         if headCount <= 0 or headDimension <= 0:
             raise ValueError(f"{op} invalid head geometry")
         if query.shape[0] != headCount * headDimension:
@@ -357,10 +393,13 @@ class CudaFlashAttention:
                                      windowSize, globalTokenCount)
         for t, n in ((query, "query"), (key, "key"), (value, "value")):
             _require(t, n)
-        if out is None:
-            out = torch.zeros_like(query)
-        if logSumExp is None:
-            logSumExp = torch.zeros(headCount, query.shape[1], dtype=torch.float32, device=query.device)
+        if value.dtype != torch.float32:
+            raise ValueError("CudaFlashAttention expects fp32 matrices")
+        _same_device(query, (key, "key"), (value, "value"))
+        # the reference resizes its outputs (ensureSize); a torch tensor handed in must already have the size
+        out = torch.zeros_like(query) if out is None else _check_out(out, query.shape, torch.float32, query, "out")
+        logSumExp = (torch.zeros(headCount, query.shape[1], dtype=torch.float32, device=query.device) if logSumExp is None
+                     else _check_out(logSumExp, (headCount, query.shape[1]), torch.float32, query, "logSumExp"))
         nbytes = lib.sntl_attn_fwd_workspace_bytes(C.byref(d))
         ws = _workspace(nbytes, query.device)
         rc = lib.sntl_attn_fwd(C.byref(d), query.data_ptr(), key.data_ptr(), value.data_ptr(), out.data_ptr(),
@@ -389,9 +428,17 @@ class CudaFlashAttention:
         for t, n in ((query, "query"), (key, "key"), (value, "value"), (out, "out"), (logSumExp, "logSumExp"),
                      (outGradient, "outGradient")):
             _require(t, n)
-        queryGradient = torch.zeros_like(query) if queryGradient is None else queryGradient
-        keyGradient = torch.zeros_like(key) if keyGradient is None else keyGradient
-        valueGradient = torch.zeros_like(value) if valueGradient is None else valueGradient
+        if key.shape != value.shape:
+            raise ValueError("CudaFlashAttention key/value rows mismatch")
+        if any(t.dtype != torch.float32 for t in (value, out, logSumExp, outGradient)):
+            raise ValueError("CudaFlashAttention expects fp32 matrices")
+        _same_device(query, (key, "key"), (value, "value"), (out, "out"), (logSumExp, "logSumExp"), (outGradient, "outGradient"))
+        queryGradient = (torch.zeros_like(query) if queryGradient is None
+                         else _check_out(queryGradient, query.shape, torch.float32, query, "queryGradient"))
+        keyGradient = (torch.zeros_like(key) if keyGradient is None
+                       else _check_out(keyGradient, key.shape, torch.float32, query, "keyGradient"))
+        valueGradient = (torch.zeros_like(value) if valueGradient is None
+                         else _check_out(valueGradient, value.shape, torch.float32, query, "valueGradient"))
         nbytes = lib.sntl_attn_bwd_workspace_bytes(C.byref(d))
         ws = _workspace(nbytes, query.device)
         rc = lib.sntl_attn_bwd(C.byref(d), query.data_ptr(), key.data_ptr(), value.data_ptr(), out.data_ptr(),

@@ -208,3 +208,38 @@ def test_pieces_ring_and_selftest_entry_points_validate_without_a_gpu(lib):
     assert lib.sntl_attn_selftest_wait_timeout(0, None) == _lib.ERR_BAD_ARGUMENT
     assert lib.sntl_attn_selftest_wait_timeout(10 ** 6, None) == _lib.ERR_BAD_ARGUMENT
     assert lib.sntl_status_string(_lib.ERR_COMM).decode().startswith("NCCL")
+
+
+def test_python_mirror_refuses_result_tensors_of_the_wrong_shape_or_dtype(lib, monkeypatch):
+    """The kernels write caller-supplied result tensors through raw pointers, so the Python mirror checks them before any
+    call.  Host tensors stand in for device tensors here (the device check is switched off); nothing is launched."""
+    import torch
+    from sentinel_b200 import flash_attention as fa
+    monkeypatch.setattr(fa, "_require", lambda t, name: None)
+    q = torch.zeros(1, 4, 128, 64, dtype=torch.bfloat16)
+    k = torch.zeros(1, 2, 128, 64, dtype=torch.bfloat16)
+    lse = torch.zeros(1, 4, 128)
+    with pytest.raises(ValueError, match="out must be"):
+        fa.attention_forward(q, k, k, out=torch.zeros(1, 4, 64, 64, dtype=torch.bfloat16))
+    with pytest.raises(ValueError, match="out must be"):
+        fa.attention_forward(q, k, k, out=torch.zeros(1, 4, 128, 64))                     # fp32 where bf16 is written
+    with pytest.raises(ValueError, match="lse must be"):
+        fa.attention_forward(q, k, k, lse=torch.zeros(1, 4, 127))
+    with pytest.raises(ValueError, match="share dtype"):
+        fa.attention_backward(q, k, k, q.float(), lse, q)                                  # o in another dtype
+    with pytest.raises(ValueError, match="dk must be"):
+        fa.attention_backward(q, k, k, q, lse, q, dk=torch.zeros_like(q))                  # query-head shaped dK
+    with pytest.raises(ValueError, match="dq must be"):
+        fa.attention_backward(q, k, k, q, lse, q, dq=torch.zeros(1, 4, 128, 64))
+    with pytest.raises(ValueError, match="o_part must match"):
+        fa.merge_partials(q.float(), lse, torch.zeros(1, 4, 64, 64), lse)
+    FA = fa.CudaFlashAttention
+    m = torch.zeros(64, 96)
+    with pytest.raises(ValueError, match="expects fp32"):
+        FA.forwardMultiHead(m.bfloat16(), m.bfloat16(), m.bfloat16(), None, None, 4, 16, 0.25)
+    with pytest.raises(ValueError, match="out must be"):
+        FA.forwardMultiHead(m, m, m, torch.zeros(64, 48), None, 4, 16, 0.25)
+    with pytest.raises(ValueError, match="logSumExp must be"):
+        FA.forwardMultiHead(m, m, m, None, torch.zeros(2, 96), 4, 16, 0.25)
+    with pytest.raises(ValueError, match="keyGradient must be"):
+        FA.backwardMultiHead(m, m, m, m, torch.zeros(4, 96), m, None, torch.zeros(32, 96), None, None, 4, 16, 0.25)
