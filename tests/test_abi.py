@@ -243,3 +243,47 @@ def test_python_mirror_refuses_result_tensors_of_the_wrong_shape_or_dtype(lib, m
         FA.forwardMultiHead(m, m, m, None, torch.zeros(2, 96), 4, 16, 0.25)
     with pytest.raises(ValueError, match="keyGradient must be"):
         FA.backwardMultiHead(m, m, m, m, torch.zeros(4, 96), m, None, torch.zeros(32, 96), None, None, 4, 16, 0.25)
+
+
+def test_header_is_plain_c_and_a_c_program_links_and_calls_the_library(lib, tmp_path):
+    """include/sntl_attn.h compiles as C99 and as C++11 without warnings, and a C program linked against the shared library
+    (no Python, no torch in between) reaches the entry points that need no GPU."""
+    import shutil
+    import subprocess
+    gcc, gxx = shutil.which("gcc"), shutil.which("g++")
+    if gcc is None or gxx is None:
+        pytest.skip("no host compiler")
+    header = os.path.join(ROOT, "include", "sntl_attn.h")
+    for cmd in ([gcc, "-std=c99", "-x", "c"], [gxx, "-std=c++11", "-x", "c++"]):
+        r = subprocess.run(cmd + ["-Wall", "-Wextra", "-pedantic", "-Werror", "-fsyntax-only", header], capture_output=True, text=True)
+        assert r.returncode == 0, r.stderr
+    src = tmp_path / "caller.c"
+    src.write_text(r'''
+#include <stdio.h>
+#include <string.h>
+#include "sntl_attn.h"
+int main(void)
+{
+    sntl_attn_desc d;
+    memset(&d, 0, sizeof d);
+    d.dtype = SNTL_DTYPE_BF16; d.layout = SNTL_LAYOUT_BHSD; d.batch = 2; d.q_heads = 28; d.kv_heads = 4;
+    d.seq_q = d.seq_kv = 8192; d.head_dim = 128; d.scale = 0.088388f; d.causal = 1;
+    printf("%d|%s|%zu|%zu\n", sntl_attn_version(), sntl_status_string(SNTL_ERR_UNSUPPORTED),
+           sntl_attn_fwd_workspace_bytes(&d), sntl_attn_bwd_workspace_bytes(&d));
+    d.head_dim = 0;                       /* an invalid descriptor is refused before anything touches a device */
+    return sntl_attn_fwd(&d, 0, 0, 0, 0, 0, 0, 0, 0) == SNTL_ERR_BAD_ARGUMENT ? 0 : 1;
+}
+''')
+    exe = tmp_path / "caller"
+    libdir = os.path.dirname(_lib.LIB_PATH)
+    r = subprocess.run([gcc, "-std=c99", "-Wall", "-Werror", "-I", os.path.join(ROOT, "include"), str(src), "-o", str(exe),
+                        "-L", libdir, "-lsntl_attn", f"-Wl,-rpath,{libdir}"], capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+    r = subprocess.run([str(exe)], capture_output=True, text=True, timeout=60)
+    assert r.returncode == 0, (r.stdout, r.stderr)
+    version, text, fwd_bytes, bwd_bytes = r.stdout.strip().split("|")
+    assert int(version) == lib.sntl_attn_version()
+    assert text == lib.sntl_status_string(_lib.ERR_UNSUPPORTED).decode()
+    d = _lib.Desc(_lib.DTYPE_BF16, _lib.LAYOUT_BHSD, 2, 28, 4, 8192, 8192, 128, 0.088388, 1, 0, 0, 0, 0, 0)
+    assert int(fwd_bytes) == lib.sntl_attn_fwd_workspace_bytes(C.byref(d))
+    assert int(bwd_bytes) == lib.sntl_attn_bwd_workspace_bytes(C.byref(d)) > 0
