@@ -422,6 +422,23 @@ class NativeRing:
         self.handle = handle
         self._ws = None
 
+    @staticmethod
+    def _check(q, k, v, o=None, lse=None, do=None):
+        """The library reads and writes these tensors through raw pointers as bf16 ``[B, H, S/W, D]``: anything else is
+        refused here."""
+        named = [(q, "q"), (k, "k"), (v, "v")] + [(t, n) for t, n in ((o, "o"), (do, "do")) if t is not None]
+        for t, n in named:
+            if not t.is_cuda or not t.is_contiguous() or t.dtype != torch.bfloat16 or t.dim() != 4 or t.device != q.device:
+                raise ValueError(f"{n} must be a contiguous bf16 [B, H, S, D] CUDA tensor on q's device")
+        if k.shape != v.shape or k.shape[0] != q.shape[0] or k.shape[2:] != q.shape[2:]:
+            raise ValueError("k and v must share shape and agree with q on batch, shard length and head_dim")
+        for t, n in ((o, "o"), (do, "do")):
+            if t is not None and t.shape != q.shape:
+                raise ValueError(f"{n} must match q")
+        if lse is not None and (not lse.is_cuda or not lse.is_contiguous() or lse.dtype != torch.float32
+                                or lse.shape != q.shape[:3] or lse.device != q.device):
+            raise ValueError("lse must be a contiguous fp32 [B, Hq, S] CUDA tensor on q's device")
+
     def _desc(self, q, k):
         B, Hq, S, D = q.shape
         flags = self._lib.FLAG_RING_ZIGZAG if self.zigzag_layout else 0
@@ -436,6 +453,7 @@ class NativeRing:
         return self._ws, need
 
     def forward(self, q, k, v, keep_state: bool = False):
+        self._check(q, k, v)
         d = self._desc(q, k)
         ws, need = self._workspace(d, q.device)
         o = torch.empty_like(q)
@@ -446,6 +464,7 @@ class NativeRing:
         return o, lse
 
     def backward(self, q, k, v, o, lse, do, use_saved_state: bool = False):
+        self._check(q, k, v, o, lse, do)
         d = self._desc(q, k)
         ws, need = self._workspace(d, q.device)
         dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
