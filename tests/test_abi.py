@@ -287,3 +287,11 @@ int main(void)
     d = _lib.Desc(_lib.DTYPE_BF16, _lib.LAYOUT_BHSD, 2, 28, 4, 8192, 8192, 128, 0.088388, 1, 0, 0, 0, 0, 0)
     assert int(fwd_bytes) == lib.sntl_attn_fwd_workspace_bytes(C.byref(d))
     assert int(bwd_bytes) == lib.sntl_attn_bwd_workspace_bytes(C.byref(d)) > 0
+
+
+def test_native_ring_binding_refuses_tensors_it_cannot_hand_to_the_library():
+    import torch
+    from sentinel_b200.ring import NativeRing
+    q = torch.zeros(1, 4, 128, 64, dtype=torch.bfloat16)
+    with pytest.raises(ValueError, match="CUDA tensor"):      # host memory: there is no CPU path
+        NativeRing._check(q, q[:, :2], q[:, :2])
